@@ -1,0 +1,184 @@
+// C entry points around the UNMODIFIED reference library -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+//
+// This file contains no reference code: it only calls the reference's public C++ API
+// (pulsatrix::Generate, ProcessLogits, top_k, CPUBackend::top_k_rows, set_seed/next_seed,
+// ShuffleSampler, PortableRng) so that Python tests and the benchmark's CPU-baseline leg can
+// reach it through ctypes.  oracle/Makefile compiles it together with the reference's own
+// sources, in place, into oracle/_ref/libpsx_ref.so.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "portable_random.hpp"  // private header of the reference, reached with -I<ref>/src
+#include "psx_oracle.h"         // the shared C structs (psxo_config, psxo_step_info, status codes)
+#include "pulsatrix/cpu_backend.hpp"
+#include "pulsatrix/determinism.hpp"
+#include "pulsatrix/generation.hpp"
+#include "pulsatrix/sampler.hpp"
+#include "pulsatrix/top_k.hpp"
+
+namespace {
+
+pulsatrix::GenerationConfig ToConfig(const psxo_config* c) {
+    pulsatrix::GenerationConfig g;
+    g.max_new_tokens = c->max_new_tokens;
+    g.min_new_tokens = c->min_new_tokens;
+    g.eos_token_ids.assign(c->eos_token_ids, c->eos_token_ids + c->num_eos_token_ids);
+    g.do_sample = c->do_sample != 0;
+    g.temperature = c->temperature;
+    g.top_k = c->top_k;
+    g.top_p = c->top_p;
+    g.min_p = c->min_p;
+    g.repetition_penalty = c->repetition_penalty;
+    return g;
+}
+
+// The reference reports every contract violation as std::invalid_argument; the message tells
+// which one (src/generation.cpp:19-38,117-138).
+int StatusOf(const std::invalid_argument& e) {
+    const std::string what = e.what();
+    if (what.find("GenerationConfig") != std::string::npos) return PSXO_BAD_CONFIG;
+    if (what.find("prompt is empty") != std::string::npos) return PSXO_EMPTY_PROMPT;
+    if (what.find("no logits") != std::string::npos) return PSXO_EMPTY_LOGITS;
+    if (what.find("non-finite") != std::string::npos) return PSXO_NON_FINITE;
+    if (what.find("every token was removed") != std::string::npos) return PSXO_ALL_REMOVED;
+    return 99;
+}
+
+void RunRow(const float* logits, int64_t vocab, const int64_t* hist, int64_t hist_len, const psxo_config* c,
+            uint64_t seed, psxo_step_info* info) {
+    std::memset(info, 0, sizeof(*info));
+    info->token = -1;
+    info->draw_margin = INFINITY;
+    info->top_p_margin = INFINITY;
+    pulsatrix::GenerationConfig g = ToConfig(c);
+    g.max_new_tokens = 1;
+    g.seed = seed;
+    const std::vector<int64_t> prompt(hist, hist + hist_len);
+    auto model = [&](const std::vector<int64_t>&) { return std::vector<float>(logits, logits + vocab); };
+    try {
+        const pulsatrix::GenerationResult r = pulsatrix::Generate(model, prompt, g);
+        info->token = r.new_tokens.at(0);
+        info->log_prob = r.log_probs.at(0);
+        info->status = PSXO_OK;
+    } catch (const std::invalid_argument& e) {
+        info->status = StatusOf(e);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int psxref_process_logits(float* logits, int64_t vocab, const int64_t* tokens, int64_t num_tokens,
+                          int64_t num_new_tokens, const psxo_config* c) {
+    std::vector<float> l(logits, logits + vocab);
+    const std::vector<int64_t> t(tokens, tokens + num_tokens);
+    try {
+        pulsatrix::ProcessLogits(l, t, num_new_tokens, ToConfig(c));
+    } catch (const std::invalid_argument& e) {
+        return StatusOf(e);
+    }
+    std::copy(l.begin(), l.end(), logits);
+    return PSXO_OK;
+}
+
+// Independent rows, one Generate(max_new_tokens = 1, seed = seeds[r]) each, fanned over threads.
+int psxref_rows(const float* logits, int64_t rows, int64_t vocab, int64_t row_stride, const int64_t* hist,
+                const int64_t* offsets, const psxo_config* c, const uint64_t* seeds, int threads,
+                psxo_step_info* infos) {
+    threads = std::max(1, std::min<int>(threads, rows > 0 ? static_cast<int>(std::min<int64_t>(rows, 1024)) : 1));
+    auto work = [&](int t) {
+        for (int64_t r = t; r < rows; r += threads) {
+            RunRow(logits + r * row_stride, vocab, hist + offsets[r], offsets[r + 1] - offsets[r], c, seeds[r],
+                   &infos[r]);
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int t = 1; t < threads; ++t) pool.emplace_back(work, t);
+    work(0);
+    for (auto& th : pool) th.join();
+    int worst = PSXO_OK;
+    for (int64_t r = 0; r < rows; ++r) {
+        if (infos[r].status != PSXO_OK) worst = infos[r].status;
+    }
+    return worst;
+}
+
+// The whole of Generate() with the model given as a table: step s returns logits_steps[s].
+int psxref_generate_table(const float* logits_steps, int64_t vocab, const int64_t* prompt, int64_t prompt_len,
+                          const psxo_config* c, int32_t has_seed, uint64_t seed, int64_t* tokens_out,
+                          float* log_probs_out, int64_t* n_new, int32_t* finished_eos) {
+    *n_new = 0;
+    *finished_eos = 0;
+    pulsatrix::GenerationConfig g = ToConfig(c);
+    if (has_seed) g.seed = seed;
+    const std::vector<int64_t> p(prompt, prompt + prompt_len);
+    int64_t step = 0;
+    auto model = [&](const std::vector<int64_t>&) {
+        const float* row = logits_steps + (step++) * vocab;
+        return std::vector<float>(row, row + vocab);
+    };
+    try {
+        const pulsatrix::GenerationResult r = pulsatrix::Generate(model, p, g);
+        std::copy(r.tokens.begin(), r.tokens.end(), tokens_out);
+        std::copy(r.log_probs.begin(), r.log_probs.end(), log_probs_out);
+        *n_new = static_cast<int64_t>(r.new_tokens.size());
+        *finished_eos = r.finish_reason == pulsatrix::FinishReason::Eos ? 1 : 0;
+    } catch (const std::invalid_argument& e) {
+        return StatusOf(e);
+    }
+    return PSXO_OK;
+}
+
+void psxref_top_k_rows(const float* in, float* values, float* indices, int64_t rows, int64_t cols, int64_t k,
+                       int largest) {
+    pulsatrix::CPUBackend cpu;
+    cpu.top_k_rows(in, values, indices, static_cast<size_t>(rows), static_cast<size_t>(cols),
+                   static_cast<size_t>(k), largest != 0);
+}
+
+// top_k() on a (rows, cols) CPU tensor: 0 on success, 1 when it throws std::invalid_argument.
+int psxref_top_k(const float* in, float* values, float* indices, int64_t rows, int64_t cols, int64_t k,
+                 int largest) {
+    pulsatrix::CPUBackend cpu;
+    try {
+        const std::vector<float> data(in, in + rows * cols);
+        pulsatrix::Tensor x(pulsatrix::Shape({rows, cols}), &cpu, data);
+        const pulsatrix::TopKResult r = pulsatrix::top_k(x, k, largest != 0);
+        std::copy(r.values.data(), r.values.data() + rows * k, values);
+        std::copy(r.indices.data(), r.indices.data() + rows * k, indices);
+    } catch (const std::invalid_argument&) {
+        return 1;
+    }
+    return 0;
+}
+
+void psxref_set_seed(uint64_t seed) { pulsatrix::set_seed(seed); }
+uint64_t psxref_next_seed(void) { return pulsatrix::next_seed(); }
+
+// ShuffleSampler's visiting order over `epochs` consecutive reset(n) calls: out has epochs*n ids.
+void psxref_shuffle_order(unsigned seed, int64_t n, int64_t epochs, int64_t* out) {
+    pulsatrix::ShuffleSampler s(seed);
+    for (int64_t e = 0; e < epochs; ++e) {
+        s.reset(n);
+        for (int64_t i = 0; i < n; ++i) out[e * n + i] = s.next().value();
+    }
+}
+
+// PortableRng streams: n raw words, then n uniforms, then n gaussians from fresh generators.
+void psxref_portable_streams(uint64_t seed, int64_t n, uint64_t* words, double* uniforms, double* gaussians) {
+    pulsatrix::PortableRng a{seed}, b{seed}, c{seed};
+    for (int64_t i = 0; i < n; ++i) {
+        words[i] = a.next();
+        uniforms[i] = b.uniform();
+        gaussians[i] = c.gaussian();
+    }
+}
+
+}  // extern "C"
