@@ -1,0 +1,166 @@
+/* psx_b200.h -- C ABI of the B200 (sm_100a) token-sampling library.
+ *
+ * A drop-in for one path of pulsatrix: logits processing + draw (ProcessLogits/Generate) and the
+ * top-k selection primitive (DeviceBackend::top_k_rows).  Plain C types only: raw device or host
+ * pointers, sizes, a CUDA stream passed as void*.  Each entry point names the reference interface
+ * it replaces (paths relative to the pulsatrix project root).
+ *
+ * Conventions
+ *   - Every function returns a psx_status (0 = ok).  psx_b200_last_error() gives the message of
+ *     the calling thread's last failure.  There is no CPU fallback: without a CUDA device every
+ *     compute call fails with PSX_ERR_CUDA.
+ *   - A psx_ctx belongs to one device and one host thread at a time (like the reference's
+ *     DeviceBackend, include/pulsatrix/cuda_backend.hpp:159-166).  It owns scratch memory that
+ *     grows on demand; growing synchronises the device, steady-state calls do not allocate.
+ *   - Device entry points are asynchronous on `stream`; outputs are valid after the stream (or
+ *     psx_b200_sync) has been synchronised.  Host entry points synchronise before returning.
+ */
+#ifndef PSX_B200_H
+#define PSX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PSX_API __attribute__((visibility("default")))
+#else
+#define PSX_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum psx_status {
+    PSX_OK = 0,
+    PSX_ERR_BAD_ARGUMENT = 1, /* the reference would throw std::invalid_argument (bad config, sizes) */
+    PSX_ERR_CUDA = 2,         /* a CUDA call failed; the reference throws std::runtime_error */
+    PSX_ERR_ROW_FAILED = 3,   /* host entry points only: some row's status is not PSX_ROW_OK */
+    PSX_ERR_UNSUPPORTED = 4   /* a shape or setting outside what the kernels handle */
+} psx_status;
+
+/* Per-row outcome written to the `row_status` output of the sampling calls. */
+typedef enum psx_row_status {
+    PSX_ROW_OK = 0,
+    PSX_ROW_NON_FINITE = 4,  /* "Generate: the model returned a non-finite logit" (src/generation.cpp:128-132) */
+    PSX_ROW_ALL_REMOVED = 5, /* "Generate: every token was removed" (src/generation.cpp:136-138) */
+    PSX_ROW_TOO_WIDE = 16    /* more tokens survive the filters (or tie at a cut) than the device
+                                path holds; nothing was drawn for this row */
+} psx_row_status;
+
+/* GenerationConfig (include/pulsatrix/generation.hpp:29-52) without the loop fields, plus the
+ * `num_new_tokens` argument of ProcessLogits (generation.hpp:83).  eos_token_ids is a HOST
+ * pointer; it is copied during the call. */
+typedef struct psx_sampling_config {
+    int64_t min_new_tokens;
+    int64_t num_new_tokens;
+    const int64_t* eos_token_ids;
+    int64_t num_eos_token_ids;
+    int32_t do_sample;   /* 0: greedy (argmax, lower index wins); 1: sample */
+    float temperature;   /* > 0, finite */
+    int64_t top_k;       /* >= 0; 0 or >= vocab keeps all */
+    float top_p;         /* (0, 1] */
+    float min_p;         /* [0, 1] */
+    float repetition_penalty; /* > 0, finite; 1 is off */
+} psx_sampling_config;
+
+/* Optional per-row diagnostics (device or host array of `rows` entries, may be NULL). */
+typedef struct psx_row_diag {
+    int32_t candidates;   /* entries the row pass handed to the survivor stage */
+    int32_t survivors;    /* tokens left after top-k / top-p / min-p */
+    double draw_margin;   /* min |u - edge| over the two CDF edges of the chosen bucket */
+    double top_p_margin;  /* min |cumulative - (1 - top_p)| seen by the top-p walk */
+} psx_row_diag;
+
+typedef struct psx_ctx psx_ctx;
+
+/* Library version, "major.minor.patch". */
+PSX_API const char* psx_b200_version(void);
+/* Message of the calling thread's most recent failure ("" if none). */
+PSX_API const char* psx_b200_last_error(void);
+
+/* Creates a context on CUDA device `device` (stream, scratch).  Replaces what the reference's
+ * CUDABackend constructor sets up (src/cuda_backend.cu:24-29). */
+PSX_API psx_status psx_b200_ctx_create(int device, psx_ctx** out);
+PSX_API void psx_b200_ctx_destroy(psx_ctx* ctx);
+/* The context's own stream (a cudaStream_t), used when `stream` is NULL. */
+PSX_API void* psx_b200_ctx_stream(psx_ctx* ctx);
+/* cudaStreamSynchronize on `stream` (NULL: the context's stream). */
+PSX_API psx_status psx_b200_sync(psx_ctx* ctx, void* stream);
+/* Number of kernels this context has launched since it was created. */
+PSX_API uint64_t psx_b200_launch_count(const psx_ctx* ctx);
+
+/* Batched sampling step on device-resident logits: for every row, what one iteration of
+ * Generate()'s loop computes (src/generation.cpp:124-156) -- finite check, raw log-softmax,
+ * ProcessLogits (src/generation.cpp:55-112: repetition penalty, EOS ban, temperature, top-k,
+ * top-p, min-p), then argmax or the inverse-CDF draw against `uniforms[row]`, and the chosen
+ * token's log-probability under the unprocessed logits.  The reference has no batched or
+ * device entry; this is what CUDA-resident callers of Generate() bind instead of copying the
+ * row to the host (src/generation.cpp:248-256).
+ *
+ *   logits        device, rows x vocab fp32, row r at logits + r*row_stride (row_stride >= vocab)
+ *   history_ids   device int64, the token sequence of every row back to back (prompt + generated)
+ *   history_offsets device int64[rows+1]; row r owns history_ids[offsets[r] .. offsets[r+1])
+ *                 (both may be NULL when repetition_penalty == 1)
+ *   uniforms      device double[rows] in [0,1): the draw of each row, from the caller's
+ *                 generator (psx_uniforms_mt19937_64 below reproduces the reference's); may be
+ *                 NULL when do_sample == 0
+ *   tokens        device int64[rows] out (-1 on a failed row)
+ *   log_probs     device float[rows] out
+ *   row_status    device int32[rows] out, a psx_row_status each
+ *   diag          device psx_row_diag[rows] out, or NULL
+ */
+PSX_API psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream, const float* logits, int64_t rows, int64_t vocab,
+                                int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
+                                const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
+                                float* log_probs, int32_t* row_status, psx_row_diag* diag);
+
+/* The same step for callers that hold everything on the host, as the reference's
+ * NextTokenLogitsFn does (include/pulsatrix/generation.hpp:25): copies inputs to the device,
+ * runs psx_b200_sample_rows, copies results back and synchronises.  Returns
+ * PSX_ERR_ROW_FAILED when any row_status is non-zero (outputs are still filled in). */
+PSX_API psx_status psx_b200_sample_rows_host(psx_ctx* ctx, const float* logits, int64_t rows, int64_t vocab,
+                                     int64_t row_stride, const int64_t* history_ids,
+                                     const int64_t* history_offsets, const psx_sampling_config* config,
+                                     const double* uniforms, int64_t* tokens, float* log_probs,
+                                     int32_t* row_status, psx_row_diag* diag);
+
+/* Vocabulary-sharded step, part 1 of 2 (no counterpart in the reference, which is single
+ * device): this GPU holds columns [shard_begin, shard_begin + shard_cols) of every row.  Writes
+ * one fixed-size record per row into `records` (device, rows * psx_b200_shard_record_bytes(config)
+ * bytes): the shard's partial max / sum-exp and its local candidates with global column ids.
+ * The caller all-gathers the records of all shards (NCCL) and passes them to part 2. */
+PSX_API size_t psx_b200_shard_record_bytes(const psx_sampling_config* config);
+PSX_API psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream, const float* shard_logits, int64_t rows,
+                               int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
+                               const int64_t* history_ids, const int64_t* history_offsets,
+                               const psx_sampling_config* config, void* records);
+/* Part 2: merges `num_shards` gathered record sets (shard s at gathered + s*rows*record_bytes,
+ * all in this GPU's own memory) and draws; every GPU that runs it gets the same result.  The
+ * records carry the raw logits of their candidates, so the logits are not read again.
+ * Sampling needs 0 < top_k < vocab here (greedy needs nothing).  Outputs as above. */
+PSX_API psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream, const void* gathered, int32_t num_shards,
+                                int64_t rows, int64_t vocab, const psx_sampling_config* config,
+                                const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
+                                psx_row_diag* diag);
+
+/* Replaces DeviceBackend::top_k_rows (include/pulsatrix/device_backend.hpp:828-837; CUDA
+ * implementation src/cuda_backend.cu:851-860, kernel src/gpu_kernels.cuh:1256-1262): per row of
+ * a row-major (rows, cols) device matrix, the k largest (or smallest) values in rank order and
+ * their column indices as whole-number floats.  NaN ranks above every number; equal values keep
+ * the lower column first.  Requires 1 <= k <= cols <= 2^24 (top_k() validates the same,
+ * src/top_k.cpp:10-21).  Asynchronous on `stream`. */
+PSX_API psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream, const float* in, float* values, float* indices,
+                               size_t rows, size_t cols, size_t k, int largest);
+
+/* Host helpers: the uniform streams the reference draws from.
+ * psx_uniforms_mt19937_64: out[i] = (std::mt19937_64(seeds[i])() >> 11) * 2^-53, the first draw
+ * of Generate() for that seed (src/generation.cpp:120,143).
+ * psx_uniforms_portable: out[i] = PortableRng{seeds[i]}.uniform() (src/portable_random.hpp:23). */
+PSX_API void psx_uniforms_mt19937_64(const uint64_t* seeds, int64_t n, double* out);
+PSX_API void psx_uniforms_portable(const uint64_t* seeds, int64_t n, double* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PSX_B200_H */

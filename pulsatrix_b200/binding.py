@@ -1,0 +1,251 @@
+"""ctypes binding of include/psx_b200.h.  Device memory comes from torch tensors; every compute
+call goes through the C ABI into the CUDA kernels."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+PACKAGE = Path(__file__).resolve().parent
+ROW_OK, ROW_NON_FINITE, ROW_ALL_REMOVED, ROW_TOO_WIDE = 0, 4, 5, 16
+OK, ERR_BAD_ARGUMENT, ERR_CUDA, ERR_ROW_FAILED, ERR_UNSUPPORTED = range(5)
+
+EXPORTS = [
+    "psx_b200_version", "psx_b200_last_error", "psx_b200_ctx_create", "psx_b200_ctx_destroy", "psx_b200_ctx_stream",
+    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_sample_rows", "psx_b200_sample_rows_host",
+    "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_top_k_rows",
+    "psx_uniforms_mt19937_64", "psx_uniforms_portable",
+]
+
+
+class PsxError(RuntimeError):
+    """A C entry point returned a non-zero psx_status.  `.status` holds it; the text is the
+    library's message (the reference's own wording for its std::invalid_argument cases)."""
+
+    def __init__(self, status, message):
+        super().__init__(message)
+        self.status = status
+
+
+class SamplingConfig(C.Structure):
+    """psx_sampling_config."""
+
+    _fields_ = [
+        ("min_new_tokens", C.c_int64),
+        ("num_new_tokens", C.c_int64),
+        ("eos_token_ids", C.POINTER(C.c_int64)),
+        ("num_eos_token_ids", C.c_int64),
+        ("do_sample", C.c_int32),
+        ("temperature", C.c_float),
+        ("top_k", C.c_int64),
+        ("top_p", C.c_float),
+        ("min_p", C.c_float),
+        ("repetition_penalty", C.c_float),
+    ]
+
+    @classmethod
+    def make(cls, do_sample=False, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, repetition_penalty=1.0,
+             min_new_tokens=0, num_new_tokens=0, eos_token_ids=()):
+        eos = np.asarray(list(eos_token_ids), dtype=np.int64)
+        cfg = cls(min_new_tokens, num_new_tokens, eos.ctypes.data_as(C.POINTER(C.c_int64)), len(eos), int(do_sample),
+                  temperature, top_k, top_p, min_p, repetition_penalty)
+        cfg._keepalive = eos
+        return cfg
+
+
+class RowDiag(C.Structure):
+    """psx_row_diag."""
+
+    _fields_ = [("candidates", C.c_int32), ("survivors", C.c_int32), ("draw_margin", C.c_double),
+                ("top_p_margin", C.c_double)]
+
+
+ROW_DIAG_DTYPE = np.dtype({"names": ["candidates", "survivors", "draw_margin", "top_p_margin"],
+                           "formats": ["<i4", "<i4", "<f8", "<f8"], "itemsize": C.sizeof(RowDiag)})
+
+_lib = None
+
+
+def library_path() -> Path:
+    return PACKAGE / "libpsx_b200.so"
+
+
+def library():
+    """Loads libpsx_b200.so.  Raises when it has not been built: there is nothing to fall back to."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not path.exists():
+            raise ImportError(f"{path} is missing: build it with `python -m pulsatrix_b200.build` (needs nvcc)")
+        lib = C.CDLL(str(path))
+        lib.psx_b200_version.restype = C.c_char_p
+        lib.psx_b200_last_error.restype = C.c_char_p
+        lib.psx_b200_ctx_stream.restype = C.c_void_p
+        lib.psx_b200_ctx_stream.argtypes = [C.c_void_p]
+        lib.psx_b200_ctx_destroy.argtypes = [C.c_void_p]
+        lib.psx_b200_launch_count.restype = C.c_uint64
+        lib.psx_b200_launch_count.argtypes = [C.c_void_p]
+        lib.psx_b200_shard_record_bytes.restype = C.c_size_t
+        lib.psx_b200_shard_record_bytes.argtypes = [C.c_void_p]
+        lib.psx_b200_ctx_create.argtypes = [C.c_int, C.c_void_p]
+        lib.psx_b200_sync.argtypes = [C.c_void_p, C.c_void_p]
+        ptr, i64 = C.c_void_p, C.c_int64
+        lib.psx_b200_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_sample_rows_host.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_shard_scan.argtypes = [ptr, ptr, ptr, i64, i64, i64, i64, i64, ptr, ptr, ptr, ptr]
+        lib.psx_b200_shard_merge.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_top_k_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int]
+        lib.psx_uniforms_mt19937_64.argtypes = [ptr, i64, ptr]
+        lib.psx_uniforms_portable.argtypes = [ptr, i64, ptr]
+        _lib = lib
+    return _lib
+
+
+def _check(status):
+    if status != OK:
+        raise PsxError(status, library().psx_b200_last_error().decode())
+
+
+def uniforms_mt19937_64(seeds) -> np.ndarray:
+    """(std::mt19937_64(seed)() >> 11) * 2^-53 per seed: Generate()'s first draw."""
+    seeds = np.ascontiguousarray(seeds, dtype=np.uint64)
+    out = np.zeros(seeds.size, dtype=np.float64)
+    library().psx_uniforms_mt19937_64(seeds.ctypes.data, seeds.size, out.ctypes.data)
+    return out
+
+
+def uniforms_portable(seeds) -> np.ndarray:
+    seeds = np.ascontiguousarray(seeds, dtype=np.uint64)
+    out = np.zeros(seeds.size, dtype=np.float64)
+    library().psx_uniforms_portable(seeds.ctypes.data, seeds.size, out.ctypes.data)
+    return out
+
+
+def _dptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class Context:
+    """A psx_ctx on one CUDA device."""
+
+    def __init__(self, device: int = 0):
+        self._lib = library()
+        self._ctx = C.c_void_p()
+        _check(self._lib.psx_b200_ctx_create(C.c_int(device), C.byref(self._ctx)))
+        self.device = device
+
+    def close(self):
+        if self._ctx:
+            self._lib.psx_b200_ctx_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def launches(self) -> int:
+        return int(self._lib.psx_b200_launch_count(self._ctx))
+
+    @property
+    def stream(self) -> int:
+        return int(self._lib.psx_b200_ctx_stream(self._ctx) or 0)
+
+    def sync(self, stream=None):
+        _check(self._lib.psx_b200_sync(self._ctx, C.c_void_p(stream) if stream else None))
+
+    # ---- device-resident sampling ------------------------------------------------------------------
+    def alloc_outputs(self, rows, with_diag=True):
+        import torch
+        dev = torch.device("cuda", self.device)
+        out = {
+            "tokens": torch.empty(rows, dtype=torch.int64, device=dev),
+            "log_probs": torch.empty(rows, dtype=torch.float32, device=dev),
+            "status": torch.empty(rows, dtype=torch.int32, device=dev),
+            "diag": torch.empty(rows * C.sizeof(RowDiag), dtype=torch.uint8, device=dev) if with_diag else None,
+        }
+        return out
+
+    def sample_rows(self, logits, history_ids, history_offsets, config, uniforms, out=None, stream=None, vocab=None):
+        """logits: cuda float32 (rows, >=vocab) with unit column stride; history/uniforms: cuda
+        tensors (int64 / float64) or None.  Asynchronous; returns the dict of output tensors."""
+        rows = logits.shape[0]
+        vocab = logits.shape[1] if vocab is None else vocab
+        assert logits.stride(1) == 1 or rows == 0
+        out = out or self.alloc_outputs(rows)
+        if stream is None:
+            import torch
+            stream = torch.cuda.current_stream(logits.device).cuda_stream
+        _check(self._lib.psx_b200_sample_rows(
+            self._ctx, C.c_void_p(stream), _dptr(logits), rows, vocab, logits.stride(0) if rows else vocab,
+            _dptr(history_ids), _dptr(history_offsets), C.addressof(config), _dptr(uniforms), _dptr(out["tokens"]),
+            _dptr(out["log_probs"]), _dptr(out["status"]), _dptr(out["diag"])))
+        return out
+
+    @staticmethod
+    def diag_to_numpy(diag_tensor):
+        return diag_tensor.cpu().numpy().view(ROW_DIAG_DTYPE)
+
+    # ---- host-resident sampling (the reference-facing call) ---------------------------------------
+    def sample_rows_host(self, logits, history_ids, history_offsets, config, uniforms, row_stride=None, vocab=None,
+                         raise_on_row_failure=True):
+        """numpy (or pinned torch CPU) inputs; returns (tokens, log_probs, status, diag) as numpy."""
+        rows = logits.shape[0]
+        vocab = logits.shape[1] if vocab is None else vocab
+        row_stride = (logits.strides[0] // 4 if hasattr(logits, "strides") else logits.stride(0)) \
+            if row_stride is None else row_stride
+        tokens = np.zeros(rows, dtype=np.int64)
+        logp = np.zeros(rows, dtype=np.float32)
+        status = np.zeros(rows, dtype=np.int32)
+        diag = np.zeros(rows, dtype=ROW_DIAG_DTYPE)
+
+        def hptr(a):
+            if a is None:
+                return None
+            return C.c_void_p(a.ctypes.data if hasattr(a, "ctypes") else a.data_ptr())
+
+        rc = self._lib.psx_b200_sample_rows_host(self._ctx, hptr(logits), rows, vocab, row_stride, hptr(history_ids),
+                                                 hptr(history_offsets), C.addressof(config), hptr(uniforms),
+                                                 hptr(tokens), hptr(logp), hptr(status), hptr(diag))
+        if rc != OK and (rc != ERR_ROW_FAILED or raise_on_row_failure):
+            _check(rc)
+        return tokens, logp, status, diag
+
+    # ---- top-k ---------------------------------------------------------------------------------------
+    def top_k_rows(self, x, k, largest=True, stream=None):
+        """x: cuda float32 contiguous (rows, cols).  Returns (values, indices) cuda float32 (rows, k)."""
+        import torch
+        rows, cols = x.shape
+        values = torch.empty((rows, max(k, 0)), dtype=torch.float32, device=x.device)
+        indices = torch.empty((rows, max(k, 0)), dtype=torch.float32, device=x.device)
+        if stream is None:
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+        _check(self._lib.psx_b200_top_k_rows(self._ctx, C.c_void_p(stream), _dptr(x), _dptr(values), _dptr(indices),
+                                             rows, cols, k if k >= 0 else 0, int(largest)))
+        return values, indices
+
+    # ---- vocabulary-sharded -----------------------------------------------------------------------------
+    def shard_record_bytes(self, config) -> int:
+        return int(self._lib.psx_b200_shard_record_bytes(C.addressof(config)))
+
+    def shard_scan(self, shard_logits, shard_begin, vocab, history_ids, history_offsets, config, records, stream=None):
+        import torch
+        rows, cols = shard_logits.shape
+        if stream is None:
+            stream = torch.cuda.current_stream(shard_logits.device).cuda_stream
+        _check(self._lib.psx_b200_shard_scan(self._ctx, C.c_void_p(stream), _dptr(shard_logits), rows, cols,
+                                             shard_logits.stride(0), shard_begin, vocab, _dptr(history_ids),
+                                             _dptr(history_offsets), C.addressof(config), _dptr(records)))
+
+    def shard_merge(self, gathered, num_shards, rows, vocab, config, uniforms, out=None, stream=None):
+        import torch
+        out = out or self.alloc_outputs(rows)
+        if stream is None:
+            stream = torch.cuda.current_stream(gathered.device).cuda_stream
+        _check(self._lib.psx_b200_shard_merge(self._ctx, C.c_void_p(stream), _dptr(gathered), num_shards, rows, vocab,
+                                              C.addressof(config), _dptr(uniforms), _dptr(out["tokens"]),
+                                              _dptr(out["log_probs"]), _dptr(out["status"]), _dptr(out["diag"])))
+        return out

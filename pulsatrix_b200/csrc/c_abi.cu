@@ -1,0 +1,518 @@
+// The C ABI (include/psx_b200.h): argument checks with the reference's own error texts, scratch
+// management, launch planning and the kernel launches.  No computation happens on the host and
+// there is no fallback: every entry point that computes needs the CUDA device of its context.
+#include "../../include/psx_b200.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "merge_rows.cuh"
+#include "scan_rows.cuh"
+#include "shard_records.cuh"
+#include "topk_rows.cuh"
+
+namespace {
+
+thread_local std::string g_error;
+
+psx_status fail(psx_status code, std::string message) {
+    g_error = std::move(message);
+    return code;
+}
+
+// Same text as the reference's PULSATRIX_CUDA_CHECK (include/pulsatrix/cuda_check.hpp:24-32).
+#define PSX_CUDA(call)                                                                                   \
+    do {                                                                                                 \
+        const cudaError_t psx_cuda_result = (call);                                                      \
+        if (psx_cuda_result != cudaSuccess) {                                                            \
+            return fail(PSX_ERR_CUDA, std::string("CUDA error: ") + cudaGetErrorString(psx_cuda_result) + \
+                                          " at " __FILE__ ":" + std::to_string(__LINE__));               \
+        }                                                                                                \
+    } while (0)
+
+struct Buffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+}  // namespace
+
+struct psx_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    int merge_capacity_configured = 0;
+    int nucleus_k = 160;  // logits every part hands on when no top-k bounds the survivors
+    // row-pass scratch
+    Buffer stats, seg_counts, candidates, banned;
+    // staging of the host entry point
+    Buffer h_logits, h_history, h_offsets, h_uniforms, h_tokens, h_log_probs, h_status, h_diag;
+    // staging of the sharded path
+    Buffer shard_uniform_scratch;
+};
+
+namespace {
+
+psx_status reserve(Buffer& b, size_t bytes) {
+    if (bytes <= b.bytes) return PSX_OK;
+    if (b.ptr) PSX_CUDA(cudaFree(b.ptr));
+    b.ptr = nullptr;
+    b.bytes = 0;
+    const size_t want = bytes + bytes / 4 + 256;
+    PSX_CUDA(cudaMalloc(&b.ptr, want));
+    b.bytes = want;
+    return PSX_OK;
+}
+
+// src/generation.cpp:19-38, with the reference's messages.
+psx_status check_config(const psx_sampling_config* c) {
+    if (!c) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: config is null");
+    if (c->min_new_tokens < 0) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "GenerationConfig: max_new_tokens and min_new_tokens must not be negative");
+    }
+    if (!(c->temperature > 0.0f) || std::isinf(c->temperature)) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "GenerationConfig: temperature must be positive and finite");
+    }
+    if (c->top_k < 0) return fail(PSX_ERR_BAD_ARGUMENT, "GenerationConfig: top_k must not be negative");
+    if (!(c->top_p > 0.0f && c->top_p <= 1.0f)) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "GenerationConfig: top_p must be in (0, 1]");
+    }
+    if (!(c->min_p >= 0.0f && c->min_p <= 1.0f)) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "GenerationConfig: min_p must be in [0, 1]");
+    }
+    if (!(c->repetition_penalty > 0.0f) || std::isinf(c->repetition_penalty)) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "GenerationConfig: repetition_penalty must be positive and finite");
+    }
+    if (c->num_eos_token_ids < 0 || (c->num_eos_token_ids > 0 && !c->eos_token_ids)) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: eos_token_ids is null");
+    }
+    return PSX_OK;
+}
+
+struct Plan {
+    int parts = 1;
+    int vecs_per_part = 1;
+    int k_need = 1;
+    bool nucleus = false;  // sampling without a top-k: the processed tail mass is needed too
+    bool apply_temperature = false;
+    int sort_capacity = 1024;
+};
+
+Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t row_stride, int64_t vocab,
+               const psx_sampling_config* c) {
+    Plan plan;
+    const bool aligned = (reinterpret_cast<uintptr_t>(logits) % 16 == 0) && (row_stride % 4 == 0);
+    const int64_t vectors = (cols + 3 + (aligned ? 0 : 3)) / 4;  // most float4 a row can span
+    plan.parts = (int)((vectors + psx::kPartVecs - 1) / psx::kPartVecs);
+    plan.vecs_per_part = (int)((vectors + plan.parts - 1) / plan.parts);
+    const bool sample = c->do_sample != 0;
+    const bool top_k_on = sample && c->top_k > 0 && c->top_k < vocab;
+    plan.apply_temperature = sample && c->temperature != 1.0f;  // src/generation.cpp:77
+    plan.nucleus = sample && !top_k_on;
+    if (!sample) plan.k_need = 1;
+    else if (top_k_on) plan.k_need = (int)std::min<int64_t>(c->top_k, 1 << 20);
+    else plan.k_need = ctx->nucleus_k;
+    plan.sort_capacity = plan.nucleus ? 4096 : 1024;
+    return plan;
+}
+
+psx_status configure_merge(psx_ctx* ctx, int capacity) {
+    if (ctx->merge_capacity_configured >= capacity) return PSX_OK;
+    PSX_CUDA(psx::configure_merge_rows(capacity));
+    ctx->merge_capacity_configured = capacity;
+    return PSX_OK;
+}
+
+// Fills the part of ScanParams that depends on the settings; uploads the banned ids.
+psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_config* c, const Plan& plan,
+                        psx::ScanParams& sp) {
+    sp.apply_penalty = c->repetition_penalty != 1.0f ? 1 : 0;  // src/generation.cpp:59
+    sp.penalty = c->repetition_penalty;
+    sp.apply_temperature = plan.apply_temperature ? 1 : 0;
+    sp.temperature = c->temperature;
+    const double log2e = 1.4426950408889634073599246810019;
+    sp.log2e_over_t = (float)(plan.apply_temperature ? log2e / (double)c->temperature : log2e);
+    sp.k_need = plan.k_need;
+    sp.parts = plan.parts;
+    sp.vecs_per_part = plan.vecs_per_part;
+    sp.num_banned = 0;
+    sp.banned_ids = nullptr;
+    if (c->num_new_tokens < c->min_new_tokens && c->num_eos_token_ids > 0) {  // src/generation.cpp:69
+        if (c->num_eos_token_ids > (1 << 20)) return fail(PSX_ERR_UNSUPPORTED, "psx_b200: too many eos ids");
+        const size_t bytes = (size_t)c->num_eos_token_ids * sizeof(int64_t);
+        if (psx_status s = reserve(ctx->banned, bytes)) return s;
+        PSX_CUDA(cudaMemcpyAsync(ctx->banned.ptr, c->eos_token_ids, bytes, cudaMemcpyHostToDevice, stream));
+        sp.banned_ids = static_cast<const int64_t*>(ctx->banned.ptr);
+        sp.num_banned = (int32_t)c->num_eos_token_ids;
+    }
+    return PSX_OK;
+}
+
+psx_status reserve_scan_scratch(psx_ctx* ctx, int64_t rows, const Plan& plan, psx::ScanParams& sp) {
+    const size_t parts = (size_t)rows * plan.parts;
+    if (psx_status s = reserve(ctx->stats, parts * sizeof(psx::PartStats))) return s;
+    if (psx_status s = reserve(ctx->seg_counts, parts * psx::kScanWarps * sizeof(uint32_t))) return s;
+    if (psx_status s = reserve(ctx->candidates, parts * psx::kScanWarps * psx::kSegCap * sizeof(uint2))) return s;
+    sp.stats = static_cast<psx::PartStats*>(ctx->stats.ptr);
+    sp.seg_counts = static_cast<uint32_t*>(ctx->seg_counts.ptr);
+    sp.candidates = static_cast<uint2*>(ctx->candidates.ptr);
+    return PSX_OK;
+}
+
+void fill_merge_settings(psx::MergeParams& mp, const psx_sampling_config* c, const Plan& plan, int64_t rows,
+                         int64_t vocab, const double* uniforms, int64_t* tokens, float* log_probs,
+                         int32_t* row_status, psx_row_diag* diag) {
+    mp.rows = rows;
+    mp.vocab = vocab;
+    mp.do_sample = c->do_sample != 0;
+    mp.apply_temperature = plan.apply_temperature ? 1 : 0;
+    mp.temperature = c->temperature;
+    mp.penalty = c->repetition_penalty;
+    mp.top_k = c->top_k;
+    mp.top_p = c->top_p;
+    mp.min_p = c->min_p;
+    mp.uniforms = uniforms;
+    mp.tokens = tokens;
+    mp.log_probs = log_probs;
+    mp.row_status = row_status;
+    mp.diag = diag;
+    mp.sort_capacity = plan.sort_capacity;
+}
+
+psx_status check_common(psx_ctx* ctx, const psx_sampling_config* config, int64_t rows, int64_t cols,
+                        int64_t row_stride, int64_t vocab, const void* logits, const void* history_ids,
+                        const void* history_offsets) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (psx_status s = check_config(config)) return s;
+    if (rows < 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: rows must not be negative");
+    if (vocab <= 0 || cols <= 0) return fail(PSX_ERR_BAD_ARGUMENT, "Generate: the model returned no logits");
+    if (vocab > (int64_t)psx::kColumnMask) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: vocabulary exceeds 2^30 - 1 columns");
+    }
+    if (row_stride < cols) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: row_stride is smaller than the row");
+    if (rows > 0 && !logits) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: logits is null");
+    if (config->repetition_penalty != 1.0f && rows > 0 && (!history_ids || !history_offsets)) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: a repetition penalty needs history_ids and history_offsets");
+    }
+    return PSX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* psx_b200_version(void) { return "0.1.0"; }
+const char* psx_b200_last_error(void) { return g_error.c_str(); }
+
+psx_status psx_b200_ctx_create(int device, psx_ctx** out) {
+    if (!out) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: out is null");
+    *out = nullptr;
+    int count = 0;
+    PSX_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: no such CUDA device");
+    PSX_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    PSX_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: the kernels are built for sm_100a (B200) only");
+    }
+    psx_ctx* ctx = new psx_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    const cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete ctx;
+        return fail(PSX_ERR_CUDA, std::string("CUDA error: ") + cudaGetErrorString(e));
+    }
+    *out = ctx;
+    return PSX_OK;
+}
+
+void psx_b200_ctx_destroy(psx_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (Buffer* b : {&ctx->stats, &ctx->seg_counts, &ctx->candidates, &ctx->banned, &ctx->h_logits, &ctx->h_history,
+                      &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
+                      &ctx->h_diag, &ctx->shard_uniform_scratch}) {
+        if (b->ptr) cudaFree(b->ptr);
+    }
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+void* psx_b200_ctx_stream(psx_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
+
+psx_status psx_b200_sync(psx_ctx* ctx, void* stream) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    PSX_CUDA(cudaStreamSynchronize(stream ? static_cast<cudaStream_t>(stream) : ctx->stream));
+    return PSX_OK;
+}
+
+uint64_t psx_b200_launch_count(const psx_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* logits, int64_t rows, int64_t vocab,
+                                int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
+                                const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
+                                float* log_probs, int32_t* row_status, psx_row_diag* diag) {
+    if (psx_status s = check_common(ctx, config, rows, vocab, row_stride, vocab, logits, history_ids, history_offsets)) {
+        return s;
+    }
+    if (rows == 0) return PSX_OK;
+    if (!tokens || !log_probs || !row_status) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: an output pointer is null");
+    if (config->do_sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
+    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    PSX_CUDA(cudaSetDevice(ctx->device));
+
+    const Plan plan = make_plan(ctx, logits, vocab, row_stride, vocab, config);
+    psx::ScanParams sp{};
+    sp.logits = logits;
+    sp.row_stride = row_stride;
+    sp.rows = rows;
+    sp.cols = vocab;
+    sp.col_begin = 0;
+    sp.vocab = vocab;
+    sp.history_ids = history_ids;
+    sp.history_offsets = history_offsets;
+    if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
+    if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp)) return s;
+    if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
+
+    PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+    ++ctx->launches;
+
+    psx::MergeParams mp{};
+    mp.stats = sp.stats;
+    mp.seg_counts = sp.seg_counts;
+    mp.candidates = sp.candidates;
+    mp.parts = plan.parts;
+    mp.segs_per_part = psx::kScanWarps;
+    mp.seg_cap = psx::kSegCap;
+    mp.stats_part_stride = sizeof(psx::PartStats);
+    mp.stats_row_stride = mp.stats_part_stride * plan.parts;
+    mp.count_seg_stride = sizeof(uint32_t);
+    mp.count_row_stride = mp.count_seg_stride * plan.parts * psx::kScanWarps;
+    mp.cand_seg_stride = sizeof(uint2) * psx::kSegCap;
+    mp.cand_row_stride = mp.cand_seg_stride * plan.parts * psx::kScanWarps;
+    fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
+    PSX_CUDA(psx::launch_merge_rows(mp, stream));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_sample_rows_host(psx_ctx* ctx, const float* logits, int64_t rows, int64_t vocab,
+                                     int64_t row_stride, const int64_t* history_ids,
+                                     const int64_t* history_offsets, const psx_sampling_config* config,
+                                     const double* uniforms, int64_t* tokens, float* log_probs,
+                                     int32_t* row_status, psx_row_diag* diag) {
+    if (psx_status s = check_common(ctx, config, rows, vocab, row_stride, vocab, logits, history_ids, history_offsets)) {
+        return s;
+    }
+    if (rows == 0) return PSX_OK;
+    if (!tokens || !log_probs || !row_status) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: an output pointer is null");
+    if (config->do_sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t stream = ctx->stream;
+    const bool with_history = history_ids && history_offsets;
+    const int64_t history_total = with_history ? history_offsets[rows] : 0;
+    if (with_history && history_total < 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: history_offsets must ascend");
+
+    if (psx_status s = reserve(ctx->h_logits, (size_t)rows * vocab * sizeof(float))) return s;
+    if (psx_status s = reserve(ctx->h_history, (size_t)std::max<int64_t>(history_total, 1) * sizeof(int64_t))) return s;
+    if (psx_status s = reserve(ctx->h_offsets, (size_t)(rows + 1) * sizeof(int64_t))) return s;
+    if (psx_status s = reserve(ctx->h_uniforms, (size_t)rows * sizeof(double))) return s;
+    if (psx_status s = reserve(ctx->h_tokens, (size_t)rows * sizeof(int64_t))) return s;
+    if (psx_status s = reserve(ctx->h_log_probs, (size_t)rows * sizeof(float))) return s;
+    if (psx_status s = reserve(ctx->h_status, (size_t)rows * sizeof(int32_t))) return s;
+    if (psx_status s = reserve(ctx->h_diag, (size_t)rows * sizeof(psx_row_diag))) return s;
+
+    // Rows are packed on the device (stride = vocab) whatever the host stride is.
+    PSX_CUDA(cudaMemcpy2DAsync(ctx->h_logits.ptr, (size_t)vocab * sizeof(float), logits,
+                               (size_t)row_stride * sizeof(float), (size_t)vocab * sizeof(float), (size_t)rows,
+                               cudaMemcpyHostToDevice, stream));
+    if (with_history) {
+        if (history_total > 0) {
+            PSX_CUDA(cudaMemcpyAsync(ctx->h_history.ptr, history_ids, (size_t)history_total * sizeof(int64_t),
+                                     cudaMemcpyHostToDevice, stream));
+        }
+        PSX_CUDA(cudaMemcpyAsync(ctx->h_offsets.ptr, history_offsets, (size_t)(rows + 1) * sizeof(int64_t),
+                                 cudaMemcpyHostToDevice, stream));
+    }
+    if (config->do_sample) {
+        PSX_CUDA(cudaMemcpyAsync(ctx->h_uniforms.ptr, uniforms, (size_t)rows * sizeof(double), cudaMemcpyHostToDevice,
+                                 stream));
+    }
+    if (psx_status s = psx_b200_sample_rows(
+            ctx, stream, static_cast<const float*>(ctx->h_logits.ptr), rows, vocab, vocab,
+            with_history ? static_cast<const int64_t*>(ctx->h_history.ptr) : nullptr,
+            with_history ? static_cast<const int64_t*>(ctx->h_offsets.ptr) : nullptr, config,
+            static_cast<const double*>(ctx->h_uniforms.ptr), static_cast<int64_t*>(ctx->h_tokens.ptr),
+            static_cast<float*>(ctx->h_log_probs.ptr), static_cast<int32_t*>(ctx->h_status.ptr),
+            diag ? static_cast<psx_row_diag*>(ctx->h_diag.ptr) : nullptr)) {
+        return s;
+    }
+    PSX_CUDA(cudaMemcpyAsync(tokens, ctx->h_tokens.ptr, (size_t)rows * sizeof(int64_t), cudaMemcpyDeviceToHost, stream));
+    PSX_CUDA(cudaMemcpyAsync(log_probs, ctx->h_log_probs.ptr, (size_t)rows * sizeof(float), cudaMemcpyDeviceToHost,
+                             stream));
+    PSX_CUDA(cudaMemcpyAsync(row_status, ctx->h_status.ptr, (size_t)rows * sizeof(int32_t), cudaMemcpyDeviceToHost,
+                             stream));
+    if (diag) {
+        PSX_CUDA(cudaMemcpyAsync(diag, ctx->h_diag.ptr, (size_t)rows * sizeof(psx_row_diag), cudaMemcpyDeviceToHost,
+                                 stream));
+    }
+    PSX_CUDA(cudaStreamSynchronize(stream));
+    for (int64_t r = 0; r < rows; ++r) {
+        if (row_status[r] != PSX_ROW_OK) {
+            const char* what = row_status[r] == PSX_ROW_NON_FINITE    ? "Generate: the model returned a non-finite logit"
+                               : row_status[r] == PSX_ROW_ALL_REMOVED ? "Generate: every token was removed"
+                                                                      : "psx_b200: too many tokens survive the filters "
+                                                                        "for the device path";
+            return fail(PSX_ERR_ROW_FAILED, std::string(what) + " (row " + std::to_string(r) + ")");
+        }
+    }
+    return PSX_OK;
+}
+
+size_t psx_b200_shard_record_bytes(const psx_sampling_config* config) {
+    return psx::shard_record_bytes(psx::shard_record_capacity(config ? config->do_sample != 0 : false,
+                                                              config ? config->top_k : 0));
+}
+
+psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shard_logits, int64_t rows,
+                               int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
+                               const int64_t* history_ids, const int64_t* history_offsets,
+                               const psx_sampling_config* config, void* records) {
+    if (psx_status s = check_common(ctx, config, rows, shard_cols, row_stride, vocab, shard_logits, history_ids,
+                                    history_offsets)) {
+        return s;
+    }
+    if (shard_begin < 0 || shard_begin + shard_cols > vocab) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the shard does not lie inside the vocabulary");
+    }
+    if (rows == 0) return PSX_OK;
+    if (!records) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: records is null");
+    const bool sample = config->do_sample != 0;
+    if (sample && !(config->top_k > 0 && config->top_k < vocab)) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: the vocabulary-sharded path samples with a top-k only");
+    }
+    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    PSX_CUDA(cudaSetDevice(ctx->device));
+
+    const Plan plan = make_plan(ctx, shard_logits, shard_cols, row_stride, vocab, config);
+    psx::ScanParams sp{};
+    sp.logits = shard_logits;
+    sp.row_stride = row_stride;
+    sp.rows = rows;
+    sp.cols = shard_cols;
+    sp.col_begin = shard_begin;
+    sp.vocab = vocab;
+    sp.history_ids = history_ids;
+    sp.history_offsets = history_offsets;
+    if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
+    if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp)) return s;
+    PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+    ++ctx->launches;
+
+    psx::PackParams pp{};
+    pp.stats = sp.stats;
+    pp.seg_counts = sp.seg_counts;
+    pp.candidates = sp.candidates;
+    pp.parts = plan.parts;
+    pp.rows = rows;
+    pp.apply_temperature = plan.apply_temperature ? 1 : 0;
+    pp.temperature = config->temperature;
+    pp.penalty = config->repetition_penalty;
+    pp.capacity = psx::shard_record_capacity(sample, config->top_k);
+    pp.records = records;
+    PSX_CUDA(psx::launch_pack_records(pp, stream));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gathered, int32_t num_shards,
+                                int64_t rows, int64_t vocab, const psx_sampling_config* config,
+                                const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
+                                psx_row_diag* diag) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (psx_status s = check_config(config)) return s;
+    if (rows < 0 || num_shards < 1 || vocab <= 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: bad sizes");
+    if (rows == 0) return PSX_OK;
+    if (!gathered || !tokens || !log_probs || !row_status) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    const bool sample = config->do_sample != 0;
+    if (sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
+    if (sample && !(config->top_k > 0 && config->top_k < vocab)) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: the vocabulary-sharded path samples with a top-k only");
+    }
+    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    PSX_CUDA(cudaSetDevice(ctx->device));
+
+    Plan plan;
+    plan.apply_temperature = sample && config->temperature != 1.0f;
+    plan.sort_capacity = 1024;
+    if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
+    const int capacity = psx::shard_record_capacity(sample, config->top_k);
+    const int64_t record = (int64_t)psx::shard_record_bytes(capacity);
+    const char* base = static_cast<const char*>(gathered);
+    psx::MergeParams mp{};
+    mp.stats = base + psx::kRecordStatsOffset;
+    mp.seg_counts = base + psx::kRecordCountOffset;
+    mp.candidates = base + psx::kRecordCandidatesOffset;
+    mp.parts = num_shards;
+    mp.segs_per_part = 1;
+    mp.seg_cap = capacity;
+    mp.stats_row_stride = mp.count_row_stride = mp.cand_row_stride = record;
+    mp.stats_part_stride = mp.count_seg_stride = mp.cand_seg_stride = record * rows;
+    fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
+    PSX_CUDA(psx::launch_merge_rows(mp, stream));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream_ptr, const float* in, float* values, float* indices,
+                               size_t rows, size_t cols, size_t k, int largest) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (rows == 0) return PSX_OK;  // src/cuda_backend.cu:853-855
+    if (cols == 0) return fail(PSX_ERR_BAD_ARGUMENT, "top_k: input must be non-empty with rank >= 1");
+    if (k < 1 || k > cols) {  // src/top_k.cpp:14-17
+        return fail(PSX_ERR_BAD_ARGUMENT,
+                    "top_k: k must be in [1, " + std::to_string(cols) + "], got " + std::to_string(k));
+    }
+    if (cols > (size_t(1) << 24)) {  // src/top_k.cpp:19-21
+        return fail(PSX_ERR_BAD_ARGUMENT, "top_k: last dimension exceeds 2^24, beyond exact float indices");
+    }
+    if (k > (size_t)psx::kTopKMax) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: top_k_rows holds at most " + std::to_string(psx::kTopKMax) +
+                                             " entries per row on the device");
+    }
+    if (rows > 0x7FFFFFFFull) return fail(PSX_ERR_UNSUPPORTED, "psx_b200: too many rows for one launch");
+    if (!in || !values || !indices) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    PSX_CUDA(psx::launch_topk_rows(in, values, indices, rows, cols, k, largest != 0, stream));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+void psx_uniforms_mt19937_64(const uint64_t* seeds, int64_t n, double* out) {
+    for (int64_t i = 0; i < n; ++i) {
+        std::mt19937_64 engine(seeds[i]);
+        out[i] = static_cast<double>(engine() >> 11) * 0x1.0p-53;
+    }
+}
+
+void psx_uniforms_portable(const uint64_t* seeds, int64_t n, double* out) {
+    for (int64_t i = 0; i < n; ++i) {
+        uint64_t z = seeds[i] + 0x9E3779B97F4A7C15ULL;  // SplitMix64: one step from state = seed
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+        z ^= z >> 31;
+        out[i] = (static_cast<double>(z >> 11) + 0.5) / static_cast<double>(1ULL << 53);
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,335 @@
+// The survivor stage: one CTA per row turns the row pass's candidates into a token.
+//
+// Input per row: for each part its raw max / tail sum-exp and a few dozen candidates (raw logit,
+// column, flags).  The stage
+//   1. joins the parts' partial log-sum-exp (raw, and processed when a full-vocabulary top-p or
+//      min-p needs it): M = max m_i, Z = sum z_i * exp(m_i - M) + sum over candidates, in double;
+//   2. keeps the candidates at or above the largest part threshold (only those can survive any
+//      filter), applies penalty and temperature with the reference's float operations, and sorts
+//      them by (value descending, column ascending) in shared memory;
+//   3. replays src/generation.cpp:80-152 on that short list in the reference's own order and
+//      precision -- the k-th value with its ties, softmax sums in column order, the top-p walk in
+//      ascending (value, column) order against 1 - (double)top_p, min-p against the first
+//      maximum, the inverse-CDF walk in column order against the row's uniform -- all in double;
+//   4. writes the token, float(log(exp(l - M) / Z)) of the raw logits (src/generation.cpp:156),
+//      a row status and the distances of the two decisions from their boundaries.
+// Reads a few KB per row; never touches the logits.
+#include "merge_rows.cuh"
+
+#include "../../include/psx_b200.h"
+
+namespace psx {
+
+namespace {
+
+using u64 = unsigned long long;
+
+struct Decision {
+    long long token;
+    int status;
+    int survivors;
+    double draw_margin;
+    double top_p_margin;
+};
+
+__device__ __forceinline__ uint32_t key_ord(u64 k) { return (uint32_t)(k >> 32); }
+__device__ __forceinline__ uint32_t key_col(u64 k) { return ~(uint32_t)k; }
+
+// Step 3, by one thread, in the reference's summation order.  keyA: the ns survivors of top-k by
+// (value desc, column asc); keyB: (column << 32 | position in keyA) ascending; ex[pos] =
+// exp(x'[pos] - x'max).  `rest` is the processed mass (relative to x'max) of everything that is
+// not in keyA and still alive, `rest_bound` an upper bound on any such entry's ex.
+__device__ void decide(const MergeParams& p, const u64* keyA, const u64* keyB, const double* ex, uint8_t* alive,
+                       int ns, bool rest_alive, double rest, double rest_bound, double u, Decision& out) {
+    out.status = PSX_ROW_OK;
+    out.token = -1;
+    out.draw_margin = INFINITY;
+    out.top_p_margin = INFINITY;
+    out.survivors = 0;
+    const bool sample = p.do_sample != 0;
+
+    if (sample && p.top_p < 1.0f) {  // src/generation.cpp:89-103
+        const double limit = 1.0 - (double)p.top_p;
+        double sum = rest_alive ? rest : 0.0;
+        for (int j = 0; j < ns; ++j) sum += ex[(uint32_t)keyB[j]];
+        double cumulative = 0.0;
+        if (rest_alive) {
+            // Everything outside the list is smaller than everything in it, so it leads the
+            // ascending walk; it must fall below the cut as a whole.
+            cumulative = rest / sum;
+            out.top_p_margin = fabs(cumulative - limit);
+            if (!(cumulative <= limit)) { out.status = PSX_ROW_TOO_WIDE; return; }
+            rest_alive = false;
+        }
+        bool crossed = false;
+        int group_end = ns;
+        while (group_end > 0 && !crossed) {
+            const uint32_t ord = key_ord(keyA[group_end - 1]);
+            int group_begin = group_end - 1;
+            while (group_begin > 0 && key_ord(keyA[group_begin - 1]) == ord) --group_begin;
+            for (int pos = group_begin; pos < group_end; ++pos) {  // equal values: lower column first
+                if (group_begin == 0 && pos == group_end - 1) break;  // the last of the walk always stays
+                cumulative += ex[pos] / sum;
+                const double dist = fabs(cumulative - limit);
+                if (dist < out.top_p_margin) out.top_p_margin = dist;
+                if (cumulative <= limit) {
+                    alive[pos] = 0;
+                } else {
+                    crossed = true;
+                    break;
+                }
+            }
+            group_end = group_begin;
+        }
+    }
+
+    if (sample && p.min_p > 0.0f) {  // src/generation.cpp:104-111
+        double sum = rest_alive ? rest : 0.0;
+        for (int j = 0; j < ns; ++j) {
+            const uint32_t pos = (uint32_t)keyB[j];
+            if (alive[pos]) sum += ex[pos];
+        }
+        const double top = ex[0] / sum;  // position 0 is the first maximum and is never removed
+        const double floor_p = p.min_p * top;
+        for (int pos = 1; pos < ns; ++pos) {
+            if (alive[pos] && ex[pos] / sum < floor_p) alive[pos] = 0;
+        }
+        if (rest_alive) {
+            if (rest_bound / sum < floor_p) rest_alive = false;
+            else { out.status = PSX_ROW_TOO_WIDE; return; }
+        }
+    }
+
+    int survivors = 0;
+    for (int pos = 0; pos < ns; ++pos) survivors += alive[pos];
+    out.survivors = survivors;
+
+    long long chosen = key_col(keyA[0]);  // src/generation.cpp:135 first maximum: lower column wins
+    if (sample) {                         // src/generation.cpp:140-152
+        if (rest_alive) { out.status = PSX_ROW_TOO_WIDE; return; }
+        double sum = 0.0;
+        for (int j = 0; j < ns; ++j) {
+            const uint32_t pos = (uint32_t)keyB[j];
+            if (alive[pos]) sum += ex[pos];
+        }
+        double cumulative = 0.0, before = 0.0;
+        for (int j = 0; j < ns; ++j) {
+            const uint32_t pos = (uint32_t)keyB[j];
+            if (!alive[pos]) continue;
+            const double pr = ex[pos] / sum;
+            if (pr == 0.0) continue;
+            before = cumulative;
+            cumulative += pr;
+            chosen = (long long)(keyB[j] >> 32);
+            if (u < cumulative) break;
+        }
+        const double lo = fabs(u - before), hi = fabs(u - cumulative);
+        out.draw_margin = before == 0.0 ? hi : fmin(lo, hi);
+    }
+    out.token = chosen;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = scratch[0];
+    for (int w = 1; w < kMergeThreads / 32; ++w) r = fmaxf(r, scratch[w]);
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ double block_sum(double v, double* scratch) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double r = 0.0;
+    for (int w = 0; w < kMergeThreads / 32; ++w) r += scratch[w];
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergeParams p) {
+    extern __shared__ u64 dyn[];
+    const int cap = p.sort_capacity;
+    u64* keyA = dyn;
+    u64* keyB = keyA + cap;
+    double* ex = reinterpret_cast<double*>(keyB + cap);
+    uint8_t* alive = reinterpret_cast<uint8_t*>(ex + cap);
+
+    __shared__ float s_f[kMergeThreads / 32];
+    __shared__ double s_d[kMergeThreads / 32];
+    __shared__ int s_count;
+    __shared__ int s_ns;
+    __shared__ uint32_t s_chosen_raw;
+    __shared__ Decision s_dec;
+
+    const int64_t row = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool apply_t = p.apply_temperature != 0;
+    const char* stats_row = static_cast<const char*>(p.stats) + row * p.stats_row_stride;
+    const char* counts_row = static_cast<const char*>(p.seg_counts) + row * p.count_row_stride;
+    const char* cands_row = static_cast<const char*>(p.candidates) + row * p.cand_row_stride;
+    auto part_stats = [&](int i) { return *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride); };
+    auto seg_count = [&](int s) {
+        return min((int)*reinterpret_cast<const uint32_t*>(counts_row + s * p.count_seg_stride), p.seg_cap);
+    };
+    auto seg_cands = [&](int s) { return reinterpret_cast<const uint2*>(cands_row + s * p.cand_seg_stride); };
+
+    // ---- 1. join the parts ------------------------------------------------------------------------
+    float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
+    double bad = 0.0, alive_tail = 0.0;
+    for (int i = tid; i < p.parts; i += kMergeThreads) {
+        const PartStats s = part_stats(i);
+        raw_max = fmaxf(raw_max, s.raw_max);
+        y_max = fmaxf(y_max, s.y_max);
+        thr = fmaxf(thr, s.thr);
+        bad += (double)(s.nonfinite * 1u + s.overflow * 65536u);
+        alive_tail += (double)s.alive_tail;
+    }
+    if (tid == 0) s_count = 0;
+    raw_max = block_max(raw_max, s_f);
+    y_max = block_max(y_max, s_f);
+    thr = block_max(thr, s_f);
+    bad = block_sum(bad, s_d);
+    alive_tail = block_sum(alive_tail, s_d);
+    const uint32_t bad_bits = (uint32_t)bad;
+    if ((bad_bits & 0xFFFFu) != 0 || bad_bits >= 65536u) {
+        if (tid == 0) {
+            p.tokens[row] = -1;
+            p.log_probs[row] = 0.0f;
+            p.row_status[row] = (bad_bits & 0xFFFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
+            if (p.diag) p.diag[row] = psx_row_diag{0, 0, INFINITY, INFINITY};
+        }
+        return;
+    }
+    const float keep_from = relax_threshold(thr, apply_t, p.temperature);
+    const float x_max = temper(y_max, apply_t, p.temperature);
+
+    // ---- 2. candidates: raw sum-exp for all, the list for those that can survive ----------------
+    double z_raw = 0.0, z_rest = 0.0, dropped = 0.0;
+    for (int i = tid; i < p.parts; i += kMergeThreads) {
+        const PartStats s = part_stats(i);
+        z_raw += s.raw_tail * exp((double)s.raw_max - (double)raw_max);
+        if (s.y_max > -INFINITY && s.proc_tail > 0.0) {
+            z_rest += s.proc_tail * exp((double)temper(s.y_max, apply_t, p.temperature) - (double)x_max);
+        }
+    }
+    const int nseg = p.parts * p.segs_per_part;
+    for (int s = warp; s < nseg; s += kMergeThreads / 32) {
+        const int cnt = seg_count(s);
+        const uint2* seg = seg_cands(s);
+        for (int i = lane; i < cnt; i += 32) {
+            const uint2 c = seg[i];
+            const float l = __uint_as_float(c.x);
+            z_raw += exp((double)l - (double)raw_max);
+            const float y = processed_before_temperature(l, c.y, p.penalty);
+            const float x = temper(y, apply_t, p.temperature);
+            if (y >= keep_from) {
+                const int slot = atomicAdd(&s_count, 1);
+                if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(c.y & kColumnMask);
+            } else if (y > -INFINITY) {
+                z_rest += exp((double)x - (double)x_max);
+                dropped += 1.0;
+            }
+        }
+    }
+    z_raw = block_sum(z_raw, s_d);
+    z_rest = block_sum(z_rest, s_d);
+    dropped = block_sum(dropped, s_d);  // ends with a barrier: s_count is final
+    const int n = s_count;
+    if (n > cap || n == 0) {
+        if (tid == 0) {
+            p.tokens[row] = -1;
+            p.log_probs[row] = 0.0f;
+            p.row_status[row] = n == 0 ? PSX_ROW_ALL_REMOVED : PSX_ROW_TOO_WIDE;
+            if (p.diag) p.diag[row] = psx_row_diag{n, 0, INFINITY, INFINITY};
+        }
+        return;
+    }
+
+    // ---- 3. sort by (value desc, column asc); top-k keeps the k-th value and its ties -----------
+    int n_pad = 2;
+    while (n_pad < n) n_pad <<= 1;
+    for (int i = n + tid; i < n_pad; i += kMergeThreads) keyA[i] = 0;
+    __syncthreads();
+    block_bitonic_sort(keyA, n_pad, /*descending=*/true);
+
+    const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
+    if (tid == 0) s_ns = 0;
+    __syncthreads();
+    bool rest_alive = false;
+    if (top_k_on && n >= p.top_k) {
+        const uint32_t kth = key_ord(keyA[p.top_k - 1]);
+        int mine = 0;
+        for (int i = tid; i < n; i += kMergeThreads) mine += key_ord(keyA[i]) >= kth ? 1 : 0;
+        if (mine) atomicAdd(&s_ns, mine);
+    } else {
+        if (tid == 0) s_ns = n;
+        // Without a top-k the rest of the vocabulary is still in play.
+        rest_alive = !top_k_on && p.do_sample && (alive_tail + dropped) > 0.0;
+    }
+    __syncthreads();
+    const int ns = s_ns;
+    const float x_first = from_ordered_key(key_ord(keyA[0]));
+    const double rest_bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_first);
+    for (int i = tid; i < ns; i += kMergeThreads) {
+        const float x = from_ordered_key(key_ord(keyA[i]));
+        ex[i] = exp((double)x - (double)x_first);  // src/generation.cpp:46
+        alive[i] = 1;
+        keyB[i] = ((u64)key_col(keyA[i]) << 32) | (uint32_t)i;
+    }
+    int ns_pad = 2;
+    while (ns_pad < ns) ns_pad <<= 1;
+    for (int i = ns + tid; i < ns_pad; i += kMergeThreads) keyB[i] = ~0ull;
+    __syncthreads();
+    block_bitonic_sort(keyB, ns_pad, /*descending=*/false);
+
+    // ---- 4. the reference's walk, by one thread ------------------------------------------------------
+    if (tid == 0) {
+        const double u = p.do_sample ? p.uniforms[row] : 0.0;
+        decide(p, keyA, keyB, ex, alive, ns, rest_alive, z_rest, rest_bound, u, s_dec);
+        s_chosen_raw = 0;
+    }
+    __syncthreads();
+    const Decision dec = s_dec;
+    if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
+        for (int s = warp; s < nseg; s += kMergeThreads / 32) {
+            const int cnt = seg_count(s);
+            const uint2* seg = seg_cands(s);
+            for (int i = lane; i < cnt; i += 32) {
+                const uint2 c = seg[i];
+                if ((long long)(c.y & kColumnMask) == dec.token) s_chosen_raw = c.x;
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        p.row_status[row] = dec.status;
+        p.tokens[row] = dec.status == PSX_ROW_OK ? dec.token : -1;
+        float lp = 0.0f;
+        if (dec.status == PSX_ROW_OK) {
+            const double l = (double)__uint_as_float(s_chosen_raw);
+            lp = (float)log(exp(l - (double)raw_max) / z_raw);  // src/generation.cpp:156
+        }
+        p.log_probs[row] = lp;
+        if (p.diag) p.diag[row] = psx_row_diag{n, dec.survivors, dec.draw_margin, dec.top_p_margin};
+    }
+}
+
+}  // namespace
+
+size_t merge_rows_shared_bytes(int sort_capacity) { return (size_t)sort_capacity * (8 + 8 + 8 + 1); }
+
+cudaError_t configure_merge_rows(int sort_capacity) {
+    return cudaFuncSetAttribute(merge_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)merge_rows_shared_bytes(sort_capacity));
+}
+
+cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
+    if (p.rows <= 0) return cudaSuccess;
+    merge_rows_kernel<<<(unsigned)p.rows, kMergeThreads, merge_rows_shared_bytes(p.sort_capacity), stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace psx

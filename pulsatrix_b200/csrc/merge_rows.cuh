@@ -1,0 +1,46 @@
+// Launch interface of the survivor stage (merge_rows.cu).
+#pragma once
+
+#include "psx_device.cuh"
+
+struct psx_row_diag;  // include/psx_b200.h
+
+namespace psx {
+
+struct MergeParams {
+    // what the row pass (or an all-gather of several GPUs' row passes) left behind
+    // Addressed with byte strides, so that the same kernel reads the row pass's own arrays
+    // (part-major within a row) and records gathered from several GPUs (GPU-major).
+    const void* stats;           // PartStats of (row, part) at stats + row*stats_row_stride + part*stats_part_stride
+    const void* seg_counts;      // uint32 of (row, segment) likewise; segment = part*segs_per_part + s
+    const void* candidates;      // uint2[seg_cap] of (row, segment) likewise
+    int64_t stats_row_stride, stats_part_stride;
+    int64_t count_row_stride, count_seg_stride;
+    int64_t cand_row_stride, cand_seg_stride;
+    int32_t parts;
+    int32_t segs_per_part;
+    int32_t seg_cap;
+    int64_t rows;
+    int64_t vocab;               // global vocabulary size
+    // settings (GenerationConfig, already validated)
+    int32_t do_sample;
+    int32_t apply_temperature;
+    float temperature;
+    float penalty;
+    int64_t top_k;               // 0 < top_k < vocab: the top-k filter is on
+    float top_p;
+    float min_p;
+    const double* uniforms;      // device, rows (unused when greedy)
+    // output
+    int64_t* tokens;
+    float* log_probs;
+    int32_t* row_status;
+    psx_row_diag* diag;          // may be null
+    int32_t sort_capacity;       // survivors + near-survivors the shared-memory sorter holds (power of two)
+};
+
+size_t merge_rows_shared_bytes(int sort_capacity);
+cudaError_t configure_merge_rows(int sort_capacity);
+cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream);
+
+}  // namespace psx

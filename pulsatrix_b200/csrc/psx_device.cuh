@@ -1,0 +1,147 @@
+// Shared device-side definitions of the sm_100a sampling kernels: layouts of the scratch records
+// that the row pass hands to the survivor stage, the few float operations whose rounding must
+// match the host reference, and small warp/block helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <float.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace psx {
+
+// ---- geometry of the row pass ----------------------------------------------------------------
+constexpr int kScanThreads = 256;
+constexpr int kScanWarps = kScanThreads / 32;
+constexpr int kVecPerThread = 16;                            // float4 held in registers per thread
+constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits per CTA
+constexpr int kSegCap = 128;                                 // candidate slots per warp segment
+constexpr int kMergeThreads = 256;
+
+// A candidate is (raw logit bits, column | flags).  The flags say how the survivor stage must
+// turn the raw logit into the processed one, with the same float operations as the row pass.
+constexpr uint32_t kFlagPenalized = 0x80000000u;
+constexpr uint32_t kFlagBanned = 0x40000000u;
+constexpr uint32_t kColumnMask = 0x3FFFFFFFu;
+
+// What one part (a contiguous run of columns of one row, scanned by one CTA or, after an
+// all-gather, by one GPU) reports besides its candidates.
+struct PartStats {
+    double raw_tail;      // sum of exp(l - raw_max) over the part's logits that are NOT candidates
+    double proc_tail;     // sum of exp(x' - x'_max) over non-candidates that are still alive
+    float raw_max;        // max raw logit of the part
+    float y_max;          // max processed logit before temperature (-inf when nothing is alive)
+    float thr;            // every alive logit >= relax(thr) of this part is a candidate
+    uint32_t nonfinite;   // 1 when the part holds a NaN or an infinity
+    uint32_t alive_tail;  // non-candidates that are still alive (not banned, not padding)
+    uint32_t overflow;    // 1 when a candidate segment ran out of slots
+};
+
+// ---- float operations that must round like the reference's host code ---------------------------
+
+// src/generation.cpp:66 -- negative logits are multiplied, the others divided (-0.0 is divided).
+__device__ __forceinline__ float penalize(float l, float penalty) {
+    return l < 0.0f ? __fmul_rn(l, penalty) : __fdiv_rn(l, penalty);
+}
+
+// Processed logit before temperature from the raw one and the candidate flags.
+__device__ __forceinline__ float processed_before_temperature(float l, uint32_t flags, float penalty) {
+    if (flags & kFlagBanned) return -INFINITY;
+    return (flags & kFlagPenalized) ? penalize(l, penalty) : l;
+}
+
+// src/generation.cpp:78 -- one IEEE float divide.
+__device__ __forceinline__ float temper(float y, bool apply, float temperature) {
+    return apply ? __fdiv_rn(y, temperature) : y;
+}
+
+// A value t' <= t such that y < t' implies y / T < t / T after rounding: dividing by the
+// temperature can map neighbouring floats to the same quotient, and every logit whose quotient
+// ties with the threshold's must be kept as a candidate.  Never below -FLT_MAX, so that -inf
+// (banned) entries never pass `y >= t'`.
+__device__ __forceinline__ float relax_threshold(float t, bool apply_temp, float temperature) {
+    float r = t;
+    if (apply_temp && t > -INFINITY) {
+        const float q = __fdiv_rn(t, temperature);
+        const float below = nextafterf(q, -INFINITY);
+        r = __fmul_rd(temperature, below);
+        if (!(r <= t)) r = (r != r) ? -INFINITY : t;
+    }
+    return fmaxf(r, -FLT_MAX);
+}
+
+// Order-preserving map of finite/infinite floats to uint32; -0.0 and +0.0 share a key because
+// the reference's comparisons treat them as equal.
+__device__ __forceinline__ uint32_t ordered_key(float x) {
+    const uint32_t u = __float_as_uint(x + 0.0f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered_key(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- warp / block helpers ------------------------------------------------------------------------
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ uint32_t warp_sum_u32(uint32_t v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+// The kp-th largest (1-based) of the 32 lane values: a bitonic sort across the lanes, largest
+// in lane 0, then a broadcast.
+__device__ __forceinline__ float warp_kth_largest(float v, int kp, int lane) {
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const float o = __shfl_xor_sync(0xFFFFFFFFu, v, j);
+            const bool descending_block = (lane & k) == 0;
+            const bool lower_lane = (lane & j) == 0;
+            v = (lower_lane == descending_block) ? fmaxf(v, o) : fminf(v, o);
+        }
+    }
+    return __shfl_sync(0xFFFFFFFFu, v, kp - 1);
+}
+
+// In-place bitonic sort of n_pad (a power of two) 64-bit keys in shared memory by the whole
+// block; descending when `descending`.  Ends with a barrier.
+__device__ __forceinline__ void block_bitonic_sort(unsigned long long* keys, int n_pad, bool descending) {
+    for (int k = 2; k <= n_pad; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < n_pad; i += blockDim.x) {
+                const int partner = i ^ j;
+                if (partner > i) {
+                    const unsigned long long a = keys[i], b = keys[partner];
+                    const bool first_block = (i & k) == 0;
+                    const bool want_a_larger = (first_block == descending);
+                    if (want_a_larger ? (a < b) : (a > b)) {
+                        keys[i] = b;
+                        keys[partner] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+}  // namespace psx

@@ -1,0 +1,37 @@
+// Launch interface of the row pass (scan_rows.cu).
+#pragma once
+
+#include "psx_device.cuh"
+
+namespace psx {
+
+struct ScanParams {
+    // input
+    const float* logits;             // row r, column c of this GPU's slice at logits[r*row_stride + c]
+    int64_t row_stride;
+    int64_t rows;
+    int64_t cols;                    // columns held by this GPU
+    int64_t col_begin;               // global id of local column 0 (0 unless the vocabulary is sharded)
+    int64_t vocab;                   // global vocabulary size (range check of history ids)
+    const int64_t* history_ids;      // device
+    const int64_t* history_offsets;  // device, rows + 1
+    const int64_t* banned_ids;       // device: EOS ids while min_new_tokens holds them off
+    int32_t num_banned;
+    int32_t apply_penalty;
+    float penalty;
+    int32_t apply_temperature;
+    float temperature;
+    float log2e_over_t;              // log2(e) / temperature (log2(e) when the temperature is off)
+    int32_t k_need;                  // every part hands on at least this many logits (or all it has)
+    int32_t parts;                   // CTAs per row
+    int32_t vecs_per_part;           // float4 vectors per part, <= kPartVecs
+    // output
+    PartStats* stats;                // rows * parts
+    uint32_t* seg_counts;            // rows * parts * kScanWarps
+    uint2* candidates;               // rows * parts * kScanWarps * kSegCap
+};
+
+// nucleus: also accumulate the processed-domain tail that a full-vocabulary top-p / min-p needs.
+cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t stream);
+
+}  // namespace psx

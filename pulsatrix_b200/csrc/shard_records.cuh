@@ -1,0 +1,42 @@
+// Vocabulary-sharded sampling: the fixed-size per-row record one GPU contributes to the all-gather
+// (shard_records.cu packs it from the row pass's output).
+//
+// Record layout, `capacity` candidates: PartStats at byte 0, the candidate count (uint32) at
+// byte 40, the candidates (uint2 each: raw logit bits, global column | flags) from byte 48.
+// The survivor stage reads gathered records directly through byte strides.
+#pragma once
+
+#include "psx_device.cuh"
+
+namespace psx {
+
+constexpr int kRecordStatsOffset = 0;
+constexpr int kRecordCountOffset = 40;
+constexpr int kRecordCandidatesOffset = 48;
+static_assert(sizeof(PartStats) == 40, "record layout assumes a 40-byte PartStats");
+
+// Candidates a record holds: the k the merged top-k needs from any one shard, plus room for
+// ties at the shard's threshold.
+inline int shard_record_capacity(bool sample, int64_t top_k) {
+    if (!sample) return 64;
+    const int64_t k = top_k < 1 ? 1 : (top_k > 960 ? 960 : top_k);
+    return (int)((k + 64 + 63) / 64 * 64);
+}
+__host__ __device__ inline size_t shard_record_bytes(int capacity) { return (size_t)kRecordCandidatesOffset + 8u * (size_t)capacity; }
+
+struct PackParams {
+    const PartStats* stats;      // rows * parts, from the row pass
+    const uint32_t* seg_counts;  // rows * parts * kScanWarps
+    const uint2* candidates;     // rows * parts * kScanWarps * kSegCap
+    int32_t parts;
+    int64_t rows;
+    int32_t apply_temperature;
+    float temperature;
+    float penalty;
+    int32_t capacity;
+    void* records;               // rows * shard_record_bytes(capacity)
+};
+
+cudaError_t launch_pack_records(const PackParams& p, cudaStream_t stream);
+
+}  // namespace psx
