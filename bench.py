@@ -1,0 +1,333 @@
+"""Benchmark of the token-sampling hot path: sampled rows/s and logits-read HBM GB/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+
+A step is one pass of the sampling path (row pass + survivor stage) over one batch of the
+workload on every GPU: each rank owns its own batch (rows split across GPUs, no collective on
+the data path), so per-GPU work is fixed and scaling is weak.  Inputs are synthetic, built on
+the device with the workload's shapes and value distribution, and rotate through more batches
+than fit in L2.  `value` is timed with CUDA events around exactly K steps with device-resident
+inputs; `e2e` is the same metric through the host-buffer entry point, copies included;
+`roofline` is the row pass alone (algorithmic bytes = 4 * rows * vocab per launch) against the
+measured HBM peak; `cpu_baseline` is the reference's CPU sampler on this box's host cores.
+
+`--impl reference` times the reference's own CPU sampler (compiled from its sources into
+oracle/_ref, or the plain-C restatement when that is absent) on a bounded sample of the same
+workload, rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path[:0] = [str(ROOT), str(ROOT / "tests")]
+
+from pulsatrix_b200.workloads import WORKLOADS  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
+    return ap.parse_args()
+
+
+def measured_hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_batches(w, device, count, seed):
+    """`count` synthetic batches on the device: logits N(0,1)*sigma - zeta*log(rank+1) with a random
+    rank per column and row, history ids uniform in [0, vocab)."""
+    import torch
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    batches = []
+    for _ in range(count):
+        logits = torch.randn((w.rows, w.vocab), generator=gen, device=device, dtype=torch.float32) * w.sigma
+        if w.zeta != 0.0:
+            ranks = torch.rand((w.rows, w.vocab), generator=gen, device=device).argsort(dim=1)
+            logits -= w.zeta * torch.log(ranks.to(torch.float32) + 1.0)
+            del ranks
+        if w.tie_row_fraction > 0:
+            n = max(1, int(round(w.rows * w.tie_row_fraction)))
+            rows = torch.randperm(w.rows, generator=gen, device=device)[:n]
+            cols = torch.randint(0, w.vocab, (n, 2), generator=gen, device=device)
+            logits[rows[:, None], cols] = logits[rows].max(dim=1, keepdim=True).values
+        hist = torch.randint(0, w.vocab, (w.rows, w.history), generator=gen, device=device, dtype=torch.int64)
+        batches.append((logits, hist.reshape(-1).contiguous()))
+    offsets = torch.arange(w.rows + 1, device=device, dtype=torch.int64) * w.history
+    return batches, offsets
+
+
+def workload_config(w):
+    import pulsatrix_b200 as psx
+    return psx.SamplingConfig.make(do_sample=w.do_sample, temperature=w.temperature, top_k=w.top_k, top_p=w.top_p,
+                                   min_p=w.min_p, repetition_penalty=w.repetition_penalty)
+
+
+def cpu_rows_per_second(w, logits, hist, offsets, seeds, cpu_seconds):
+    """Times the reference's CPU sampler (oracle/_ref; the plain-C restatement when absent) on
+    host rows with every host core.  Returns (rows/s, kind, cores, description of the sample)."""
+    import oracle_lib as ol
+    kind = "reference" if (ROOT / "oracle" / "_ref" / "libpsx_ref.so").exists() or ol.reference_available() else "port"
+    which = "reference" if kind == "reference" else "oracle"
+    cores = os.cpu_count() or 1
+    cfg = ol.make_config(max_new_tokens=1, do_sample=w.do_sample, temperature=w.temperature, top_k=w.top_k,
+                         top_p=w.top_p, min_p=w.min_p, repetition_penalty=w.repetition_penalty)
+    t0 = time.perf_counter()
+    ol.rows(which, logits, hist, offsets, cfg, seeds, threads=cores)  # also sizes the sample
+    once = time.perf_counter() - t0
+    repeats = max(1, min(50, int(cpu_seconds / max(once * cores, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        ol.rows(which, logits, hist, offsets, cfg, seeds, threads=cores)
+    elapsed = time.perf_counter() - t0
+    n = logits.shape[0] * repeats
+    return n / elapsed, kind, cores, f"{logits.shape[0]} rows of {w.name} x {repeats} repeats, {cores} threads"
+
+
+def host_sample(w, batch, offsets, rows):
+    logits, hist = batch
+    rows = min(rows, w.rows)
+    return (logits[:rows].cpu().numpy(), hist.view(w.rows, w.history)[:rows].cpu().numpy().reshape(-1),
+            offsets[: rows + 1].cpu().numpy(), np.arange(rows, dtype=np.uint64))
+
+
+def run_ours(args, rank, world):
+    import torch
+    import torch.distributed as dist
+    import pulsatrix_b200 as psx
+
+    w = WORKLOADS[args.workload]
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    ctx = psx.Context(local)
+    cfg = workload_config(w)
+    n_batches = max(2, (2 * L2_BYTES) // w.logits_bytes + 2)
+    batches, offsets = build_batches(w, device, n_batches, seed=1234 + rank)
+    seeds = np.arange(w.rows, dtype=np.uint64)
+    uniforms = torch.from_numpy(psx.uniforms_mt19937_64(seeds)).to(device)
+    out = ctx.alloc_outputs(w.rows)
+    stream = torch.cuda.current_stream(device)
+
+    def step(i):
+        logits, hist = batches[i % n_batches]
+        ctx.sample_rows(logits, hist, offsets, cfg, uniforms, out=out, stream=stream.cuda_stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    status = out["status"].cpu().numpy()
+    failed = int((status != 0).sum())
+
+    # ---- value: K steps, device-resident inputs, CUDA events on the launching stream ----
+    sampler = ClockSampler(local)
+    sampler.start()
+    ctx.enable_timing(True)
+    ctx.read_timing()
+    launches0 = ctx.launches
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    begin.record(stream)
+    for i in range(args.steps):
+        step(i)
+    end.record(stream)
+    barrier()
+    elapsed_ms = begin.elapsed_time(end)
+    launches = ctx.launches - launches0
+    scan_ms, merge_ms, calls = ctx.read_timing()
+    ctx.enable_timing(False)
+    clocks = sampler.stop()
+
+    # ---- e2e: the host-buffer entry point, pinned inputs, copies inside the timed region ----
+    h_logits = batches[0][0].cpu().pin_memory()
+    h_hist = batches[0][1].cpu().pin_memory()
+    h_off = offsets.cpu().pin_memory()
+    h_u = uniforms.cpu().pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        ctx.sample_rows_host(h_logits, h_hist, h_off, cfg, h_u, raise_on_row_failure=False)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        ctx.sample_rows_host(h_logits, h_hist, h_off, cfg, h_u, raise_on_row_failure=False)
+    e2e_s = time.perf_counter() - t0
+    h2d = h_logits.numel() * 4 + h_hist.numel() * 8 + h_off.numel() * 8 + (h_u.numel() * 8 if w.do_sample else 0)
+    d2h = w.rows * (8 + 4 + 4 + 24)
+
+    times = torch.tensor([elapsed_ms, e2e_s * 1e3, scan_ms / max(calls, 1), merge_ms / max(calls, 1)],
+                         dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, scan_avg_ms, merge_avg_ms = times.tolist()
+    if rank != 0:
+        return
+
+    peak, peak_kind = measured_hbm_peak()
+    achieved = w.logits_bytes / (scan_avg_ms * 1e-3) / 1e9
+    result = {
+        "metric": "sampled rows/sec and logits-read HBM GB/s vs B200 peak",
+        "value": w.rows * world * args.steps / (elapsed_ms * 1e-3),
+        "unit": "rows/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": elapsed_ms / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32 logits; f64 survivor stage",
+        "data": "synthetic",
+        "config": {"workload": f"{w.name}: batch={w.rows} rows per GPU, vocab={w.vocab}, history={w.history}, "
+                               f"penalty={w.repetition_penalty}, T={w.temperature}, top_k={w.top_k}, top_p={w.top_p}, "
+                               f"do_sample={w.do_sample}",
+                   "parallelism": f"rows split over {world} GPU(s), no data-path collective",
+                   "l2": f"inputs rotate over {n_batches} batches = {n_batches * w.logits_bytes / 2**20:.0f} MiB > L2"},
+        "e2e": {"value": w.rows * world * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": int(launches) * world,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "scan_rows_kernel", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "launch_ms": scan_avg_ms, "survivor_stage_ms": merge_avg_ms,
+                     "frac_of_nominal_8TBs": achieved / 8000.0},
+        "failed_rows": failed,
+    }
+    if world == 1:
+        sample = host_sample(w, batches[0], offsets, 64)
+        value, kind, cores, text = cpu_rows_per_second(w, *sample, args.cpu_seconds)
+        result["cpu_baseline"] = {"value": value, "unit": "rows/s", "cores": cores, "kind": kind, "sample": text}
+    print(json.dumps(result), flush=True)
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    import oracle_lib as ol
+    w = WORKLOADS[args.workload]
+    import workload_rows
+    rows = min(w.rows, 64)
+    logits, hist, offsets, seeds = workload_rows.build(w.name, np.arange(rows))
+    kind = "reference" if ol.reference_available() else "port"
+    which = "reference" if kind == "reference" else "oracle"
+    cores = os.cpu_count() or 1
+    cfg = workload_rows.config_of(w)
+    hist = hist.reshape(-1)
+    for _ in range(max(args.warmup, 1)):
+        ol.rows(which, logits, hist, offsets, cfg, seeds, threads=cores)
+    steps = max(1, min(args.steps, 40))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ol.rows(which, logits, hist, offsets, cfg, seeds, threads=cores)
+    elapsed = time.perf_counter() - t0
+    value = rows * steps / elapsed
+    text = f"{rows} rows of {w.name} per step, {cores} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "sampled rows/sec and logits-read HBM GB/s vs B200 peak", "value": value,
+        "unit": "rows/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 1),
+        "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 logits; f64 softmax", "data": "synthetic",
+        "config": {"workload": f"{w.name}: vocab={w.vocab}, history={w.history}, top_k={w.top_k}, top_p={w.top_p}",
+                   "parallelism": "host threads, one row each"},
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": kind, "sample": text},
+        "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        dist.init_process_group("nccl")
+    try:
+        run_ours(args, rank, world)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

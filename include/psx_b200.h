@@ -90,6 +90,15 @@ PSX_API psx_status psx_b200_sync(psx_ctx* ctx, void* stream);
 /* Number of kernels this context has launched since it was created. */
 PSX_API uint64_t psx_b200_launch_count(const psx_ctx* ctx);
 
+/* Per-kernel device timing for benchmarks.  While enabled, every psx_b200_sample_rows call
+ * brackets its row pass and its survivor stage with CUDA events on the launching stream.
+ * psx_b200_ctx_read_timing synchronises those events, adds the elapsed milliseconds of all calls
+ * since the last read into the two totals, reports the number of calls, and clears the record.
+ * No counterpart in the reference. */
+PSX_API psx_status psx_b200_ctx_enable_timing(psx_ctx* ctx, int enable);
+PSX_API psx_status psx_b200_ctx_read_timing(psx_ctx* ctx, double* row_pass_ms, double* survivor_stage_ms,
+                                            uint64_t* calls);
+
 /* Batched sampling step on device-resident logits: for every row, what one iteration of
  * Generate()'s loop computes (src/generation.cpp:124-156) -- finite check, raw log-softmax,
  * ProcessLogits (src/generation.cpp:55-112: repetition penalty, EOS ban, temperature, top-k,

@@ -13,7 +13,7 @@ OK, ERR_BAD_ARGUMENT, ERR_CUDA, ERR_ROW_FAILED, ERR_UNSUPPORTED = range(5)
 
 EXPORTS = [
     "psx_b200_version", "psx_b200_last_error", "psx_b200_ctx_create", "psx_b200_ctx_destroy", "psx_b200_ctx_stream",
-    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_sample_rows", "psx_b200_sample_rows_host",
+    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_sample_rows", "psx_b200_sample_rows_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_top_k_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
@@ -90,6 +90,8 @@ def library():
         lib.psx_b200_shard_record_bytes.argtypes = [C.c_void_p]
         lib.psx_b200_ctx_create.argtypes = [C.c_int, C.c_void_p]
         lib.psx_b200_sync.argtypes = [C.c_void_p, C.c_void_p]
+        lib.psx_b200_ctx_enable_timing.argtypes = [C.c_void_p, C.c_int]
+        lib.psx_b200_ctx_read_timing.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         ptr, i64 = C.c_void_p, C.c_int64
         lib.psx_b200_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_sample_rows_host.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
@@ -153,6 +155,16 @@ class Context:
     @property
     def stream(self) -> int:
         return int(self._lib.psx_b200_ctx_stream(self._ctx) or 0)
+
+    def enable_timing(self, on=True):
+        _check(self._lib.psx_b200_ctx_enable_timing(self._ctx, int(on)))
+
+    def read_timing(self):
+        """(row-pass ms, survivor-stage ms, calls) summed over the calls since the last read."""
+        scan, merge, calls = C.c_double(0), C.c_double(0), C.c_uint64(0)
+        _check(self._lib.psx_b200_ctx_read_timing(self._ctx, C.addressof(scan), C.addressof(merge),
+                                                  C.addressof(calls)))
+        return scan.value, merge.value, calls.value
 
     def sync(self, stream=None):
         _check(self._lib.psx_b200_sync(self._ctx, C.c_void_p(stream) if stream else None))

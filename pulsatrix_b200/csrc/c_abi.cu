@@ -54,6 +54,9 @@ struct psx_ctx {
     Buffer h_logits, h_history, h_offsets, h_uniforms, h_tokens, h_log_probs, h_status, h_diag;
     // staging of the sharded path
     Buffer shard_uniform_scratch;
+    // optional per-kernel timing: (before row pass, between, after survivor stage) per call
+    bool timing = false;
+    std::vector<cudaEvent_t> timing_events;
 };
 
 namespace {
@@ -117,6 +120,9 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     if (!sample) plan.k_need = 1;
     else if (top_k_on) plan.k_need = (int)std::min<int64_t>(c->top_k, 1 << 20);
     else plan.k_need = ctx->nucleus_k;
+    // A row of at most 256 vectors fits the candidate segments whole (one vector per thread, 128
+    // logits per warp): hand everything on, and every filter is exact whatever the settings.
+    if (vectors <= psx::kScanThreads) plan.k_need = 1 << 30;
     plan.sort_capacity = plan.nucleus ? 4096 : 1024;
     return plan;
 }
@@ -242,6 +248,7 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
         if (b->ptr) cudaFree(b->ptr);
     }
+    for (cudaEvent_t e : ctx->timing_events) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -283,8 +290,14 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp)) return s;
     if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
 
+    cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
+    if (ctx->timing) {
+        for (cudaEvent_t& e : marks) PSX_CUDA(cudaEventCreate(&e));
+        PSX_CUDA(cudaEventRecord(marks[0], stream));
+    }
     PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
     ++ctx->launches;
+    if (ctx->timing) PSX_CUDA(cudaEventRecord(marks[1], stream));
 
     psx::MergeParams mp{};
     mp.stats = sp.stats;
@@ -302,6 +315,37 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
     PSX_CUDA(psx::launch_merge_rows(mp, stream));
     ++ctx->launches;
+    if (ctx->timing) {
+        PSX_CUDA(cudaEventRecord(marks[2], stream));
+        ctx->timing_events.insert(ctx->timing_events.end(), marks, marks + 3);
+    }
+    return PSX_OK;
+}
+
+psx_status psx_b200_ctx_enable_timing(psx_ctx* ctx, int enable) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    ctx->timing = enable != 0;
+    return PSX_OK;
+}
+
+psx_status psx_b200_ctx_read_timing(psx_ctx* ctx, double* row_pass_ms, double* survivor_stage_ms, uint64_t* calls) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    double scan = 0.0, merge = 0.0;
+    const size_t n = ctx->timing_events.size() / 3;
+    for (size_t i = 0; i < n; ++i) {
+        cudaEvent_t* e = &ctx->timing_events[3 * i];
+        float a = 0.0f, b = 0.0f;
+        PSX_CUDA(cudaEventSynchronize(e[2]));
+        PSX_CUDA(cudaEventElapsedTime(&a, e[0], e[1]));
+        PSX_CUDA(cudaEventElapsedTime(&b, e[1], e[2]));
+        scan += a;
+        merge += b;
+    }
+    for (cudaEvent_t e : ctx->timing_events) cudaEventDestroy(e);
+    ctx->timing_events.clear();
+    if (row_pass_ms) *row_pass_ms = scan;
+    if (survivor_stage_ms) *survivor_stage_ms = merge;
+    if (calls) *calls = n;
     return PSX_OK;
 }
 
