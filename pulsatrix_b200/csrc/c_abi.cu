@@ -123,7 +123,7 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     // A row of at most 256 vectors fits the candidate segments whole (one vector per thread, 128
     // logits per warp): hand everything on, and every filter is exact whatever the settings.
     if (vectors <= psx::kScanThreads) plan.k_need = 1 << 30;
-    plan.sort_capacity = plan.nucleus ? 4096 : 1024;
+    plan.sort_capacity = plan.nucleus ? 4096 : 2048;
     return plan;
 }
 
@@ -497,7 +497,7 @@ psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gath
 
     Plan plan;
     plan.apply_temperature = sample && config->temperature != 1.0f;
-    plan.sort_capacity = 1024;
+    plan.sort_capacity = 2048;
     if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
     const int capacity = psx::shard_record_capacity(sample, config->top_k);
     const int64_t record = (int64_t)psx::shard_record_bytes(capacity);

@@ -149,6 +149,50 @@ __device__ __forceinline__ double block_sum(double v, double* scratch) {
     return r;
 }
 
+// The k-th largest (1-based, k <= m) of m uint32 keys in shared memory: four 8-bit radix passes,
+// most significant digit first.  hist has 256 entries, state two.  Called by the whole block.
+__device__ uint32_t block_select_kth(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, uint32_t* state) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    uint32_t prefix = 0, mask = 0, remaining = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        hist[tid] = 0;  // kMergeThreads == 256 bins
+        __syncthreads();
+        for (int i = tid; i < m; i += kMergeThreads) {
+            const uint32_t key = keys[i];
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) {
+            // lane L owns digits 255-8L down to 248-8L; find where the count from the top reaches `remaining`
+            uint32_t local = 0;
+            for (int b = 0; b < 8; ++b) local += hist[255 - 8 * lane - b];
+            uint32_t incl = local;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const uint32_t excl = incl - local;
+            if (excl < remaining && remaining <= incl) {
+                uint32_t above = excl;
+                int digit = 255 - 8 * lane;
+                for (int b = 0; b < 8; ++b, --digit) {
+                    if (above + hist[digit] >= remaining) break;
+                    above += hist[digit];
+                }
+                state[0] = prefix | ((uint32_t)digit << shift);
+                state[1] = remaining - above;
+            }
+        }
+        __syncthreads();
+        prefix = state[0];
+        remaining = state[1];
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    return prefix;
+}
+
 __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergeParams p) {
     extern __shared__ u64 dyn[];
     const int cap = p.sort_capacity;
@@ -163,6 +207,8 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     __shared__ int s_ns;
     __shared__ uint32_t s_chosen_raw;
     __shared__ Decision s_dec;
+    __shared__ uint32_t s_hist[256];
+    __shared__ uint32_t s_state[2];
 
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -203,8 +249,42 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         }
         return;
     }
-    const float keep_from = relax_threshold(thr, apply_t, p.temperature);
+    float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
+    const int nseg = p.parts * p.segs_per_part;
+    const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
+
+    // Every part handed on at least k logits, so together they hold far more than the k that a
+    // top-k keeps.  The k-th largest of everything collected IS the row's k-th largest (the union
+    // contains the true top k): select it, and only it and what ties with it after the
+    // temperature divide go on to the sort.  Greedy keeps the maximum and its ties.
+    if (!p.do_sample) {
+        keep_from = fmaxf(y_max, -FLT_MAX);
+    } else if (top_k_on) {
+        uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);
+        const int ycap = cap * 6;  // the three sort arrays are still unused
+        for (int s = warp; s < nseg; s += kMergeThreads / 32) {
+            const int cnt = seg_count(s);
+            const uint2* seg = seg_cands(s);
+            for (int i = lane; i < cnt; i += 32) {
+                const uint2 c = seg[i];
+                const float y = processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty);
+                if (y >= keep_from) {
+                    const int slot = atomicAdd(&s_count, 1);
+                    if (slot < ycap) ykeys[slot] = ordered_key(y);
+                }
+            }
+        }
+        __syncthreads();
+        const int m = s_count;
+        __syncthreads();
+        if (tid == 0) s_count = 0;
+        if (m <= ycap && m > p.top_k) {
+            const uint32_t kth = block_select_kth(ykeys, m, (uint32_t)p.top_k, s_hist, s_state);
+            keep_from = relax_threshold(from_ordered_key(kth), apply_t, p.temperature);
+        }
+        __syncthreads();
+    }
 
     // ---- 2. candidates: raw sum-exp for all, the list for those that can survive ----------------
     double z_raw = 0.0, z_rest = 0.0, dropped = 0.0;
@@ -215,7 +295,6 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
             z_rest += s.proc_tail * exp((double)temper(s.y_max, apply_t, p.temperature) - (double)x_max);
         }
     }
-    const int nseg = p.parts * p.segs_per_part;
     for (int s = warp; s < nseg; s += kMergeThreads / 32) {
         const int cnt = seg_count(s);
         const uint2* seg = seg_cands(s);
@@ -255,7 +334,6 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     __syncthreads();
     block_bitonic_sort(keyA, n_pad, /*descending=*/true);
 
-    const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
     if (tid == 0) s_ns = 0;
     __syncthreads();
     bool rest_alive = false;
