@@ -124,6 +124,13 @@ PSX_API psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream, const float*
                                 const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
                                 float* log_probs, int32_t* row_status, psx_row_diag* diag);
 
+/* Only the first kernel of psx_b200_sample_rows (the pass that reads the logits), leaving its
+ * output in the context's scratch: for benchmarks and profilers that time that kernel alone.
+ * No counterpart in the reference. */
+PSX_API psx_status psx_b200_row_pass_only(psx_ctx* ctx, void* stream, const float* logits, int64_t rows,
+                                          int64_t vocab, int64_t row_stride, const int64_t* history_ids,
+                                          const int64_t* history_offsets, const psx_sampling_config* config);
+
 /* The same step for callers that hold everything on the host, as the reference's
  * NextTokenLogitsFn does (include/pulsatrix/generation.hpp:25): copies inputs to the device,
  * runs psx_b200_sample_rows, copies results back and synchronises.  Returns

@@ -263,6 +263,52 @@ psx_status psx_b200_sync(psx_ctx* ctx, void* stream) {
 
 uint64_t psx_b200_launch_count(const psx_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+}  // extern "C"
+
+namespace {
+
+// Argument checks, plan, scratch and parameters shared by the sampling entry points.
+psx_status plan_row_pass(psx_ctx* ctx, cudaStream_t stream, const float* logits, int64_t rows, int64_t vocab,
+                         int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
+                         const psx_sampling_config* config, Plan& plan, psx::ScanParams& sp) {
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    plan = make_plan(ctx, logits, vocab, row_stride, vocab, config);
+    sp = psx::ScanParams{};
+    sp.logits = logits;
+    sp.row_stride = row_stride;
+    sp.rows = rows;
+    sp.cols = vocab;
+    sp.col_begin = 0;
+    sp.vocab = vocab;
+    sp.history_ids = history_ids;
+    sp.history_offsets = history_offsets;
+    if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
+    return reserve_scan_scratch(ctx, rows, plan, sp);
+}
+
+}  // namespace
+
+extern "C" {
+
+psx_status psx_b200_row_pass_only(psx_ctx* ctx, void* stream_ptr, const float* logits, int64_t rows, int64_t vocab,
+                                  int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
+                                  const psx_sampling_config* config) {
+    if (psx_status s = check_common(ctx, config, rows, vocab, row_stride, vocab, logits, history_ids, history_offsets)) {
+        return s;
+    }
+    if (rows == 0) return PSX_OK;
+    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    Plan plan;
+    psx::ScanParams sp;
+    if (psx_status s = plan_row_pass(ctx, stream, logits, rows, vocab, row_stride, history_ids, history_offsets, config,
+                                     plan, sp)) {
+        return s;
+    }
+    PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
 psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* logits, int64_t rows, int64_t vocab,
                                 int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
                                 const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
@@ -274,20 +320,12 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     if (!tokens || !log_probs || !row_status) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: an output pointer is null");
     if (config->do_sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
     cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
-    PSX_CUDA(cudaSetDevice(ctx->device));
-
-    const Plan plan = make_plan(ctx, logits, vocab, row_stride, vocab, config);
-    psx::ScanParams sp{};
-    sp.logits = logits;
-    sp.row_stride = row_stride;
-    sp.rows = rows;
-    sp.cols = vocab;
-    sp.col_begin = 0;
-    sp.vocab = vocab;
-    sp.history_ids = history_ids;
-    sp.history_offsets = history_offsets;
-    if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
-    if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp)) return s;
+    Plan plan;
+    psx::ScanParams sp;
+    if (psx_status s = plan_row_pass(ctx, stream, logits, rows, vocab, row_stride, history_ids, history_offsets, config,
+                                     plan, sp)) {
+        return s;
+    }
     if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
 
     cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};

@@ -50,7 +50,16 @@ def check_rows_against_oracle(logits, hist, offsets, cfg, seeds, *, expect_ok=Tr
     uniforms = psx.uniforms_mt19937_64(seeds)
     hist_flat = np.ascontiguousarray(hist, dtype=np.int64).ravel()
     tokens, logp, status, diag = sample_on_gpu(logits, hist_flat, offsets, cfg, uniforms, **gpu_kwargs)
-    want = ol.rows("oracle", logits, hist_flat, offsets, cfg, seeds, threads=8)
+    # The checker's rows are step 0 of Generate(); a later step only changes whether the EOS ban
+    # still holds (src/generation.cpp:69), which min_new_tokens - num_new_tokens expresses.
+    oracle_cfg = cfg
+    if gpu_kwargs.get("num_new_tokens", 0):
+        eos = [cfg.eos_token_ids[i] for i in range(cfg.num_eos_token_ids)]
+        oracle_cfg = ol.make_config(max_new_tokens=1, do_sample=bool(cfg.do_sample), temperature=cfg.temperature,
+                                    top_k=cfg.top_k, top_p=cfg.top_p, min_p=cfg.min_p,
+                                    repetition_penalty=cfg.repetition_penalty, eos_token_ids=eos,
+                                    min_new_tokens=max(0, cfg.min_new_tokens - gpu_kwargs["num_new_tokens"]))
+    want = ol.rows("oracle", logits, hist_flat, offsets, oracle_cfg, seeds, threads=8)
     if expect_ok:
         assert (status == 0).all(), f"row status {status[status != 0][:8]} at rows {np.nonzero(status)[0][:8]}"
     ok = status == 0
