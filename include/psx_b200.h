@@ -12,8 +12,9 @@
  *   - A psx_ctx belongs to one device and one host thread at a time (like the reference's
  *     DeviceBackend, include/pulsatrix/cuda_backend.hpp:159-166).  It owns scratch memory that
  *     grows on demand; growing synchronises the device, steady-state calls do not allocate.
- *   - Device entry points are asynchronous on `stream`; outputs are valid after the stream (or
- *     psx_b200_sync) has been synchronised.  Host entry points synchronise before returning.
+ *   - Device entry points are asynchronous on `stream` (a cudaStream_t; NULL is CUDA's default
+ *     stream, as everywhere in CUDA); outputs are valid once that stream has been synchronised.
+ *     Host entry points run on the context's own stream and synchronise before returning.
  */
 #ifndef PSX_B200_H
 #define PSX_B200_H
@@ -44,8 +45,10 @@ typedef enum psx_row_status {
     PSX_ROW_OK = 0,
     PSX_ROW_NON_FINITE = 4,  /* "Generate: the model returned a non-finite logit" (src/generation.cpp:128-132) */
     PSX_ROW_ALL_REMOVED = 5, /* "Generate: every token was removed" (src/generation.cpp:136-138) */
-    PSX_ROW_TOO_WIDE = 16    /* more tokens survive the filters (or tie at a cut) than the device
+    PSX_ROW_TOO_WIDE = 16,   /* more tokens survive the filters (or tie at a cut) than the device
                                 path holds; nothing was drawn for this row */
+    PSX_ROW_DEVICE_TIMEOUT = 32 /* a bounded device-side wait (the bulk copy of the row into shared
+                                memory) ran out; nothing was drawn for this row */
 } psx_row_status;
 
 /* GenerationConfig (include/pulsatrix/generation.hpp:29-52) without the loop fields, plus the
@@ -83,9 +86,9 @@ PSX_API const char* psx_b200_last_error(void);
  * CUDABackend constructor sets up (src/cuda_backend.cu:24-29). */
 PSX_API psx_status psx_b200_ctx_create(int device, psx_ctx** out);
 PSX_API void psx_b200_ctx_destroy(psx_ctx* ctx);
-/* The context's own stream (a cudaStream_t), used when `stream` is NULL. */
+/* The context's own non-blocking stream (a cudaStream_t), for callers that want one. */
 PSX_API void* psx_b200_ctx_stream(psx_ctx* ctx);
-/* cudaStreamSynchronize on `stream` (NULL: the context's stream). */
+/* cudaStreamSynchronize on `stream`. */
 PSX_API psx_status psx_b200_sync(psx_ctx* ctx, void* stream);
 /* Number of kernels this context has launched since it was created. */
 PSX_API uint64_t psx_b200_launch_count(const psx_ctx* ctx);

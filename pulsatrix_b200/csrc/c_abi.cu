@@ -47,6 +47,7 @@ struct psx_ctx {
     int sm_count = 0;
     uint64_t launches = 0;
     int merge_capacity_configured = 0;
+    bool scan_configured = false;
     int nucleus_k = 160;  // logits every part hands on when no top-k bounds the survivors
     // row-pass scratch
     Buffer stats, seg_counts, candidates, banned;
@@ -257,7 +258,7 @@ void* psx_b200_ctx_stream(psx_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
 
 psx_status psx_b200_sync(psx_ctx* ctx, void* stream) {
     if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
-    PSX_CUDA(cudaStreamSynchronize(stream ? static_cast<cudaStream_t>(stream) : ctx->stream));
+    PSX_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     return PSX_OK;
 }
 
@@ -282,6 +283,10 @@ psx_status plan_row_pass(psx_ctx* ctx, cudaStream_t stream, const float* logits,
     sp.vocab = vocab;
     sp.history_ids = history_ids;
     sp.history_offsets = history_offsets;
+    if (!ctx->scan_configured) {
+        PSX_CUDA(psx::configure_scan_rows());
+        ctx->scan_configured = true;
+    }
     if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
     return reserve_scan_scratch(ctx, rows, plan, sp);
 }
@@ -297,7 +302,7 @@ psx_status psx_b200_row_pass_only(psx_ctx* ctx, void* stream_ptr, const float* l
         return s;
     }
     if (rows == 0) return PSX_OK;
-    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     Plan plan;
     psx::ScanParams sp;
     if (psx_status s = plan_row_pass(ctx, stream, logits, rows, vocab, row_stride, history_ids, history_offsets, config,
@@ -319,7 +324,7 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     if (rows == 0) return PSX_OK;
     if (!tokens || !log_probs || !row_status) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: an output pointer is null");
     if (config->do_sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
-    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     Plan plan;
     psx::ScanParams sp;
     if (psx_status s = plan_row_pass(ctx, stream, logits, rows, vocab, row_stride, history_ids, history_offsets, config,
@@ -482,7 +487,7 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
     if (sample && !(config->top_k > 0 && config->top_k < vocab)) {
         return fail(PSX_ERR_UNSUPPORTED, "psx_b200: the vocabulary-sharded path samples with a top-k only");
     }
-    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
 
     const Plan plan = make_plan(ctx, shard_logits, shard_cols, row_stride, vocab, config);
@@ -530,7 +535,7 @@ psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gath
     if (sample && !(config->top_k > 0 && config->top_k < vocab)) {
         return fail(PSX_ERR_UNSUPPORTED, "psx_b200: the vocabulary-sharded path samples with a top-k only");
     }
-    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
 
     Plan plan;
@@ -573,7 +578,7 @@ psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream_ptr, const float* in, 
     }
     if (rows > 0x7FFFFFFFull) return fail(PSX_ERR_UNSUPPORTED, "psx_b200: too many rows for one launch");
     if (!in || !values || !indices) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
-    cudaStream_t stream = stream_ptr ? static_cast<cudaStream_t>(stream_ptr) : ctx->stream;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
     PSX_CUDA(psx::launch_topk_rows(in, values, indices, rows, cols, k, largest != 0, stream));
     ++ctx->launches;

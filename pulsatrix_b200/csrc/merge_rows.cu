@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         raw_max = fmaxf(raw_max, s.raw_max);
         y_max = fmaxf(y_max, s.y_max);
         thr = fmaxf(thr, s.thr);
-        bad += (double)(s.nonfinite * 1u + s.overflow * 65536u);
+        bad += (double)((s.nonfinite & 1u) + (s.nonfinite >> 1) * 256u + s.overflow * 65536u);
         alive_tail += (double)s.alive_tail;
     }
     if (tid == 0) s_count = 0;
@@ -244,7 +244,8 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         if (tid == 0) {
             p.tokens[row] = -1;
             p.log_probs[row] = 0.0f;
-            p.row_status[row] = (bad_bits & 0xFFFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
+            p.row_status[row] = (bad_bits & 0xFF00u) ? PSX_ROW_DEVICE_TIMEOUT
+                                : (bad_bits & 0xFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
             if (p.diag) p.diag[row] = psx_row_diag{0, 0, INFINITY, INFINITY};
         }
         return;

@@ -1,21 +1,25 @@
 // The row pass: the one kernel that reads the logits from HBM.
 //
-// Each CTA owns one "part" of one row: up to 4096 float4 vectors (16384 logits) that it loads
-// with 128-bit streaming loads, all issued up front, and then keeps in registers.  From the
-// registers it derives, without touching HBM again,
-//   * the part's raw maximum and, against it, the sum of exp over everything that is not handed
-//     on as a candidate (the unprocessed log-softmax of src/generation.cpp:133,156 needs both),
-//   * the repetition penalty and EOS ban for the few columns the row's history names
-//     (src/generation.cpp:59-73), found through a per-thread bit mask built in shared memory,
-//   * a threshold that at least `k_need` of the part's processed logits reach -- the smallest of
-//     the per-warp kp-th largest per-thread maxima, so no sort of the data is needed -- and
-//   * every logit at or above that threshold as a candidate (raw value, column, flags), written
-//     warp by warp in a fixed order so that the survivor stage is reproducible bit for bit.
+// Each CTA owns one "part" of one row: up to 4096 aligned float4 vectors (16384 logits, 64 KB).
+// One thread asks the TMA unit for the whole part with bulk asynchronous copies
+// (cp.async.bulk global -> shared, completion on an mbarrier; no multicast), so the bytes stream
+// from HBM into shared memory without passing through registers while the other threads turn
+// the row's token history into a bitmap.  Everything after that reads shared memory:
+//   1. the few logits the history (repetition penalty, src/generation.cpp:59-68) or the EOS ban
+//      (:69-73) names are handed on as candidates whatever their value, in a fixed order, and
+//      blanked in shared memory, so the dense passes below never look at a flag;
+//   2. pass one takes per-thread maxima; the smallest over the warps of the kp-th largest
+//      per-thread maximum is a threshold that at least k_need logits of the part reach, found
+//      without sorting the data;
+//   3. pass two sums exp(l - max) over everything below the threshold (the unprocessed
+//      log-softmax of src/generation.cpp:133,156 needs it) and hands on every logit at or above
+//      it (raw value, column, flags), warp by warp in a fixed order, so the survivor stage is
+//      reproducible bit for bit.
 // Selection works on the logits BEFORE the temperature divide: dividing by a positive number is
 // monotonic, so the k-th largest commutes with it, and the threshold is relaxed by the few ulps
-// that the divide can merge (relax_threshold).
+// the divide can merge (relax_threshold).
 //
-// HBM bound: 4 bytes per logit read once; everything written is a few hundred bytes per part.
+// HBM bound: 4 bytes per logit, read once; what is written is a few hundred bytes per part.
 #include "scan_rows.cuh"
 
 namespace psx {
@@ -25,47 +29,89 @@ namespace {
 constexpr float kLog2e = 1.4426950408889634f;
 // log2(e) = kLog2e * (1 + kLog2eRel): the part of log2(e) that the float constant drops.
 constexpr float kLog2eRel = (float)(1.4426950408889634073599246810019 / (double)1.4426950408889634f - 1.0);
-constexpr float kPad = -FLT_MAX;  // stands for "no logit here": finite, never the maximum
+constexpr float kPad = -FLT_MAX;  // stands for "no logit here": finite, never above a real logit
+constexpr int kBitmapWords = kPartVecs * 4 / 32;  // one bit per logit of a part
+constexpr uint32_t kCopyChunk = 16384;            // bytes per bulk copy
 
 __device__ __forceinline__ float max4(const float4& v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
 __device__ __forceinline__ float amax4(const float4& v) {
     return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 }
-__device__ __forceinline__ float comp(const float4& v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; }
-__device__ __forceinline__ void blank(float4& v, int c) {
-    if (c == 0) v.x = kPad; else if (c == 1) v.y = kPad; else if (c == 2) v.z = kPad; else v.w = kPad;
+
+// ---- mbarrier + bulk copy (PTX; the destination and the barrier are this CTA's shared memory) ----
+
+__device__ __forceinline__ uint32_t smem_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void barrier_init(uint64_t* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)), "r"(arrivals) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-// Marks, in the per-thread bit masks, the columns of this part that `ids` names.
+__device__ __forceinline__ void barrier_expect_bytes(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_copy_to_shared(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_address(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_address(bar))
+                 : "memory");
+}
+
+// Waits for phase `parity` of the barrier, but not for ever: gives up after about a second.
+__device__ __forceinline__ bool barrier_wait_bounded(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_address(bar);
+    for (uint32_t tries = 0; tries < (1u << 22); ++tries) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (tries > 64) __nanosleep(200);
+    }
+    return false;
+}
+
+// Sets, in a bitmap with one bit per logit of this part, the columns that `ids` names.
 __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int64_t end, const ScanParams& p,
-                                         uint32_t misalign, int v0, int v1, uint32_t* masks) {
+                                         uint32_t misalign, int v0, int v1, uint32_t* bitmap) {
     for (int64_t i = begin + threadIdx.x; i < end; i += kScanThreads) {
         const int64_t id = ids[i];
         if (id < 0 || id >= p.vocab) continue;  // src/generation.cpp:62: ids outside the vocabulary are ignored
         const int64_t col = id - p.col_begin;
         if (col < 0 || col >= p.cols) continue;
-        const int64_t pos = col + misalign;
+        const int64_t pos = col + misalign;  // position in the row's aligned window
         const int64_t v = pos >> 2;
         if (v < v0 || v >= v1) continue;
-        const int rel = (int)(v - v0);
-        const int bit = (rel >> 8) * 4 + (int)(pos & 3);
-        atomicOr(&masks[(rel & 255) * 2 + (bit >> 5)], 1u << (bit & 31));
+        const uint32_t e = (uint32_t)(pos - (int64_t)v0 * 4);  // position in this part
+        atomicOr(&bitmap[e >> 5], 1u << (e & 31));
     }
 }
 
 }  // namespace
 
 template <bool kNucleus>
-__global__ void __launch_bounds__(kScanThreads, 2) scan_rows_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParams p) {
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    float* data = reinterpret_cast<float*>(dyn_smem);
+    const float4* data4 = reinterpret_cast<const float4*>(dyn_smem);
+
+    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ uint32_t s_pen[kBitmapWords], s_ban[kBitmapWords];
+    __shared__ float s_wraw[kScanWarps], s_wamax[kScanWarps], s_wymax[kScanWarps], s_wthr[kScanWarps];
+    __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
+    __shared__ uint32_t s_wfill[kScanWarps];
+
     const int part = blockIdx.x % p.parts;
     const int64_t row = blockIdx.x / p.parts;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-
-    __shared__ uint32_t s_pen[kScanThreads * 2];
-    __shared__ uint32_t s_ban[kScanThreads * 2];
-    __shared__ float s_wraw[kScanWarps], s_wamax[kScanWarps], s_wymax[kScanWarps], s_wthr[kScanWarps];
-    __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
-    __shared__ uint32_t s_walive[kScanWarps], s_wover[kScanWarps];
+    const size_t part_index = (size_t)row * p.parts + part;
+    const size_t seg = part_index * kScanWarps + warp;
 
     // ---- geometry: the row as aligned float4 vectors ------------------------------------------
     const float* row_ptr = p.logits + row * p.row_stride;
@@ -74,99 +120,120 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_rows_kernel(const ScanPa
     const int nv = (int)((misalign + p.cols + 3) >> 2);
     const int v0 = part * p.vecs_per_part;
     const int v1 = min(v0 + p.vecs_per_part, nv);
-    if (v1 <= v0) {  // a part past the end of a row that starts on a 16-byte boundary: nothing to report
-        if (tid < kScanWarps) p.seg_counts[((size_t)row * p.parts + part) * kScanWarps + tid] = 0;
+    const int nvec = v1 - v0;
+    if (nvec <= 0) {  // a part past the end of a row that starts on a 16-byte boundary: nothing to report
+        if (lane == 0) p.seg_counts[seg] = 0;
         if (tid == 0) {
             PartStats s;
             s.raw_tail = 0.0; s.proc_tail = 0.0; s.raw_max = kPad; s.y_max = -INFINITY; s.thr = -INFINITY;
             s.nonfinite = 0; s.alive_tail = 0; s.overflow = 0;
-            p.stats[(size_t)row * p.parts + part] = s;
+            p.stats[part_index] = s;
         }
         return;
     }
 
-    // ---- all loads first: 16 independent 128-bit streaming loads per thread ---------------------
-    float4 d[kVecPerThread];
-    uint64_t dead = 0;  // bit 4j+c set: component c of vector j holds no logit of this row
-#pragma unroll
-    for (int j = 0; j < kVecPerThread; ++j) {
-        const int v = v0 + j * kScanThreads + tid;
-        if (v < v1) {
-            d[j] = __ldcs(vbase + v);
-        } else {
-            d[j] = make_float4(kPad, kPad, kPad, kPad);
-            dead |= 0xFull << (4 * j);
+    // ---- start the copy, and build the history bitmaps while it is in flight ----------------------
+    if (tid == 0) barrier_init(&s_bar, 1);
+    for (int w = tid; w < kBitmapWords; w += kScanThreads) {
+        s_pen[w] = 0;
+        s_ban[w] = 0;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t bytes = (uint32_t)nvec * 16u;
+        const char* src = reinterpret_cast<const char*>(vbase + v0);
+        barrier_expect_bytes(&s_bar, bytes);
+        for (uint32_t off = 0; off < bytes; off += kCopyChunk) {
+            bulk_copy_to_shared(dyn_smem + off, src + off, min(kCopyChunk, bytes - off), &s_bar);
         }
     }
-
-    // ---- history -> per-thread masks, while the loads are in flight --------------------------------
-    s_pen[tid * 2] = 0; s_pen[tid * 2 + 1] = 0;
-    s_ban[tid * 2] = 0; s_ban[tid * 2 + 1] = 0;
-    __syncthreads();
+    const bool use_flags = p.apply_penalty || p.num_banned > 0;
     if (p.apply_penalty) {
         mark_ids(p.history_ids, p.history_offsets[row], p.history_offsets[row + 1], p, misalign, v0, v1, s_pen);
     }
     if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, misalign, v0, v1, s_ban);
+    const bool landed = barrier_wait_bounded(&s_bar, 0);
+    if (!__syncthreads_and(landed ? 1 : 0)) {
+        // The copy did not complete in time: report it, give it one more bounded chance to drain
+        // (shared memory must not be handed to the next CTA under a copy in flight), and leave.
+        if (lane == 0) p.seg_counts[seg] = 0;
+        if (tid == 0) {
+            PartStats s;
+            s.raw_tail = 0.0; s.proc_tail = 0.0; s.raw_max = kPad; s.y_max = -INFINITY; s.thr = -INFINITY;
+            s.nonfinite = 2; s.alive_tail = 0; s.overflow = 0;
+            p.stats[part_index] = s;
+        }
+        barrier_wait_bounded(&s_bar, 0);
+        return;
+    }
+
+    // Components of the first and last vector that lie outside the row are blanked.
+    if (tid == 0) {
+        if (v0 == 0) {
+            for (uint32_t c = 0; c < misalign; ++c) data[c] = kPad;
+        }
+        if (v1 == nv) {
+            for (int64_t pos = (int64_t)misalign + p.cols; pos < (int64_t)nv * 4; ++pos) data[pos - (int64_t)v0 * 4] = kPad;
+        }
+    }
+
+    // ---- 1. flagged logits: handed on in bitmap order, then blanked ---------------------------------
+    uint2* seg_out = p.candidates + seg * kSegCap;
+    uint32_t seg_fill = 0;  // warp-uniform
+    float f_raw = kPad, f_amax = 0.0f, f_y = -INFINITY;
+    if (use_flags) {
+        constexpr int kWordsPerWarp = kBitmapWords / kScanWarps;
+        for (int r = 0; r < kWordsPerWarp / 32; ++r) {
+            const int word = warp * kWordsPerWarp + r * 32 + lane;
+            const uint32_t banned_bits = s_ban[word];
+            uint32_t bits = s_pen[word] | banned_bits;
+            const uint32_t count = __popc(bits);
+            uint32_t incl = count;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            uint32_t slot = seg_fill + incl - count;
+            seg_fill += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            while (bits) {
+                const int b = __ffs(bits) - 1;
+                bits &= bits - 1;
+                const uint32_t e = (uint32_t)word * 32u + (uint32_t)b;
+                const float l = data[e];
+                const bool banned = (banned_bits >> b) & 1u;
+                const float y = banned ? -INFINITY : penalize(l, p.penalty);
+                f_raw = fmaxf(f_raw, l);
+                f_amax = (l != l) ? INFINITY : fmaxf(f_amax, fabsf(l));
+                f_y = fmaxf(f_y, y);
+                if (slot < (uint32_t)kSegCap) {
+                    const int64_t col = (int64_t)v0 * 4 + e - misalign + p.col_begin;
+                    seg_out[slot] = make_uint2(__float_as_uint(l), (uint32_t)col | (banned ? kFlagBanned : kFlagPenalized));
+                }
+                ++slot;
+                data[e] = kPad;
+            }
+        }
+    }
     __syncthreads();
-    const uint64_t pen = (uint64_t)s_pen[tid * 2] | ((uint64_t)s_pen[tid * 2 + 1] << 32);
-    uint64_t ban = (uint64_t)s_ban[tid * 2] | ((uint64_t)s_ban[tid * 2 + 1] << 32);
 
-    // The first and last vector of a row can reach outside it (rows need not start or end on a
-    // 16-byte boundary): blank those components.
-#pragma unroll
-    for (int j = 0; j < kVecPerThread; ++j) {
-        const int v = v0 + j * kScanThreads + tid;
-        if (v < v1 && (v == 0 || v == nv - 1)) {
-            const int64_t first_col = (int64_t)v * 4 - misalign;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (first_col + c < 0 || first_col + c >= p.cols) {
-                    blank(d[j], c);
-                    dead |= 1ull << (4 * j + c);
-                }
-            }
-        }
+    // ---- 2. per-thread maxima, then the part's raw max and selection threshold -------------------------
+    float m = kPad, amax = f_amax;
+    for (int v = tid; v < nvec; v += kScanThreads) {
+        const float4 d = data4[v];
+        m = fmaxf(m, max4(d));
+        amax = fmaxf(amax, amax4(d));
     }
-    ban |= dead;
-    const uint64_t special = pen | ban;
-
-    // ---- per-thread maxima ----------------------------------------------------------------------------
-    float m_raw = kPad, amax = 0.0f, ymax = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kVecPerThread; ++j) {
-        m_raw = fmaxf(m_raw, max4(d[j]));
-        amax = fmaxf(amax, amax4(d[j]));
-    }
-    // Padding must not look like an infinity, and it does not: |kPad| is finite.
-    if (special == 0) {
-        ymax = m_raw;
-    } else {
-#pragma unroll
-        for (int j = 0; j < kVecPerThread; ++j) {
-            const uint32_t nib_p = (uint32_t)(pen >> (4 * j)) & 0xFu, nib_b = (uint32_t)(ban >> (4 * j)) & 0xFu;
-            if ((nib_p | nib_b) == 0) {
-                ymax = fmaxf(ymax, max4(d[j]));
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float l = comp(d[j], c);
-                    const float y = ((nib_b >> c) & 1) ? -INFINITY : ((nib_p >> c) & 1) ? penalize(l, p.penalty) : l;
-                    ymax = fmaxf(ymax, y);
-                }
-            }
-        }
-    }
-
-    // ---- block: raw max, finite check, selection threshold ----------------------------------------
-    const int live_threads = min(kScanThreads, max(v1 - v0, 0));
+    const float m_alive = (m == kPad) ? -INFINITY : m;  // a thread without logits takes no part in the selection
+    const int live_threads = min(kScanThreads, nvec);
     const int full_warps = live_threads >> 5;
     int kp = 33;  // > 32: no threshold, hand everything on
     if (full_warps > 0) kp = (p.k_need + full_warps - 1) / full_warps;
     {
-        const float wraw = warp_max(m_raw), wamax = warp_max(amax), wymax = warp_max(ymax);
+        const float wraw = warp_max(fmaxf(m, f_raw)), wamax = warp_max(amax), wymax = warp_max(fmaxf(m_alive, f_y));
         float wthr = -INFINITY;
-        if (kp == 1) wthr = wymax;
-        else if (kp <= 32) wthr = warp_kth_largest(ymax, kp, lane);
+        if (kp == 1) wthr = warp_max(m_alive);
+        else if (kp <= 32) wthr = warp_kth_largest(m_alive, kp, lane);
         if (lane == 0) {
             s_wraw[warp] = wraw;
             s_wamax[warp] = wamax;
@@ -184,68 +251,50 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_rows_kernel(const ScanPa
         if (w < full_warps) thr = fminf(thr, s_wthr[w]);
     }
     if (full_warps == 0 || kp > 32) thr = -INFINITY;
-    const float tprime = relax_threshold(thr, p.apply_temperature != 0, p.temperature);
+    // Blanked slots hold kPad and must never pass: the threshold stays one step above it.
+    const float tprime = fmaxf(relax_threshold(thr, p.apply_temperature != 0, p.temperature), -3.4028233e38f);
 
-    // ---- exp-sum of the non-candidates and candidate hand-off ------------------------------------------
+    // ---- 3. exp-sum of what stays behind, hand-off of what reaches the threshold -------------------------
     const float c_l2 = __fmul_rn(cmax, kLog2e);
     const float c_res = __fmaf_rn(cmax, kLog2e, -c_l2);  // cmax*kLog2e = c_l2 + c_res exactly
-    const bool proc_same = !p.apply_temperature && (cymax == cmax);
     const float pc_l2 = __fmul_rn(cymax, p.log2e_over_t);
     const float pc_res = __fmaf_rn(cymax, p.log2e_over_t, -pc_l2);
-
-    const size_t seg = ((size_t)row * p.parts + part) * kScanWarps + warp;
-    uint2* seg_out = p.candidates + seg * kSegCap;
-    uint32_t seg_fill = 0;       // warp-uniform
-    uint32_t pushed = 0;         // this thread's candidates
+    const bool second_exp = kNucleus && p.apply_temperature != 0;
     double tail = 0.0, proc = 0.0;
     const uint32_t lanes_below = (1u << lane) - 1u;
+    const int64_t col0 = (int64_t)v0 * 4 - misalign + p.col_begin;  // global column of data[0]
 
-#pragma unroll
-    for (int j = 0; j < kVecPerThread; ++j) {
-        const uint32_t nib_p = (uint32_t)(pen >> (4 * j)) & 0xFu, nib_b = (uint32_t)(ban >> (4 * j)) & 0xFu;
+    for (int base = warp * 32; base < nvec; base += kScanThreads) {
+        const int v = base + lane;
+        const float4 d = v < nvec ? data4[v] : make_float4(kPad, kPad, kPad, kPad);
+        const float l[4] = {d.x, d.y, d.z, d.w};
         float e[4], ep[4];
         bool cand[4];
-        uint32_t flags[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float l = comp(d[j], c);
-            float y = l;
-            flags[c] = 0;
-            if ((nib_p | nib_b) != 0) {
-                if ((nib_b >> c) & 1) { y = -INFINITY; flags[c] = kFlagBanned; }
-                else if ((nib_p >> c) & 1) { y = penalize(l, p.penalty); flags[c] = kFlagPenalized; }
-            }
-            cand[c] = y >= tprime;
-            float x = __fmaf_rn(l, kLog2e, -c_l2);
+            cand[c] = l[c] >= tprime;
+            float x = __fmaf_rn(l[c], kLog2e, -c_l2);
             if (kNucleus) x = __fmaf_rn(x, kLog2eRel, x);
             e[c] = cand[c] ? 0.0f : ex2_approx(x);
-            if (kNucleus) {
-                if (cand[c] || y == -INFINITY) {
-                    ep[c] = 0.0f;
-                } else if (proc_same && flags[c] == 0) {
-                    ep[c] = e[c];
-                } else {
-                    float xp = __fmaf_rn(y, p.log2e_over_t, -pc_l2);
-                    xp = __fmaf_rn(xp, kLog2eRel, xp);
-                    ep[c] = ex2_approx(xp);
-                }
+            ep[c] = 0.0f;
+            if (second_exp) {
+                float xp = __fmaf_rn(l[c], p.log2e_over_t, -pc_l2);
+                xp = __fmaf_rn(xp, kLog2eRel, xp);
+                ep[c] = cand[c] ? 0.0f : ex2_approx(xp);
             }
         }
         tail += (double)((e[0] + e[1]) + (e[2] + e[3]));
-        if (kNucleus) proc += (double)((ep[0] + ep[1]) + (ep[2] + ep[3]));
+        if (second_exp) proc += (double)((ep[0] + ep[1]) + (ep[2] + ep[3]));
 
         if (__any_sync(0xFFFFFFFFu, cand[0] | cand[1] | cand[2] | cand[3])) {
-            const int v = v0 + j * kScanThreads + tid;
-            const int64_t first_col = (int64_t)v * 4 - misalign + p.col_begin;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const uint32_t votes = __ballot_sync(0xFFFFFFFFu, cand[c]);
                 if (cand[c]) {
                     const uint32_t slot = seg_fill + __popc(votes & lanes_below);
                     if (slot < (uint32_t)kSegCap) {
-                        seg_out[slot] = make_uint2(__float_as_uint(comp(d[j], c)), (uint32_t)(first_col + c) | flags[c]);
+                        seg_out[slot] = make_uint2(__float_as_uint(l[c]), (uint32_t)(col0 + (int64_t)v * 4 + c));
                     }
-                    ++pushed;
                 }
                 seg_fill += __popc(votes);
             }
@@ -253,51 +302,63 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_rows_kernel(const ScanPa
     }
 
     // ---- block reduction in a fixed order, then the part's record ---------------------------------------
-    const uint32_t alive = 4u * kVecPerThread - (uint32_t)__popcll(ban) - pushed;
     {
         const double wt = warp_sum(tail), wp = warp_sum(proc);
-        const uint32_t wa = warp_sum_u32(alive);
         if (lane == 0) {
             s_wtail[warp] = wt;
             s_wproc[warp] = wp;
-            s_walive[warp] = wa;
-            s_wover[warp] = seg_fill > (uint32_t)kSegCap ? 1u : 0u;
+            s_wfill[warp] = seg_fill;
             p.seg_counts[seg] = min(seg_fill, (uint32_t)kSegCap);
         }
     }
     __syncthreads();
     if (tid == 0) {
         double t = 0.0, q = 0.0;
-        uint32_t a = 0, over = 0;
+        uint32_t handed_on = 0, over = 0;
 #pragma unroll
         for (int w = 0; w < kScanWarps; ++w) {
             t += s_wtail[w];
             q += s_wproc[w];
-            a += s_walive[w];
-            over |= s_wover[w];
+            handed_on += s_wfill[w];
+            over |= s_wfill[w] > (uint32_t)kSegCap ? 1u : 0u;
         }
-        // The exponent used c_l2 where cmax*log2(e) was meant: put the dropped part back.
-        const double fix = exp2(-(double)c_res);
-        const double pfix = exp2(-(double)pc_res);
+        const int64_t first = max((int64_t)v0 * 4 - (int64_t)misalign, (int64_t)0);
+        const int64_t last = min((int64_t)v1 * 4 - (int64_t)misalign, p.cols);
+        const uint32_t logits_here = (uint32_t)(last - first);
+        // The exponents used c_l2 where cmax*log2(e) was meant: put the dropped part back.
+        const double raw_tail = t * exp2(-(double)c_res);
         PartStats s;
-        s.raw_tail = t * fix;
-        s.proc_tail = q * (proc_same ? fix : pfix);
+        s.raw_tail = raw_tail;
+        s.proc_tail = 0.0;
+        if (kNucleus && cymax > -INFINITY) {
+            // What stays behind is unflagged, so its processed value is l / T; without a
+            // temperature the processed tail is the raw one measured against the other maximum.
+            s.proc_tail = second_exp ? q * exp2(-(double)pc_res) : raw_tail * exp((double)cmax - (double)cymax);
+        }
         s.raw_max = cmax;
         s.y_max = cymax;
         s.thr = thr;
-        s.nonfinite = (!(camax < INFINITY) || t != t) ? 1u : 0u;
-        s.alive_tail = a;
+        s.nonfinite = (!(camax < INFINITY) || t != t || q != q) ? 1u : 0u;
+        s.alive_tail = logits_here > handed_on ? logits_here - handed_on : 0u;
         s.overflow = over;
-        p.stats[(size_t)row * p.parts + part] = s;
+        p.stats[part_index] = s;
     }
+}
+
+cudaError_t configure_scan_rows() {
+    cudaError_t e = cudaFuncSetAttribute(scan_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kPartVecs * 16);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(scan_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPartVecs * 16);
 }
 
 cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t stream) {
     const long long blocks = (long long)p.rows * p.parts;
     if (blocks <= 0) return cudaSuccess;
-    if (blocks > 0x7FFFFFFFll) return cudaErrorInvalidConfiguration;
-    if (nucleus) scan_rows_kernel<true><<<(unsigned)blocks, kScanThreads, 0, stream>>>(p);
-    else scan_rows_kernel<false><<<(unsigned)blocks, kScanThreads, 0, stream>>>(p);
+    if (blocks > 0x7FFFFFFFll || p.vecs_per_part > kPartVecs) return cudaErrorInvalidConfiguration;
+    const size_t shared = ((size_t)p.vecs_per_part * 16 + 127) / 128 * 128;
+    if (nucleus) scan_rows_kernel<true><<<(unsigned)blocks, kScanThreads, shared, stream>>>(p);
+    else scan_rows_kernel<false><<<(unsigned)blocks, kScanThreads, shared, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -32,6 +32,8 @@ struct ScanParams {
 };
 
 // nucleus: also accumulate the processed-domain tail that a full-vocabulary top-p / min-p needs.
+// Opts the kernel in to 64 KB of dynamic shared memory; once per device, before the first launch.
+cudaError_t configure_scan_rows();
 cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t stream);
 
 }  // namespace psx
