@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <random>
 #include <string>
@@ -105,6 +106,7 @@ struct Plan {
     bool nucleus = false;  // sampling without a top-k: the processed tail mass is needed too
     bool apply_temperature = false;
     int sort_capacity = 1024;
+    int gather_capacity = 4096;
 };
 
 Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t row_stride, int64_t vocab,
@@ -112,7 +114,11 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     Plan plan;
     const bool aligned = (reinterpret_cast<uintptr_t>(logits) % 16 == 0) && (row_stride % 4 == 0);
     const int64_t vectors = (cols + 3 + (aligned ? 0 : 3)) / 4;  // most float4 a row can span
-    plan.parts = (int)((vectors + psx::kPartVecs - 1) / psx::kPartVecs);
+    int part_vecs = psx::kPartVecs;
+    if (const char* env = std::getenv("PSX_B200_PART_VECS")) {  // tuning knob: vectors per CTA, 256..4096
+        part_vecs = std::max(256, std::min(psx::kPartVecs, std::atoi(env)));
+    }
+    plan.parts = (int)((vectors + part_vecs - 1) / part_vecs);
     plan.vecs_per_part = (int)((vectors + plan.parts - 1) / plan.parts);
     const bool sample = c->do_sample != 0;
     const bool top_k_on = sample && c->top_k > 0 && c->top_k < vocab;
@@ -124,14 +130,20 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     // A row of at most 256 vectors fits the candidate segments whole (one vector per thread, 128
     // logits per warp): hand everything on, and every filter is exact whatever the settings.
     if (vectors <= psx::kScanThreads) plan.k_need = 1 << 30;
-    plan.sort_capacity = plan.nucleus ? 4096 : 2048;
+    plan.sort_capacity = plan.nucleus ? 4096 : 1024;
+    plan.gather_capacity = plan.nucleus ? 8192 : 4096;
     return plan;
 }
 
-psx_status configure_merge(psx_ctx* ctx, int capacity) {
-    if (ctx->merge_capacity_configured >= capacity) return PSX_OK;
-    PSX_CUDA(psx::configure_merge_rows(capacity));
-    ctx->merge_capacity_configured = capacity;
+// The survivor stage holds one row's segment table and candidates in shared memory.
+psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int segments) {
+    if (segments > 4096) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: rows wider than 8M logits per GPU are not supported");
+    }
+    const int bytes = (int)psx::merge_rows_shared_bytes(plan.sort_capacity, plan.gather_capacity, segments);
+    if (ctx->merge_capacity_configured >= bytes) return PSX_OK;
+    PSX_CUDA(psx::configure_merge_rows((size_t)bytes));
+    ctx->merge_capacity_configured = bytes;
     return PSX_OK;
 }
 
@@ -189,6 +201,7 @@ void fill_merge_settings(psx::MergeParams& mp, const psx_sampling_config* c, con
     mp.row_status = row_status;
     mp.diag = diag;
     mp.sort_capacity = plan.sort_capacity;
+    mp.gather_capacity = plan.gather_capacity;
 }
 
 psx_status check_common(psx_ctx* ctx, const psx_sampling_config* config, int64_t rows, int64_t cols,
@@ -331,7 +344,7 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
                                      plan, sp)) {
         return s;
     }
-    if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
+    if (psx_status s = configure_merge(ctx, plan, plan.parts * psx::kScanWarps)) return s;
 
     cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
     if (ctx->timing) {
@@ -540,8 +553,9 @@ psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gath
 
     Plan plan;
     plan.apply_temperature = sample && config->temperature != 1.0f;
-    plan.sort_capacity = 2048;
-    if (psx_status s = configure_merge(ctx, plan.sort_capacity)) return s;
+    plan.sort_capacity = 1024;
+    plan.gather_capacity = 4096;
+    if (psx_status s = configure_merge(ctx, plan, num_shards)) return s;
     const int capacity = psx::shard_record_capacity(sample, config->top_k);
     const int64_t record = (int64_t)psx::shard_record_bytes(capacity);
     const char* base = static_cast<const char*>(gathered);

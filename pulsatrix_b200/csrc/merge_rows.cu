@@ -195,14 +195,21 @@ __device__ uint32_t block_select_kth(const uint32_t* keys, int m, uint32_t k, ui
 
 __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergeParams p) {
     extern __shared__ u64 dyn[];
-    const int cap = p.sort_capacity;
+    const int cap = p.sort_capacity, gcap = p.gather_capacity;
+    const int nseg = p.parts * p.segs_per_part;
     u64* keyA = dyn;
     u64* keyB = keyA + cap;
     double* ex = reinterpret_cast<double*>(keyB + cap);
     uint8_t* alive = reinterpret_cast<uint8_t*>(ex + cap);
+    uint32_t* cand_l = reinterpret_cast<uint32_t*>(alive + cap);  // raw logit bits of every candidate
+    uint32_t* cand_c = cand_l + gcap;                             // column | flags
+    uint32_t* seg_begin = cand_c + gcap;                          // nseg + 1 exclusive prefix of the counts
+    uint32_t* seg_size = seg_begin + nseg + 1;                    // nseg
+    uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);           // scratch over the (still unused) sort arrays
 
     __shared__ float s_f[kMergeThreads / 32];
     __shared__ double s_d[kMergeThreads / 32];
+    __shared__ uint32_t s_u[kMergeThreads / 32];
     __shared__ int s_count;
     __shared__ int s_ns;
     __shared__ uint32_t s_chosen_raw;
@@ -217,12 +224,8 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     const char* counts_row = static_cast<const char*>(p.seg_counts) + row * p.count_row_stride;
     const char* cands_row = static_cast<const char*>(p.candidates) + row * p.cand_row_stride;
     auto part_stats = [&](int i) { return *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride); };
-    auto seg_count = [&](int s) {
-        return min((int)*reinterpret_cast<const uint32_t*>(counts_row + s * p.count_seg_stride), p.seg_cap);
-    };
-    auto seg_cands = [&](int s) { return reinterpret_cast<const uint2*>(cands_row + s * p.cand_seg_stride); };
 
-    // ---- 1. join the parts ------------------------------------------------------------------------
+    // ---- 1. join the parts; lay the candidate segments out back to back ---------------------------
     float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
     double bad = 0.0, alive_tail = 0.0;
     for (int i = tid; i < p.parts; i += kMergeThreads) {
@@ -233,26 +236,68 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         bad += (double)((s.nonfinite & 1u) + (s.nonfinite >> 1) * 256u + s.overflow * 65536u);
         alive_tail += (double)s.alive_tail;
     }
+    const int per_thread = (nseg + kMergeThreads - 1) / kMergeThreads;
+    uint32_t mine = 0;
+    for (int j = 0; j < per_thread; ++j) {
+        const int s = tid * per_thread + j;
+        if (s < nseg) {
+            const uint32_t c = min(*reinterpret_cast<const uint32_t*>(counts_row + s * p.count_seg_stride),
+                                   (uint32_t)p.seg_cap);
+            seg_size[s] = c;
+            mine += c;
+        }
+    }
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    if (lane == 31) s_u[warp] = incl;
     if (tid == 0) s_count = 0;
-    raw_max = block_max(raw_max, s_f);
+    raw_max = block_max(raw_max, s_f);  // the barriers inside also publish s_u and seg_size
     y_max = block_max(y_max, s_f);
     thr = block_max(thr, s_f);
     bad = block_sum(bad, s_d);
     alive_tail = block_sum(alive_tail, s_d);
+    uint32_t running = incl - mine;
+    for (int w = 0; w < warp; ++w) running += s_u[w];
+    for (int j = 0; j < per_thread; ++j) {
+        const int s = tid * per_thread + j;
+        if (s < nseg) {
+            seg_begin[s] = running;
+            running += seg_size[s];
+            if (s == nseg - 1) seg_begin[nseg] = running;
+        }
+    }
+    __syncthreads();
+    const int total = (int)seg_begin[nseg];
     const uint32_t bad_bits = (uint32_t)bad;
-    if ((bad_bits & 0xFFFFu) != 0 || bad_bits >= 65536u) {
+    if (bad_bits != 0 || total > gcap) {
         if (tid == 0) {
             p.tokens[row] = -1;
             p.log_probs[row] = 0.0f;
             p.row_status[row] = (bad_bits & 0xFF00u) ? PSX_ROW_DEVICE_TIMEOUT
                                 : (bad_bits & 0xFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
-            if (p.diag) p.diag[row] = psx_row_diag{0, 0, INFINITY, INFINITY};
+            if (p.diag) p.diag[row] = psx_row_diag{total, 0, INFINITY, INFINITY};
         }
         return;
     }
+    // Independent loads, a few per thread: every candidate of the row into shared memory.
+    for (int i = tid; i < total; i += kMergeThreads) {
+        int lo = 0, hi = nseg;  // the segment s with seg_begin[s] <= i < seg_begin[s + 1]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (seg_begin[mid] <= (uint32_t)i) lo = mid; else hi = mid;
+        }
+        const uint2 c = reinterpret_cast<const uint2*>(cands_row + lo * p.cand_seg_stride)[i - (int)seg_begin[lo]];
+        cand_l[i] = c.x;
+        cand_c[i] = c.y;
+    }
+    __syncthreads();
+
     float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
-    const int nseg = p.parts * p.segs_per_part;
     const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
 
     // Every part handed on at least k logits, so together they hold far more than the k that a
@@ -261,33 +306,16 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     // temperature divide go on to the sort.  Greedy keeps the maximum and its ties.
     if (!p.do_sample) {
         keep_from = fmaxf(y_max, -FLT_MAX);
-    } else if (top_k_on) {
-        uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);
-        const int ycap = cap * 6;  // the three sort arrays are still unused
-        for (int s = warp; s < nseg; s += kMergeThreads / 32) {
-            const int cnt = seg_count(s);
-            const uint2* seg = seg_cands(s);
-            for (int i = lane; i < cnt; i += 32) {
-                const uint2 c = seg[i];
-                const float y = processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty);
-                if (y >= keep_from) {
-                    const int slot = atomicAdd(&s_count, 1);
-                    if (slot < ycap) ykeys[slot] = ordered_key(y);
-                }
-            }
+    } else if (top_k_on && total > p.top_k) {
+        for (int i = tid; i < total; i += kMergeThreads) {
+            ykeys[i] = ordered_key(processed_before_temperature(__uint_as_float(cand_l[i]), cand_c[i], p.penalty));
         }
         __syncthreads();
-        const int m = s_count;
-        __syncthreads();
-        if (tid == 0) s_count = 0;
-        if (m <= ycap && m > p.top_k) {
-            const uint32_t kth = block_select_kth(ykeys, m, (uint32_t)p.top_k, s_hist, s_state);
-            keep_from = relax_threshold(from_ordered_key(kth), apply_t, p.temperature);
-        }
-        __syncthreads();
+        const uint32_t kth = block_select_kth(ykeys, total, (uint32_t)p.top_k, s_hist, s_state);
+        keep_from = fmaxf(keep_from, relax_threshold(from_ordered_key(kth), apply_t, p.temperature));
     }
 
-    // ---- 2. candidates: raw sum-exp for all, the list for those that can survive ----------------
+    // ---- 2. raw sum-exp over everything; the list of those that can survive ------------------------
     double z_raw = 0.0, z_rest = 0.0, dropped = 0.0;
     for (int i = tid; i < p.parts; i += kMergeThreads) {
         const PartStats s = part_stats(i);
@@ -296,22 +324,18 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
             z_rest += s.proc_tail * exp((double)temper(s.y_max, apply_t, p.temperature) - (double)x_max);
         }
     }
-    for (int s = warp; s < nseg; s += kMergeThreads / 32) {
-        const int cnt = seg_count(s);
-        const uint2* seg = seg_cands(s);
-        for (int i = lane; i < cnt; i += 32) {
-            const uint2 c = seg[i];
-            const float l = __uint_as_float(c.x);
-            z_raw += exp((double)l - (double)raw_max);
-            const float y = processed_before_temperature(l, c.y, p.penalty);
+    for (int i = tid; i < total; i += kMergeThreads) {
+        const float l = __uint_as_float(cand_l[i]);
+        const uint32_t cf = cand_c[i];
+        z_raw += exp((double)l - (double)raw_max);
+        const float y = processed_before_temperature(l, cf, p.penalty);
+        if (y >= keep_from) {
             const float x = temper(y, apply_t, p.temperature);
-            if (y >= keep_from) {
-                const int slot = atomicAdd(&s_count, 1);
-                if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(c.y & kColumnMask);
-            } else if (y > -INFINITY) {
-                z_rest += exp((double)x - (double)x_max);
-                dropped += 1.0;
-            }
+            const int slot = atomicAdd(&s_count, 1);
+            if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(cf & kColumnMask);
+        } else if (y > -INFINITY && !top_k_on) {
+            z_rest += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
+            dropped += 1.0;
         }
     }
     z_raw = block_sum(z_raw, s_d);
@@ -340,9 +364,9 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     bool rest_alive = false;
     if (top_k_on && n >= p.top_k) {
         const uint32_t kth = key_ord(keyA[p.top_k - 1]);
-        int mine = 0;
-        for (int i = tid; i < n; i += kMergeThreads) mine += key_ord(keyA[i]) >= kth ? 1 : 0;
-        if (mine) atomicAdd(&s_ns, mine);
+        int count = 0;
+        for (int i = tid; i < n; i += kMergeThreads) count += key_ord(keyA[i]) >= kth ? 1 : 0;
+        if (count) atomicAdd(&s_ns, count);
     } else {
         if (tid == 0) s_ns = n;
         // Without a top-k the rest of the vocabulary is still in play.
@@ -373,13 +397,8 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     __syncthreads();
     const Decision dec = s_dec;
     if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
-        for (int s = warp; s < nseg; s += kMergeThreads / 32) {
-            const int cnt = seg_count(s);
-            const uint2* seg = seg_cands(s);
-            for (int i = lane; i < cnt; i += 32) {
-                const uint2 c = seg[i];
-                if ((long long)(c.y & kColumnMask) == dec.token) s_chosen_raw = c.x;
-            }
+        for (int i = tid; i < total; i += kMergeThreads) {
+            if ((long long)(cand_c[i] & kColumnMask) == dec.token) s_chosen_raw = cand_l[i];
         }
     }
     __syncthreads();
@@ -398,16 +417,18 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
 
 }  // namespace
 
-size_t merge_rows_shared_bytes(int sort_capacity) { return (size_t)sort_capacity * (8 + 8 + 8 + 1); }
+size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, int segments) {
+    return (size_t)sort_capacity * (8 + 8 + 8 + 1) + (size_t)gather_capacity * 8 + (size_t)(2 * segments + 1) * 4 + 16;
+}
 
-cudaError_t configure_merge_rows(int sort_capacity) {
-    return cudaFuncSetAttribute(merge_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)merge_rows_shared_bytes(sort_capacity));
+cudaError_t configure_merge_rows(size_t shared_bytes) {
+    return cudaFuncSetAttribute(merge_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes);
 }
 
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;
-    merge_rows_kernel<<<(unsigned)p.rows, kMergeThreads, merge_rows_shared_bytes(p.sort_capacity), stream>>>(p);
+    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, p.parts * p.segs_per_part);
+    merge_rows_kernel<<<(unsigned)p.rows, kMergeThreads, shared, stream>>>(p);
     return cudaGetLastError();
 }
 

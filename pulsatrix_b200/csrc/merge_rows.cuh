@@ -37,10 +37,11 @@ struct MergeParams {
     int32_t* row_status;
     psx_row_diag* diag;          // may be null
     int32_t sort_capacity;       // survivors + near-survivors the shared-memory sorter holds (power of two)
+    int32_t gather_capacity;     // candidates of one row held in shared memory (<= 6 * sort_capacity)
 };
 
-size_t merge_rows_shared_bytes(int sort_capacity);
-cudaError_t configure_merge_rows(int sort_capacity);
+size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, int segments);
+cudaError_t configure_merge_rows(size_t shared_bytes);
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream);
 
 }  // namespace psx

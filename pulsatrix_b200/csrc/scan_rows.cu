@@ -182,9 +182,13 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     uint32_t seg_fill = 0;  // warp-uniform
     float f_raw = kPad, f_amax = 0.0f, f_y = -INFINITY;
     if (use_flags) {
+        // A warp takes the bitmap words of the logits its own threads own in the dense passes
+        // (vector v belongs to thread v % 256), so a row that is handed on whole fills every
+        // warp's segment with exactly its own 128 logits per 256 vectors.
         constexpr int kWordsPerWarp = kBitmapWords / kScanWarps;
         for (int r = 0; r < kWordsPerWarp / 32; ++r) {
-            const int word = warp * kWordsPerWarp + r * 32 + lane;
+            const int idx = r * 32 + lane;
+            const int word = 32 * (idx >> 2) + 4 * warp + (idx & 3);
             const uint32_t banned_bits = s_ban[word];
             uint32_t bits = s_pen[word] | banned_bits;
             const uint32_t count = __popc(bits);
