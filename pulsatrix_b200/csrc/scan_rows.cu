@@ -33,9 +33,10 @@ constexpr float kPad = -FLT_MAX;  // stands for "no logit here": finite, never a
 constexpr int kBitmapWords = kPartVecs * 4 / 32;  // one bit per logit of a part
 constexpr uint32_t kCopyChunk = 16384;            // bytes per bulk copy
 
-__device__ __forceinline__ float max4(const float4& v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
-__device__ __forceinline__ float amax4(const float4& v) {
-    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+// acc = max(acc, all four) in two three-input instructions.
+__device__ __forceinline__ float max_into(float acc, const float4& v) { return fmax3(fmax3(v.x, v.y, v.z), v.w, acc); }
+__device__ __forceinline__ float amax_into(float acc, const float4& v) {
+    return fmax3(fmax3(fabsf(v.x), fabsf(v.y), fabsf(v.z)), fabsf(v.w), acc);
 }
 
 // ---- mbarrier + bulk copy (PTX; the destination and the barrier are this CTA's shared memory) ----
@@ -72,7 +73,7 @@ __device__ __forceinline__ bool barrier_wait_bounded(uint64_t* bar, uint32_t par
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if (tries > 64) __nanosleep(200);
+        __nanosleep(tries < 16 ? 64 : 256);
     }
     return false;
 }
@@ -223,10 +224,18 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
 
     // ---- 2. per-thread maxima, then the part's raw max and selection threshold -------------------------
     float m = kPad, amax = f_amax;
-    for (int v = tid; v < nvec; v += kScanThreads) {
-        const float4 d = data4[v];
-        m = fmaxf(m, max4(d));
-        amax = fmaxf(amax, amax4(d));
+    {
+        int v = tid;
+        for (; v + kScanThreads < nvec; v += 2 * kScanThreads) {  // two independent loads per trip
+            const float4 d0 = data4[v], d1 = data4[v + kScanThreads];
+            m = max_into(max_into(m, d0), d1);
+            amax = amax_into(amax_into(amax, d0), d1);
+        }
+        if (v < nvec) {
+            const float4 d = data4[v];
+            m = max_into(m, d);
+            amax = amax_into(amax, d);
+        }
     }
     const float m_alive = (m == kPad) ? -INFINITY : m;  // a thread without logits takes no part in the selection
     const int live_threads = min(kScanThreads, nvec);
@@ -271,38 +280,60 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     for (int base = warp * 32; base < nvec; base += kScanThreads) {
         const int v = base + lane;
         const float4 d = v < nvec ? data4[v] : make_float4(kPad, kPad, kPad, kPad);
-        const float l[4] = {d.x, d.y, d.z, d.w};
-        float e[4], ep[4];
-        bool cand[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            cand[c] = l[c] >= tprime;
-            float x = __fmaf_rn(l[c], kLog2e, -c_l2);
-            if (kNucleus) x = __fmaf_rn(x, kLog2eRel, x);
-            e[c] = cand[c] ? 0.0f : ex2_approx(x);
-            ep[c] = 0.0f;
-            if (second_exp) {
-                float xp = __fmaf_rn(l[c], p.log2e_over_t, -pc_l2);
-                xp = __fmaf_rn(xp, kLog2eRel, xp);
-                ep[c] = cand[c] ? 0.0f : ex2_approx(xp);
-            }
+        float x0 = __fmaf_rn(d.x, kLog2e, -c_l2), x1 = __fmaf_rn(d.y, kLog2e, -c_l2);
+        float x2 = __fmaf_rn(d.z, kLog2e, -c_l2), x3 = __fmaf_rn(d.w, kLog2e, -c_l2);
+        if (kNucleus) {
+            x0 = __fmaf_rn(x0, kLog2eRel, x0); x1 = __fmaf_rn(x1, kLog2eRel, x1);
+            x2 = __fmaf_rn(x2, kLog2eRel, x2); x3 = __fmaf_rn(x3, kLog2eRel, x3);
         }
-        tail += (double)((e[0] + e[1]) + (e[2] + e[3]));
-        if (second_exp) proc += (double)((ep[0] + ep[1]) + (ep[2] + ep[3]));
-
-        if (__any_sync(0xFFFFFFFFu, cand[0] | cand[1] | cand[2] | cand[3])) {
+        float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
+        float q0 = 0.0f, q1 = 0.0f, q2 = 0.0f, q3 = 0.0f;
+        if (second_exp) {
+            float y0 = __fmaf_rn(d.x, p.log2e_over_t, -pc_l2), y1 = __fmaf_rn(d.y, p.log2e_over_t, -pc_l2);
+            float y2 = __fmaf_rn(d.z, p.log2e_over_t, -pc_l2), y3 = __fmaf_rn(d.w, p.log2e_over_t, -pc_l2);
+            q0 = ex2_approx(__fmaf_rn(y0, kLog2eRel, y0)); q1 = ex2_approx(__fmaf_rn(y1, kLog2eRel, y1));
+            q2 = ex2_approx(__fmaf_rn(y2, kLog2eRel, y2)); q3 = ex2_approx(__fmaf_rn(y3, kLog2eRel, y3));
+        }
+        // One vote per trip: which lanes hold a vector that reaches the threshold at all.
+        const bool any_here = fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime;
+        const uint32_t votes = __ballot_sync(0xFFFFFFFFu, any_here);
+        if (votes != 0) {
+            const float l[4] = {d.x, d.y, d.z, d.w};
+            uint32_t mine = 0;  // which of my four components are handed on
+            if (any_here) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mine |= (l[c] >= tprime ? 1u : 0u) << c;
+                // What is handed on leaves the sums (its exp is taken in double by the survivor stage).
+                if (mine & 1u) { e0 = 0.0f; q0 = 0.0f; }
+                if (mine & 2u) { e1 = 0.0f; q1 = 0.0f; }
+                if (mine & 4u) { e2 = 0.0f; q2 = 0.0f; }
+                if (mine & 8u) { e3 = 0.0f; q3 = 0.0f; }
+            }
+            // Slots in lane order, components in order within a lane.  Usually every voting lane
+            // hands on one logit; otherwise the lanes' counts are summed with a few more votes.
+            const uint32_t count = __popc(mine);
+            uint32_t before = __popc(votes & lanes_below), total = __popc(votes);
+            const uint32_t multi = __ballot_sync(0xFFFFFFFFu, count > 1);
+            if (multi != 0) {
+                const uint32_t two = __ballot_sync(0xFFFFFFFFu, count > 1 && ((count - 1) & 2u));  // counts 3 and 4
+                const uint32_t odd = __ballot_sync(0xFFFFFFFFu, count > 1 && ((count - 1) & 1u));  // counts 2 and 4
+                before += 2 * __popc(two & lanes_below) + __popc(odd & lanes_below);
+                total += 2 * __popc(two) + __popc(odd);
+            }
+            uint32_t slot = seg_fill + before;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const uint32_t votes = __ballot_sync(0xFFFFFFFFu, cand[c]);
-                if (cand[c]) {
-                    const uint32_t slot = seg_fill + __popc(votes & lanes_below);
+                if (mine & (1u << c)) {
                     if (slot < (uint32_t)kSegCap) {
                         seg_out[slot] = make_uint2(__float_as_uint(l[c]), (uint32_t)(col0 + (int64_t)v * 4 + c));
                     }
+                    ++slot;
                 }
-                seg_fill += __popc(votes);
             }
+            seg_fill += total;
         }
+        tail += (double)((e0 + e1) + (e2 + e3));
+        if (second_exp) proc += (double)((q0 + q1) + (q2 + q3));
     }
 
     // ---- block reduction in a fixed order, then the part's record ---------------------------------------
