@@ -159,6 +159,10 @@ psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_co
     sp.k_need = plan.k_need;
     sp.parts = plan.parts;
     sp.vecs_per_part = plan.vecs_per_part;
+    {
+        const char* skip = std::getenv("PSX_B200_DEBUG_SKIP");  // profiling only
+        sp.debug_skip = skip ? std::atoi(skip) : 0;
+    }
     sp.num_banned = 0;
     sp.banned_ids = nullptr;
     if (c->num_new_tokens < c->min_new_tokens && c->num_eos_token_ids > 0) {  // src/generation.cpp:69

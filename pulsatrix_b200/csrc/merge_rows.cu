@@ -129,24 +129,23 @@ __device__ void decide(const MergeParams& p, const u64* keyA, const u64* keyB, c
     out.token = chosen;
 }
 
-__device__ __forceinline__ float block_max(float v, float* scratch) {
-    v = warp_max(v);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+// Sorts n <= blockDim.x distinct 64-bit keys in shared memory by counting, one key per thread:
+// a key's place is the number of keys that come before it.  Starts and ends with a barrier.
+__device__ __forceinline__ void block_rank_sort(u64* keys, int n, bool descending) {
     __syncthreads();
-    float r = scratch[0];
-    for (int w = 1; w < kMergeThreads / 32; ++w) r = fmaxf(r, scratch[w]);
+    const int i = threadIdx.x;
+    u64 mine = 0;
+    int place = 0;
+    if (i < n) {
+        mine = keys[i];
+        for (int j = 0; j < n; ++j) {
+            const u64 other = keys[j];
+            place += (descending ? other > mine : other < mine) ? 1 : 0;
+        }
+    }
     __syncthreads();
-    return r;
-}
-
-__device__ __forceinline__ double block_sum(double v, double* scratch) {
-    v = warp_sum(v);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    if (i < n) keys[place] = mine;
     __syncthreads();
-    double r = 0.0;
-    for (int w = 0; w < kMergeThreads / 32; ++w) r += scratch[w];
-    __syncthreads();
-    return r;
 }
 
 // The k-th largest (1-based, k <= m) of m uint32 keys in shared memory: four 8-bit radix passes,
@@ -207,8 +206,8 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     uint32_t* seg_size = seg_begin + nseg + 1;                    // nseg
     uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);           // scratch over the (still unused) sort arrays
 
-    __shared__ float s_f[kMergeThreads / 32];
-    __shared__ double s_d[kMergeThreads / 32];
+    __shared__ float s_f[3][kMergeThreads / 32];
+    __shared__ double s_d[3][kMergeThreads / 32];
     __shared__ uint32_t s_u[kMergeThreads / 32];
     __shared__ int s_count;
     __shared__ int s_ns;
@@ -255,11 +254,28 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     }
     if (lane == 31) s_u[warp] = incl;
     if (tid == 0) s_count = 0;
-    raw_max = block_max(raw_max, s_f);  // the barriers inside also publish s_u and seg_size
-    y_max = block_max(y_max, s_f);
-    thr = block_max(thr, s_f);
-    bad = block_sum(bad, s_d);
-    alive_tail = block_sum(alive_tail, s_d);
+    {   // one barrier for all five reductions; it also publishes s_u and seg_size
+        raw_max = warp_max(raw_max);
+        y_max = warp_max(y_max);
+        thr = warp_max(thr);
+        bad = warp_sum(bad);
+        alive_tail = warp_sum(alive_tail);
+        if (lane == 0) {
+            s_f[0][warp] = raw_max; s_f[1][warp] = y_max; s_f[2][warp] = thr;
+            s_d[0][warp] = bad; s_d[1][warp] = alive_tail;
+        }
+        __syncthreads();
+        raw_max = s_f[0][0]; y_max = s_f[1][0]; thr = s_f[2][0];
+        bad = 0.0; alive_tail = 0.0;
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; ++w) {
+            raw_max = fmaxf(raw_max, s_f[0][w]);
+            y_max = fmaxf(y_max, s_f[1][w]);
+            thr = fmaxf(thr, s_f[2][w]);
+            bad += s_d[0][w];
+            alive_tail += s_d[1][w];
+        }
+    }
     uint32_t running = incl - mine;
     for (int w = 0; w < warp; ++w) running += s_u[w];
     for (int j = 0; j < per_thread; ++j) {
@@ -338,9 +354,21 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
             dropped += 1.0;
         }
     }
-    z_raw = block_sum(z_raw, s_d);
-    z_rest = block_sum(z_rest, s_d);
-    dropped = block_sum(dropped, s_d);  // ends with a barrier: s_count is final
+    {   // three sums, one barrier (which also makes s_count final); fixed order
+        z_raw = warp_sum(z_raw);
+        z_rest = warp_sum(z_rest);
+        dropped = warp_sum(dropped);
+        __syncthreads();  // the reads of s_d above are done
+        if (lane == 0) { s_d[0][warp] = z_raw; s_d[1][warp] = z_rest; s_d[2][warp] = dropped; }
+        __syncthreads();
+        z_raw = 0.0; z_rest = 0.0; dropped = 0.0;
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; ++w) {
+            z_raw += s_d[0][w];
+            z_rest += s_d[1][w];
+            dropped += s_d[2][w];
+        }
+    }
     const int n = s_count;
     if (n > cap || n == 0) {
         if (tid == 0) {
@@ -353,11 +381,15 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
     }
 
     // ---- 3. sort by (value desc, column asc); top-k keeps the k-th value and its ties -----------
-    int n_pad = 2;
-    while (n_pad < n) n_pad <<= 1;
-    for (int i = n + tid; i < n_pad; i += kMergeThreads) keyA[i] = 0;
-    __syncthreads();
-    block_bitonic_sort(keyA, n_pad, /*descending=*/true);
+    if (n <= kMergeThreads) {
+        block_rank_sort(keyA, n, /*descending=*/true);
+    } else {
+        int n_pad = 2;
+        while (n_pad < n) n_pad <<= 1;
+        for (int i = n + tid; i < n_pad; i += kMergeThreads) keyA[i] = 0;
+        __syncthreads();
+        block_bitonic_sort(keyA, n_pad, /*descending=*/true);
+    }
 
     if (tid == 0) s_ns = 0;
     __syncthreads();
@@ -382,11 +414,15 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         alive[i] = 1;
         keyB[i] = ((u64)key_col(keyA[i]) << 32) | (uint32_t)i;
     }
-    int ns_pad = 2;
-    while (ns_pad < ns) ns_pad <<= 1;
-    for (int i = ns + tid; i < ns_pad; i += kMergeThreads) keyB[i] = ~0ull;
-    __syncthreads();
-    block_bitonic_sort(keyB, ns_pad, /*descending=*/false);
+    if (ns <= kMergeThreads) {
+        block_rank_sort(keyB, ns, /*descending=*/false);
+    } else {
+        int ns_pad = 2;
+        while (ns_pad < ns) ns_pad <<= 1;
+        for (int i = ns + tid; i < ns_pad; i += kMergeThreads) keyB[i] = ~0ull;
+        __syncthreads();
+        block_bitonic_sort(keyB, ns_pad, /*descending=*/false);
+    }
 
     // ---- 4. the reference's walk, by one thread ------------------------------------------------------
     if (tid == 0) {

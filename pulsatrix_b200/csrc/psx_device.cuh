@@ -113,6 +113,28 @@ __device__ __forceinline__ uint32_t warp_sum_u32(uint32_t v) {
     return v;
 }
 
+// Warp maximum through the integer reduction unit: one REDUX on an order-preserving key instead
+// of five shuffle/max pairs.  v must not be NaN.
+__device__ __forceinline__ uint32_t monotone_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float warp_max_redux(float v) {
+    return from_ordered_key(__reduce_max_sync(0xFFFFFFFFu, monotone_key(v)));
+}
+
+// The kp-th largest (1-based, small kp) of the 32 lane values: take the maximum away kp - 1
+// times (one lane each time, the lowest lane among equals), then the maximum of what is left.
+__device__ __forceinline__ float warp_kth_largest_small(float v, int kp, int lane) {
+    uint32_t key = monotone_key(v);
+    for (int i = 1; i < kp; ++i) {
+        const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, key);
+        const uint32_t holders = __ballot_sync(0xFFFFFFFFu, key == top);
+        if (lane == __ffs(holders) - 1) key = 0;
+    }
+    return from_ordered_key(__reduce_max_sync(0xFFFFFFFFu, key));
+}
+
 // The kp-th largest (1-based) of the 32 lane values: a bitonic sort across the lanes, largest
 // in lane 0, then a broadcast.
 __device__ __forceinline__ float warp_kth_largest(float v, int kp, int lane) {

@@ -73,24 +73,23 @@ __device__ __forceinline__ bool barrier_wait_bounded(uint64_t* bar, uint32_t par
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        __nanosleep(tries < 16 ? 64 : 256);
+        __nanosleep(tries < 64 ? 100 : 400);
     }
     return false;
 }
 
 // Sets, in a bitmap with one bit per logit of this part, the columns that `ids` names.
 __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int64_t end, const ScanParams& p,
-                                         uint32_t misalign, int v0, int v1, uint32_t* bitmap) {
+                                         int first_pos, int part_logits, uint32_t* bitmap) {
+    // first_pos: position of this part's first slot in the row's aligned window, minus the
+    // row's misalignment, i.e. the (possibly negative) local column of data[0].
     for (int64_t i = begin + threadIdx.x; i < end; i += kScanThreads) {
         const int64_t id = ids[i];
-        if (id < 0 || id >= p.vocab) continue;  // src/generation.cpp:62: ids outside the vocabulary are ignored
-        const int64_t col = id - p.col_begin;
-        if (col < 0 || col >= p.cols) continue;
-        const int64_t pos = col + misalign;  // position in the row's aligned window
-        const int64_t v = pos >> 2;
-        if (v < v0 || v >= v1) continue;
-        const uint32_t e = (uint32_t)(pos - (int64_t)v0 * 4);  // position in this part
-        atomicOr(&bitmap[e >> 5], 1u << (e & 31));
+        if ((uint64_t)id >= (uint64_t)p.vocab) continue;  // src/generation.cpp:62: ids outside the vocabulary are ignored
+        const uint64_t col = (uint64_t)(id - p.col_begin);
+        if (col >= (uint64_t)p.cols) continue;             // not in this GPU's columns
+        const uint32_t e = (uint32_t)((int)col - first_pos);  // slot in this part, if below part_logits
+        if (e < (uint32_t)part_logits) atomicOr(&bitmap[e >> 5], 1u << (e & 31));
     }
 }
 
@@ -103,7 +102,9 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const float4* data4 = reinterpret_cast<const float4*>(dyn_smem);
 
     __shared__ __align__(8) uint64_t s_bar;
-    __shared__ uint32_t s_pen[kBitmapWords], s_ban[kBitmapWords];
+    __shared__ __align__(16) uint32_t s_bits[2 * kBitmapWords];
+    uint32_t* const s_pen = s_bits;
+    uint32_t* const s_ban = s_bits + kBitmapWords;
     __shared__ float s_wraw[kScanWarps], s_wamax[kScanWarps], s_wymax[kScanWarps], s_wthr[kScanWarps];
     __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
     __shared__ uint32_t s_wfill[kScanWarps];
@@ -135,10 +136,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
 
     // ---- start the copy, and build the history bitmaps while it is in flight ----------------------
     if (tid == 0) barrier_init(&s_bar, 1);
-    for (int w = tid; w < kBitmapWords; w += kScanThreads) {
-        s_pen[w] = 0;
-        s_ban[w] = 0;
-    }
+    static_assert(2 * kBitmapWords == 4 * kScanThreads, "one 16-byte store per thread clears both bitmaps");
+    reinterpret_cast<uint4*>(s_bits)[tid] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     if (tid == 0) {
         const uint32_t bytes = (uint32_t)nvec * 16u;
@@ -149,11 +148,14 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         }
     }
     const bool use_flags = p.apply_penalty || p.num_banned > 0;
-    if (p.apply_penalty) {
-        mark_ids(p.history_ids, p.history_offsets[row], p.history_offsets[row + 1], p, misalign, v0, v1, s_pen);
+    const int first_pos = v0 * 4 - (int)misalign;
+    if (p.apply_penalty && !(p.debug_skip & 16)) {
+        mark_ids(p.history_ids, p.history_offsets[row], p.history_offsets[row + 1], p, first_pos, nvec * 4, s_pen);
     }
-    if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, misalign, v0, v1, s_ban);
-    const bool landed = barrier_wait_bounded(&s_bar, 0);
+    if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, first_pos, nvec * 4, s_ban);
+    // One warp watches the copy; the others sleep in the block barrier, which also orders the
+    // copied bytes before everybody's reads.
+    const bool landed = warp == 0 ? barrier_wait_bounded(&s_bar, 0) : true;
     if (!__syncthreads_and(landed ? 1 : 0)) {
         // The copy did not complete in time: report it, give it one more bounded chance to drain
         // (shared memory must not be handed to the next CTA under a copy in flight), and leave.
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             s.nonfinite = 2; s.alive_tail = 0; s.overflow = 0;
             p.stats[part_index] = s;
         }
-        barrier_wait_bounded(&s_bar, 0);
+        if (warp == 0) barrier_wait_bounded(&s_bar, 0);
         return;
     }
 
@@ -181,8 +183,9 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     // ---- 1. flagged logits: handed on in bitmap order, then blanked ---------------------------------
     uint2* seg_out = p.candidates + seg * kSegCap;
     uint32_t seg_fill = 0;  // warp-uniform
+    const int col_base = (int)((int64_t)v0 * 4 - misalign + p.col_begin);  // global column of data[0]; fits 31 bits
     float f_raw = kPad, f_amax = 0.0f, f_y = -INFINITY;
-    if (use_flags) {
+    if (use_flags && !(p.debug_skip & 1)) {
         // A warp takes the bitmap words of the logits its own threads own in the dense passes
         // (vector v belongs to thread v % 256), so a row that is handed on whole fills every
         // warp's segment with exactly its own 128 logits per 256 vectors.
@@ -193,14 +196,22 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             const uint32_t banned_bits = s_ban[word];
             uint32_t bits = s_pen[word] | banned_bits;
             const uint32_t count = __popc(bits);
-            uint32_t incl = count;
+            const uint32_t voters = __ballot_sync(0xFFFFFFFFu, count != 0);
+            if (voters == 0) continue;
+            // Slots in lane order.  Usually a lane flags one logit; otherwise scan the counts.
+            uint32_t slot = seg_fill + __popc(voters & ((1u << lane) - 1u));
+            uint32_t total = __popc(voters);
+            if (__ballot_sync(0xFFFFFFFFu, count > 1) != 0) {
+                uint32_t incl = count;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += up;
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                slot = seg_fill + incl - count;
+                total = __shfl_sync(0xFFFFFFFFu, incl, 31);
             }
-            uint32_t slot = seg_fill + incl - count;
-            seg_fill += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            seg_fill += total;
             while (bits) {
                 const int b = __ffs(bits) - 1;
                 bits &= bits - 1;
@@ -212,8 +223,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
                 f_amax = (l != l) ? INFINITY : fmaxf(f_amax, fabsf(l));
                 f_y = fmaxf(f_y, y);
                 if (slot < (uint32_t)kSegCap) {
-                    const int64_t col = (int64_t)v0 * 4 + e - misalign + p.col_begin;
-                    seg_out[slot] = make_uint2(__float_as_uint(l), (uint32_t)col | (banned ? kFlagBanned : kFlagPenalized));
+                    seg_out[slot] = make_uint2(__float_as_uint(l),
+                                               (uint32_t)(col_base + (int)e) | (banned ? kFlagBanned : kFlagPenalized));
                 }
                 ++slot;
                 data[e] = kPad;
@@ -224,7 +235,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
 
     // ---- 2. per-thread maxima, then the part's raw max and selection threshold -------------------------
     float m = kPad, amax = f_amax;
-    {
+    if (!(p.debug_skip & 8)) {
         int v = tid;
         for (; v + kScanThreads < nvec; v += 2 * kScanThreads) {  // two independent loads per trip
             const float4 d0 = data4[v], d1 = data4[v + kScanThreads];
@@ -243,9 +254,10 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     int kp = 33;  // > 32: no threshold, hand everything on
     if (full_warps > 0) kp = (p.k_need + full_warps - 1) / full_warps;
     {
-        const float wraw = warp_max(fmaxf(m, f_raw)), wamax = warp_max(amax), wymax = warp_max(fmaxf(m_alive, f_y));
+        const float wraw = warp_max_redux(fmaxf(m, f_raw)), wamax = warp_max_redux(amax);
+        const float wymax = warp_max_redux(fmaxf(m_alive, f_y));
         float wthr = -INFINITY;
-        if (kp == 1) wthr = warp_max(m_alive);
+        if (kp <= 8) wthr = warp_kth_largest_small(m_alive, kp, lane);
         else if (kp <= 32) wthr = warp_kth_largest(m_alive, kp, lane);
         if (lane == 0) {
             s_wraw[warp] = wraw;
@@ -273,11 +285,11 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const float pc_l2 = __fmul_rn(cymax, p.log2e_over_t);
     const float pc_res = __fmaf_rn(cymax, p.log2e_over_t, -pc_l2);
     const bool second_exp = kNucleus && p.apply_temperature != 0;
-    double tail = 0.0, proc = 0.0;
+    // Per-lane float sums of at most 16 four-element sums each; they go to double in the reduction.
+    float tail = 0.0f, proc = 0.0f;
     const uint32_t lanes_below = (1u << lane) - 1u;
-    const int64_t col0 = (int64_t)v0 * 4 - misalign + p.col_begin;  // global column of data[0]
 
-    for (int base = warp * 32; base < nvec; base += kScanThreads) {
+    for (int base = warp * 32; base < nvec && !(p.debug_skip & 4); base += kScanThreads) {
         const int v = base + lane;
         const float4 d = v < nvec ? data4[v] : make_float4(kPad, kPad, kPad, kPad);
         float x0 = __fmaf_rn(d.x, kLog2e, -c_l2), x1 = __fmaf_rn(d.y, kLog2e, -c_l2);
@@ -297,7 +309,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         // One vote per trip: which lanes hold a vector that reaches the threshold at all.
         const bool any_here = fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime;
         const uint32_t votes = __ballot_sync(0xFFFFFFFFu, any_here);
-        if (votes != 0) {
+        if (votes != 0 && !(p.debug_skip & 2)) {
             const float l[4] = {d.x, d.y, d.z, d.w};
             uint32_t mine = 0;  // which of my four components are handed on
             if (any_here) {
@@ -325,20 +337,20 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             for (int c = 0; c < 4; ++c) {
                 if (mine & (1u << c)) {
                     if (slot < (uint32_t)kSegCap) {
-                        seg_out[slot] = make_uint2(__float_as_uint(l[c]), (uint32_t)(col0 + (int64_t)v * 4 + c));
+                        seg_out[slot] = make_uint2(__float_as_uint(l[c]), (uint32_t)(col_base + v * 4 + c));
                     }
                     ++slot;
                 }
             }
             seg_fill += total;
         }
-        tail += (double)((e0 + e1) + (e2 + e3));
-        if (second_exp) proc += (double)((q0 + q1) + (q2 + q3));
+        tail += (e0 + e1) + (e2 + e3);
+        if (second_exp) proc += (q0 + q1) + (q2 + q3);
     }
 
     // ---- block reduction in a fixed order, then the part's record ---------------------------------------
     {
-        const double wt = warp_sum(tail), wp = warp_sum(proc);
+        const double wt = warp_sum((double)tail), wp = second_exp ? warp_sum((double)proc) : 0.0;
         if (lane == 0) {
             s_wtail[warp] = wt;
             s_wproc[warp] = wp;

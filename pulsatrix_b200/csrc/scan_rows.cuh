@@ -25,6 +25,7 @@ struct ScanParams {
     int32_t k_need;                  // every part hands on at least this many logits (or all it has)
     int32_t parts;                   // CTAs per row
     int32_t vecs_per_part;           // float4 vectors per part, <= kPartVecs
+    int32_t debug_skip;              // profiling only: bit mask of kernel stages to leave out (results are then wrong)
     // output
     PartStats* stats;                // rows * parts
     uint32_t* seg_counts;            // rows * parts * kScanWarps
