@@ -532,6 +532,8 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
     pp.temperature = config->temperature;
     pp.penalty = config->repetition_penalty;
     pp.capacity = psx::shard_record_capacity(sample, config->top_k);
+    pp.do_sample = sample ? 1 : 0;
+    pp.top_k = sample ? (int32_t)std::min<int64_t>(config->top_k, 1 << 20) : 0;
     pp.records = records;
     PSX_CUDA(psx::launch_pack_records(pp, stream));
     ++ctx->launches;

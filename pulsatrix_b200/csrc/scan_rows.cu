@@ -93,6 +93,13 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
     }
 }
 
+constexpr int kPool = 8;  // per-thread maxima a warp can offer to the pooled threshold
+
+// What warp 0 works out for the part after pass one and every thread needs in pass two.
+struct PartConstants {
+    float cmax, cymax, camax, thr, tprime, c_l2, c_res, pc_l2, pc_res;
+};
+
 }  // namespace
 
 template <bool kNucleus>
@@ -106,6 +113,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     uint32_t* const s_pen = s_bits;
     uint32_t* const s_ban = s_bits + kBitmapWords;
     __shared__ float s_wraw[kScanWarps], s_wamax[kScanWarps], s_wymax[kScanWarps], s_wthr[kScanWarps];
+    __shared__ uint32_t s_pool[kScanWarps * kPool];
+    __shared__ PartConstants s_const;
     __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
     __shared__ uint32_t s_wfill[kScanWarps];
 
@@ -250,15 +259,29 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     }
     const float m_alive = (m == kPad) ? -INFINITY : m;  // a thread without logits takes no part in the selection
     const int live_threads = min(kScanThreads, nvec);
-    const int full_warps = live_threads >> 5;
+    const int full_warps = live_threads >> 5;  // warps whose every thread owns a vector
     int kp = 33;  // > 32: no threshold, hand everything on
     if (full_warps > 0) kp = (p.k_need + full_warps - 1) / full_warps;
+    // Threshold: every full warp offers its kp largest per-thread maxima; the k_need-th largest
+    // of that pool (at least k_need values) is reached by at least k_need logits.  For kp <= 8
+    // the pool is kept and the surplus (fewer than 8 values) is taken away from the bottom;
+    // beyond that each warp offers only its kp-th largest and the smallest of those is used.
+    const bool pooled = kp <= kPool;
     {
         const float wraw = warp_max_redux(fmaxf(m, f_raw)), wamax = warp_max_redux(amax);
         const float wymax = warp_max_redux(fmaxf(m_alive, f_y));
         float wthr = -INFINITY;
-        if (kp <= 8) wthr = warp_kth_largest_small(m_alive, kp, lane);
-        else if (kp <= 32) wthr = warp_kth_largest(m_alive, kp, lane);
+        if (pooled) {
+            uint32_t key = monotone_key(m_alive);
+            for (int i = 0; i < kp; ++i) {  // the warp's kp largest, in descending order
+                const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, key);
+                if (lane == 0) s_pool[warp * kPool + i] = top;
+                const uint32_t holders = __ballot_sync(0xFFFFFFFFu, key == top);
+                if (lane == __ffs(holders) - 1) key = 0;
+            }
+        } else if (kp <= 32) {
+            wthr = warp_kth_largest(m_alive, kp, lane);
+        }
         if (lane == 0) {
             s_wraw[warp] = wraw;
             s_wamax[warp] = wamax;
@@ -267,23 +290,52 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         }
     }
     __syncthreads();
-    float cmax = kPad, camax = 0.0f, cymax = -INFINITY, thr = INFINITY;
-#pragma unroll
-    for (int w = 0; w < kScanWarps; ++w) {
-        cmax = fmaxf(cmax, s_wraw[w]);
-        camax = fmaxf(camax, s_wamax[w]);
-        cymax = fmaxf(cymax, s_wymax[w]);
-        if (w < full_warps) thr = fminf(thr, s_wthr[w]);
+
+    // ---- warp 0 joins the warps and works out the part's constants ----------------------------------
+    if (warp == 0) {
+        const float cmax = warp_max_redux(lane < kScanWarps ? s_wraw[lane] : kPad);
+        const float camax = warp_max_redux(lane < kScanWarps ? s_wamax[lane] : 0.0f);
+        const float cymax = warp_max_redux(lane < kScanWarps ? s_wymax[lane] : -INFINITY);
+        float thr = -INFINITY;
+        if (pooled) {
+            // Lane L holds pool entries L and L + 32 (absent: all ones); drop the smallest
+            // entries until k_need are left, whose minimum is the threshold.
+            const int entries = full_warps * kp;
+            const int i0 = lane, i1 = lane + 32;
+            uint32_t a = i0 < entries ? s_pool[(i0 / kp) * kPool + i0 % kp] : 0xFFFFFFFFu;
+            uint32_t b2 = i1 < entries ? s_pool[(i1 / kp) * kPool + i1 % kp] : 0xFFFFFFFFu;
+            for (int i = p.k_need; i < entries; ++i) {
+                const uint32_t mine = min(a, b2);
+                const uint32_t low = __reduce_min_sync(0xFFFFFFFFu, mine);
+                const uint32_t holders = __ballot_sync(0xFFFFFFFFu, mine == low);
+                if (lane == __ffs(holders) - 1) {
+                    if (a == low) a = 0xFFFFFFFFu; else b2 = 0xFFFFFFFFu;
+                }
+            }
+            thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, min(a, b2)));
+        } else if (full_warps > 0 && kp <= 32) {
+            const uint32_t key = lane < full_warps ? monotone_key(s_wthr[lane]) : 0xFFFFFFFFu;
+            thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, key));
+        }
+        if (lane == 0) {
+            PartConstants c;
+            c.cmax = cmax;
+            c.cymax = cymax;
+            c.camax = camax;
+            c.thr = thr;
+            // Blanked slots hold kPad and must never pass: the threshold stays one step above it.
+            c.tprime = fmaxf(relax_threshold(thr, p.apply_temperature != 0, p.temperature), -3.4028233e38f);
+            c.c_l2 = __fmul_rn(cmax, kLog2e);
+            c.c_res = __fmaf_rn(cmax, kLog2e, -c.c_l2);  // cmax*kLog2e = c_l2 + c_res exactly
+            c.pc_l2 = __fmul_rn(cymax, p.log2e_over_t);
+            c.pc_res = __fmaf_rn(cymax, p.log2e_over_t, -c.pc_l2);
+            s_const = c;
+        }
     }
-    if (full_warps == 0 || kp > 32) thr = -INFINITY;
-    // Blanked slots hold kPad and must never pass: the threshold stays one step above it.
-    const float tprime = fmaxf(relax_threshold(thr, p.apply_temperature != 0, p.temperature), -3.4028233e38f);
+    __syncthreads();
+    const float tprime = s_const.tprime, c_l2 = s_const.c_l2, pc_l2 = s_const.pc_l2;
 
     // ---- 3. exp-sum of what stays behind, hand-off of what reaches the threshold -------------------------
-    const float c_l2 = __fmul_rn(cmax, kLog2e);
-    const float c_res = __fmaf_rn(cmax, kLog2e, -c_l2);  // cmax*kLog2e = c_l2 + c_res exactly
-    const float pc_l2 = __fmul_rn(cymax, p.log2e_over_t);
-    const float pc_res = __fmaf_rn(cymax, p.log2e_over_t, -pc_l2);
     const bool second_exp = kNucleus && p.apply_temperature != 0;
     // Per-lane float sums of at most 16 four-element sums each; they go to double in the reduction.
     float tail = 0.0f, proc = 0.0f;
@@ -360,6 +412,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     }
     __syncthreads();
     if (tid == 0) {
+        const float cmax = s_const.cmax, cymax = s_const.cymax, camax = s_const.camax, thr = s_const.thr;
+        const float c_res = s_const.c_res, pc_res = s_const.pc_res;
         double t = 0.0, q = 0.0;
         uint32_t handed_on = 0, over = 0;
 #pragma unroll

@@ -9,7 +9,54 @@ namespace psx {
 
 namespace {
 
+constexpr int kPackKeys = 4096;  // candidates of one row the exact local selection can look at
+
+// The k-th largest (1-based, k <= m) of m keys in shared memory, by one warp: four 8-bit radix
+// passes, most significant digit first.
+__device__ uint32_t warp_select_kth(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, int lane) {
+    uint32_t prefix = 0, mask = 0, remaining = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int b = lane; b < 256; b += 32) hist[b] = 0;
+        __syncwarp();
+        for (int i = lane; i < m; i += 32) {
+            const uint32_t key = keys[i];
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncwarp();
+        uint32_t local = 0;  // lane L owns digits 255-8L down to 248-8L
+        for (int b = 0; b < 8; ++b) local += hist[255 - 8 * lane - b];
+        uint32_t incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const uint32_t excl = incl - local;
+        const bool here = excl < remaining && remaining <= incl;
+        uint32_t digit = 0, above = 0;
+        if (here) {
+            above = excl;
+            int d = 255 - 8 * lane;
+            for (int b = 0; b < 8; ++b, --d) {
+                if (above + hist[d] >= remaining) break;
+                above += hist[d];
+            }
+            digit = (uint32_t)d;
+        }
+        const int owner = __ffs(__ballot_sync(0xFFFFFFFFu, here)) - 1;
+        digit = __shfl_sync(0xFFFFFFFFu, digit, owner);
+        above = __shfl_sync(0xFFFFFFFFu, above, owner);
+        prefix |= digit << shift;
+        remaining -= above;
+        mask |= 255u << shift;
+        __syncwarp();
+    }
+    return prefix;
+}
+
 __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
+    __shared__ uint32_t s_keys[kPackKeys];
+    __shared__ uint32_t s_hist[256];
     const int64_t row = blockIdx.x;
     const int lane = threadIdx.x;
     const bool apply_t = p.apply_temperature != 0;
@@ -32,8 +79,34 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
     nonfinite = __any_sync(0xFFFFFFFFu, nonfinite != 0) ? 1u : 0u;
     overflow = __any_sync(0xFFFFFFFFu, overflow != 0) ? 1u : 0u;
     alive_tail = warp_sum_u32(alive_tail);
-    const float keep_from = relax_threshold(thr, apply_t, p.temperature);
+    float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
+    const int nseg = p.parts * kScanWarps;
+    const uint32_t* seg_counts = p.seg_counts + row * nseg;
+    const uint2* cands = p.candidates + (size_t)row * nseg * kSegCap;
+
+    // The shard's own k-th largest processed value is a lower bound on the row's: nothing below
+    // it (after the temperature divide's ties) can survive the merged top-k, so it need not travel.
+    if (p.top_k > 0) {
+        int m = 0;  // warp-uniform
+        for (int s = 0; s < nseg; ++s) {
+            const int cnt = min((int)seg_counts[s], kSegCap);
+            for (int i = lane; i < cnt; i += 32) {
+                if (m + i < kPackKeys) {
+                    const uint2 c = cands[(size_t)s * kSegCap + i];
+                    s_keys[m + i] = ordered_key(processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty));
+                }
+            }
+            m += cnt;
+        }
+        __syncwarp();
+        if (m <= kPackKeys && m > p.top_k) {
+            const uint32_t kth = warp_select_kth(s_keys, m, (uint32_t)p.top_k, s_hist, lane);
+            keep_from = fmaxf(keep_from, relax_threshold(from_ordered_key(kth), apply_t, p.temperature));
+        }
+    } else if (!p.do_sample) {
+        keep_from = fmaxf(y_max, -FLT_MAX);  // greedy: the maximum and its ties
+    }
 
     double raw_tail = 0.0, proc_tail = 0.0;
     for (int i = lane; i < p.parts; i += 32) {
@@ -46,9 +119,6 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
 
     char* record = static_cast<char*>(p.records) + row * (int64_t)shard_record_bytes(p.capacity);
     uint2* out = reinterpret_cast<uint2*>(record + kRecordCandidatesOffset);
-    const int nseg = p.parts * kScanWarps;
-    const uint32_t* seg_counts = p.seg_counts + row * nseg;
-    const uint2* cands = p.candidates + (size_t)row * nseg * kSegCap;
     uint32_t kept = 0, dropped = 0;  // warp-uniform
     for (int s = 0; s < nseg; ++s) {
         const int cnt = min((int)seg_counts[s], kSegCap);

@@ -34,6 +34,8 @@ struct PackParams {
     float temperature;
     float penalty;
     int32_t capacity;
+    int32_t do_sample;
+    int32_t top_k;               // > 0: the top-k filter is on (sampling); 0: greedy
     void* records;               // rows * shard_record_bytes(capacity)
 };
 

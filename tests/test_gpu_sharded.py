@@ -1,0 +1,71 @@
+"""The vocabulary-sharded entry points on one GPU: the eight column shards of workload C5 are
+scanned one after another into the buffer an all-gather would fill, then merged; the result must
+equal the reference fixture (and therefore the unsharded path) bit for bit.  The collective itself
+is covered by tests/test_sharding_cpu.py (gloo) and by the multi-GPU benchmark."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import gpu_harness as gh
+import oracle_lib as ol
+import pulsatrix_b200 as psx
+import workload_rows
+from pulsatrix_b200.sharded import gathered_layout, shard_bounds
+from pulsatrix_b200.workloads import WORKLOADS
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def run_sharded(logits, hist_flat, offsets, cfg, uniforms, world):
+    import torch
+    rows, vocab = logits.shape
+    ctx = gh.ctx()
+    config = gh.psx_config(cfg)
+    record = ctx.shard_record_bytes(config)
+    layout, per = gathered_layout(rows, record, world)
+    gathered = torch.zeros(world * per, dtype=torch.uint8, device="cuda")
+    d_logits = torch.from_numpy(logits).cuda()
+    d_hist = torch.from_numpy(hist_flat).cuda()
+    d_off = torch.from_numpy(offsets).cuda()
+    for s in range(world):
+        begin, cols = shard_bounds(vocab, world, s)
+        shard = d_logits[:, begin: begin + cols]  # a strided view: row stride stays the full vocabulary
+        ctx.shard_scan(shard, begin, vocab, d_hist, d_off, config, gathered[layout[s]: layout[s] + per])
+    d_u = torch.from_numpy(uniforms).cuda() if uniforms is not None else None
+    out = ctx.shard_merge(gathered, world, rows, vocab, config, d_u)
+    torch.cuda.synchronize()
+    return out["tokens"].cpu().numpy(), out["log_probs"].cpu().numpy(), out["status"].cpu().numpy()
+
+
+def test_c5_in_eight_shards_matches_the_reference_fixture():
+    w = WORKLOADS["c5"]
+    gold = np.load(GOLDEN / "workload_c5.npz")
+    cfg = workload_rows.config_of(w)
+    ids = np.arange(0, 96)
+    logits, hist, offsets, seeds = workload_rows.build("c5", ids)
+    tokens, logp, status = run_sharded(logits, hist.ravel(), offsets, cfg, psx.uniforms_mt19937_64(seeds), w.shards)
+    assert (status == 0).all(), status
+    assert tokens.tolist() == gold["token"][ids].tolist()
+    assert (np.abs(logp - gold["log_prob"][ids]) <= 1e-5 * np.abs(gold["log_prob"][ids]) + 1e-9).all()
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_sharded_equals_unsharded_for_greedy_and_top_k(world):
+    rng = np.random.RandomState(world)
+    rows, vocab, hlen = 24, 50000, 100
+    logits = (rng.randn(rows, vocab) * 3).astype(np.float32)
+    logits[5, [11, 20000, 49999]] = logits[5].max() + 2.0  # ties across shards: lowest column wins
+    hist = rng.randint(0, vocab, size=(rows, hlen)).astype(np.int64)
+    offsets = np.arange(rows + 1, dtype=np.int64) * hlen
+    seeds = np.arange(rows, dtype=np.uint64) + 100
+    u = psx.uniforms_mt19937_64(seeds)
+    for cfg in (ol.make_config(max_new_tokens=1, repetition_penalty=1.3),
+                ol.make_config(max_new_tokens=1, do_sample=True, top_k=40, top_p=0.9, temperature=0.8,
+                               repetition_penalty=1.1)):
+        want = ol.rows("oracle", logits, hist.ravel(), offsets, cfg, seeds)
+        tokens, logp, status = run_sharded(logits, hist.ravel(), offsets, cfg, u, world)
+        assert (status == 0).all()
+        assert tokens.tolist() == want["token"].tolist()
+        assert (np.abs(logp - want["log_prob"]) <= 1e-5 * np.abs(want["log_prob"]) + 1e-9).all()

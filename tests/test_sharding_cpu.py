@@ -1,0 +1,74 @@
+"""Host-side logic of the multi-GPU paths on CPU: the column partition, and, with two gloo
+ranks, that an all-gather of per-rank records lands shard-major as the survivor stage reads it
+and that the row split of the benchmark covers every row once."""
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+
+from pulsatrix_b200.sharded import gathered_layout, shard_bounds
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("vocab,world", [(262144, 8), (151936, 8), (49152, 4), (1001, 3), (7, 8), (128256, 2)])
+def test_shards_tile_the_vocabulary(vocab, world):
+    covered = 0
+    for rank in range(world):
+        begin, cols = shard_bounds(vocab, world, rank)
+        assert begin == covered or cols == 0
+        assert begin % 4 == 0 or cols == 0
+        covered = begin + cols
+    assert covered == vocab
+    with pytest.raises(ValueError):
+        shard_bounds(vocab, world, world)
+
+
+def test_gathered_layout_is_shard_major():
+    offsets, per = gathered_layout(rows=512, record_bytes=1072, world=8)
+    assert per == 512 * 1072 and offsets == [s * per for s in range(8)]
+
+
+WORKER = textwrap.dedent("""
+    import os, sys
+    import torch, torch.distributed as dist
+    sys.path.insert(0, sys.argv[1])
+    from pulsatrix_b200.sharded import gathered_layout, shard_bounds
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    rows, record = 6, 40
+    mine = torch.full((rows * record,), rank + 1, dtype=torch.uint8)
+    mine[::record] = torch.arange(rows, dtype=torch.uint8)           # first byte of each record: its row
+    gathered = torch.empty(world * rows * record, dtype=torch.uint8)
+    dist.all_gather_into_tensor(gathered, mine)
+    offsets, per = gathered_layout(rows, record, world)
+    for s in range(world):
+        block = gathered[offsets[s]: offsets[s] + per].view(rows, record)
+        assert (block[:, 0] == torch.arange(rows, dtype=torch.uint8)).all()
+        assert (block[:, 1:] == s + 1).all()
+    # row split: contiguous blocks, every row exactly once
+    total = 13
+    lo, hi = rank * total // world, (rank + 1) * total // world
+    seen = torch.zeros(total, dtype=torch.int32); seen[lo:hi] += 1
+    dist.all_reduce(seen)
+    assert (seen == 1).all()
+    begin, cols = shard_bounds(1000, world, rank)
+    width = torch.tensor([cols]); dist.all_reduce(width)
+    assert int(width) == 1000
+    dist.destroy_process_group()
+    print("ok", rank)
+""")
+
+
+def test_two_gloo_ranks_gather_records_shard_major(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    proc = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29671", str(script), str(ROOT)],
+                          capture_output=True, text=True, timeout=240, env=env)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert proc.stdout.count("ok") == 2
