@@ -134,6 +134,22 @@ PSX_API psx_status psx_b200_row_pass_only(psx_ctx* ctx, void* stream, const floa
                                           int64_t vocab, int64_t row_stride, const int64_t* history_ids,
                                           const int64_t* history_offsets, const psx_sampling_config* config);
 
+/* The same step as psx_b200_sample_rows for callers that must not allocate device memory: a
+ * decode loop inside a serving process whose own pool already owns the GPU's memory (a cudaMalloc
+ * from a plug-in would fail or stall), or a latency-critical loop that cannot afford cudaMalloc's
+ * device-wide synchronisation.  It takes no context and calls no cudaMalloc / cudaFree: the
+ * scratch between its two kernels is a fixed array inside the library image on every GPU (about
+ * 8.1 MiB).  Limits: rows * ceil(vocab / 16384) <= 1024 and at most 256 banned EOS ids, else
+ * PSX_ERR_UNSUPPORTED.  The first call on a device looks up that array's address and should come
+ * before any stream capture on that device.  All calls share the array: calls that overlap on
+ * the GPU race, so keep them stream-ordered per device.  Same inputs, outputs and statuses as
+ * psx_b200_sample_rows (no diagnostics).  This entry point has no counterpart in the reference. */
+PSX_API psx_status psx_b200_sample_rows_static(void* stream, const float* logits, int64_t rows, int64_t vocab,
+                                               int64_t row_stride, const int64_t* history_ids,
+                                               const int64_t* history_offsets, const psx_sampling_config* config,
+                                               const double* uniforms, int64_t* tokens, float* log_probs,
+                                               int32_t* row_status);
+
 /* The same step for callers that hold everything on the host, as the reference's
  * NextTokenLogitsFn does (include/pulsatrix/generation.hpp:25): copies inputs to the device,
  * runs psx_b200_sample_rows, copies results back and synchronises.  Returns

@@ -13,7 +13,7 @@ OK, ERR_BAD_ARGUMENT, ERR_CUDA, ERR_ROW_FAILED, ERR_UNSUPPORTED = range(5)
 
 EXPORTS = [
     "psx_b200_version", "psx_b200_last_error", "psx_b200_ctx_create", "psx_b200_ctx_destroy", "psx_b200_ctx_stream",
-    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only",
+    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_top_k_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
@@ -94,6 +94,7 @@ def library():
         lib.psx_b200_ctx_read_timing.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         ptr, i64 = C.c_void_p, C.c_int64
         lib.psx_b200_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_sample_rows_static.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_row_pass_only.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr]
         lib.psx_b200_sample_rows_host.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_scan.argtypes = [ptr, ptr, ptr, i64, i64, i64, i64, i64, ptr, ptr, ptr, ptr]
@@ -127,6 +128,22 @@ def uniforms_portable(seeds) -> np.ndarray:
 
 def _dptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def sample_rows_static(logits, history_ids, history_offsets, config, uniforms, tokens, log_probs, status, stream=None,
+                       vocab=None):
+    """psx_b200_sample_rows_static: the sampling step without a context and without any device
+    allocation (its scratch is a fixed array inside the library).  All tensors are the caller's:
+    cuda inputs as for Context.sample_rows, and preallocated cuda outputs tokens (int64),
+    log_probs (float32), status (int32).  Asynchronous on `stream` (default: torch's current)."""
+    rows = logits.shape[0]
+    vocab = logits.shape[1] if vocab is None else vocab
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream(logits.device).cuda_stream
+    _check(library().psx_b200_sample_rows_static(
+        C.c_void_p(stream), _dptr(logits), rows, vocab, logits.stride(0) if rows else vocab, _dptr(history_ids),
+        _dptr(history_offsets), C.addressof(config), _dptr(uniforms), _dptr(tokens), _dptr(log_probs), _dptr(status)))
 
 
 class Context:

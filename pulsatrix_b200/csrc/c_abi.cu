@@ -42,6 +42,11 @@ struct Buffer {
 
 }  // namespace
 
+// For the library's other translation units: record an error where psx_b200_last_error() finds it.
+namespace psx_internal {
+psx_status set_error(psx_status code, const std::string& message) { return fail(code, message); }
+}
+
 struct psx_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
