@@ -148,6 +148,172 @@ __device__ __forceinline__ void block_rank_sort(u64* keys, int n, bool descendin
     __syncthreads();
 }
 
+// Block-wide sum in a fixed order (same result in every thread); scratch holds one double per warp.
+__device__ __forceinline__ double block_sum_fixed(double v, double* scratch) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double r = 0.0;
+#pragma unroll
+    for (int w = 0; w < kMergeThreads / 32; ++w) r += scratch[w];
+    return r;
+}
+
+// Block-wide maximum / minimum of 32-bit keys and minimum of doubles (same result in every thread).
+__device__ __forceinline__ uint32_t block_max_u32(uint32_t v, double* scratch) {
+    v = __reduce_max_sync(0xFFFFFFFFu, v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = (double)v;  // exact: 32-bit integers fit a double
+    __syncthreads();
+    double r = 0.0;
+#pragma unroll
+    for (int w = 0; w < kMergeThreads / 32; ++w) r = fmax(r, scratch[w]);
+    return (uint32_t)r;
+}
+__device__ __forceinline__ uint32_t block_min_u32(uint32_t v, double* scratch) {
+    return ~block_max_u32(~v, scratch);
+}
+__device__ __forceinline__ double block_min_f64(double v, double* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmin(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double r = scratch[0];
+#pragma unroll
+    for (int w = 1; w < kMergeThreads / 32; ++w) r = fmin(r, scratch[w]);
+    return r;
+}
+
+// Steps 3 of the survivor stage for a LONG list (sampling without a top-k: hundreds to thousands
+// of entries), by the whole block and without sorting.  The reference's decisions are threshold
+// decisions on monotone cumulative sums -- the top-p cut along ascending (value, column), the
+// min-p floor, the CDF crossing along ascending column -- so each is found by a bisection whose
+// probes are block-wide masked sums of exp in a fixed order.  Those sums differ from the
+// reference's sequential ones by rounding only (~n * 1e-16), so whenever a decision comes closer
+// than kExactMargin to its boundary the function gives up (returns false) and the caller takes the
+// sorted, sequential replay instead.  keyA: n unsorted keys (ordered value << 32 | ~column);
+// ex[i] = exp(x_i - x_max); alive[i] is set here.
+constexpr double kExactMargin = 1e-9;
+
+__device__ bool decide_wide(const MergeParams& p, const u64* keyA, const double* ex, uint8_t* alive, int n,
+                            bool rest_alive, double rest, double rest_bound, double u, double* scratch,
+                            Decision& out) {
+    const int tid = threadIdx.x;
+    out.status = PSX_ROW_OK;
+    out.token = -1;
+    out.draw_margin = INFINITY;
+    out.top_p_margin = INFINITY;
+    out.survivors = 0;
+    auto masked_sum = [&](auto keep) {
+        double v = 0.0;
+        for (int i = tid; i < n; i += kMergeThreads) {
+            if (keep(i)) v += ex[i];
+        }
+        return block_sum_fixed(v, scratch);
+    };
+    uint32_t top_key = 0;
+    for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
+    top_key = block_max_u32(top_key, scratch);
+    for (int i = tid; i < n; i += kMergeThreads) alive[i] = 1;
+    __syncthreads();
+
+    if (p.top_p < 1.0f) {  // src/generation.cpp:89-103
+        const double limit = 1.0 - (double)p.top_p;
+        const double base = rest_alive ? rest : 0.0;
+        const double sum = base + masked_sum([&](int) { return true; });
+        double margin = INFINITY;
+        if (rest_alive) {
+            const double lead = base / sum;  // everything outside the list leads the ascending walk
+            margin = fabs(lead - limit);
+            if (!(lead <= limit)) { out.status = PSX_ROW_TOO_WIDE; return true; }
+            rest_alive = false;
+        }
+        // Smallest value key whose entries push the cumulative mass past the limit.
+        uint32_t lo = 0, hi = top_key;  // mass up to lo stays within the limit, mass up to hi (all of it) exceeds it
+        if (limit >= 1.0 - 1e-12) return false;
+        while (hi - lo > 1) {
+            const uint32_t mid = lo + (hi - lo) / 2;
+            const double c = (base + masked_sum([&](int i) { return key_ord(keyA[i]) <= mid; })) / sum;
+            if (c <= limit) lo = mid; else hi = mid;
+        }
+        const uint32_t cut = hi;
+        const double below = (base + masked_sum([&](int i) { return key_ord(keyA[i]) < cut; })) / sum;
+        margin = fmin(margin, fabs(below - limit));
+        // Entries equal to the cut value go in ascending column order, one probability each.
+        double ties = 0.0;
+        for (int i = tid; i < n; i += kMergeThreads) ties += key_ord(keyA[i]) == cut ? 1.0 : 0.0;
+        const int group = (int)block_sum_fixed(ties, scratch);
+        const double each = exp((double)from_ordered_key(cut) - (double)from_ordered_key(top_key)) / sum;
+        double cumulative = below;
+        int removed = 0;
+        for (int j = 0; j < group; ++j) {
+            cumulative += each;
+            margin = fmin(margin, fabs(cumulative - limit));
+            if (cumulative <= limit) ++removed; else break;
+        }
+        if (cut == top_key && removed >= group) removed = group - 1;  // the last of the walk always stays
+        out.top_p_margin = margin;
+        if (margin < kExactMargin) return false;
+        for (int i = tid; i < n; i += kMergeThreads) {
+            const uint32_t k = key_ord(keyA[i]);
+            if (k < cut) {
+                alive[i] = 0;
+            } else if (k == cut && removed > 0) {
+                const uint32_t col = key_col(keyA[i]);
+                int before = 0;  // ties with a lower column
+                for (int j = 0; j < n; ++j) before += (key_ord(keyA[j]) == cut && key_col(keyA[j]) < col) ? 1 : 0;
+                if (before < removed) alive[i] = 0;
+            }
+        }
+        __syncthreads();
+    }
+
+    if (p.min_p > 0.0f) {  // src/generation.cpp:104-111
+        const double sum = (rest_alive ? rest : 0.0) + masked_sum([&](int i) { return alive[i] != 0; });
+        const double floor_p = p.min_p * (1.0 / sum);  // the most likely entry has exp(0) = 1
+        uint32_t best = 0xFFFFFFFFu;  // the first maximum: lowest column among the top values
+        for (int i = tid; i < n; i += kMergeThreads) {
+            if (key_ord(keyA[i]) == top_key) best = min(best, key_col(keyA[i]));
+        }
+        best = block_min_u32(best, scratch);
+        double closest = INFINITY;
+        for (int i = tid; i < n; i += kMergeThreads) {
+            if (!alive[i] || (key_ord(keyA[i]) == top_key && key_col(keyA[i]) == best)) continue;
+            const double pr = ex[i] / sum;
+            closest = fmin(closest, fabs(pr - floor_p) / floor_p);
+            if (pr < floor_p) alive[i] = 0;
+        }
+        closest = block_min_f64(closest, scratch);  // its barriers also publish the alive flags
+        if (closest < 1e-12) return false;
+        if (rest_alive) {
+            if (rest_bound / sum < floor_p) rest_alive = false;
+            else { out.status = PSX_ROW_TOO_WIDE; return true; }
+        }
+    }
+
+    double count = 0.0;
+    for (int i = tid; i < n; i += kMergeThreads) count += alive[i] ? 1.0 : 0.0;
+    out.survivors = (int)block_sum_fixed(count, scratch);
+
+    // src/generation.cpp:140-152: the first column whose cumulative probability exceeds u.
+    if (rest_alive) { out.status = PSX_ROW_TOO_WIDE; return true; }
+    const double sum = masked_sum([&](int i) { return alive[i] != 0; });
+    long long lo = -1, hi = p.vocab - 1;  // mass up to column lo is <= u, mass up to column hi (all, 1.0) is > u
+    while (hi - lo > 1) {
+        const long long mid = lo + (hi - lo) / 2;
+        const double f = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) <= mid; }) / sum;
+        if (f > u) hi = mid; else lo = mid;
+    }
+    const double before = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) < hi; }) / sum;
+    const double upto = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) <= hi; }) / sum;
+    out.draw_margin = before == 0.0 ? fabs(u - upto) : fmin(fabs(u - before), fabs(u - upto));
+    if (out.draw_margin < kExactMargin) return false;
+    out.token = hi;
+    return true;
+}
+
 // The k-th largest (1-based, k <= m) of m uint32 keys in shared memory: four 8-bit radix passes,
 // most significant digit first.  hist has 256 entries, state two.  Called by the whole block.
 __device__ uint32_t block_select_kth(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, uint32_t* state) {
@@ -380,6 +546,29 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         return;
     }
 
+    // ---- 3'. a long list without a top-k: decided by the whole block, without sorting --------------
+    bool decided = false;
+    if (p.do_sample && !top_k_on && n > kMergeThreads) {
+        uint32_t top_key = 0;
+        for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
+        top_key = block_max_u32(top_key, s_d[0]);
+        const float x_top = from_ordered_key(top_key);
+        for (int i = tid; i < n; i += kMergeThreads) {
+            ex[i] = exp((double)from_ordered_key(key_ord(keyA[i])) - (double)x_top);  // src/generation.cpp:46
+        }
+        __syncthreads();
+        const bool rest_in_play = (alive_tail + dropped) > 0.0;
+        const double bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_top);
+        Decision wide;
+        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, p.uniforms[row], s_d[0], wide);
+        __syncthreads();
+        if (decided && tid == 0) {
+            s_dec = wide;
+            s_chosen_raw = 0;
+        }
+    }
+
+    if (!decided) {
     // ---- 3. sort by (value desc, column asc); top-k keeps the k-th value and its ties -----------
     if (n <= kMergeThreads) {
         block_rank_sort(keyA, n, /*descending=*/true);
@@ -430,6 +619,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergePa
         decide(p, keyA, keyB, ex, alive, ns, rest_alive, z_rest, rest_bound, u, s_dec);
         s_chosen_raw = 0;
     }
+    }  // !decided
     __syncthreads();
     const Decision dec = s_dec;
     if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
