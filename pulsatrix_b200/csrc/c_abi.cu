@@ -210,6 +210,10 @@ void fill_merge_settings(psx::MergeParams& mp, const psx_sampling_config* c, con
     mp.row_status = row_status;
     mp.diag = diag;
     mp.sort_capacity = plan.sort_capacity;
+    {
+        const char* stop = std::getenv("PSX_B200_DEBUG_MERGE_STOP");  // profiling only
+        mp.debug_stop = stop ? std::atoi(stop) : 0;
+    }
     mp.gather_capacity = plan.gather_capacity;
 }
 
@@ -355,15 +359,6 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     }
     if (psx_status s = configure_merge(ctx, plan, plan.parts * psx::kScanWarps)) return s;
 
-    cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
-    if (ctx->timing) {
-        for (cudaEvent_t& e : marks) PSX_CUDA(cudaEventCreate(&e));
-        PSX_CUDA(cudaEventRecord(marks[0], stream));
-    }
-    PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
-    ++ctx->launches;
-    if (ctx->timing) PSX_CUDA(cudaEventRecord(marks[1], stream));
-
     psx::MergeParams mp{};
     mp.stats = sp.stats;
     mp.seg_counts = sp.seg_counts;
@@ -378,6 +373,15 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     mp.cand_seg_stride = sizeof(uint2) * psx::kSegCap;
     mp.cand_row_stride = mp.cand_seg_stride * plan.parts * psx::kScanWarps;
     fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
+
+    cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
+    if (ctx->timing) {
+        for (cudaEvent_t& e : marks) PSX_CUDA(cudaEventCreate(&e));
+        PSX_CUDA(cudaEventRecord(marks[0], stream));
+    }
+    PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+    ++ctx->launches;
+    if (ctx->timing) PSX_CUDA(cudaEventRecord(marks[1], stream));
     PSX_CUDA(psx::launch_merge_rows(mp, stream));
     ++ctx->launches;
     if (ctx->timing) {

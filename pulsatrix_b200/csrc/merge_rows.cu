@@ -14,631 +14,15 @@
 //   4. writes the token, float(log(exp(l - M) / Z)) of the raw logits (src/generation.cpp:156),
 //      a row status and the distances of the two decisions from their boundaries.
 // Reads a few KB per row; never touches the logits.
-#include "merge_rows.cuh"
-
-#include "../../include/psx_b200.h"
+#include "merge_rows_impl.cuh"
 
 namespace psx {
 
 namespace {
 
-using u64 = unsigned long long;
-
-struct Decision {
-    long long token;
-    int status;
-    int survivors;
-    double draw_margin;
-    double top_p_margin;
-};
-
-__device__ __forceinline__ uint32_t key_ord(u64 k) { return (uint32_t)(k >> 32); }
-__device__ __forceinline__ uint32_t key_col(u64 k) { return ~(uint32_t)k; }
-
-// Step 3, by one thread, in the reference's summation order.  keyA: the ns survivors of top-k by
-// (value desc, column asc); keyB: (column << 32 | position in keyA) ascending; ex[pos] =
-// exp(x'[pos] - x'max).  `rest` is the processed mass (relative to x'max) of everything that is
-// not in keyA and still alive, `rest_bound` an upper bound on any such entry's ex.
-__device__ void decide(const MergeParams& p, const u64* keyA, const u64* keyB, const double* ex, uint8_t* alive,
-                       int ns, bool rest_alive, double rest, double rest_bound, double u, Decision& out) {
-    out.status = PSX_ROW_OK;
-    out.token = -1;
-    out.draw_margin = INFINITY;
-    out.top_p_margin = INFINITY;
-    out.survivors = 0;
-    const bool sample = p.do_sample != 0;
-
-    if (sample && p.top_p < 1.0f) {  // src/generation.cpp:89-103
-        const double limit = 1.0 - (double)p.top_p;
-        double sum = rest_alive ? rest : 0.0;
-        for (int j = 0; j < ns; ++j) sum += ex[(uint32_t)keyB[j]];
-        double cumulative = 0.0;
-        if (rest_alive) {
-            // Everything outside the list is smaller than everything in it, so it leads the
-            // ascending walk; it must fall below the cut as a whole.
-            cumulative = rest / sum;
-            out.top_p_margin = fabs(cumulative - limit);
-            if (!(cumulative <= limit)) { out.status = PSX_ROW_TOO_WIDE; return; }
-            rest_alive = false;
-        }
-        bool crossed = false;
-        int group_end = ns;
-        while (group_end > 0 && !crossed) {
-            const uint32_t ord = key_ord(keyA[group_end - 1]);
-            int group_begin = group_end - 1;
-            while (group_begin > 0 && key_ord(keyA[group_begin - 1]) == ord) --group_begin;
-            for (int pos = group_begin; pos < group_end; ++pos) {  // equal values: lower column first
-                if (group_begin == 0 && pos == group_end - 1) break;  // the last of the walk always stays
-                cumulative += ex[pos] / sum;
-                const double dist = fabs(cumulative - limit);
-                if (dist < out.top_p_margin) out.top_p_margin = dist;
-                if (cumulative <= limit) {
-                    alive[pos] = 0;
-                } else {
-                    crossed = true;
-                    break;
-                }
-            }
-            group_end = group_begin;
-        }
-    }
-
-    if (sample && p.min_p > 0.0f) {  // src/generation.cpp:104-111
-        double sum = rest_alive ? rest : 0.0;
-        for (int j = 0; j < ns; ++j) {
-            const uint32_t pos = (uint32_t)keyB[j];
-            if (alive[pos]) sum += ex[pos];
-        }
-        const double top = ex[0] / sum;  // position 0 is the first maximum and is never removed
-        const double floor_p = p.min_p * top;
-        for (int pos = 1; pos < ns; ++pos) {
-            if (alive[pos] && ex[pos] / sum < floor_p) alive[pos] = 0;
-        }
-        if (rest_alive) {
-            if (rest_bound / sum < floor_p) rest_alive = false;
-            else { out.status = PSX_ROW_TOO_WIDE; return; }
-        }
-    }
-
-    int survivors = 0;
-    for (int pos = 0; pos < ns; ++pos) survivors += alive[pos];
-    out.survivors = survivors;
-
-    long long chosen = key_col(keyA[0]);  // src/generation.cpp:135 first maximum: lower column wins
-    if (sample) {                         // src/generation.cpp:140-152
-        if (rest_alive) { out.status = PSX_ROW_TOO_WIDE; return; }
-        double sum = 0.0;
-        for (int j = 0; j < ns; ++j) {
-            const uint32_t pos = (uint32_t)keyB[j];
-            if (alive[pos]) sum += ex[pos];
-        }
-        double cumulative = 0.0, before = 0.0;
-        for (int j = 0; j < ns; ++j) {
-            const uint32_t pos = (uint32_t)keyB[j];
-            if (!alive[pos]) continue;
-            const double pr = ex[pos] / sum;
-            if (pr == 0.0) continue;
-            before = cumulative;
-            cumulative += pr;
-            chosen = (long long)(keyB[j] >> 32);
-            if (u < cumulative) break;
-        }
-        const double lo = fabs(u - before), hi = fabs(u - cumulative);
-        out.draw_margin = before == 0.0 ? hi : fmin(lo, hi);
-    }
-    out.token = chosen;
-}
-
-// Sorts n <= blockDim.x distinct 64-bit keys in shared memory by counting, one key per thread:
-// a key's place is the number of keys that come before it.  Starts and ends with a barrier.
-__device__ __forceinline__ void block_rank_sort(u64* keys, int n, bool descending) {
-    __syncthreads();
-    const int i = threadIdx.x;
-    u64 mine = 0;
-    int place = 0;
-    if (i < n) {
-        mine = keys[i];
-        for (int j = 0; j < n; ++j) {
-            const u64 other = keys[j];
-            place += (descending ? other > mine : other < mine) ? 1 : 0;
-        }
-    }
-    __syncthreads();
-    if (i < n) keys[place] = mine;
-    __syncthreads();
-}
-
-// Block-wide sum in a fixed order (same result in every thread); scratch holds one double per warp.
-__device__ __forceinline__ double block_sum_fixed(double v, double* scratch) {
-    v = warp_sum(v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    double r = 0.0;
-#pragma unroll
-    for (int w = 0; w < kMergeThreads / 32; ++w) r += scratch[w];
-    return r;
-}
-
-// Block-wide maximum / minimum of 32-bit keys and minimum of doubles (same result in every thread).
-__device__ __forceinline__ uint32_t block_max_u32(uint32_t v, double* scratch) {
-    v = __reduce_max_sync(0xFFFFFFFFu, v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = (double)v;  // exact: 32-bit integers fit a double
-    __syncthreads();
-    double r = 0.0;
-#pragma unroll
-    for (int w = 0; w < kMergeThreads / 32; ++w) r = fmax(r, scratch[w]);
-    return (uint32_t)r;
-}
-__device__ __forceinline__ uint32_t block_min_u32(uint32_t v, double* scratch) {
-    return ~block_max_u32(~v, scratch);
-}
-__device__ __forceinline__ double block_min_f64(double v, double* scratch) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmin(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    double r = scratch[0];
-#pragma unroll
-    for (int w = 1; w < kMergeThreads / 32; ++w) r = fmin(r, scratch[w]);
-    return r;
-}
-
-// Steps 3 of the survivor stage for a LONG list (sampling without a top-k: hundreds to thousands
-// of entries), by the whole block and without sorting.  The reference's decisions are threshold
-// decisions on monotone cumulative sums -- the top-p cut along ascending (value, column), the
-// min-p floor, the CDF crossing along ascending column -- so each is found by a bisection whose
-// probes are block-wide masked sums of exp in a fixed order.  Those sums differ from the
-// reference's sequential ones by rounding only (~n * 1e-16), so whenever a decision comes closer
-// than kExactMargin to its boundary the function gives up (returns false) and the caller takes the
-// sorted, sequential replay instead.  keyA: n unsorted keys (ordered value << 32 | ~column);
-// ex[i] = exp(x_i - x_max); alive[i] is set here.
-constexpr double kExactMargin = 1e-9;
-
-__device__ bool decide_wide(const MergeParams& p, const u64* keyA, const double* ex, uint8_t* alive, int n,
-                            bool rest_alive, double rest, double rest_bound, double u, double* scratch,
-                            Decision& out) {
-    const int tid = threadIdx.x;
-    out.status = PSX_ROW_OK;
-    out.token = -1;
-    out.draw_margin = INFINITY;
-    out.top_p_margin = INFINITY;
-    out.survivors = 0;
-    auto masked_sum = [&](auto keep) {
-        double v = 0.0;
-        for (int i = tid; i < n; i += kMergeThreads) {
-            if (keep(i)) v += ex[i];
-        }
-        return block_sum_fixed(v, scratch);
-    };
-    uint32_t top_key = 0;
-    for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
-    top_key = block_max_u32(top_key, scratch);
-    for (int i = tid; i < n; i += kMergeThreads) alive[i] = 1;
-    __syncthreads();
-
-    if (p.top_p < 1.0f) {  // src/generation.cpp:89-103
-        const double limit = 1.0 - (double)p.top_p;
-        const double base = rest_alive ? rest : 0.0;
-        const double sum = base + masked_sum([&](int) { return true; });
-        double margin = INFINITY;
-        if (rest_alive) {
-            const double lead = base / sum;  // everything outside the list leads the ascending walk
-            margin = fabs(lead - limit);
-            if (!(lead <= limit)) { out.status = PSX_ROW_TOO_WIDE; return true; }
-            rest_alive = false;
-        }
-        // Smallest value key whose entries push the cumulative mass past the limit.
-        uint32_t lo = 0, hi = top_key;  // mass up to lo stays within the limit, mass up to hi (all of it) exceeds it
-        if (limit >= 1.0 - 1e-12) return false;
-        while (hi - lo > 1) {
-            const uint32_t mid = lo + (hi - lo) / 2;
-            const double c = (base + masked_sum([&](int i) { return key_ord(keyA[i]) <= mid; })) / sum;
-            if (c <= limit) lo = mid; else hi = mid;
-        }
-        const uint32_t cut = hi;
-        const double below = (base + masked_sum([&](int i) { return key_ord(keyA[i]) < cut; })) / sum;
-        margin = fmin(margin, fabs(below - limit));
-        // Entries equal to the cut value go in ascending column order, one probability each.
-        double ties = 0.0;
-        for (int i = tid; i < n; i += kMergeThreads) ties += key_ord(keyA[i]) == cut ? 1.0 : 0.0;
-        const int group = (int)block_sum_fixed(ties, scratch);
-        const double each = exp((double)from_ordered_key(cut) - (double)from_ordered_key(top_key)) / sum;
-        double cumulative = below;
-        int removed = 0;
-        for (int j = 0; j < group; ++j) {
-            cumulative += each;
-            margin = fmin(margin, fabs(cumulative - limit));
-            if (cumulative <= limit) ++removed; else break;
-        }
-        if (cut == top_key && removed >= group) removed = group - 1;  // the last of the walk always stays
-        out.top_p_margin = margin;
-        if (margin < kExactMargin) return false;
-        for (int i = tid; i < n; i += kMergeThreads) {
-            const uint32_t k = key_ord(keyA[i]);
-            if (k < cut) {
-                alive[i] = 0;
-            } else if (k == cut && removed > 0) {
-                const uint32_t col = key_col(keyA[i]);
-                int before = 0;  // ties with a lower column
-                for (int j = 0; j < n; ++j) before += (key_ord(keyA[j]) == cut && key_col(keyA[j]) < col) ? 1 : 0;
-                if (before < removed) alive[i] = 0;
-            }
-        }
-        __syncthreads();
-    }
-
-    if (p.min_p > 0.0f) {  // src/generation.cpp:104-111
-        const double sum = (rest_alive ? rest : 0.0) + masked_sum([&](int i) { return alive[i] != 0; });
-        const double floor_p = p.min_p * (1.0 / sum);  // the most likely entry has exp(0) = 1
-        uint32_t best = 0xFFFFFFFFu;  // the first maximum: lowest column among the top values
-        for (int i = tid; i < n; i += kMergeThreads) {
-            if (key_ord(keyA[i]) == top_key) best = min(best, key_col(keyA[i]));
-        }
-        best = block_min_u32(best, scratch);
-        double closest = INFINITY;
-        for (int i = tid; i < n; i += kMergeThreads) {
-            if (!alive[i] || (key_ord(keyA[i]) == top_key && key_col(keyA[i]) == best)) continue;
-            const double pr = ex[i] / sum;
-            closest = fmin(closest, fabs(pr - floor_p) / floor_p);
-            if (pr < floor_p) alive[i] = 0;
-        }
-        closest = block_min_f64(closest, scratch);  // its barriers also publish the alive flags
-        if (closest < 1e-12) return false;
-        if (rest_alive) {
-            if (rest_bound / sum < floor_p) rest_alive = false;
-            else { out.status = PSX_ROW_TOO_WIDE; return true; }
-        }
-    }
-
-    double count = 0.0;
-    for (int i = tid; i < n; i += kMergeThreads) count += alive[i] ? 1.0 : 0.0;
-    out.survivors = (int)block_sum_fixed(count, scratch);
-
-    // src/generation.cpp:140-152: the first column whose cumulative probability exceeds u.
-    if (rest_alive) { out.status = PSX_ROW_TOO_WIDE; return true; }
-    const double sum = masked_sum([&](int i) { return alive[i] != 0; });
-    long long lo = -1, hi = p.vocab - 1;  // mass up to column lo is <= u, mass up to column hi (all, 1.0) is > u
-    while (hi - lo > 1) {
-        const long long mid = lo + (hi - lo) / 2;
-        const double f = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) <= mid; }) / sum;
-        if (f > u) hi = mid; else lo = mid;
-    }
-    const double before = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) < hi; }) / sum;
-    const double upto = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) <= hi; }) / sum;
-    out.draw_margin = before == 0.0 ? fabs(u - upto) : fmin(fabs(u - before), fabs(u - upto));
-    if (out.draw_margin < kExactMargin) return false;
-    out.token = hi;
-    return true;
-}
-
-// The k-th largest (1-based, k <= m) of m uint32 keys in shared memory: four 8-bit radix passes,
-// most significant digit first.  hist has 256 entries, state two.  Called by the whole block.
-__device__ uint32_t block_select_kth(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, uint32_t* state) {
-    const int tid = threadIdx.x, lane = tid & 31;
-    uint32_t prefix = 0, mask = 0, remaining = k;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        hist[tid] = 0;  // kMergeThreads == 256 bins
-        __syncthreads();
-        for (int i = tid; i < m; i += kMergeThreads) {
-            const uint32_t key = keys[i];
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (tid < 32) {
-            // lane L owns digits 255-8L down to 248-8L; find where the count from the top reaches `remaining`
-            uint32_t local = 0;
-            for (int b = 0; b < 8; ++b) local += hist[255 - 8 * lane - b];
-            uint32_t incl = local;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += up;
-            }
-            const uint32_t excl = incl - local;
-            if (excl < remaining && remaining <= incl) {
-                uint32_t above = excl;
-                int digit = 255 - 8 * lane;
-                for (int b = 0; b < 8; ++b, --digit) {
-                    if (above + hist[digit] >= remaining) break;
-                    above += hist[digit];
-                }
-                state[0] = prefix | ((uint32_t)digit << shift);
-                state[1] = remaining - above;
-            }
-        }
-        __syncthreads();
-        prefix = state[0];
-        remaining = state[1];
-        mask |= 255u << shift;
-        __syncthreads();
-    }
-    return prefix;
-}
-
 __global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergeParams p) {
-    extern __shared__ u64 dyn[];
-    const int cap = p.sort_capacity, gcap = p.gather_capacity;
-    const int nseg = p.parts * p.segs_per_part;
-    u64* keyA = dyn;
-    u64* keyB = keyA + cap;
-    double* ex = reinterpret_cast<double*>(keyB + cap);
-    uint8_t* alive = reinterpret_cast<uint8_t*>(ex + cap);
-    uint32_t* cand_l = reinterpret_cast<uint32_t*>(alive + cap);  // raw logit bits of every candidate
-    uint32_t* cand_c = cand_l + gcap;                             // column | flags
-    uint32_t* seg_begin = cand_c + gcap;                          // nseg + 1 exclusive prefix of the counts
-    uint32_t* seg_size = seg_begin + nseg + 1;                    // nseg
-    uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);           // scratch over the (still unused) sort arrays
-
-    __shared__ float s_f[3][kMergeThreads / 32];
-    __shared__ double s_d[3][kMergeThreads / 32];
-    __shared__ uint32_t s_u[kMergeThreads / 32];
-    __shared__ int s_count;
-    __shared__ int s_ns;
-    __shared__ uint32_t s_chosen_raw;
-    __shared__ Decision s_dec;
-    __shared__ uint32_t s_hist[256];
-    __shared__ uint32_t s_state[2];
-
-    const int64_t row = blockIdx.x;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool apply_t = p.apply_temperature != 0;
-    const char* stats_row = static_cast<const char*>(p.stats) + row * p.stats_row_stride;
-    const char* counts_row = static_cast<const char*>(p.seg_counts) + row * p.count_row_stride;
-    const char* cands_row = static_cast<const char*>(p.candidates) + row * p.cand_row_stride;
-    auto part_stats = [&](int i) { return *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride); };
-
-    // ---- 1. join the parts; lay the candidate segments out back to back ---------------------------
-    float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
-    double bad = 0.0, alive_tail = 0.0;
-    for (int i = tid; i < p.parts; i += kMergeThreads) {
-        const PartStats s = part_stats(i);
-        raw_max = fmaxf(raw_max, s.raw_max);
-        y_max = fmaxf(y_max, s.y_max);
-        thr = fmaxf(thr, s.thr);
-        bad += (double)((s.nonfinite & 1u) + (s.nonfinite >> 1) * 256u + s.overflow * 65536u);
-        alive_tail += (double)s.alive_tail;
-    }
-    const int per_thread = (nseg + kMergeThreads - 1) / kMergeThreads;
-    uint32_t mine = 0;
-    for (int j = 0; j < per_thread; ++j) {
-        const int s = tid * per_thread + j;
-        if (s < nseg) {
-            const uint32_t c = min(*reinterpret_cast<const uint32_t*>(counts_row + s * p.count_seg_stride),
-                                   (uint32_t)p.seg_cap);
-            seg_size[s] = c;
-            mine += c;
-        }
-    }
-    uint32_t incl = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += up;
-    }
-    if (lane == 31) s_u[warp] = incl;
-    if (tid == 0) s_count = 0;
-    {   // one barrier for all five reductions; it also publishes s_u and seg_size
-        raw_max = warp_max(raw_max);
-        y_max = warp_max(y_max);
-        thr = warp_max(thr);
-        bad = warp_sum(bad);
-        alive_tail = warp_sum(alive_tail);
-        if (lane == 0) {
-            s_f[0][warp] = raw_max; s_f[1][warp] = y_max; s_f[2][warp] = thr;
-            s_d[0][warp] = bad; s_d[1][warp] = alive_tail;
-        }
-        __syncthreads();
-        raw_max = s_f[0][0]; y_max = s_f[1][0]; thr = s_f[2][0];
-        bad = 0.0; alive_tail = 0.0;
-#pragma unroll
-        for (int w = 0; w < kMergeThreads / 32; ++w) {
-            raw_max = fmaxf(raw_max, s_f[0][w]);
-            y_max = fmaxf(y_max, s_f[1][w]);
-            thr = fmaxf(thr, s_f[2][w]);
-            bad += s_d[0][w];
-            alive_tail += s_d[1][w];
-        }
-    }
-    uint32_t running = incl - mine;
-    for (int w = 0; w < warp; ++w) running += s_u[w];
-    for (int j = 0; j < per_thread; ++j) {
-        const int s = tid * per_thread + j;
-        if (s < nseg) {
-            seg_begin[s] = running;
-            running += seg_size[s];
-            if (s == nseg - 1) seg_begin[nseg] = running;
-        }
-    }
-    __syncthreads();
-    const int total = (int)seg_begin[nseg];
-    const uint32_t bad_bits = (uint32_t)bad;
-    if (bad_bits != 0 || total > gcap) {
-        if (tid == 0) {
-            p.tokens[row] = -1;
-            p.log_probs[row] = 0.0f;
-            p.row_status[row] = (bad_bits & 0xFF00u) ? PSX_ROW_DEVICE_TIMEOUT
-                                : (bad_bits & 0xFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
-            if (p.diag) p.diag[row] = psx_row_diag{total, 0, INFINITY, INFINITY};
-        }
-        return;
-    }
-    // Independent loads, a few per thread: every candidate of the row into shared memory.
-    for (int i = tid; i < total; i += kMergeThreads) {
-        int lo = 0, hi = nseg;  // the segment s with seg_begin[s] <= i < seg_begin[s + 1]
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (seg_begin[mid] <= (uint32_t)i) lo = mid; else hi = mid;
-        }
-        const uint2 c = reinterpret_cast<const uint2*>(cands_row + lo * p.cand_seg_stride)[i - (int)seg_begin[lo]];
-        cand_l[i] = c.x;
-        cand_c[i] = c.y;
-    }
-    __syncthreads();
-
-    float keep_from = relax_threshold(thr, apply_t, p.temperature);
-    const float x_max = temper(y_max, apply_t, p.temperature);
-    const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
-
-    // Every part handed on at least k logits, so together they hold far more than the k that a
-    // top-k keeps.  The k-th largest of everything collected IS the row's k-th largest (the union
-    // contains the true top k): select it, and only it and what ties with it after the
-    // temperature divide go on to the sort.  Greedy keeps the maximum and its ties.
-    if (!p.do_sample) {
-        keep_from = fmaxf(y_max, -FLT_MAX);
-    } else if (top_k_on && total > p.top_k) {
-        for (int i = tid; i < total; i += kMergeThreads) {
-            ykeys[i] = ordered_key(processed_before_temperature(__uint_as_float(cand_l[i]), cand_c[i], p.penalty));
-        }
-        __syncthreads();
-        const uint32_t kth = block_select_kth(ykeys, total, (uint32_t)p.top_k, s_hist, s_state);
-        keep_from = fmaxf(keep_from, relax_threshold(from_ordered_key(kth), apply_t, p.temperature));
-    }
-
-    // ---- 2. raw sum-exp over everything; the list of those that can survive ------------------------
-    double z_raw = 0.0, z_rest = 0.0, dropped = 0.0;
-    for (int i = tid; i < p.parts; i += kMergeThreads) {
-        const PartStats s = part_stats(i);
-        z_raw += s.raw_tail * exp((double)s.raw_max - (double)raw_max);
-        if (s.y_max > -INFINITY && s.proc_tail > 0.0) {
-            z_rest += s.proc_tail * exp((double)temper(s.y_max, apply_t, p.temperature) - (double)x_max);
-        }
-    }
-    for (int i = tid; i < total; i += kMergeThreads) {
-        const float l = __uint_as_float(cand_l[i]);
-        const uint32_t cf = cand_c[i];
-        z_raw += exp((double)l - (double)raw_max);
-        const float y = processed_before_temperature(l, cf, p.penalty);
-        if (y >= keep_from) {
-            const float x = temper(y, apply_t, p.temperature);
-            const int slot = atomicAdd(&s_count, 1);
-            if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(cf & kColumnMask);
-        } else if (y > -INFINITY && !top_k_on) {
-            z_rest += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
-            dropped += 1.0;
-        }
-    }
-    {   // three sums, one barrier (which also makes s_count final); fixed order
-        z_raw = warp_sum(z_raw);
-        z_rest = warp_sum(z_rest);
-        dropped = warp_sum(dropped);
-        __syncthreads();  // the reads of s_d above are done
-        if (lane == 0) { s_d[0][warp] = z_raw; s_d[1][warp] = z_rest; s_d[2][warp] = dropped; }
-        __syncthreads();
-        z_raw = 0.0; z_rest = 0.0; dropped = 0.0;
-#pragma unroll
-        for (int w = 0; w < kMergeThreads / 32; ++w) {
-            z_raw += s_d[0][w];
-            z_rest += s_d[1][w];
-            dropped += s_d[2][w];
-        }
-    }
-    const int n = s_count;
-    if (n > cap || n == 0) {
-        if (tid == 0) {
-            p.tokens[row] = -1;
-            p.log_probs[row] = 0.0f;
-            p.row_status[row] = n == 0 ? PSX_ROW_ALL_REMOVED : PSX_ROW_TOO_WIDE;
-            if (p.diag) p.diag[row] = psx_row_diag{n, 0, INFINITY, INFINITY};
-        }
-        return;
-    }
-
-    // ---- 3'. a long list without a top-k: decided by the whole block, without sorting --------------
-    bool decided = false;
-    if (p.do_sample && !top_k_on && n > kMergeThreads) {
-        uint32_t top_key = 0;
-        for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
-        top_key = block_max_u32(top_key, s_d[0]);
-        const float x_top = from_ordered_key(top_key);
-        for (int i = tid; i < n; i += kMergeThreads) {
-            ex[i] = exp((double)from_ordered_key(key_ord(keyA[i])) - (double)x_top);  // src/generation.cpp:46
-        }
-        __syncthreads();
-        const bool rest_in_play = (alive_tail + dropped) > 0.0;
-        const double bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_top);
-        Decision wide;
-        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, p.uniforms[row], s_d[0], wide);
-        __syncthreads();
-        if (decided && tid == 0) {
-            s_dec = wide;
-            s_chosen_raw = 0;
-        }
-    }
-
-    if (!decided) {
-    // ---- 3. sort by (value desc, column asc); top-k keeps the k-th value and its ties -----------
-    if (n <= kMergeThreads) {
-        block_rank_sort(keyA, n, /*descending=*/true);
-    } else {
-        int n_pad = 2;
-        while (n_pad < n) n_pad <<= 1;
-        for (int i = n + tid; i < n_pad; i += kMergeThreads) keyA[i] = 0;
-        __syncthreads();
-        block_bitonic_sort(keyA, n_pad, /*descending=*/true);
-    }
-
-    if (tid == 0) s_ns = 0;
-    __syncthreads();
-    bool rest_alive = false;
-    if (top_k_on && n >= p.top_k) {
-        const uint32_t kth = key_ord(keyA[p.top_k - 1]);
-        int count = 0;
-        for (int i = tid; i < n; i += kMergeThreads) count += key_ord(keyA[i]) >= kth ? 1 : 0;
-        if (count) atomicAdd(&s_ns, count);
-    } else {
-        if (tid == 0) s_ns = n;
-        // Without a top-k the rest of the vocabulary is still in play.
-        rest_alive = !top_k_on && p.do_sample && (alive_tail + dropped) > 0.0;
-    }
-    __syncthreads();
-    const int ns = s_ns;
-    const float x_first = from_ordered_key(key_ord(keyA[0]));
-    const double rest_bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_first);
-    for (int i = tid; i < ns; i += kMergeThreads) {
-        const float x = from_ordered_key(key_ord(keyA[i]));
-        ex[i] = exp((double)x - (double)x_first);  // src/generation.cpp:46
-        alive[i] = 1;
-        keyB[i] = ((u64)key_col(keyA[i]) << 32) | (uint32_t)i;
-    }
-    if (ns <= kMergeThreads) {
-        block_rank_sort(keyB, ns, /*descending=*/false);
-    } else {
-        int ns_pad = 2;
-        while (ns_pad < ns) ns_pad <<= 1;
-        for (int i = ns + tid; i < ns_pad; i += kMergeThreads) keyB[i] = ~0ull;
-        __syncthreads();
-        block_bitonic_sort(keyB, ns_pad, /*descending=*/false);
-    }
-
-    // ---- 4. the reference's walk, by one thread ------------------------------------------------------
-    if (tid == 0) {
-        const double u = p.do_sample ? p.uniforms[row] : 0.0;
-        decide(p, keyA, keyB, ex, alive, ns, rest_alive, z_rest, rest_bound, u, s_dec);
-        s_chosen_raw = 0;
-    }
-    }  // !decided
-    __syncthreads();
-    const Decision dec = s_dec;
-    if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
-        for (int i = tid; i < total; i += kMergeThreads) {
-            if ((long long)(cand_c[i] & kColumnMask) == dec.token) s_chosen_raw = cand_l[i];
-        }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        p.row_status[row] = dec.status;
-        p.tokens[row] = dec.status == PSX_ROW_OK ? dec.token : -1;
-        float lp = 0.0f;
-        if (dec.status == PSX_ROW_OK) {
-            const double l = (double)__uint_as_float(s_chosen_raw);
-            lp = (float)log(exp(l - (double)raw_max) / z_raw);  // src/generation.cpp:156
-        }
-        p.log_probs[row] = lp;
-        if (p.diag) p.diag[row] = psx_row_diag{n, dec.survivors, dec.draw_margin, dec.top_p_margin};
-    }
+    extern __shared__ unsigned long long dyn[];
+    survivor::merge_row(p, blockIdx.x, dyn);
 }
 
 }  // namespace
