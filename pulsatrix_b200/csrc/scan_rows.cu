@@ -118,8 +118,9 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
     __shared__ uint32_t s_wfill[kScanWarps];
 
-    const int part = blockIdx.x % p.parts;
-    const int64_t row = blockIdx.x / p.parts;
+    const int part = blockIdx.x;  // grid: (parts, rows in chunks of 65535, chunks)
+    const int64_t row = (int64_t)blockIdx.z * 65535 + blockIdx.y;
+    if (row >= p.rows) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t part_index = (size_t)row * p.parts + part;
     const size_t seg = part_index * kScanWarps + warp;
@@ -179,6 +180,11 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         return;
     }
 
+    // Pad the part to whole 256-vector trips (at most one vector per thread).
+    {
+        const int padded = (nvec + kScanThreads - 1) / kScanThreads * kScanThreads;
+        if (nvec + tid < padded) reinterpret_cast<float4*>(dyn_smem)[nvec + tid] = make_float4(kPad, kPad, kPad, kPad);
+    }
     // Components of the first and last vector that lie outside the row are blanked.
     if (tid == 0) {
         if (v0 == 0) {
@@ -339,65 +345,71 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const bool second_exp = kNucleus && p.apply_temperature != 0;
     // Per-lane float sums of at most 16 four-element sums each; they go to double in the reduction.
     float tail = 0.0f, proc = 0.0f;
-    const uint32_t lanes_below = (1u << lane) - 1u;
 
-    for (int base = warp * 32; base < nvec && !(p.debug_skip & 4); base += kScanThreads) {
-        const int v = base + lane;
-        const float4 d = v < nvec ? data4[v] : make_float4(kPad, kPad, kPad, kPad);
-        float x0 = __fmaf_rn(d.x, kLog2e, -c_l2), x1 = __fmaf_rn(d.y, kLog2e, -c_l2);
-        float x2 = __fmaf_rn(d.z, kLog2e, -c_l2), x3 = __fmaf_rn(d.w, kLog2e, -c_l2);
-        if (kNucleus) {
-            x0 = __fmaf_rn(x0, kLog2eRel, x0); x1 = __fmaf_rn(x1, kLog2eRel, x1);
-            x2 = __fmaf_rn(x2, kLog2eRel, x2); x3 = __fmaf_rn(x3, kLog2eRel, x3);
-        }
-        float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
-        float q0 = 0.0f, q1 = 0.0f, q2 = 0.0f, q3 = 0.0f;
-        if (second_exp) {
-            float y0 = __fmaf_rn(d.x, p.log2e_over_t, -pc_l2), y1 = __fmaf_rn(d.y, p.log2e_over_t, -pc_l2);
-            float y2 = __fmaf_rn(d.z, p.log2e_over_t, -pc_l2), y3 = __fmaf_rn(d.w, p.log2e_over_t, -pc_l2);
-            q0 = ex2_approx(__fmaf_rn(y0, kLog2eRel, y0)); q1 = ex2_approx(__fmaf_rn(y1, kLog2eRel, y1));
-            q2 = ex2_approx(__fmaf_rn(y2, kLog2eRel, y2)); q3 = ex2_approx(__fmaf_rn(y3, kLog2eRel, y3));
-        }
-        // One vote per trip: which lanes hold a vector that reaches the threshold at all.
-        const bool any_here = fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime;
-        const uint32_t votes = __ballot_sync(0xFFFFFFFFu, any_here);
-        if (votes != 0 && !(p.debug_skip & 2)) {
-            const float l[4] = {d.x, d.y, d.z, d.w};
-            uint32_t mine = 0;  // which of my four components are handed on
-            if (any_here) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) mine |= (l[c] >= tprime ? 1u : 0u) << c;
+    // The part was padded to whole 256-vector trips, so the loop is branch-free but for the rare
+    // vector that reaches the threshold; those are only noted here (one bit per trip) and handed
+    // on after the loop, which lets the compiler keep several trips in flight.
+    const int trips = (nvec + kScanThreads - 1) / kScanThreads;
+    uint32_t noted = 0;
+    if (!(p.debug_skip & 4)) {
+#pragma unroll 4
+        for (int t = 0; t < trips; ++t) {
+            const float4 d = data4[t * kScanThreads + tid];
+            float x0 = __fmaf_rn(d.x, kLog2e, -c_l2), x1 = __fmaf_rn(d.y, kLog2e, -c_l2);
+            float x2 = __fmaf_rn(d.z, kLog2e, -c_l2), x3 = __fmaf_rn(d.w, kLog2e, -c_l2);
+            if (kNucleus) {
+                x0 = __fmaf_rn(x0, kLog2eRel, x0); x1 = __fmaf_rn(x1, kLog2eRel, x1);
+                x2 = __fmaf_rn(x2, kLog2eRel, x2); x3 = __fmaf_rn(x3, kLog2eRel, x3);
+            }
+            float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
+            float q0 = 0.0f, q1 = 0.0f, q2 = 0.0f, q3 = 0.0f;
+            if (second_exp) {
+                float y0 = __fmaf_rn(d.x, p.log2e_over_t, -pc_l2), y1 = __fmaf_rn(d.y, p.log2e_over_t, -pc_l2);
+                float y2 = __fmaf_rn(d.z, p.log2e_over_t, -pc_l2), y3 = __fmaf_rn(d.w, p.log2e_over_t, -pc_l2);
+                q0 = ex2_approx(__fmaf_rn(y0, kLog2eRel, y0)); q1 = ex2_approx(__fmaf_rn(y1, kLog2eRel, y1));
+                q2 = ex2_approx(__fmaf_rn(y2, kLog2eRel, y2)); q3 = ex2_approx(__fmaf_rn(y3, kLog2eRel, y3));
+            }
+            if (fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime) {
                 // What is handed on leaves the sums (its exp is taken in double by the survivor stage).
-                if (mine & 1u) { e0 = 0.0f; q0 = 0.0f; }
-                if (mine & 2u) { e1 = 0.0f; q1 = 0.0f; }
-                if (mine & 4u) { e2 = 0.0f; q2 = 0.0f; }
-                if (mine & 8u) { e3 = 0.0f; q3 = 0.0f; }
+                if (d.x >= tprime) { e0 = 0.0f; q0 = 0.0f; }
+                if (d.y >= tprime) { e1 = 0.0f; q1 = 0.0f; }
+                if (d.z >= tprime) { e2 = 0.0f; q2 = 0.0f; }
+                if (d.w >= tprime) { e3 = 0.0f; q3 = 0.0f; }
+                noted |= 1u << t;
             }
-            // Slots in lane order, components in order within a lane.  Usually every voting lane
-            // hands on one logit; otherwise the lanes' counts are summed with a few more votes.
-            const uint32_t count = __popc(mine);
-            uint32_t before = __popc(votes & lanes_below), total = __popc(votes);
-            const uint32_t multi = __ballot_sync(0xFFFFFFFFu, count > 1);
-            if (multi != 0) {
-                const uint32_t two = __ballot_sync(0xFFFFFFFFu, count > 1 && ((count - 1) & 2u));  // counts 3 and 4
-                const uint32_t odd = __ballot_sync(0xFFFFFFFFu, count > 1 && ((count - 1) & 1u));  // counts 2 and 4
-                before += 2 * __popc(two & lanes_below) + __popc(odd & lanes_below);
-                total += 2 * __popc(two) + __popc(odd);
-            }
-            uint32_t slot = seg_fill + before;
+            tail += (e0 + e1) + (e2 + e3);
+            if (second_exp) proc += (q0 + q1) + (q2 + q3);
+        }
+    }
+    // Hand-off: slots in lane order, then trip, then component -- a fixed order.
+    if (__ballot_sync(0xFFFFFFFFu, noted != 0) != 0 && !(p.debug_skip & 2)) {
+        uint32_t count = 0;
+        for (uint32_t m2 = noted; m2; m2 &= m2 - 1) {
+            const float4 d = data4[(__ffs(m2) - 1) * kScanThreads + tid];
+            count += (d.x >= tprime ? 1u : 0u) + (d.y >= tprime ? 1u : 0u) + (d.z >= tprime ? 1u : 0u) +
+                     (d.w >= tprime ? 1u : 0u);
+        }
+        uint32_t incl = count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        uint32_t slot = seg_fill + incl - count;
+        seg_fill += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        for (uint32_t m2 = noted; m2; m2 &= m2 - 1) {
+            const int v = (__ffs(m2) - 1) * kScanThreads + tid;
+            const float4 d = data4[v];
+            const float l[4] = {d.x, d.y, d.z, d.w};
+            const uint32_t col = (uint32_t)(col_base + v * 4);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                if (mine & (1u << c)) {
-                    if (slot < (uint32_t)kSegCap) {
-                        seg_out[slot] = make_uint2(__float_as_uint(l[c]), (uint32_t)(col_base + v * 4 + c));
-                    }
+                if (l[c] >= tprime) {
+                    if (slot < (uint32_t)kSegCap) seg_out[slot] = make_uint2(__float_as_uint(l[c]), col + c);
                     ++slot;
                 }
             }
-            seg_fill += total;
         }
-        tail += (e0 + e1) + (e2 + e3);
-        if (second_exp) proc += (q0 + q1) + (q2 + q3);
     }
 
     // ---- block reduction in a fixed order, then the part's record ---------------------------------------
@@ -454,12 +466,12 @@ cudaError_t configure_scan_rows() {
 }
 
 cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t stream) {
-    const long long blocks = (long long)p.rows * p.parts;
-    if (blocks <= 0) return cudaSuccess;
-    if (blocks > 0x7FFFFFFFll || p.vecs_per_part > kPartVecs) return cudaErrorInvalidConfiguration;
-    const size_t shared = ((size_t)p.vecs_per_part * 16 + 127) / 128 * 128;
-    if (nucleus) scan_rows_kernel<true><<<(unsigned)blocks, kScanThreads, shared, stream>>>(p);
-    else scan_rows_kernel<false><<<(unsigned)blocks, kScanThreads, shared, stream>>>(p);
+    if (p.rows <= 0 || p.parts <= 0) return cudaSuccess;
+    if (p.vecs_per_part > kPartVecs || p.rows > 65535ll * 65535ll) return cudaErrorInvalidConfiguration;
+    const size_t shared = (size_t)((p.vecs_per_part + kScanThreads - 1) / kScanThreads * kScanThreads) * 16;
+    const dim3 grid((unsigned)p.parts, (unsigned)(p.rows < 65535 ? p.rows : 65535), (unsigned)((p.rows + 65534) / 65535));
+    if (nucleus) scan_rows_kernel<true><<<grid, kScanThreads, shared, stream>>>(p);
+    else scan_rows_kernel<false><<<grid, kScanThreads, shared, stream>>>(p);
     return cudaGetLastError();
 }
 
