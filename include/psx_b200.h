@@ -134,6 +134,12 @@ PSX_API psx_status psx_b200_row_pass_only(psx_ctx* ctx, void* stream, const floa
                                           int64_t vocab, int64_t row_stride, const int64_t* history_ids,
                                           const int64_t* history_offsets, const psx_sampling_config* config);
 
+/* Benchmark aid: a kernel that only reads `bytes` bytes at `data` (16-byte aligned, device) with
+ * 128-bit streaming loads and writes nothing (`sink`: one device float it practically never
+ * touches).  Timed beside the row pass, it shows what reading a batch of that size can reach at
+ * all.  No counterpart in the reference. */
+PSX_API psx_status psx_b200_read_only_pass(void* stream, const void* data, size_t bytes, float* sink);
+
 /* The same step as psx_b200_sample_rows for callers that must not allocate device memory: a
  * decode loop inside a serving process whose own pool already owns the GPU's memory (a cudaMalloc
  * from a plug-in would fail or stall), or a latency-critical loop that cannot afford cudaMalloc's
@@ -149,6 +155,22 @@ PSX_API psx_status psx_b200_sample_rows_static(void* stream, const float* logits
                                                const int64_t* history_offsets, const psx_sampling_config* config,
                                                const double* uniforms, int64_t* tokens, float* log_probs,
                                                int32_t* row_status);
+
+/* ProcessLogits (include/pulsatrix/generation.hpp:83, src/generation.cpp:55-112) for a batch of
+ * device rows, in place: repetition penalty, EOS ban before min_new_tokens, and -- when sampling
+ * -- temperature, top-k, top-p and min-p; removed entries become -infinity.  row_status (device,
+ * may be NULL) receives PSX_ROW_OK, PSX_ROW_ALL_REMOVED (the row is all -infinity, as the
+ * reference would leave it) or PSX_ROW_TOO_WIDE (the row is left unchanged).  Unlike Generate(),
+ * and like the reference's ProcessLogits, non-finite input is not looked for.
+ * psx_b200_process_logits_host does the same for host rows (copy in, process, copy back, sync). */
+PSX_API psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream, float* logits, int64_t rows, int64_t vocab,
+                                           int64_t row_stride, const int64_t* history_ids,
+                                           const int64_t* history_offsets, const psx_sampling_config* config,
+                                           int32_t* row_status);
+PSX_API psx_status psx_b200_process_logits_host(psx_ctx* ctx, float* logits, int64_t rows, int64_t vocab,
+                                                int64_t row_stride, const int64_t* history_ids,
+                                                const int64_t* history_offsets, const psx_sampling_config* config,
+                                                int32_t* row_status);
 
 /* The same step for callers that hold everything on the host, as the reference's
  * NextTokenLogitsFn does (include/pulsatrix/generation.hpp:25): copies inputs to the device,

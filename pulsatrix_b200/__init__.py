@@ -5,7 +5,7 @@ is the thin Python loader used by the tests and the benchmark: it binds the C en
 ctypes and hands them device pointers of torch tensors.  There is no Python or CPU
 implementation of the path; when the library is missing, loading fails.
 """
-from .binding import (Context, sample_rows_static, RowDiag, SamplingConfig, library, library_path, uniforms_mt19937_64,  # noqa: F401
+from .binding import (Context, sample_rows_static, read_only_pass, RowDiag, SamplingConfig, library, library_path, uniforms_mt19937_64,  # noqa: F401
                       uniforms_portable, PsxError, ROW_OK, ROW_NON_FINITE, ROW_ALL_REMOVED, ROW_TOO_WIDE)
 from .workloads import WORKLOADS, Workload  # noqa: F401
 

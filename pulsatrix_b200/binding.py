@@ -13,7 +13,7 @@ OK, ERR_BAD_ARGUMENT, ERR_CUDA, ERR_ROW_FAILED, ERR_UNSUPPORTED = range(5)
 
 EXPORTS = [
     "psx_b200_version", "psx_b200_last_error", "psx_b200_ctx_create", "psx_b200_ctx_destroy", "psx_b200_ctx_stream",
-    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static",
+    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_top_k_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
@@ -95,6 +95,9 @@ def library():
         ptr, i64 = C.c_void_p, C.c_int64
         lib.psx_b200_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_sample_rows_static.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_read_only_pass.argtypes = [ptr, ptr, C.c_size_t, ptr]
+        lib.psx_b200_process_logits.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr]
+        lib.psx_b200_process_logits_host.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr]
         lib.psx_b200_row_pass_only.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr]
         lib.psx_b200_sample_rows_host.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_scan.argtypes = [ptr, ptr, ptr, i64, i64, i64, i64, i64, ptr, ptr, ptr, ptr]
@@ -128,6 +131,15 @@ def uniforms_portable(seeds) -> np.ndarray:
 
 def _dptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def read_only_pass(tensor, sink, stream=None):
+    """Launches the read-only kernel over a contiguous cuda tensor (benchmark aid)."""
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream(tensor.device).cuda_stream
+    _check(library().psx_b200_read_only_pass(C.c_void_p(stream), _dptr(tensor), tensor.numel() * tensor.element_size(),
+                                             _dptr(sink)))
 
 
 def sample_rows_static(logits, history_ids, history_offsets, config, uniforms, tokens, log_probs, status, stream=None,
@@ -214,6 +226,20 @@ class Context:
             _dptr(history_ids), _dptr(history_offsets), C.addressof(config), _dptr(uniforms), _dptr(out["tokens"]),
             _dptr(out["log_probs"]), _dptr(out["status"]), _dptr(out["diag"])))
         return out
+
+    def process_logits_host(self, logits, history_ids, history_offsets, config):
+        """ProcessLogits on host rows (numpy float32 (rows, vocab), modified in place).  Returns the
+        per-row status array; raises when the device path declines a row."""
+        rows, vocab = logits.shape
+        status = np.zeros(rows, dtype=np.int32)
+
+        def hptr(a):
+            return None if a is None else C.c_void_p(a.ctypes.data)
+
+        _check(self._lib.psx_b200_process_logits_host(self._ctx, hptr(logits), rows, vocab, logits.strides[0] // 4,
+                                                      hptr(history_ids), hptr(history_offsets), C.addressof(config),
+                                                      hptr(status)))
+        return status
 
     def row_pass_only(self, logits, history_ids, history_offsets, config, stream=None, vocab=None):
         """Launches only the kernel that reads the logits (for timing and profiling)."""

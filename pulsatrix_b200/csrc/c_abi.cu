@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "merge_rows.cuh"
+#include "process_rows.cuh"
 #include "scan_rows.cuh"
 #include "shard_records.cuh"
 #include "topk_rows.cuh"
@@ -57,6 +58,8 @@ struct psx_ctx {
     int nucleus_k = 160;  // logits every part hands on when no top-k bounds the survivors
     // row-pass scratch
     Buffer stats, seg_counts, candidates, banned;
+    // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
+    Buffer surv_cols, surv_vals, surv_counts, pl_tokens, pl_log_probs, pl_status;
     // staging of the host entry point
     Buffer h_logits, h_history, h_offsets, h_uniforms, h_tokens, h_log_probs, h_status, h_diag;
     // staging of the sharded path
@@ -270,7 +273,8 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (Buffer* b : {&ctx->stats, &ctx->seg_counts, &ctx->candidates, &ctx->banned, &ctx->h_logits, &ctx->h_history,
+    for (Buffer* b : {&ctx->stats, &ctx->seg_counts, &ctx->candidates, &ctx->banned, &ctx->surv_cols, &ctx->surv_vals,
+                      &ctx->surv_counts, &ctx->pl_tokens, &ctx->pl_log_probs, &ctx->pl_status, &ctx->h_logits, &ctx->h_history,
                       &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
         if (b->ptr) cudaFree(b->ptr);
@@ -387,6 +391,135 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     if (ctx->timing) {
         PSX_CUDA(cudaEventRecord(marks[2], stream));
         ctx->timing_events.insert(ctx->timing_events.end(), marks, marks + 3);
+    }
+    return PSX_OK;
+}
+
+psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream_ptr, float* logits, int64_t rows, int64_t vocab,
+                                   int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
+                                   const psx_sampling_config* config, int32_t* row_status) {
+    if (psx_status s = check_common(ctx, config, rows, vocab, row_stride, vocab, logits, history_ids, history_offsets)) {
+        return s;
+    }
+    if (rows == 0) return PSX_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    const bool sample = config->do_sample != 0;
+    const bool top_k_on = sample && config->top_k > 0 && config->top_k < vocab;
+    // src/generation.cpp:74-76: greedy stops after the penalty and the EOS ban.
+    const bool filters_on = sample && (top_k_on || config->top_p < 1.0f || config->min_p > 0.0f);
+    Plan plan;
+    psx::ScanParams sp;
+    if (psx_status s = plan_row_pass(ctx, stream, logits, rows, vocab, row_stride, history_ids, history_offsets, config,
+                                     plan, sp)) {
+        return s;
+    }
+    if (psx_status s = reserve(ctx->pl_status, (size_t)rows * sizeof(int32_t))) return s;
+    int32_t* status = row_status ? row_status : static_cast<int32_t*>(ctx->pl_status.ptr);
+
+    psx::ProcessParams pp{};
+    pp.logits = logits;
+    pp.row_stride = row_stride;
+    pp.rows = rows;
+    pp.vocab = vocab;
+    pp.history_ids = history_ids;
+    pp.history_offsets = history_offsets;
+    pp.banned_ids = sp.banned_ids;
+    pp.num_banned = sp.num_banned;
+    pp.apply_penalty = sp.apply_penalty;
+    pp.penalty = sp.penalty;
+    pp.apply_temperature = sp.apply_temperature;
+    pp.temperature = sp.temperature;
+    pp.filters_on = filters_on ? 1 : 0;
+    pp.row_status = status;
+    if (filters_on) {
+        if (psx_status s = configure_merge(ctx, plan, plan.parts * psx::kScanWarps)) return s;
+        const size_t slots = (size_t)rows * plan.sort_capacity;
+        if (psx_status s = reserve(ctx->surv_cols, slots * sizeof(uint32_t))) return s;
+        if (psx_status s = reserve(ctx->surv_vals, slots * sizeof(float))) return s;
+        if (psx_status s = reserve(ctx->surv_counts, (size_t)rows * sizeof(uint32_t))) return s;
+        if (psx_status s = reserve(ctx->pl_tokens, (size_t)rows * sizeof(int64_t))) return s;
+        if (psx_status s = reserve(ctx->pl_log_probs, (size_t)rows * sizeof(float))) return s;
+        PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+        ++ctx->launches;
+        psx::MergeParams mp{};
+        mp.stats = sp.stats;
+        mp.seg_counts = sp.seg_counts;
+        mp.candidates = sp.candidates;
+        mp.parts = plan.parts;
+        mp.segs_per_part = psx::kScanWarps;
+        mp.seg_cap = psx::kSegCap;
+        mp.stats_part_stride = sizeof(psx::PartStats);
+        mp.stats_row_stride = mp.stats_part_stride * plan.parts;
+        mp.count_seg_stride = sizeof(uint32_t);
+        mp.count_row_stride = mp.count_seg_stride * plan.parts * psx::kScanWarps;
+        mp.cand_seg_stride = sizeof(uint2) * psx::kSegCap;
+        mp.cand_row_stride = mp.cand_seg_stride * plan.parts * psx::kScanWarps;
+        fill_merge_settings(mp, config, plan, rows, vocab, /*uniforms=*/nullptr,
+                            static_cast<int64_t*>(ctx->pl_tokens.ptr), static_cast<float*>(ctx->pl_log_probs.ptr), status,
+                            nullptr);
+        mp.survivor_cols = static_cast<uint32_t*>(ctx->surv_cols.ptr);
+        mp.survivor_vals = static_cast<float*>(ctx->surv_vals.ptr);
+        mp.survivor_counts = static_cast<uint32_t*>(ctx->surv_counts.ptr);
+        mp.survivor_cap = plan.sort_capacity;
+        PSX_CUDA(psx::launch_merge_rows(mp, stream));
+        ++ctx->launches;
+        pp.survivor_cols = mp.survivor_cols;
+        pp.survivor_vals = mp.survivor_vals;
+        pp.survivor_counts = mp.survivor_counts;
+        pp.survivor_cap = mp.survivor_cap;
+    } else if (row_status) {
+        PSX_CUDA(cudaMemsetAsync(row_status, 0, (size_t)rows * sizeof(int32_t), stream));
+    }
+    PSX_CUDA(psx::launch_process_rows(pp, stream));
+    ctx->launches += filters_on ? 2 : 1;
+    return PSX_OK;
+}
+
+psx_status psx_b200_process_logits_host(psx_ctx* ctx, float* logits, int64_t rows, int64_t vocab, int64_t row_stride,
+                                        const int64_t* history_ids, const int64_t* history_offsets,
+                                        const psx_sampling_config* config, int32_t* row_status) {
+    if (psx_status s = check_common(ctx, config, rows, vocab, row_stride, vocab, logits, history_ids, history_offsets)) {
+        return s;
+    }
+    if (rows == 0) return PSX_OK;
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t stream = ctx->stream;
+    const bool with_history = history_ids && history_offsets;
+    const int64_t history_total = with_history ? history_offsets[rows] : 0;
+    if (psx_status s = reserve(ctx->h_logits, (size_t)rows * vocab * sizeof(float))) return s;
+    if (psx_status s = reserve(ctx->h_history, (size_t)std::max<int64_t>(history_total, 1) * sizeof(int64_t))) return s;
+    if (psx_status s = reserve(ctx->h_offsets, (size_t)(rows + 1) * sizeof(int64_t))) return s;
+    if (psx_status s = reserve(ctx->h_status, (size_t)rows * sizeof(int32_t))) return s;
+    PSX_CUDA(cudaMemcpy2DAsync(ctx->h_logits.ptr, (size_t)vocab * sizeof(float), logits, (size_t)row_stride * sizeof(float),
+                               (size_t)vocab * sizeof(float), (size_t)rows, cudaMemcpyHostToDevice, stream));
+    if (with_history) {
+        if (history_total > 0) {
+            PSX_CUDA(cudaMemcpyAsync(ctx->h_history.ptr, history_ids, (size_t)history_total * sizeof(int64_t),
+                                     cudaMemcpyHostToDevice, stream));
+        }
+        PSX_CUDA(cudaMemcpyAsync(ctx->h_offsets.ptr, history_offsets, (size_t)(rows + 1) * sizeof(int64_t),
+                                 cudaMemcpyHostToDevice, stream));
+    }
+    if (psx_status s = psx_b200_process_logits(ctx, stream, static_cast<float*>(ctx->h_logits.ptr), rows, vocab, vocab,
+                                               with_history ? static_cast<const int64_t*>(ctx->h_history.ptr) : nullptr,
+                                               with_history ? static_cast<const int64_t*>(ctx->h_offsets.ptr) : nullptr,
+                                               config, static_cast<int32_t*>(ctx->h_status.ptr))) {
+        return s;
+    }
+    PSX_CUDA(cudaMemcpy2DAsync(logits, (size_t)row_stride * sizeof(float), ctx->h_logits.ptr, (size_t)vocab * sizeof(float),
+                               (size_t)vocab * sizeof(float), (size_t)rows, cudaMemcpyDeviceToHost, stream));
+    std::vector<int32_t> local((size_t)rows);
+    int32_t* out_status = row_status ? row_status : local.data();
+    PSX_CUDA(cudaMemcpyAsync(out_status, ctx->h_status.ptr, (size_t)rows * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    PSX_CUDA(cudaStreamSynchronize(stream));
+    for (int64_t r = 0; r < rows; ++r) {
+        if (out_status[r] != PSX_ROW_OK && out_status[r] != PSX_ROW_ALL_REMOVED) {
+            return fail(PSX_ERR_ROW_FAILED,
+                        std::string(out_status[r] == PSX_ROW_NON_FINITE
+                                        ? "psx_b200: a logit is not finite"
+                                        : "psx_b200: too many tokens survive the filters for the device path") +
+                            " (row " + std::to_string(r) + ")");
+        }
     }
     return PSX_OK;
 }

@@ -37,6 +37,11 @@ struct MergeParams {
     int32_t* row_status;
     psx_row_diag* diag;          // may be null
     int32_t sort_capacity;       // survivors + near-survivors the shared-memory sorter holds (power of two)
+    // Optional: the surviving set itself (for ProcessLogits), up to survivor_cap per row; null = off.
+    uint32_t* survivor_cols;     // rows * survivor_cap global columns, in no particular order
+    float* survivor_vals;        // their processed logits
+    uint32_t* survivor_counts;   // rows
+    int32_t survivor_cap;
     int32_t debug_stop;          // profiling only: leave the kernel after this stage (0: run everything)
     int32_t gather_capacity;     // candidates of one row held in shared memory (<= 6 * sort_capacity)
 };

@@ -186,6 +186,8 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
         w.order_w[place_w] = (uint32_t)tid;
         w.ex[tid] = my_ex;
         w.alive[tid] = 1;
+    } else if (have) {
+        w.alive[tid] = 0;
     }
     Decision d;
     d.status = PSX_ROW_OK;
@@ -700,7 +702,8 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         const bool rest_in_play = (alive_tail + dropped) > 0.0;
         const double bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_top);
         Decision wide;
-        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, p.uniforms[row], s_d[0], wide);
+        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, p.uniforms ? p.uniforms[row] : 0.5,
+                              s_d[0], wide);
         __syncthreads();
         if (decided && tid == 0) {
             s_dec = wide;
@@ -721,7 +724,8 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         if (tid < 8) w.shared[tid] = 1;
         __syncthreads();
         decide_small(p, keyA, n, top_k_on, (alive_tail + dropped) > 0.0, z_rest,
-                     temper(keep_from, apply_t, p.temperature), p.do_sample ? p.uniforms[row] : 0.0, w, &s_dec);
+                     temper(keep_from, apply_t, p.temperature),
+                     (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5, w, &s_dec);
         if (tid == 0) s_chosen_raw = 0;
         decided = true;
     }
@@ -753,7 +757,8 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     const int ns = s_ns;
     const float x_first = from_ordered_key(key_ord(keyA[0]));
     const double rest_bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_first);
-    for (int i = tid; i < ns; i += kMergeThreads) {
+    for (int i = tid; i < n; i += kMergeThreads) {
+        if (i >= ns) { alive[i] = 0; continue; }
         const float x = from_ordered_key(key_ord(keyA[i]));
         ex[i] = exp((double)x - (double)x_first);  // src/generation.cpp:46
         alive[i] = 1;
@@ -771,14 +776,29 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
 
     // ---- 4. the reference's walk, by one thread ------------------------------------------------------
     if (tid == 0) {
-        const double u = p.do_sample ? p.uniforms[row] : 0.0;
+        const double u = (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5;
         decide(p, keyA, keyB, ex, alive, ns, rest_alive, z_rest, rest_bound, u, s_dec);
         s_chosen_raw = 0;
     }
     }  // !decided
     __syncthreads();
     if (p.debug_stop == 4) return;
-    const Decision dec = s_dec;
+    Decision dec = s_dec;
+    if (p.survivor_cols != nullptr && dec.status == PSX_ROW_OK) {  // hand the surviving set itself out
+        if (tid == 0) s_count = 0;
+        __syncthreads();
+        for (int i = tid; i < n; i += kMergeThreads) {
+            if (!alive[i]) continue;
+            const int slot = atomicAdd(&s_count, 1);
+            if (slot < p.survivor_cap) {
+                p.survivor_cols[row * p.survivor_cap + slot] = key_col(keyA[i]);
+                p.survivor_vals[row * p.survivor_cap + slot] = from_ordered_key(key_ord(keyA[i]));
+            }
+        }
+        __syncthreads();
+        if (s_count > p.survivor_cap) dec.status = PSX_ROW_TOO_WIDE;
+        if (tid == 0) p.survivor_counts[row] = (uint32_t)min(s_count, p.survivor_cap);
+    }
     if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
         for (int i = tid; i < total; i += kMergeThreads) {
             if ((long long)(cand_c[i] & kColumnMask) == dec.token) s_chosen_raw = cand_l[i];

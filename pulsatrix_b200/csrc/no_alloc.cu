@@ -10,7 +10,7 @@
 // library image on every GPU (kStaticParts parts, about 8.1 MiB, held until the process exits).
 //
 // Consequences the caller must know:
-//   * rows * parts-per-row may not exceed kStaticParts (a part is 16384 logits of one row; C2's
+//   * rows * parts-per-row may not exceed kStaticParts (a part is 16384 logits of one row; a
 //     64 x 151,936 batch is 640 parts); bigger batches and more than kStaticBanned EOS ids are
 //     refused with PSX_ERR_UNSUPPORTED, nothing is launched;
 //   * the first call on a device looks up the array's device address (cudaGetSymbolAddress, with

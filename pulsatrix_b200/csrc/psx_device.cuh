@@ -14,7 +14,7 @@ namespace psx {
 constexpr int kScanThreads = 256;
 constexpr int kScanWarps = kScanThreads / 32;
 constexpr int kVecPerThread = 16;                            // float4 held in registers per thread
-constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits per CTA
+constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits = 64 KB per CTA
 constexpr int kSegCap = 128;                                 // candidate slots per warp segment
 constexpr int kMergeThreads = 256;
 

@@ -93,7 +93,7 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
     }
 }
 
-constexpr int kPool = 8;  // per-thread maxima a warp can offer to the pooled threshold
+constexpr int kPool = 64 / kScanWarps;  // per-thread maxima a warp can offer to the pooled threshold (64 in all)
 
 // What warp 0 works out for the part after pass one and every thread needs in pass two.
 struct PartConstants {
@@ -202,12 +202,12 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     float f_raw = kPad, f_amax = 0.0f, f_y = -INFINITY;
     if (use_flags && !(p.debug_skip & 1)) {
         // A warp takes the bitmap words of the logits its own threads own in the dense passes
-        // (vector v belongs to thread v % 256), so a row that is handed on whole fills every
-        // warp's segment with exactly its own 128 logits per 256 vectors.
+        // (vector v belongs to thread v % kScanThreads), so a row that is handed on whole fills every
+        // warp's segment with exactly its own 128 logits.
         constexpr int kWordsPerWarp = kBitmapWords / kScanWarps;
         for (int r = 0; r < kWordsPerWarp / 32; ++r) {
             const int idx = r * 32 + lane;
-            const int word = 32 * (idx >> 2) + 4 * warp + (idx & 3);
+            const int word = (kScanThreads / 8) * (idx >> 2) + 4 * warp + (idx & 3);
             const uint32_t banned_bits = s_ban[word];
             uint32_t bits = s_pen[word] | banned_bits;
             const uint32_t count = __popc(bits);
