@@ -15,6 +15,8 @@ PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libpsx_b200.so"
 SOURCES = ["c_abi.cu", "scan_rows.cu", "merge_rows.cu", "topk_rows.cu", "shard_records.cu", "no_alloc.cu", "read_floor.cu", "process_rows.cu"]
+HOST_SOURCES = ["determinism.cpp", "sampler.cpp", "backend.cpp", "generation.cpp"]  # the C++ API over the C ABI
+CPP_TEST = PACKAGE.parent / "tests" / "cpp" / "host_api_test"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=true",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
@@ -23,7 +25,8 @@ def _stale() -> bool:
     if not LIBRARY.exists():
         return True
     built = LIBRARY.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PACKAGE.parent / "include" / "psx_b200.h"]
+    deps = (list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list((PACKAGE / "host").glob("*.cpp")) +
+            list((PACKAGE.parent / "include").rglob("*.h*")))
     return any(p.stat().st_mtime > built for p in deps)
 
 
@@ -39,6 +42,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", str(CSRC / src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objects.append(str(obj))
+    include = str(PACKAGE.parent / "include")
+    for src in HOST_SOURCES:
+        obj = build_dir / (src + ".o")
+        cmd = ["nvcc", "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-I", include,
+               "-c", str(PACKAGE / "host" / src), "-o", str(obj)]
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objects.append(str(obj))
     for src, proc in procs:
         out, _ = proc.communicate()
         if verbose or proc.returncode != 0:
@@ -46,7 +56,18 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
     subprocess.run(["nvcc", "-arch=sm_100a", "-shared", "-o", str(LIBRARY), *objects, "-lcudart"], check=True)
+    build_cpp_test()
     return LIBRARY
+
+
+def build_cpp_test() -> Path:
+    """The C++ test program of the host API (tests/cpp/host_api_test.cpp), linked against the library."""
+    source = CPP_TEST.with_suffix(".cpp")
+    if source.exists():
+        subprocess.run(["g++", "-std=c++17", "-O1", "-I", str(PACKAGE.parent / "include"), str(source), "-o", str(CPP_TEST),
+                        "-L", str(PACKAGE), "-lpsx_b200", f"-Wl,-rpath,{PACKAGE}", "-Wl,-rpath,$ORIGIN/../../pulsatrix_b200"],
+                       check=True)
+    return CPP_TEST
 
 
 if __name__ == "__main__":
