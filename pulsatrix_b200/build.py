@@ -7,6 +7,7 @@ nvcc cross-compiles, so this works on a machine without a GPU.
 """
 from __future__ import annotations
 
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -19,6 +20,12 @@ HOST_SOURCES = ["determinism.cpp", "sampler.cpp", "backend.cpp", "generation.cpp
 CPP_TEST = PACKAGE.parent / "tests" / "cpp" / "host_api_test"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=true",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+
+def _profiling_flags() -> list[str]:
+    """PSX_B200_STAGE_CLOCKS=1 builds the kernels with per-stage clock stamps (a profiling aid: the
+    library then also exports psx_debug_stage_clocks / psx_debug_merge_clocks to read them back)."""
+    return ["-DPSX_STAGE_CLOCKS"] if os.environ.get("PSX_B200_STAGE_CLOCKS") == "1" else []
 
 
 def _stale() -> bool:
@@ -39,7 +46,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in SOURCES:
         obj = build_dir / (src + ".o")
-        cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = ["nvcc", *NVCC_FLAGS, *_profiling_flags(), *(["-Xptxas", "-v"] if verbose else []), "-c", str(CSRC / src),
+               "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objects.append(str(obj))
     include = str(PACKAGE.parent / "include")

@@ -14,18 +14,30 @@
 //   4. writes the token, float(log(exp(l - M) / Z)) of the raw logits (src/generation.cpp:156),
 //      a row status and the distances of the two decisions from their boundaries.
 // Reads a few KB per row; never touches the logits.
+#ifdef PSX_STAGE_CLOCKS
+// Profiling build only: thread 0 of each row's CTA stamps the SM clock at the stage boundaries.
+__device__ unsigned long long g_merge_clocks[1024 * 16];
+#define PSX_MERGE_STAGE(i) \
+    do { if (threadIdx.x == 0) g_merge_clocks[(size_t)(blockIdx.x & 1023) * 16 + (i)] = clock64(); } while (0)
+#endif
 #include "merge_rows_impl.cuh"
 
 namespace psx {
 
 namespace {
 
-__global__ void __launch_bounds__(kMergeThreads) merge_rows_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(kMergeThreads, 1) merge_rows_kernel(const MergeParams p) {
     extern __shared__ unsigned long long dyn[];
     survivor::merge_row(p, blockIdx.x, dyn);
 }
 
 }  // namespace
+
+#ifdef PSX_STAGE_CLOCKS
+extern "C" __attribute__((visibility("default"))) int psx_debug_merge_clocks(unsigned long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, g_merge_clocks, sizeof(unsigned long long) * n);
+}
+#endif
 
 size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, int segments) {
     return (size_t)sort_capacity * (8 + 8 + 8 + 1) + (size_t)gather_capacity * 8 + (size_t)(2 * segments + 1) * 4 + 16;

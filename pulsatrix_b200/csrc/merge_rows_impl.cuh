@@ -1,9 +1,12 @@
-// The survivor stage as device code, shared by its own kernel (merge_rows.cu) and by the row
-// pass (scan_rows.cu), whose last CTA of a row runs it directly when the list fits.
+// The survivor stage as device code, shared by the kernels that run it: one row per CTA.
 #pragma once
 
 #include "../../include/psx_b200.h"
 #include "merge_rows.cuh"
+
+#ifndef PSX_MERGE_STAGE
+#define PSX_MERGE_STAGE(i) do {} while (0)
+#endif
 
 namespace psx {
 namespace survivor {
@@ -137,58 +140,85 @@ __device__ __forceinline__ void block_rank_sort(u64* keys, int n, bool descendin
 // Step 3 of the survivor stage for a SHORT list (n <= blockDim.x, the usual case after a top-k or
 // for greedy): thread i owns entry i of the unsorted keys.  Places in the three orders the
 // reference walks (value descending, column ascending, and the top-p walk: value ascending then
-// column ascending) come from counting, so nothing is sorted; the per-entry divisions by the
-// softmax sums run in parallel; only the additions, whose order the reference fixes, are left to
-// thread 0 (src/generation.cpp:80-152).  Exact: same operations, same order, same precision.
-// work: shared scratch of at least 5 * blockDim.x 32-bit words + 2 * blockDim.x doubles.
+// column ascending) come from counting, so nothing is sorted; every thread drops what it
+// contributes into the slot of its place, so the additions, whose order the reference fixes, are
+// one thread running down a contiguous array, and the per-entry divisions by the softmax sums
+// run in parallel (src/generation.cpp:80-152).  Exact: same operations, same order, same precision.
 struct SmallScratch {
     uint32_t* order_b;  // entry of the j-th survivor by ascending column
-    uint32_t* order_w;  // entry of the j-th survivor of the ascending (value, column) walk
-    double* ex;         // exp(x - x_max) per entry
-    double* pr;         // ex / current sum per entry
-    uint8_t* alive;
+    uint32_t* cols;     // column of the j-th entry by (value descending, column ascending)
+    double* ex;         // per place: exp(x - x_max) by ascending column (0 for what a filter removed)
+    double* pr;         // per place: probabilities, in the order of the walk that reads them
+    uint8_t* alive;     // per entry (the min-p filter and the survivor export read it)
     uint32_t* shared;   // a few broadcast words
     double* sum;        // one broadcast double
 };
+
+// sum of v[0..n) in index order; the loads run ahead of the additions
+__device__ __forceinline__ double ordered_sum(const double* v, int n, double start) {
+    double sum = start;
+    int j = 0;
+    for (; j + 4 <= n; j += 4) {
+        const double a = v[j], b = v[j + 1], c = v[j + 2], d = v[j + 3];
+        sum += a; sum += b; sum += c; sum += d;
+    }
+    for (; j < n; ++j) sum += v[j];
+    return sum;
+}
 
 __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n, bool top_k_on, bool rest_in_play,
                              double rest, float keep_from_x, double u, const SmallScratch& w, Decision* result) {
     const int tid = threadIdx.x;
     const bool sample = p.do_sample != 0;
-    const bool have = tid < n;
-    const u64 mine = have ? keyA[tid] : 0;
+    // T threads (a power of two, neighbours in a warp) share the counting loop of one entry.
+    int n_pad = 8;
+    while (n_pad < n) n_pad <<= 1;
+    const int T = kMergeThreads / n_pad, shift_t = __ffs(T) - 1;
+    const int e = tid >> shift_t, slice = tid & (T - 1);
+    const bool in_range = e < n;
+    const bool have = in_range && slice == 0;  // the thread that owns entry e from here on
+    const u64 mine = in_range ? keyA[e] : 0;
     const uint32_t my_ord = key_ord(mine), my_col = key_col(mine);
+    const bool cut_k = top_k_on && n >= p.top_k;
 
-    int place = 0;  // among all n by (value desc, column asc): the keys compare that way as integers
-    if (have) {
-        for (int j = 0; j < n; ++j) place += keyA[j] > mine ? 1 : 0;
-        if (place == 0) { w.shared[0] = my_ord; w.shared[1] = (uint32_t)tid; }          // the first maximum
-        if (top_k_on && n >= p.top_k && place == (int)p.top_k - 1) w.shared[2] = my_ord;  // the k-th value
+    // Among all n: how many come before mine by (value desc, column asc) -- the keys compare that
+    // way as integers --, how many of those share my value, and how many share my value at all.
+    uint32_t counts = 0;  // three 10-bit fields
+    if (in_range) {
+        for (int j = slice; j < n; j += T) {
+            const u64 other = keyA[j];
+            const uint32_t before = other > mine ? 1u : 0u, same = key_ord(other) == my_ord ? 1u : 0u;
+            counts += before + ((before & same) << 10) + (same << 20);
+        }
     }
-    if (tid == 0 && !(top_k_on && n >= p.top_k)) w.shared[2] = 0;
+    for (int o = T >> 1; o > 0; o >>= 1) counts += __shfl_xor_sync(0xFFFFFFFFu, counts, o);
+    const int place = (int)(counts & 1023u), same_before = (int)((counts >> 10) & 1023u), same = (int)(counts >> 20);
+    if (have) {
+        if (place == 0) { w.shared[0] = my_ord; w.shared[1] = (uint32_t)e; }  // the first maximum
+        if (cut_k && place == (int)p.top_k - 1) w.shared[2] = my_ord;        // the k-th value
+    }
+    if (tid == 0 && !cut_k) w.shared[2] = 0;
     __syncthreads();
+    PSX_MERGE_STAGE(10);
     const uint32_t top_ord = w.shared[0], best = w.shared[1], kth = w.shared[2];
     const bool survivor = have && my_ord >= kth;  // src/generation.cpp:85: ties at the k-th value stay
+    if (survivor) w.cols[place] = my_col;         // the survivors are exactly the first ns places
     const int ns = __syncthreads_count(survivor ? 1 : 0);
     bool rest_alive = !top_k_on && sample && rest_in_play;
 
-    int place_b = 0, place_w = 0;
+    // Place by ascending column among the survivors, and in the top-p walk (value ascending, then
+    // column ascending): the survivors below my value, plus those of my value at lower columns.
+    int place_b = 0;
+    const int place_w = ns - (place - same_before) - same + same_before;
     double my_ex = 0.0;
     if (survivor) {
-        for (int j = 0; j < n; ++j) {
-            const uint32_t o = key_ord(keyA[j]), c = key_col(keyA[j]);
-            if (o < kth) continue;
-            place_b += c < my_col ? 1 : 0;
-            place_w += (o < my_ord || (o == my_ord && c < my_col)) ? 1 : 0;
-        }
+        for (int j = 0; j < ns; ++j) place_b += w.cols[j] < my_col ? 1 : 0;
         my_ex = exp((double)from_ordered_key(my_ord) - (double)from_ordered_key(top_ord));  // src/generation.cpp:46
-        w.order_b[place_b] = (uint32_t)tid;
-        w.order_w[place_w] = (uint32_t)tid;
-        w.ex[tid] = my_ex;
-        w.alive[tid] = 1;
-    } else if (have) {
-        w.alive[tid] = 0;
+        w.order_b[place_b] = (uint32_t)e;
+        w.ex[place_b] = my_ex;
     }
+    PSX_MERGE_STAGE(11);
+    bool alive = survivor;
     Decision d;
     d.status = PSX_ROW_OK;
     d.token = -1;
@@ -198,44 +228,54 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
     __syncthreads();
 
     if (sample && p.top_p < 1.0f) {  // src/generation.cpp:89-103
-        if (tid == 0) {
-            double sum = rest_alive ? rest : 0.0;
-            for (int j = 0; j < ns; ++j) sum += w.ex[w.order_b[j]];  // column order, as the reference sums
-            *w.sum = sum;
-        }
+        if (tid == 0) *w.sum = ordered_sum(w.ex, ns, rest_alive ? rest : 0.0);  // column order, as the reference sums
         __syncthreads();
-        if (survivor) w.pr[tid] = my_ex / *w.sum;
+        if (survivor) w.pr[place_w] = my_ex / *w.sum;
         __syncthreads();
         if (tid == 0) {
             const double limit = 1.0 - (double)p.top_p;
             double cumulative = 0.0;
             if (rest_alive) {  // everything outside the list leads the ascending walk and must fall as a whole
                 cumulative = rest / *w.sum;
-                d.top_p_margin = fabs(cumulative - limit);
                 if (!(cumulative <= limit)) d.status = PSX_ROW_TOO_WIDE;
             }
-            for (int j = 0; j + 1 < ns && d.status == PSX_ROW_OK; ++j) {  // the last of the walk always stays
-                const uint32_t e = w.order_w[j];
-                cumulative += w.pr[e];
-                d.top_p_margin = fmin(d.top_p_margin, fabs(cumulative - limit));
-                if (cumulative <= limit) w.alive[e] = 0; else break;
+            int cut = 0;  // places of the walk below `cut` are removed; the last of the walk always stays
+            double over = INFINITY;
+            if (d.status == PSX_ROW_OK) {
+                double next = ns > 1 ? w.pr[0] : 0.0;
+                for (; cut + 1 < ns; ++cut) {
+                    const double upto = cumulative + next;
+                    next = w.pr[cut + 1];  // in range: cut + 1 < ns
+                    if (!(upto <= limit)) { over = upto; break; }
+                    cumulative = upto;
+                }
             }
+            // The running sum only grows, so of all the sums compared with the limit the nearest
+            // are the last one at or below it and the first one above it.
+            if (cut > 0 || rest_alive) d.top_p_margin = fabs(cumulative - limit);
+            d.top_p_margin = fmin(d.top_p_margin, fabs(over - limit));
+            w.shared[4] = (uint32_t)cut;
         }
         rest_alive = false;
         __syncthreads();
+        alive = survivor && place_w >= (int)w.shared[4];
     }
+    PSX_MERGE_STAGE(12);
 
     if (sample && p.min_p > 0.0f) {  // src/generation.cpp:104-111 (rare: left to one thread)
+        if (have) w.alive[e] = alive ? 1 : 0;
+        if (have && e == (int)best) w.shared[5] = (uint32_t)place_b;
+        __syncthreads();
         if (tid == 0 && d.status == PSX_ROW_OK) {
             double sum = rest_alive ? rest : 0.0;
             for (int j = 0; j < ns; ++j) {
-                const uint32_t e = w.order_b[j];
-                if (w.alive[e]) sum += w.ex[e];
+                if (w.alive[w.order_b[j]]) sum += w.ex[j];
             }
-            const double floor_p = p.min_p * (w.ex[best] / sum);
+            const uint32_t best_place = w.shared[5];
+            const double floor_p = p.min_p * (w.ex[best_place] / sum);
             for (int j = 0; j < ns; ++j) {
-                const uint32_t e = w.order_b[j];
-                if (w.alive[e] && e != best && w.ex[e] / sum < floor_p) w.alive[e] = 0;
+                const uint32_t o = w.order_b[j];
+                if (w.alive[o] && o != best && w.ex[j] / sum < floor_p) w.alive[o] = 0;
             }
             if (rest_alive) {
                 const double bound = exp((double)keep_from_x - (double)from_ordered_key(top_ord));
@@ -245,44 +285,44 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
         if (tid == 0) w.shared[3] = (rest_alive && d.status == PSX_ROW_OK && w.shared[3] != 0) ? 1u : 0u;
         __syncthreads();
         rest_alive = rest_alive && w.shared[3] != 0;
+        alive = have && w.alive[e] != 0;
     }
+    PSX_MERGE_STAGE(13);
 
     if (sample) {  // src/generation.cpp:140-152
+        if (survivor) w.ex[place_b] = alive ? my_ex : 0.0;  // adding 0.0 leaves the sum as skipping does
+        const int alive_count = __syncthreads_count(alive ? 1 : 0);
         if (tid == 0) {
-            double sum = 0.0;
-            int alive_count = 0;
-            for (int j = 0; j < ns; ++j) {
-                const uint32_t e = w.order_b[j];
-                if (w.alive[e]) { sum += w.ex[e]; ++alive_count; }
-            }
-            *w.sum = sum;
+            *w.sum = ordered_sum(w.ex, ns, 0.0);
             d.survivors = alive_count;
             if (rest_alive && d.status == PSX_ROW_OK) d.status = PSX_ROW_TOO_WIDE;
         }
         __syncthreads();
-        if (survivor) w.pr[tid] = my_ex / *w.sum;
+        if (survivor) w.pr[place_b] = alive ? my_ex / *w.sum : 0.0;
         __syncthreads();
         if (tid == 0 && d.status == PSX_ROW_OK) {
             double cumulative = 0.0, before = 0.0;
-            long long chosen = key_col(keyA[best]);
+            int chosen = -1;
+            double next = w.pr[0];
             for (int j = 0; j < ns; ++j) {
-                const uint32_t e = w.order_b[j];
-                if (!w.alive[e]) continue;
-                const double pr = w.pr[e];
-                if (pr == 0.0) continue;
+                const double pr = next;
+                if (j + 1 < ns) next = w.pr[j + 1];
+                if (pr == 0.0) continue;  // removed, or a probability that underflowed: never drawn
                 before = cumulative;
                 cumulative += pr;
-                chosen = key_col(keyA[e]);
+                chosen = j;
                 if (u < cumulative) break;
             }
             const double lo = fabs(u - before), hi = fabs(u - cumulative);
             d.draw_margin = before == 0.0 ? hi : fmin(lo, hi);
-            d.token = chosen;
+            d.token = key_col(keyA[chosen >= 0 ? w.order_b[chosen] : best]);
         }
     } else if (tid == 0) {
         d.survivors = ns;
         d.token = key_col(keyA[best]);  // src/generation.cpp:135: the first maximum, lower column wins
     }
+    PSX_MERGE_STAGE(14);
+    if (have) w.alive[e] = alive ? 1 : 0;  // what survived, for a caller that wants the set itself
     if (tid == 0) *result = d;
     __syncthreads();
 }
@@ -453,46 +493,58 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
     return true;
 }
 
-// The k-th largest (1-based, k <= m) of m uint32 keys in shared memory: four 8-bit radix passes,
-// most significant digit first.  hist has 256 entries, state two.  Called by the whole block.
-__device__ inline uint32_t block_select_kth(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, uint32_t* state) {
+// The k-th largest (1-based, k <= m) of m 32-bit keys (key_at(i), i < m): four 8-bit radix
+// passes, most significant digit first, one barrier each -- every pass has its own 256-bin
+// histogram (hist: 1024 words, all zero on entry, not zero on exit), and every warp scans the
+// bins for itself instead of waiting for one warp's answer.  Called by the whole block.
+template <class KeyAt>
+__device__ inline uint32_t block_select_kth(KeyAt key_at, int m, uint32_t k, uint32_t* hist) {
     const int tid = threadIdx.x, lane = tid & 31;
     uint32_t prefix = 0, mask = 0, remaining = k;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        hist[tid] = 0;  // kMergeThreads == 256 bins
-        __syncthreads();
-        for (int i = tid; i < m; i += kMergeThreads) {
-            const uint32_t key = keys[i];
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+#pragma unroll 1
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        uint32_t* h = hist + 256 * pass;
+        for (int base = 0; base < m; base += kMergeThreads) {
+            // Keys that share a digit (the leading digits of neighbouring floats, or plain ties) are
+            // counted by one lane for all of them.
+            const int i = base + tid;
+            const uint32_t key = i < m ? key_at(i) : 0u;
+            const bool counted = i < m && (key & mask) == prefix;
+            const uint32_t bin = counted ? (key >> shift) & 255u : 256u;
+            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, bin);
+            if (counted && lane == __ffs(peers) - 1) atomicAdd(&h[bin], (uint32_t)__popc(peers));
         }
         __syncthreads();
-        if (tid < 32) {
-            // lane L owns digits 255-8L down to 248-8L; find where the count from the top reaches `remaining`
-            uint32_t local = 0;
-            for (int b = 0; b < 8; ++b) local += hist[255 - 8 * lane - b];
-            uint32_t incl = local;
+        // lane L owns digits 255-8L down to 248-8L; find where the count from the top reaches `remaining`
+        const uint4 lo4 = reinterpret_cast<const uint4*>(h)[62 - 2 * lane], hi4 = reinterpret_cast<const uint4*>(h)[63 - 2 * lane];
+        const uint32_t bins[8] = {hi4.w, hi4.z, hi4.y, hi4.x, lo4.w, lo4.z, lo4.y, lo4.x};  // digit 255-8L first
+        uint32_t local = 0;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += up;
-            }
-            const uint32_t excl = incl - local;
-            if (excl < remaining && remaining <= incl) {
-                uint32_t above = excl;
-                int digit = 255 - 8 * lane;
-                for (int b = 0; b < 8; ++b, --digit) {
-                    if (above + hist[digit] >= remaining) break;
-                    above += hist[digit];
-                }
-                state[0] = prefix | ((uint32_t)digit << shift);
-                state[1] = remaining - above;
-            }
+        for (int b2 = 0; b2 < 8; ++b2) local += bins[b2];
+        uint32_t incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
         }
-        __syncthreads();
-        prefix = state[0];
-        remaining = state[1];
+        const uint32_t excl = incl - local;
+        const bool here = excl < remaining && remaining <= incl;
+        uint32_t digit = 0, left = 0;
+        if (here) {
+            uint32_t above = excl;
+            int b2 = 0;
+#pragma unroll
+            for (int q = 0; q < 7; ++q) {
+                if (b2 == q && above + bins[q] < remaining) { above += bins[q]; b2 = q + 1; }
+            }
+            digit = (uint32_t)(255 - 8 * lane - b2);
+            left = remaining - above;
+        }
+        const int src = __ffs(__ballot_sync(0xFFFFFFFFu, here)) - 1;  // exactly one lane while k <= m
+        prefix |= __shfl_sync(0xFFFFFFFFu, digit, src < 0 ? 0 : src) << shift;
+        remaining = __shfl_sync(0xFFFFFFFFu, left, src < 0 ? 0 : src);
         mask |= 255u << shift;
-        __syncthreads();
     }
     return prefix;
 }
@@ -519,8 +571,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     __shared__ int s_ns;
     __shared__ uint32_t s_chosen_raw;
     __shared__ Decision s_dec;
-    __shared__ uint32_t s_hist[256];
-    __shared__ uint32_t s_state[2];
+    __shared__ __align__(16) uint32_t s_hist[4 * 256];  // the selection's histograms, one per pass
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool apply_t = p.apply_temperature != 0;
@@ -528,6 +579,19 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     const char* counts_row = static_cast<const char*>(p.seg_counts) + row * p.count_row_stride;
     const char* cands_row = static_cast<const char*>(p.candidates) + row * p.cand_row_stride;
     auto part_stats = [&](int i) { return *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride); };
+
+    PSX_MERGE_STAGE(0);
+    // The first 32 slots of this warp's first kSpec segments are fetched before their counts are
+    // known (the slots exist whatever the count), so the candidates cost one trip to memory, not two.
+    constexpr int kSpec = 16;
+    constexpr int kWarps = kMergeThreads / 32;
+    uint2 spec[kSpec];
+#pragma unroll
+    for (int q = 0; q < kSpec; ++q) {
+        const int sg = warp + q * kWarps;
+        if (sg < nseg) spec[q] = reinterpret_cast<const uint2*>(cands_row + sg * p.cand_seg_stride)[lane];
+    }
+    const double u_row = (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5;
 
     // ---- 1. join the parts; lay the candidate segments out back to back ---------------------------
     float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
@@ -559,7 +623,9 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     }
     if (lane == 31) s_u[warp] = incl;
     if (tid == 0) s_count = 0;
-    {   // one barrier for all five reductions; it also publishes s_u and seg_size
+    reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);
+    bool hist_clean = true;
+    {   // one barrier for all five reductions; it also publishes s_u, seg_size and the cleared s_hist
         raw_max = warp_max(raw_max);
         y_max = warp_max(y_max);
         thr = warp_max(thr);
@@ -581,6 +647,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
             alive_tail += s_d[1][w];
         }
     }
+    PSX_MERGE_STAGE(1);
     uint32_t running = incl - mine;
     for (int w = 0; w < warp; ++w) running += s_u[w];
     for (int j = 0; j < per_thread; ++j) {
@@ -592,6 +659,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         }
     }
     __syncthreads();
+    PSX_MERGE_STAGE(2);
     const int total = (int)seg_begin[nseg];
     const uint32_t bad_bits = (uint32_t)bad;
     if (bad_bits != 0 || total > gcap) {
@@ -604,39 +672,46 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         }
         return;
     }
-    // Independent loads, a few per thread: every candidate of the row into shared memory.
-    for (int i = tid; i < total; i += kMergeThreads) {
-        int lo = 0, hi = nseg;  // the segment s with seg_begin[s] <= i < seg_begin[s + 1]
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (seg_begin[mid] <= (uint32_t)i) lo = mid; else hi = mid;
+    // Every candidate of the row into shared memory, segment by segment.
+#pragma unroll
+    for (int q = 0; q < kSpec; ++q) {
+        const int sg = warp + q * kWarps;
+        if (sg < nseg) {
+            const int count = (int)seg_size[sg], begin = (int)seg_begin[sg];
+            if (lane < count) {
+                cand_l[begin + lane] = spec[q].x;
+                cand_c[begin + lane] = spec[q].y;
+            }
+            for (int i = lane + 32; i < count; i += 32) {
+                const uint2 c = reinterpret_cast<const uint2*>(cands_row + sg * p.cand_seg_stride)[i];
+                cand_l[begin + i] = c.x;
+                cand_c[begin + i] = c.y;
+            }
         }
-        const uint2 c = reinterpret_cast<const uint2*>(cands_row + lo * p.cand_seg_stride)[i - (int)seg_begin[lo]];
-        cand_l[i] = c.x;
-        cand_c[i] = c.y;
+    }
+    for (int sg = warp + kSpec * kWarps; sg < nseg; sg += kWarps) {
+        const int count = (int)seg_size[sg], begin = (int)seg_begin[sg];
+        for (int i = lane; i < count; i += 32) {
+            const uint2 c = reinterpret_cast<const uint2*>(cands_row + sg * p.cand_seg_stride)[i];
+            cand_l[begin + i] = c.x;
+            cand_c[begin + i] = c.y;
+        }
     }
     __syncthreads();
 
+    PSX_MERGE_STAGE(3);
     if (p.debug_stop == 1) return;
     float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
     const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
 
-    // Every part handed on at least k logits, so together they hold far more than the k that a
-    // top-k keeps.  The k-th largest of everything collected IS the row's k-th largest (the union
-    // contains the true top k): select it, and only it and what ties with it after the
-    // temperature divide go on to the sort.  Greedy keeps the maximum and its ties.
-    if (!p.do_sample) {
-        keep_from = fmaxf(y_max, -FLT_MAX);
-    } else if (top_k_on && total > p.top_k) {
-        for (int i = tid; i < total; i += kMergeThreads) {
-            ykeys[i] = ordered_key(processed_before_temperature(__uint_as_float(cand_l[i]), cand_c[i], p.penalty));
-        }
-        __syncthreads();
-        const uint32_t kth = block_select_kth(ykeys, total, (uint32_t)p.top_k, s_hist, s_state);
-        keep_from = fmaxf(keep_from, relax_threshold(from_ordered_key(kth), apply_t, p.temperature));
-    }
+    // Greedy keeps the maximum and its ties.  With a top-k, the largest part threshold is already a
+    // lower bound of the row's k-th largest (that part alone has k logits at or above it), and
+    // what reaches it is usually short enough for the one-entry-per-thread path, which finds the
+    // k-th value itself; only a longer list pays for an exact selection first (below).
+    if (!p.do_sample) keep_from = fmaxf(y_max, -FLT_MAX);
 
+    PSX_MERGE_STAGE(4);
     if (p.debug_stop == 2) return;
     // ---- 2. raw sum-exp over everything; the list of those that can survive ------------------------
     double z_raw = 0.0, z_rest = 0.0, dropped = 0.0;
@@ -676,7 +751,35 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
             dropped += s_d[2][w];
         }
     }
-    const int n = s_count;
+    PSX_MERGE_STAGE(5);
+    int n = s_count;
+    if (top_k_on && total > p.top_k && n > cap) {
+        // Too many reach the largest part threshold for the list.  Every part handed on at least
+        // k logits, so together they hold the k that a top-k keeps: the k-th largest of everything
+        // collected IS the row's k-th largest.  Select it; only it and what ties with it after the
+        // temperature divide go on the list.
+        for (int i = tid; i < total; i += kMergeThreads) {
+            ykeys[i] = ordered_key(processed_before_temperature(__uint_as_float(cand_l[i]), cand_c[i], p.penalty));
+        }
+        if (tid == 0) s_count = 0;
+        __syncthreads();
+        const uint32_t kth = block_select_kth([&](int i) { return ykeys[i]; }, total, (uint32_t)p.top_k, s_hist);
+        hist_clean = false;
+        keep_from = fmaxf(keep_from, relax_threshold(from_ordered_key(kth), apply_t, p.temperature));
+        __syncthreads();  // ykeys lies over the list that is written next
+        for (int i = tid; i < total; i += kMergeThreads) {
+            const uint32_t cf = cand_c[i];
+            const float y = processed_before_temperature(__uint_as_float(cand_l[i]), cf, p.penalty);
+            if (y >= keep_from) {
+                const int slot = atomicAdd(&s_count, 1);
+                if (slot < cap) {
+                    keyA[slot] = ((u64)ordered_key(temper(y, apply_t, p.temperature)) << 32) | (uint32_t)~(cf & kColumnMask);
+                }
+            }
+        }
+        __syncthreads();
+        n = s_count;
+    }
     if (n > cap || n == 0) {
         if (tid == 0) {
             p.tokens[row] = -1;
@@ -687,6 +790,27 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         return;
     }
 
+    constexpr int kCountDirectly = 64;  // up to here the one-entry-per-thread path finds the k-th value by counting
+    if (top_k_on && n > kCountDirectly && n > p.top_k) {
+        // A top-k over a longer list: the k-th largest value by radix selection, then only it, its
+        // ties and what lies above stay (src/generation.cpp:80-87).
+        if (!hist_clean) {
+            for (int i = tid; i < 4 * 256; i += kMergeThreads) s_hist[i] = 0;
+        }
+        if (tid == 0) s_ns = 0;
+        __syncthreads();
+        const uint32_t kth = block_select_kth([&](int i) { return key_ord(keyA[i]); }, n, (uint32_t)p.top_k, s_hist);
+        u64* kept = reinterpret_cast<u64*>(ex);
+        for (int i = tid; i < n; i += kMergeThreads) {
+            const u64 key = keyA[i];
+            if (key_ord(key) >= kth) kept[atomicAdd(&s_ns, 1)] = key;
+        }
+        __syncthreads();
+        n = s_ns;
+        for (int i = tid; i < n; i += kMergeThreads) keyA[i] = kept[i];
+        __syncthreads();
+    }
+    PSX_MERGE_STAGE(6);
     if (p.debug_stop == 3) return;
     // ---- 3'. a long list without a top-k: decided by the whole block, without sorting --------------
     bool decided = false;
@@ -702,7 +826,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         const bool rest_in_play = (alive_tail + dropped) > 0.0;
         const double bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_top);
         Decision wide;
-        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, p.uniforms ? p.uniforms[row] : 0.5,
+        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, u_row,
                               s_d[0], wide);
         __syncthreads();
         if (decided && tid == 0) {
@@ -715,8 +839,8 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         // ---- 3''. a short list (the usual case): one entry per thread, nothing sorted ---------------
         SmallScratch w;
         w.order_b = reinterpret_cast<uint32_t*>(keyB);
-        w.order_w = w.order_b + kMergeThreads;
-        w.shared = w.order_w + kMergeThreads;          // 8 words
+        w.cols = w.order_b + kMergeThreads;
+        w.shared = w.cols + kMergeThreads;             // 8 words
         w.pr = reinterpret_cast<double*>(w.shared + 8);
         w.ex = ex;
         w.alive = alive;
@@ -725,7 +849,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         __syncthreads();
         decide_small(p, keyA, n, top_k_on, (alive_tail + dropped) > 0.0, z_rest,
                      temper(keep_from, apply_t, p.temperature),
-                     (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5, w, &s_dec);
+                     u_row, w, &s_dec);
         if (tid == 0) s_chosen_raw = 0;
         decided = true;
     }
@@ -776,12 +900,12 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
 
     // ---- 4. the reference's walk, by one thread ------------------------------------------------------
     if (tid == 0) {
-        const double u = (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5;
-        decide(p, keyA, keyB, ex, alive, ns, rest_alive, z_rest, rest_bound, u, s_dec);
+        decide(p, keyA, keyB, ex, alive, ns, rest_alive, z_rest, rest_bound, u_row, s_dec);
         s_chosen_raw = 0;
     }
     }  // !decided
     __syncthreads();
+    PSX_MERGE_STAGE(7);
     if (p.debug_stop == 4) return;
     Decision dec = s_dec;
     if (p.survivor_cols != nullptr && dec.status == PSX_ROW_OK) {  // hand the surviving set itself out
@@ -799,6 +923,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         if (s_count > p.survivor_cap) dec.status = PSX_ROW_TOO_WIDE;
         if (tid == 0) p.survivor_counts[row] = (uint32_t)min(s_count, p.survivor_cap);
     }
+    PSX_MERGE_STAGE(8);
     if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
         for (int i = tid; i < total; i += kMergeThreads) {
             if ((long long)(cand_c[i] & kColumnMask) == dec.token) s_chosen_raw = cand_l[i];
@@ -816,6 +941,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         p.log_probs[row] = lp;
         if (p.diag) p.diag[row] = psx_row_diag{n, dec.survivors, dec.draw_margin, dec.top_p_margin};
     }
+    PSX_MERGE_STAGE(9);
 }
 
 

@@ -55,6 +55,14 @@ __device__ __forceinline__ float temper(float y, bool apply, float temperature) 
     return apply ? __fdiv_rn(y, temperature) : y;
 }
 
+// The float just below q (nextafterf(q, -inf)) in integer arithmetic; -inf and NaN stay as they are.
+__device__ __forceinline__ float next_below(float q) {
+    const uint32_t b = __float_as_uint(q);
+    if (q != q || b == 0xFF800000u) return q;
+    if ((b << 1) == 0u) return __uint_as_float(0x80000001u);  // below +-0: the smallest negative subnormal
+    return __uint_as_float((b & 0x80000000u) ? b + 1u : b - 1u);
+}
+
 // A value t' <= t such that y < t' implies y / T < t / T after rounding: dividing by the
 // temperature can map neighbouring floats to the same quotient, and every logit whose quotient
 // ties with the threshold's must be kept as a candidate.  Never below -FLT_MAX, so that -inf
@@ -63,7 +71,7 @@ __device__ __forceinline__ float relax_threshold(float t, bool apply_temp, float
     float r = t;
     if (apply_temp && t > -INFINITY) {
         const float q = __fdiv_rn(t, temperature);
-        const float below = nextafterf(q, -INFINITY);
+        const float below = next_below(q);
         r = __fmul_rd(temperature, below);
         if (!(r <= t)) r = (r != r) ? -INFINITY : t;
     }

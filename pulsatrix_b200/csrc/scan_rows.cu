@@ -95,15 +95,25 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
 
 constexpr int kPool = 64 / kScanWarps;  // per-thread maxima a warp can offer to the pooled threshold (64 in all)
 
-// What warp 0 works out for the part after pass one and every thread needs in pass two.
-struct PartConstants {
-    float cmax, cymax, camax, thr, tprime, c_l2, c_res, pc_l2, pc_res;
-};
-
 }  // namespace
+
+// Profiling build only (-DPSX_STAGE_CLOCKS): thread 0 of each CTA stamps the SM clock at the stage
+// boundaries; the stamps of the first 4096 CTAs are kept for psx_debug_stage_clocks to read back.
+#ifdef PSX_STAGE_CLOCKS
+__device__ unsigned long long g_stage_clocks[4096 * 16];
+#define STAGE(i) do { if (threadIdx.x == 0) clk[i] = clock64(); } while (0)
+#else
+#define STAGE(i) do {} while (0)
+#endif
 
 template <bool kNucleus>
 __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParams p) {
+#ifdef PSX_STAGE_CLOCKS
+    unsigned long long clk[16];
+    for (int i = 0; i < 16; ++i) clk[i] = 0;
+    unsigned long long gt0; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt0));
+    STAGE(0);
+#endif
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     float* data = reinterpret_cast<float*>(dyn_smem);
     const float4* data4 = reinterpret_cast<const float4*>(dyn_smem);
@@ -114,7 +124,6 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     uint32_t* const s_ban = s_bits + kBitmapWords;
     __shared__ float s_wraw[kScanWarps], s_wamax[kScanWarps], s_wymax[kScanWarps], s_wthr[kScanWarps];
     __shared__ uint32_t s_pool[kScanWarps * kPool];
-    __shared__ PartConstants s_const;
     __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
     __shared__ uint32_t s_wfill[kScanWarps];
 
@@ -149,6 +158,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     static_assert(2 * kBitmapWords == 4 * kScanThreads, "one 16-byte store per thread clears both bitmaps");
     reinterpret_cast<uint4*>(s_bits)[tid] = make_uint4(0, 0, 0, 0);
     __syncthreads();
+    STAGE(1);
     if (tid == 0) {
         const uint32_t bytes = (uint32_t)nvec * 16u;
         const char* src = reinterpret_cast<const char*>(vbase + v0);
@@ -165,6 +175,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, first_pos, nvec * 4, s_ban);
     // One warp watches the copy; the others sleep in the block barrier, which also orders the
     // copied bytes before everybody's reads.
+    STAGE(2);
     const bool landed = warp == 0 ? barrier_wait_bounded(&s_bar, 0) : true;
     if (!__syncthreads_and(landed ? 1 : 0)) {
         // The copy did not complete in time: report it, give it one more bounded chance to drain
@@ -180,20 +191,25 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         return;
     }
 
+    STAGE(3);
     // Pad the part to whole 256-vector trips (at most one vector per thread).
     {
+        // Every shared-memory write from here on is made by the thread that owns the vector in the
+        // dense passes (vector v belongs to thread v % kScanThreads) or by a thread of its warp, so
+        // warp-level ordering is enough and the warps run on without meeting again until the
+        // threshold.
         const int padded = (nvec + kScanThreads - 1) / kScanThreads * kScanThreads;
-        if (nvec + tid < padded) reinterpret_cast<float4*>(dyn_smem)[nvec + tid] = make_float4(kPad, kPad, kPad, kPad);
+        const int v = padded - kScanThreads + tid;
+        if (v >= nvec) reinterpret_cast<float4*>(dyn_smem)[v] = make_float4(kPad, kPad, kPad, kPad);
     }
     // Components of the first and last vector that lie outside the row are blanked.
-    if (tid == 0) {
-        if (v0 == 0) {
-            for (uint32_t c = 0; c < misalign; ++c) data[c] = kPad;
-        }
-        if (v1 == nv) {
-            for (int64_t pos = (int64_t)misalign + p.cols; pos < (int64_t)nv * 4; ++pos) data[pos - (int64_t)v0 * 4] = kPad;
-        }
+    if (v0 == 0 && tid == 0) {
+        for (uint32_t c = 0; c < misalign; ++c) data[c] = kPad;
     }
+    if (v1 == nv && tid == ((nvec - 1) & (kScanThreads - 1))) {
+        for (int64_t pos = (int64_t)misalign + p.cols; pos < (int64_t)nv * 4; ++pos) data[pos - (int64_t)v0 * 4] = kPad;
+    }
+    __syncwarp();
 
     // ---- 1. flagged logits: handed on in bitmap order, then blanked ---------------------------------
     uint2* seg_out = p.candidates + seg * kSegCap;
@@ -246,7 +262,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             }
         }
     }
-    __syncthreads();
+    __syncwarp();
+    STAGE(4);
 
     // ---- 2. per-thread maxima, then the part's raw max and selection threshold -------------------------
     float m = kPad, amax = f_amax;
@@ -263,6 +280,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             amax = amax_into(amax, d);
         }
     }
+    STAGE(5);
     const float m_alive = (m == kPad) ? -INFINITY : m;  // a thread without logits takes no part in the selection
     const int live_threads = min(kScanThreads, nvec);
     const int full_warps = live_threads >> 5;  // warps whose every thread owns a vector
@@ -278,13 +296,17 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         const float wymax = warp_max_redux(fmaxf(m_alive, f_y));
         float wthr = -INFINITY;
         if (pooled) {
-            uint32_t key = monotone_key(m_alive);
-            for (int i = 0; i < kp; ++i) {  // the warp's kp largest, in descending order
-                const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, key);
-                if (lane == 0) s_pool[warp * kPool + i] = top;
-                const uint32_t holders = __ballot_sync(0xFFFFFFFFu, key == top);
-                if (lane == __ffs(holders) - 1) key = 0;
+            uint32_t offer = 0xFFFFFFFFu;  // lane i ends up with the warp's i-th largest; all ones: no entry
+            if (warp < full_warps) {
+                uint32_t key = monotone_key(m_alive);
+                for (int i = 0; i < kp; ++i) {
+                    const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, key);
+                    if (lane == i) offer = top;
+                    const uint32_t holders = __ballot_sync(0xFFFFFFFFu, key == top);
+                    if (lane == __ffs(holders) - 1) key = 0;
+                }
             }
+            if (lane < kPool) s_pool[warp * kPool + lane] = offer;
         } else if (kp <= 32) {
             wthr = warp_kth_largest(m_alive, kp, lane);
         }
@@ -296,21 +318,24 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         }
     }
     __syncthreads();
+    STAGE(6);
 
-    // ---- warp 0 joins the warps and works out the part's constants ----------------------------------
-    if (warp == 0) {
-        const float cmax = warp_max_redux(lane < kScanWarps ? s_wraw[lane] : kPad);
-        const float camax = warp_max_redux(lane < kScanWarps ? s_wamax[lane] : 0.0f);
-        const float cymax = warp_max_redux(lane < kScanWarps ? s_wymax[lane] : -INFINITY);
-        float thr = -INFINITY;
-        if (pooled) {
-            // Lane L holds pool entries L and L + 32 (absent: all ones); drop the smallest
-            // entries until k_need are left, whose minimum is the threshold.
-            const int entries = full_warps * kp;
-            const int i0 = lane, i1 = lane + 32;
-            uint32_t a = i0 < entries ? s_pool[(i0 / kp) * kPool + i0 % kp] : 0xFFFFFFFFu;
-            uint32_t b2 = i1 < entries ? s_pool[(i1 / kp) * kPool + i1 % kp] : 0xFFFFFFFFu;
-            for (int i = p.k_need; i < entries; ++i) {
+    // ---- every warp joins the warps' results and works out the part's constants for itself --------------
+    const float cmax = warp_max_redux(lane < kScanWarps ? s_wraw[lane] : kPad);
+    const float camax = warp_max_redux(lane < kScanWarps ? s_wamax[lane] : 0.0f);
+    const float cymax = warp_max_redux(lane < kScanWarps ? s_wymax[lane] : -INFINITY);
+    float thr = -INFINITY;
+    if (pooled) {
+        // Lane L holds pool entries L and L + 32; the smallest entries are dropped until k_need
+        // are left, whose minimum is the threshold.
+        static_assert(kPool * kScanWarps == 64, "two pool entries per lane");
+        uint32_t a = s_pool[lane], b2 = s_pool[lane + 32];
+        if (p.k_need == 1) {  // the largest entry
+            const uint32_t top = max(a == 0xFFFFFFFFu ? 0u : a, b2 == 0xFFFFFFFFu ? 0u : b2);
+            thr = from_ordered_key(__reduce_max_sync(0xFFFFFFFFu, top));
+        } else {
+            const int surplus = full_warps * kp - p.k_need;
+            for (int i = 0; i < surplus; ++i) {
                 const uint32_t mine = min(a, b2);
                 const uint32_t low = __reduce_min_sync(0xFFFFFFFFu, mine);
                 const uint32_t holders = __ballot_sync(0xFFFFFFFFu, mine == low);
@@ -319,27 +344,18 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
                 }
             }
             thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, min(a, b2)));
-        } else if (full_warps > 0 && kp <= 32) {
-            const uint32_t key = lane < full_warps ? monotone_key(s_wthr[lane]) : 0xFFFFFFFFu;
-            thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, key));
         }
-        if (lane == 0) {
-            PartConstants c;
-            c.cmax = cmax;
-            c.cymax = cymax;
-            c.camax = camax;
-            c.thr = thr;
-            // Blanked slots hold kPad and must never pass: the threshold stays one step above it.
-            c.tprime = fmaxf(relax_threshold(thr, p.apply_temperature != 0, p.temperature), -3.4028233e38f);
-            c.c_l2 = __fmul_rn(cmax, kLog2e);
-            c.c_res = __fmaf_rn(cmax, kLog2e, -c.c_l2);  // cmax*kLog2e = c_l2 + c_res exactly
-            c.pc_l2 = __fmul_rn(cymax, p.log2e_over_t);
-            c.pc_res = __fmaf_rn(cymax, p.log2e_over_t, -c.pc_l2);
-            s_const = c;
-        }
+    } else if (full_warps > 0 && kp <= 32) {
+        const uint32_t key = lane < full_warps ? monotone_key(s_wthr[lane]) : 0xFFFFFFFFu;
+        thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, key));
     }
-    __syncthreads();
-    const float tprime = s_const.tprime, c_l2 = s_const.c_l2, pc_l2 = s_const.pc_l2;
+    // Blanked slots hold kPad and must never pass: the threshold stays one step above it.
+    const float tprime = fmaxf(relax_threshold(thr, p.apply_temperature != 0, p.temperature), -3.4028233e38f);
+    const float c_l2 = __fmul_rn(cmax, kLog2e);
+    const float c_res = __fmaf_rn(cmax, kLog2e, -c_l2);  // cmax*kLog2e = c_l2 + c_res exactly
+    const float pc_l2 = __fmul_rn(cymax, p.log2e_over_t);
+    const float pc_res = __fmaf_rn(cymax, p.log2e_over_t, -pc_l2);
+    STAGE(7);
 
     // ---- 3. exp-sum of what stays behind, hand-off of what reaches the threshold -------------------------
     const bool second_exp = kNucleus && p.apply_temperature != 0;
@@ -381,6 +397,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             if (second_exp) proc += (q0 + q1) + (q2 + q3);
         }
     }
+    STAGE(8);
     // Hand-off: slots in lane order, then trip, then component -- a fixed order.
     if (__ballot_sync(0xFFFFFFFFu, noted != 0) != 0 && !(p.debug_skip & 2)) {
         uint32_t count = 0;
@@ -412,6 +429,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         }
     }
 
+    STAGE(9);
     // ---- block reduction in a fixed order, then the part's record ---------------------------------------
     {
         const double wt = warp_sum((double)tail), wp = second_exp ? warp_sum((double)proc) : 0.0;
@@ -423,9 +441,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         }
     }
     __syncthreads();
+    STAGE(10);
     if (tid == 0) {
-        const float cmax = s_const.cmax, cymax = s_const.cymax, camax = s_const.camax, thr = s_const.thr;
-        const float c_res = s_const.c_res, pc_res = s_const.pc_res;
         double t = 0.0, q = 0.0;
         uint32_t handed_on = 0, over = 0;
 #pragma unroll
@@ -456,7 +473,22 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         s.overflow = over;
         p.stats[part_index] = s;
     }
+#ifdef PSX_STAGE_CLOCKS
+    STAGE(11);
+    if (tid == 0 && part_index < 4096) {
+        unsigned long long gt1; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt1));
+        unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
+        clk[12] = gt0; clk[13] = gt1; clk[14] = sm;
+        for (int i = 0; i < 16; ++i) g_stage_clocks[part_index * 16 + i] = clk[i];
+    }
+#endif
 }
+
+#ifdef PSX_STAGE_CLOCKS
+extern "C" __attribute__((visibility("default"))) int psx_debug_stage_clocks(unsigned long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, g_stage_clocks, sizeof(unsigned long long) * n);
+}
+#endif
 
 cudaError_t configure_scan_rows() {
     cudaError_t e = cudaFuncSetAttribute(scan_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
