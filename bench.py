@@ -171,6 +171,9 @@ def run_ours(args, rank, world):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     ctx = psx.Context(local)
+    # Every batch is complete in HBM before the first timed call: the row pass of a step may start
+    # reading while the survivor stage of the step before it is still running.
+    ctx.inputs_are_ready(True)
     cfg = workload_config(w)
     n_batches = max(2, (2 * L2_BYTES) // w.logits_bytes + 2)
     batches, offsets = build_batches(w, device, n_batches, seed=1234 + rank)

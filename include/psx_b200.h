@@ -102,6 +102,15 @@ PSX_API psx_status psx_b200_ctx_enable_timing(psx_ctx* ctx, int enable);
 PSX_API psx_status psx_b200_ctx_read_timing(psx_ctx* ctx, double* row_pass_ms, double* survivor_stage_ms,
                                             uint64_t* calls);
 
+/* A promise about the calls that follow on this context (default 0: no promise).  ready != 0 says
+ * that the inputs of a call (logits, history ids and offsets) are complete in device memory when
+ * the call is made: they are not still being written by a kernel enqueued just before it on the
+ * same stream that announces its completion early (programmatic dependent launch).  The row pass
+ * then starts reading while the kernel before it in the stream -- usually the survivor stage of
+ * the previous call -- is still running; it never writes before that kernel has finished.
+ * Without the promise it waits for the kernel before it first.  No counterpart in the reference. */
+PSX_API psx_status psx_b200_ctx_inputs_are_ready(psx_ctx* ctx, int ready);
+
 /* Batched sampling step on device-resident logits: for every row, what one iteration of
  * Generate()'s loop computes (src/generation.cpp:124-156) -- finite check, raw log-softmax,
  * ProcessLogits (src/generation.cpp:55-112: repetition penalty, EOS ban, temperature, top-k,

@@ -3,6 +3,7 @@ call goes through the C ABI into the CUDA kernels."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import numpy as np
@@ -13,7 +14,7 @@ OK, ERR_BAD_ARGUMENT, ERR_CUDA, ERR_ROW_FAILED, ERR_UNSUPPORTED = range(5)
 
 EXPORTS = [
     "psx_b200_version", "psx_b200_last_error", "psx_b200_ctx_create", "psx_b200_ctx_destroy", "psx_b200_ctx_stream",
-    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
+    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_top_k_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
@@ -68,6 +69,8 @@ _lib = None
 
 
 def library_path() -> Path:
+    if os.environ.get("PSX_B200_STAGE_CLOCKS") == "1":  # the profiling build (see build.py)
+        return PACKAGE / "libpsx_b200_clocks.so"
     return PACKAGE / "libpsx_b200.so"
 
 
@@ -91,6 +94,7 @@ def library():
         lib.psx_b200_ctx_create.argtypes = [C.c_int, C.c_void_p]
         lib.psx_b200_sync.argtypes = [C.c_void_p, C.c_void_p]
         lib.psx_b200_ctx_enable_timing.argtypes = [C.c_void_p, C.c_int]
+        lib.psx_b200_ctx_inputs_are_ready.argtypes = [C.c_void_p, C.c_int]
         lib.psx_b200_ctx_read_timing.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         ptr, i64 = C.c_void_p, C.c_int64
         lib.psx_b200_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
@@ -185,6 +189,11 @@ class Context:
     @property
     def stream(self) -> int:
         return int(self._lib.psx_b200_ctx_stream(self._ctx) or 0)
+
+    def inputs_are_ready(self, ready=True):
+        """Promise that the inputs of the calls that follow are complete before each call is made
+        (see psx_b200_ctx_inputs_are_ready): the row pass then overlaps the kernel before it."""
+        _check(self._lib.psx_b200_ctx_inputs_are_ready(self._ctx, int(ready)))
 
     def enable_timing(self, on=True):
         _check(self._lib.psx_b200_ctx_enable_timing(self._ctx, int(on)))

@@ -22,10 +22,11 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 
-def _profiling_flags() -> list[str]:
-    """PSX_B200_STAGE_CLOCKS=1 builds the kernels with per-stage clock stamps (a profiling aid: the
-    library then also exports psx_debug_stage_clocks / psx_debug_merge_clocks to read them back)."""
-    return ["-DPSX_STAGE_CLOCKS"] if os.environ.get("PSX_B200_STAGE_CLOCKS") == "1" else []
+def _profiling() -> bool:
+    """PSX_B200_STAGE_CLOCKS=1 builds a second library, libpsx_b200_clocks.so, whose kernels stamp the SM
+    clock at their stage boundaries (a profiling aid: it also exports psx_debug_stage_clocks and
+    psx_debug_merge_clocks to read the stamps back); the Python binding loads it under the same variable."""
+    return os.environ.get("PSX_B200_STAGE_CLOCKS") == "1"
 
 
 def _stale() -> bool:
@@ -38,16 +39,18 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not _stale():
+    profiling = _profiling()
+    library = PACKAGE / "libpsx_b200_clocks.so" if profiling else LIBRARY
+    if not force and not profiling and not _stale():
         return LIBRARY
     objects = []
-    build_dir = PACKAGE / "build"
+    build_dir = PACKAGE / ("build_clocks" if profiling else "build")
     build_dir.mkdir(exist_ok=True)
     procs = []
     for src in SOURCES:
         obj = build_dir / (src + ".o")
-        cmd = ["nvcc", *NVCC_FLAGS, *_profiling_flags(), *(["-Xptxas", "-v"] if verbose else []), "-c", str(CSRC / src),
-               "-o", str(obj)]
+        cmd = ["nvcc", *NVCC_FLAGS, *(["-DPSX_STAGE_CLOCKS"] if profiling else []), *(["-Xptxas", "-v"] if verbose else []),
+               "-c", str(CSRC / src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objects.append(str(obj))
     include = str(PACKAGE.parent / "include")
@@ -63,9 +66,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    subprocess.run(["nvcc", "-arch=sm_100a", "-shared", "-o", str(LIBRARY), *objects, "-lcudart"], check=True)
-    build_cpp_test()
-    return LIBRARY
+    subprocess.run(["nvcc", "-arch=sm_100a", "-shared", "-o", str(library), *objects, "-lcudart"], check=True)
+    if not profiling:
+        build_cpp_test()
+    return library
 
 
 def build_cpp_test() -> Path:

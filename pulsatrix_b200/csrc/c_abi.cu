@@ -57,7 +57,7 @@ struct psx_ctx {
     bool scan_configured = false;
     int nucleus_k = 160;  // logits every part hands on when no top-k bounds the survivors
     // row-pass scratch
-    Buffer stats, seg_counts, candidates, banned;
+    Buffer stats, part_counts, candidates, banned;
     // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
     Buffer surv_cols, surv_vals, surv_counts, pl_tokens, pl_log_probs, pl_status;
     // staging of the host entry point
@@ -67,6 +67,7 @@ struct psx_ctx {
     // optional per-kernel timing: (before row pass, between, after survivor stage) per call
     bool timing = false;
     std::vector<cudaEvent_t> timing_events;
+    bool inputs_ready = false;  // psx_b200_ctx_inputs_are_ready
 };
 
 namespace {
@@ -115,6 +116,7 @@ struct Plan {
     bool apply_temperature = false;
     int sort_capacity = 1024;
     int gather_capacity = 4096;
+    int slot_shift = 0;    // the survivor stage fetches 2^slot_shift slots of every part's list at once
 };
 
 Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t row_stride, int64_t vocab,
@@ -135,20 +137,23 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     if (!sample) plan.k_need = 1;
     else if (top_k_on) plan.k_need = (int)std::min<int64_t>(c->top_k, 1 << 20);
     else plan.k_need = ctx->nucleus_k;
-    // A row of at most 256 vectors fits the candidate segments whole (one vector per thread, 128
-    // logits per warp): hand everything on, and every filter is exact whatever the settings.
+    // A row of at most 256 vectors fits a part's candidate list whole (one vector per thread, 1024
+    // logits): hand everything on, and every filter is exact whatever the settings.
     if (vectors <= psx::kScanThreads) plan.k_need = 1 << 30;
     plan.sort_capacity = plan.nucleus ? 4096 : 1024;
     plan.gather_capacity = plan.nucleus ? 8192 : 4096;
+    // A part usually hands on a little over k_need logits, plus the few its share of the history flags.
+    const int expected = plan.k_need >= psx::kPartCap ? psx::kPartCap : plan.k_need + plan.k_need / 4 + 24;
+    plan.slot_shift = psx::merge_slot_shift(plan.parts, psx::kPartCap, expected);
     return plan;
 }
 
-// The survivor stage holds one row's segment table and candidates in shared memory.
-psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int segments) {
-    if (segments > 4096) {
-        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: rows wider than 8M logits per GPU are not supported");
+// The survivor stage holds one row's candidates in shared memory.
+psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int parts) {
+    if (parts > 16 * psx::kMergeThreads) {
+        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: rows wider than 64M logits per GPU are not supported");
     }
-    const int bytes = (int)psx::merge_rows_shared_bytes(plan.sort_capacity, plan.gather_capacity, segments);
+    const int bytes = (int)psx::merge_rows_shared_bytes(plan.sort_capacity, plan.gather_capacity);
     if (ctx->merge_capacity_configured >= bytes) return PSX_OK;
     PSX_CUDA(psx::configure_merge_rows((size_t)bytes));
     ctx->merge_capacity_configured = bytes;
@@ -171,6 +176,7 @@ psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_co
         const char* skip = std::getenv("PSX_B200_DEBUG_SKIP");  // profiling only
         sp.debug_skip = skip ? std::atoi(skip) : 0;
     }
+    sp.inputs_ready = ctx->inputs_ready ? 1 : 0;
     sp.num_banned = 0;
     sp.banned_ids = nullptr;
     if (c->num_new_tokens < c->min_new_tokens && c->num_eos_token_ids > 0) {  // src/generation.cpp:69
@@ -187,10 +193,10 @@ psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_co
 psx_status reserve_scan_scratch(psx_ctx* ctx, int64_t rows, const Plan& plan, psx::ScanParams& sp) {
     const size_t parts = (size_t)rows * plan.parts;
     if (psx_status s = reserve(ctx->stats, parts * sizeof(psx::PartStats))) return s;
-    if (psx_status s = reserve(ctx->seg_counts, parts * psx::kScanWarps * sizeof(uint32_t))) return s;
-    if (psx_status s = reserve(ctx->candidates, parts * psx::kScanWarps * psx::kSegCap * sizeof(uint2))) return s;
+    if (psx_status s = reserve(ctx->part_counts, parts * sizeof(uint32_t))) return s;
+    if (psx_status s = reserve(ctx->candidates, parts * psx::kPartCap * sizeof(uint2))) return s;
     sp.stats = static_cast<psx::PartStats*>(ctx->stats.ptr);
-    sp.seg_counts = static_cast<uint32_t*>(ctx->seg_counts.ptr);
+    sp.part_counts = static_cast<uint32_t*>(ctx->part_counts.ptr);
     sp.candidates = static_cast<uint2*>(ctx->candidates.ptr);
     return PSX_OK;
 }
@@ -273,7 +279,7 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (Buffer* b : {&ctx->stats, &ctx->seg_counts, &ctx->candidates, &ctx->banned, &ctx->surv_cols, &ctx->surv_vals,
+    for (Buffer* b : {&ctx->stats, &ctx->part_counts, &ctx->candidates, &ctx->banned, &ctx->surv_cols, &ctx->surv_vals,
                       &ctx->surv_counts, &ctx->pl_tokens, &ctx->pl_log_probs, &ctx->pl_status, &ctx->h_logits, &ctx->h_history,
                       &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
@@ -361,21 +367,21 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
                                      plan, sp)) {
         return s;
     }
-    if (psx_status s = configure_merge(ctx, plan, plan.parts * psx::kScanWarps)) return s;
+    if (psx_status s = configure_merge(ctx, plan, plan.parts)) return s;
 
     psx::MergeParams mp{};
     mp.stats = sp.stats;
-    mp.seg_counts = sp.seg_counts;
+    mp.part_counts = sp.part_counts;
     mp.candidates = sp.candidates;
     mp.parts = plan.parts;
-    mp.segs_per_part = psx::kScanWarps;
-    mp.seg_cap = psx::kSegCap;
+    mp.part_cap = psx::kPartCap;
+    mp.slot_shift = plan.slot_shift;
     mp.stats_part_stride = sizeof(psx::PartStats);
     mp.stats_row_stride = mp.stats_part_stride * plan.parts;
-    mp.count_seg_stride = sizeof(uint32_t);
-    mp.count_row_stride = mp.count_seg_stride * plan.parts * psx::kScanWarps;
-    mp.cand_seg_stride = sizeof(uint2) * psx::kSegCap;
-    mp.cand_row_stride = mp.cand_seg_stride * plan.parts * psx::kScanWarps;
+    mp.count_part_stride = sizeof(uint32_t);
+    mp.count_row_stride = mp.count_part_stride * plan.parts;
+    mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
+    mp.cand_row_stride = mp.cand_part_stride * plan.parts;
     fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
 
     cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
@@ -432,7 +438,7 @@ psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream_ptr, float* logits
     pp.filters_on = filters_on ? 1 : 0;
     pp.row_status = status;
     if (filters_on) {
-        if (psx_status s = configure_merge(ctx, plan, plan.parts * psx::kScanWarps)) return s;
+        if (psx_status s = configure_merge(ctx, plan, plan.parts)) return s;
         const size_t slots = (size_t)rows * plan.sort_capacity;
         if (psx_status s = reserve(ctx->surv_cols, slots * sizeof(uint32_t))) return s;
         if (psx_status s = reserve(ctx->surv_vals, slots * sizeof(float))) return s;
@@ -443,17 +449,17 @@ psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream_ptr, float* logits
         ++ctx->launches;
         psx::MergeParams mp{};
         mp.stats = sp.stats;
-        mp.seg_counts = sp.seg_counts;
+        mp.part_counts = sp.part_counts;
         mp.candidates = sp.candidates;
         mp.parts = plan.parts;
-        mp.segs_per_part = psx::kScanWarps;
-        mp.seg_cap = psx::kSegCap;
+        mp.part_cap = psx::kPartCap;
+        mp.slot_shift = plan.slot_shift;
         mp.stats_part_stride = sizeof(psx::PartStats);
         mp.stats_row_stride = mp.stats_part_stride * plan.parts;
-        mp.count_seg_stride = sizeof(uint32_t);
-        mp.count_row_stride = mp.count_seg_stride * plan.parts * psx::kScanWarps;
-        mp.cand_seg_stride = sizeof(uint2) * psx::kSegCap;
-        mp.cand_row_stride = mp.cand_seg_stride * plan.parts * psx::kScanWarps;
+        mp.count_part_stride = sizeof(uint32_t);
+        mp.count_row_stride = mp.count_part_stride * plan.parts;
+        mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
+        mp.cand_row_stride = mp.cand_part_stride * plan.parts;
         fill_merge_settings(mp, config, plan, rows, vocab, /*uniforms=*/nullptr,
                             static_cast<int64_t*>(ctx->pl_tokens.ptr), static_cast<float*>(ctx->pl_log_probs.ptr), status,
                             nullptr);
@@ -500,6 +506,12 @@ psx_status psx_b200_process_logits_host(psx_ctx* ctx, float* logits, int64_t row
         PSX_CUDA(cudaMemcpyAsync(ctx->h_offsets.ptr, history_offsets, (size_t)(rows + 1) * sizeof(int64_t),
                                  cudaMemcpyHostToDevice, stream));
     }
+    struct RestorePromise {  // the staged inputs are being copied in by the transfers just enqueued
+        psx_ctx* ctx;
+        bool saved;
+        ~RestorePromise() { ctx->inputs_ready = saved; }
+    } restore{ctx, ctx->inputs_ready};
+    ctx->inputs_ready = false;
     if (psx_status s = psx_b200_process_logits(ctx, stream, static_cast<float*>(ctx->h_logits.ptr), rows, vocab, vocab,
                                                with_history ? static_cast<const int64_t*>(ctx->h_history.ptr) : nullptr,
                                                with_history ? static_cast<const int64_t*>(ctx->h_offsets.ptr) : nullptr,
@@ -527,6 +539,12 @@ psx_status psx_b200_process_logits_host(psx_ctx* ctx, float* logits, int64_t row
 psx_status psx_b200_ctx_enable_timing(psx_ctx* ctx, int enable) {
     if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
     ctx->timing = enable != 0;
+    return PSX_OK;
+}
+
+psx_status psx_b200_ctx_inputs_are_ready(psx_ctx* ctx, int ready) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    ctx->inputs_ready = ready != 0;
     return PSX_OK;
 }
 
@@ -593,6 +611,13 @@ psx_status psx_b200_sample_rows_host(psx_ctx* ctx, const float* logits, int64_t 
         PSX_CUDA(cudaMemcpyAsync(ctx->h_uniforms.ptr, uniforms, (size_t)rows * sizeof(double), cudaMemcpyHostToDevice,
                                  stream));
     }
+    // The staged inputs are being copied in by the transfers just enqueued: no promise holds for them.
+    struct RestorePromise {
+        psx_ctx* ctx;
+        bool saved;
+        ~RestorePromise() { ctx->inputs_ready = saved; }
+    } restore{ctx, ctx->inputs_ready};
+    ctx->inputs_ready = false;
     if (psx_status s = psx_b200_sample_rows(
             ctx, stream, static_cast<const float*>(ctx->h_logits.ptr), rows, vocab, vocab,
             with_history ? static_cast<const int64_t*>(ctx->h_history.ptr) : nullptr,
@@ -666,7 +691,7 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
 
     psx::PackParams pp{};
     pp.stats = sp.stats;
-    pp.seg_counts = sp.seg_counts;
+    pp.part_counts = sp.part_counts;
     pp.candidates = sp.candidates;
     pp.parts = plan.parts;
     pp.rows = rows;
@@ -709,13 +734,13 @@ psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gath
     const char* base = static_cast<const char*>(gathered);
     psx::MergeParams mp{};
     mp.stats = base + psx::kRecordStatsOffset;
-    mp.seg_counts = base + psx::kRecordCountOffset;
+    mp.part_counts = base + psx::kRecordCountOffset;
     mp.candidates = base + psx::kRecordCandidatesOffset;
     mp.parts = num_shards;
-    mp.segs_per_part = 1;
-    mp.seg_cap = capacity;
+    mp.part_cap = capacity;
+    mp.slot_shift = psx::merge_slot_shift(num_shards, capacity, capacity / 2);
     mp.stats_row_stride = mp.count_row_stride = mp.cand_row_stride = record;
-    mp.stats_part_stride = mp.count_seg_stride = mp.cand_seg_stride = record * rows;
+    mp.stats_part_stride = mp.count_part_stride = mp.cand_part_stride = record * rows;
     fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
     PSX_CUDA(psx::launch_merge_rows(mp, stream));
     ++ctx->launches;

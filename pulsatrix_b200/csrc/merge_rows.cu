@@ -26,8 +26,10 @@ namespace psx {
 
 namespace {
 
-__global__ void __launch_bounds__(kMergeThreads, 1) merge_rows_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(kMergeThreads, 2) merge_rows_kernel(const MergeParams p) {
     extern __shared__ unsigned long long dyn[];
+    grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
+    grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
     survivor::merge_row(p, blockIdx.x, dyn);
 }
 
@@ -39,8 +41,17 @@ extern "C" __attribute__((visibility("default"))) int psx_debug_merge_clocks(uns
 }
 #endif
 
-size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, int segments) {
-    return (size_t)sort_capacity * (8 + 8 + 8 + 1) + (size_t)gather_capacity * 8 + (size_t)(2 * segments + 1) * 4 + 16;
+size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity) {
+    return (size_t)sort_capacity * (8 + 8 + 8 + 1) + (size_t)gather_capacity * 8 + 16;
+}
+
+int merge_slot_shift(int parts, int part_cap, int expected) {
+    int shift = 0;
+    // room for about twice what is expected, inside a list, inside what 16 fetches per thread reach
+    while ((1 << shift) < 2 * expected && (2 << shift) <= part_cap && ((long long)parts << (shift + 1)) <= 16 * kMergeThreads) {
+        ++shift;
+    }
+    return shift;
 }
 
 cudaError_t configure_merge_rows(size_t shared_bytes) {
@@ -49,9 +60,8 @@ cudaError_t configure_merge_rows(size_t shared_bytes) {
 
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;
-    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, p.parts * p.segs_per_part);
-    merge_rows_kernel<<<(unsigned)p.rows, kMergeThreads, shared, stream>>>(p);
-    return cudaGetLastError();
+    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity);
+    return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, p);
 }
 
 }  // namespace psx

@@ -12,14 +12,15 @@ struct MergeParams {
     // Addressed with byte strides, so that the same kernel reads the row pass's own arrays
     // (part-major within a row) and records gathered from several GPUs (GPU-major).
     const void* stats;           // PartStats of (row, part) at stats + row*stats_row_stride + part*stats_part_stride
-    const void* seg_counts;      // uint32 of (row, segment) likewise; segment = part*segs_per_part + s
-    const void* candidates;      // uint2[seg_cap] of (row, segment) likewise
+    const void* part_counts;     // uint32 of (row, part) likewise: candidates in the part's list
+    const void* candidates;      // uint2[part_cap] of (row, part) likewise
     int64_t stats_row_stride, stats_part_stride;
-    int64_t count_row_stride, count_seg_stride;
-    int64_t cand_row_stride, cand_seg_stride;
+    int64_t count_row_stride, count_part_stride;
+    int64_t cand_row_stride, cand_part_stride;
     int32_t parts;
-    int32_t segs_per_part;
-    int32_t seg_cap;
+    int32_t part_cap;            // slots of a part's list
+    int32_t slot_shift;          // 2^slot_shift slots of every list are fetched before the counts are known;
+                                 // parts << slot_shift <= 16 * kMergeThreads
     int64_t rows;
     int64_t vocab;               // global vocabulary size
     // settings (GenerationConfig, already validated)
@@ -43,10 +44,12 @@ struct MergeParams {
     uint32_t* survivor_counts;   // rows
     int32_t survivor_cap;
     int32_t debug_stop;          // profiling only: leave the kernel after this stage (0: run everything)
-    int32_t gather_capacity;     // candidates of one row held in shared memory (<= 6 * sort_capacity)
+    int32_t gather_capacity;     // candidates of one row held in shared memory (<= 4 * sort_capacity)
 };
 
-size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, int segments);
+size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity);
+// The slot_shift for lists that usually hold about `expected` candidates, within the fetch budget.
+int merge_slot_shift(int parts, int part_cap, int expected);
 cudaError_t configure_merge_rows(size_t shared_bytes);
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream);
 

@@ -145,25 +145,90 @@ __device__ __forceinline__ void block_rank_sort(u64* keys, int n, bool descendin
 // one thread running down a contiguous array, and the per-entry divisions by the softmax sums
 // run in parallel (src/generation.cpp:80-152).  Exact: same operations, same order, same precision.
 struct SmallScratch {
-    uint32_t* order_b;  // entry of the j-th survivor by ascending column
-    uint32_t* cols;     // column of the j-th entry by (value descending, column ascending)
-    double* ex;         // per place: exp(x - x_max) by ascending column (0 for what a filter removed)
-    double* pr;         // per place: probabilities, in the order of the walk that reads them
-    uint8_t* alive;     // per entry (the min-p filter and the survivor export read it)
-    uint32_t* shared;   // a few broadcast words
-    double* sum;        // one broadcast double
+    uint32_t* order_b;   // entry of the j-th survivor by ascending column
+    uint32_t* cols;      // column of the j-th entry by (value descending, column ascending)
+    double* ex;          // exp(x - x_max) of the j-th survivor by ascending column (0 once a filter removed it)
+    double* pr;          // probabilities, in the order of the walk that reads them
+    uint8_t* alive;      // per entry: what survived (the min-p filter and the survivor export read it)
+    uint32_t* shared;    // a few broadcast words
+    double* sum;         // one broadcast double
 };
 
-// sum of v[0..n) in index order; the loads run ahead of the additions
-__device__ __forceinline__ double ordered_sum(const double* v, int n, double start) {
+// Eight doubles from index j of v (zero beyond n), by one thread; the loads are independent.
+__device__ __forceinline__ void load8(const double* __restrict__ v, int j, int n, double (&x)[8]) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) x[q] = j + q < n ? v[j + q] : 0.0;
+}
+
+// sum of v[0..n) in index order by one thread: the next eight loads are in flight while eight
+// additions, each waiting for the one before, are made.
+__device__ __forceinline__ double ordered_sum(const double* __restrict__ v, int n, double start) {
     double sum = start;
-    int j = 0;
-    for (; j + 4 <= n; j += 4) {
-        const double a = v[j], b = v[j + 1], c = v[j + 2], d = v[j + 3];
-        sum += a; sum += b; sum += c; sum += d;
+    double x[8], y[8];
+    load8(v, 0, n, x);
+    for (int j = 0; j < n; j += 8) {
+        load8(v, j + 8, n, y);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) sum += x[q];  // adding the zeros beyond n changes nothing
+#pragma unroll
+        for (int q = 0; q < 8; ++q) x[q] = y[q];
     }
-    for (; j < n; ++j) sum += v[j];
     return sum;
+}
+
+// The reference's running-sum walks (src/generation.cpp:96-102 and :144-151) by one thread: adds
+// v[0], v[1], ... to `start` in index order and stops at the first index whose sum is above
+// `level` (kStrict: level < sum; else: !(sum <= level)).  Eight sums are formed before they are
+// compared, so the comparisons do not sit in the chain of additions.
+struct WalkEnd {
+    int index;      // where the sum first went above the level; n when it never did
+    double before;  // the sum before that index's own share (the final sum when index == n)
+    double upto;    // the sum including it (the final sum when index == n)
+    int last;       // when index == n: the last index with a share that is not zero; -1 when none
+};
+template <bool kStrict>
+__device__ __forceinline__ WalkEnd ordered_walk(const double* __restrict__ v, int n, double start, double level) {
+    WalkEnd end;
+    end.index = n;
+    end.last = -1;
+    double carried = start;  // the sum before index j
+    double x[8], y[8];
+    load8(v, 0, n, x);
+    for (int j = 0; j < n; j += 8) {
+        load8(v, j + 8, n, y);
+        double run[8];
+        double sum = carried;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            sum += x[q];
+            run[q] = sum;
+        }
+        uint32_t above = 0, some = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const bool over = kStrict ? level < run[q] : !(run[q] <= level);
+            above |= (over && j + q < n ? 1u : 0u) << q;
+            some |= (x[q] != 0.0 ? 1u : 0u) << q;
+        }
+        if (above != 0) {
+            const int q = __ffs(above) - 1;
+            end.index = j + q;
+            end.before = carried;
+            end.upto = run[0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) {
+                if (r <= q) { end.before = run[r - 1]; end.upto = run[r]; }
+            }
+            return end;
+        }
+        if (some != 0) end.last = j + 31 - __clz(some);
+        carried = sum;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) x[q] = y[q];
+    }
+    end.before = carried;
+    end.upto = carried;
+    return end;
 }
 
 __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n, bool top_k_on, bool rest_in_play,
@@ -216,6 +281,7 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
         my_ex = exp((double)from_ordered_key(my_ord) - (double)from_ordered_key(top_ord));  // src/generation.cpp:46
         w.order_b[place_b] = (uint32_t)e;
         w.ex[place_b] = my_ex;
+        if (e == (int)best) w.shared[5] = (uint32_t)place_b;
     }
     PSX_MERGE_STAGE(11);
     bool alive = survivor;
@@ -234,26 +300,22 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
         __syncthreads();
         if (tid == 0) {
             const double limit = 1.0 - (double)p.top_p;
-            double cumulative = 0.0;
+            double start = 0.0;
             if (rest_alive) {  // everything outside the list leads the ascending walk and must fall as a whole
-                cumulative = rest / *w.sum;
-                if (!(cumulative <= limit)) d.status = PSX_ROW_TOO_WIDE;
+                start = rest / *w.sum;
+                if (!(start <= limit)) d.status = PSX_ROW_TOO_WIDE;
             }
             int cut = 0;  // places of the walk below `cut` are removed; the last of the walk always stays
-            double over = INFINITY;
             if (d.status == PSX_ROW_OK) {
-                double next = ns > 1 ? w.pr[0] : 0.0;
-                for (; cut + 1 < ns; ++cut) {
-                    const double upto = cumulative + next;
-                    next = w.pr[cut + 1];  // in range: cut + 1 < ns
-                    if (!(upto <= limit)) { over = upto; break; }
-                    cumulative = upto;
-                }
+                const WalkEnd end = ordered_walk<false>(w.pr, ns - 1, start, limit);
+                cut = end.index;
+                // The running sum only grows, so of all the sums compared with the limit the nearest
+                // are the last one at or below it and the first one above it.
+                if (cut > 0 || rest_alive) d.top_p_margin = fabs(end.before - limit);
+                if (cut < ns - 1) d.top_p_margin = fmin(d.top_p_margin, fabs(end.upto - limit));
+            } else {
+                d.top_p_margin = fabs(start - limit);
             }
-            // The running sum only grows, so of all the sums compared with the limit the nearest
-            // are the last one at or below it and the first one above it.
-            if (cut > 0 || rest_alive) d.top_p_margin = fabs(cumulative - limit);
-            d.top_p_margin = fmin(d.top_p_margin, fabs(over - limit));
             w.shared[4] = (uint32_t)cut;
         }
         rest_alive = false;
@@ -264,15 +326,13 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
 
     if (sample && p.min_p > 0.0f) {  // src/generation.cpp:104-111 (rare: left to one thread)
         if (have) w.alive[e] = alive ? 1 : 0;
-        if (have && e == (int)best) w.shared[5] = (uint32_t)place_b;
         __syncthreads();
         if (tid == 0 && d.status == PSX_ROW_OK) {
             double sum = rest_alive ? rest : 0.0;
             for (int j = 0; j < ns; ++j) {
                 if (w.alive[w.order_b[j]]) sum += w.ex[j];
             }
-            const uint32_t best_place = w.shared[5];
-            const double floor_p = p.min_p * (w.ex[best_place] / sum);
+            const double floor_p = p.min_p * (w.ex[w.shared[5]] / sum);
             for (int j = 0; j < ns; ++j) {
                 const uint32_t o = w.order_b[j];
                 if (w.alive[o] && o != best && w.ex[j] / sum < floor_p) w.alive[o] = 0;
@@ -301,20 +361,17 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
         if (survivor) w.pr[place_b] = alive ? my_ex / *w.sum : 0.0;
         __syncthreads();
         if (tid == 0 && d.status == PSX_ROW_OK) {
-            double cumulative = 0.0, before = 0.0;
-            int chosen = -1;
-            double next = w.pr[0];
-            for (int j = 0; j < ns; ++j) {
-                const double pr = next;
-                if (j + 1 < ns) next = w.pr[j + 1];
-                if (pr == 0.0) continue;  // removed, or a probability that underflowed: never drawn
-                before = cumulative;
-                cumulative += pr;
-                chosen = j;
-                if (u < cumulative) break;
+            // The first place whose running sum exceeds u; a probability of zero (removed, or
+            // underflowed) leaves the sum where it was and is never the first.  If u is not
+            // below the last sum either, the last place with a probability is drawn.
+            const WalkEnd end = ordered_walk<true>(w.pr, ns, 0.0, u);
+            const int chosen = end.index < ns ? end.index : end.last;
+            if (end.index < ns) {
+                const double lo = fabs(u - end.before), hi = fabs(u - end.upto);
+                d.draw_margin = end.before == 0.0 ? hi : fmin(lo, hi);
+            } else {
+                d.draw_margin = fabs(u - end.upto);
             }
-            const double lo = fabs(u - before), hi = fabs(u - cumulative);
-            d.draw_margin = before == 0.0 ? hi : fmin(lo, hi);
             d.token = key_col(keyA[chosen >= 0 ? w.order_b[chosen] : best]);
         }
     } else if (tid == 0) {
@@ -549,24 +606,141 @@ __device__ inline uint32_t block_select_kth(KeyAt key_at, int m, uint32_t k, uin
     return prefix;
 }
 
+// What the parts of a row say together, and how many candidates the row has.
+struct Joined {
+    float raw_max, y_max, thr;
+    uint32_t bad_bits;  // bit 0..7: a non-finite logit; 8..15: a copy that timed out; 16..: a list that overflowed
+    double alive_tail;
+    int total;          // candidates of the row (they are in shared memory when it is <= gather_capacity)
+};
+
+// Step 1 of the survivor stage: joins the parts' records and brings every candidate of the row
+// into shared memory, back to back in a fixed order.  The first 2^slot_shift slots of every
+// part's list are fetched together with the counts (the slots exist whatever the count), so the
+// usual row costs one trip to memory, not two; N such slots per thread.  What a longer list holds
+// beyond them is appended afterwards.
+template <int N>
+__device__ __forceinline__ Joined join_and_gather(const MergeParams& p, const char* stats_row, const char* counts_row,
+                                                  const char* cands_row, uint32_t* cand_l, uint32_t* cand_c,
+                                                  float (*s_f)[kMergeThreads / 32], double (*s_d)[kMergeThreads / 32],
+                                                  uint32_t (*s_u)[kMergeThreads / 32]) {
+    constexpr int kWarps = kMergeThreads / 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int shift = p.slot_shift, slots_per_part = 1 << shift, slots = p.parts << shift;
+    uint2 fetched[N];
+    uint32_t count_of[N];
+#pragma unroll
+    for (int q = 0; q < N; ++q) {
+        const int i = q * kMergeThreads + tid;
+        count_of[q] = 0;
+        fetched[q] = make_uint2(0, 0);
+        if (i < slots) {
+            const int part = i >> shift, slot = i & (slots_per_part - 1);
+            count_of[q] = min(*reinterpret_cast<const uint32_t*>(counts_row + part * p.count_part_stride), (uint32_t)p.part_cap);
+            fetched[q] = reinterpret_cast<const uint2*>(cands_row + part * p.cand_part_stride)[slot];
+        }
+    }
+    float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
+    double bad = 0.0, alive_tail = 0.0;
+    for (int i = tid; i < p.parts; i += kMergeThreads) {
+        const PartStats s = *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride);
+        raw_max = fmaxf(raw_max, s.raw_max);
+        y_max = fmaxf(y_max, s.y_max);
+        thr = fmaxf(thr, s.thr);
+        bad += (double)((s.nonfinite & 1u) + (s.nonfinite >> 1) * 256u + s.overflow * 65536u);
+        alive_tail += (double)s.alive_tail;
+    }
+    uint32_t warp_total = 0, beyond = 0;
+#pragma unroll
+    for (int q = 0; q < N; ++q) {
+        const uint32_t slot = (uint32_t)(q * kMergeThreads + tid) & (uint32_t)(slots_per_part - 1);
+        warp_total += __popc(__ballot_sync(0xFFFFFFFFu, slot < count_of[q]));
+        if (slot == 0 && count_of[q] > (uint32_t)slots_per_part) beyond += count_of[q] - (uint32_t)slots_per_part;
+    }
+    beyond = __reduce_add_sync(0xFFFFFFFFu, beyond);
+    {   // one barrier for all the reductions
+        raw_max = warp_max(raw_max);
+        y_max = warp_max(y_max);
+        thr = warp_max(thr);
+        bad = warp_sum(bad);
+        alive_tail = warp_sum(alive_tail);
+        if (lane == 0) {
+            s_f[0][warp] = raw_max; s_f[1][warp] = y_max; s_f[2][warp] = thr;
+            s_d[0][warp] = bad; s_d[1][warp] = alive_tail;
+            s_u[0][warp] = warp_total; s_u[1][warp] = beyond;
+        }
+        __syncthreads();
+        raw_max = s_f[0][0]; y_max = s_f[1][0]; thr = s_f[2][0];
+        bad = 0.0; alive_tail = 0.0;
+        warp_total = 0; beyond = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            raw_max = fmaxf(raw_max, s_f[0][w]);
+            y_max = fmaxf(y_max, s_f[1][w]);
+            thr = fmaxf(thr, s_f[2][w]);
+            bad += s_d[0][w];
+            alive_tail += s_d[1][w];
+            beyond += s_u[1][w];
+        }
+    }
+    uint32_t running = 0, fetched_total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const uint32_t c = s_u[0][w];
+        running += w < warp ? c : 0u;
+        fetched_total += c;
+    }
+    Joined j;
+    j.raw_max = raw_max; j.y_max = y_max; j.thr = thr;
+    j.bad_bits = (uint32_t)bad;
+    j.alive_tail = alive_tail;
+    j.total = (int)(fetched_total + beyond);
+    if (j.bad_bits != 0 || j.total > p.gather_capacity) return j;
+#pragma unroll
+    for (int q = 0; q < N; ++q) {  // warp after warp, then fetch by fetch, then lane by lane
+        const uint32_t slot = (uint32_t)(q * kMergeThreads + tid) & (uint32_t)(slots_per_part - 1);
+        const bool valid = slot < count_of[q];
+        const uint32_t voters = __ballot_sync(0xFFFFFFFFu, valid);
+        if (valid) {
+            const uint32_t at = running + __popc(voters & ((1u << lane) - 1u));
+            cand_l[at] = fetched[q].x;
+            cand_c[at] = fetched[q].y;
+        }
+        running += __popc(voters);
+    }
+    if (beyond != 0) {  // rare: the rest of the long lists, part after part
+        uint32_t at = fetched_total;
+        for (int part = 0; part < p.parts; ++part) {
+            const uint32_t count = min(*reinterpret_cast<const uint32_t*>(counts_row + part * p.count_part_stride), (uint32_t)p.part_cap);
+            if (count <= (uint32_t)slots_per_part) continue;
+            for (uint32_t i = (uint32_t)slots_per_part + tid; i < count; i += kMergeThreads) {
+                const uint2 c = reinterpret_cast<const uint2*>(cands_row + part * p.cand_part_stride)[i];
+                cand_l[at + i - slots_per_part] = c.x;
+                cand_c[at + i - slots_per_part] = c.y;
+            }
+            at += count - (uint32_t)slots_per_part;
+        }
+    }
+    __syncthreads();
+    return j;
+}
+
 // One row of the survivor stage, by a whole block of kMergeThreads threads; `dyn` is the block's
 // dynamic shared memory (merge_rows_shared_bytes(...) bytes, 8-byte aligned).
 __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t row, u64* dyn) {
     const int cap = p.sort_capacity, gcap = p.gather_capacity;
-    const int nseg = p.parts * p.segs_per_part;
     u64* keyA = dyn;
     u64* keyB = keyA + cap;
     double* ex = reinterpret_cast<double*>(keyB + cap);
     uint8_t* alive = reinterpret_cast<uint8_t*>(ex + cap);
     uint32_t* cand_l = reinterpret_cast<uint32_t*>(alive + cap);  // raw logit bits of every candidate
     uint32_t* cand_c = cand_l + gcap;                             // column | flags
-    uint32_t* seg_begin = cand_c + gcap;                          // nseg + 1 exclusive prefix of the counts
-    uint32_t* seg_size = seg_begin + nseg + 1;                    // nseg
     uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);           // scratch over the (still unused) sort arrays
+    uint32_t* xkeys = reinterpret_cast<uint32_t*>(keyB);          // likewise, clear of the list itself: 4 * cap words
 
     __shared__ float s_f[3][kMergeThreads / 32];
     __shared__ double s_d[3][kMergeThreads / 32];
-    __shared__ uint32_t s_u[kMergeThreads / 32];
+    __shared__ uint32_t s_u[2][kMergeThreads / 32];
     __shared__ int s_count;
     __shared__ int s_ns;
     __shared__ uint32_t s_chosen_raw;
@@ -576,128 +750,38 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool apply_t = p.apply_temperature != 0;
     const char* stats_row = static_cast<const char*>(p.stats) + row * p.stats_row_stride;
-    const char* counts_row = static_cast<const char*>(p.seg_counts) + row * p.count_row_stride;
+    const char* counts_row = static_cast<const char*>(p.part_counts) + row * p.count_row_stride;
     const char* cands_row = static_cast<const char*>(p.candidates) + row * p.cand_row_stride;
     auto part_stats = [&](int i) { return *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride); };
 
     PSX_MERGE_STAGE(0);
-    // The first 32 slots of this warp's first kSpec segments are fetched before their counts are
-    // known (the slots exist whatever the count), so the candidates cost one trip to memory, not two.
-    constexpr int kSpec = 16;
-    constexpr int kWarps = kMergeThreads / 32;
-    uint2 spec[kSpec];
-#pragma unroll
-    for (int q = 0; q < kSpec; ++q) {
-        const int sg = warp + q * kWarps;
-        if (sg < nseg) spec[q] = reinterpret_cast<const uint2*>(cands_row + sg * p.cand_seg_stride)[lane];
-    }
     const double u_row = (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5;
-
-    // ---- 1. join the parts; lay the candidate segments out back to back ---------------------------
-    float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
-    double bad = 0.0, alive_tail = 0.0;
-    for (int i = tid; i < p.parts; i += kMergeThreads) {
-        const PartStats s = part_stats(i);
-        raw_max = fmaxf(raw_max, s.raw_max);
-        y_max = fmaxf(y_max, s.y_max);
-        thr = fmaxf(thr, s.thr);
-        bad += (double)((s.nonfinite & 1u) + (s.nonfinite >> 1) * 256u + s.overflow * 65536u);
-        alive_tail += (double)s.alive_tail;
-    }
-    const int per_thread = (nseg + kMergeThreads - 1) / kMergeThreads;
-    uint32_t mine = 0;
-    for (int j = 0; j < per_thread; ++j) {
-        const int s = tid * per_thread + j;
-        if (s < nseg) {
-            const uint32_t c = min(*reinterpret_cast<const uint32_t*>(counts_row + s * p.count_seg_stride),
-                                   (uint32_t)p.seg_cap);
-            seg_size[s] = c;
-            mine += c;
-        }
-    }
-    uint32_t incl = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += up;
-    }
-    if (lane == 31) s_u[warp] = incl;
     if (tid == 0) s_count = 0;
-    reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);
+    reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);  // published by the barrier of step 1
     bool hist_clean = true;
-    {   // one barrier for all five reductions; it also publishes s_u, seg_size and the cleared s_hist
-        raw_max = warp_max(raw_max);
-        y_max = warp_max(y_max);
-        thr = warp_max(thr);
-        bad = warp_sum(bad);
-        alive_tail = warp_sum(alive_tail);
-        if (lane == 0) {
-            s_f[0][warp] = raw_max; s_f[1][warp] = y_max; s_f[2][warp] = thr;
-            s_d[0][warp] = bad; s_d[1][warp] = alive_tail;
-        }
-        __syncthreads();
-        raw_max = s_f[0][0]; y_max = s_f[1][0]; thr = s_f[2][0];
-        bad = 0.0; alive_tail = 0.0;
-#pragma unroll
-        for (int w = 0; w < kMergeThreads / 32; ++w) {
-            raw_max = fmaxf(raw_max, s_f[0][w]);
-            y_max = fmaxf(y_max, s_f[1][w]);
-            thr = fmaxf(thr, s_f[2][w]);
-            bad += s_d[0][w];
-            alive_tail += s_d[1][w];
-        }
+
+    // ---- 1. join the parts; every candidate of the row into shared memory ----------------------------
+    Joined joined;
+    {
+        const int per_thread = ((p.parts << p.slot_shift) + kMergeThreads - 1) / kMergeThreads;
+        if (per_thread <= 2) joined = join_and_gather<2>(p, stats_row, counts_row, cands_row, cand_l, cand_c, s_f, s_d, s_u);
+        else if (per_thread <= 4) joined = join_and_gather<4>(p, stats_row, counts_row, cands_row, cand_l, cand_c, s_f, s_d, s_u);
+        else if (per_thread <= 8) joined = join_and_gather<8>(p, stats_row, counts_row, cands_row, cand_l, cand_c, s_f, s_d, s_u);
+        else joined = join_and_gather<16>(p, stats_row, counts_row, cands_row, cand_l, cand_c, s_f, s_d, s_u);
     }
-    PSX_MERGE_STAGE(1);
-    uint32_t running = incl - mine;
-    for (int w = 0; w < warp; ++w) running += s_u[w];
-    for (int j = 0; j < per_thread; ++j) {
-        const int s = tid * per_thread + j;
-        if (s < nseg) {
-            seg_begin[s] = running;
-            running += seg_size[s];
-            if (s == nseg - 1) seg_begin[nseg] = running;
-        }
-    }
-    __syncthreads();
-    PSX_MERGE_STAGE(2);
-    const int total = (int)seg_begin[nseg];
-    const uint32_t bad_bits = (uint32_t)bad;
-    if (bad_bits != 0 || total > gcap) {
+    const float raw_max = joined.raw_max, y_max = joined.y_max, thr = joined.thr;
+    const double alive_tail = joined.alive_tail;
+    const int total = joined.total;
+    if (joined.bad_bits != 0 || total > gcap) {
         if (tid == 0) {
             p.tokens[row] = -1;
             p.log_probs[row] = 0.0f;
-            p.row_status[row] = (bad_bits & 0xFF00u) ? PSX_ROW_DEVICE_TIMEOUT
-                                : (bad_bits & 0xFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
+            p.row_status[row] = (joined.bad_bits & 0xFF00u) ? PSX_ROW_DEVICE_TIMEOUT
+                                : (joined.bad_bits & 0xFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
             if (p.diag) p.diag[row] = psx_row_diag{total, 0, INFINITY, INFINITY};
         }
         return;
     }
-    // Every candidate of the row into shared memory, segment by segment.
-#pragma unroll
-    for (int q = 0; q < kSpec; ++q) {
-        const int sg = warp + q * kWarps;
-        if (sg < nseg) {
-            const int count = (int)seg_size[sg], begin = (int)seg_begin[sg];
-            if (lane < count) {
-                cand_l[begin + lane] = spec[q].x;
-                cand_c[begin + lane] = spec[q].y;
-            }
-            for (int i = lane + 32; i < count; i += 32) {
-                const uint2 c = reinterpret_cast<const uint2*>(cands_row + sg * p.cand_seg_stride)[i];
-                cand_l[begin + i] = c.x;
-                cand_c[begin + i] = c.y;
-            }
-        }
-    }
-    for (int sg = warp + kSpec * kWarps; sg < nseg; sg += kWarps) {
-        const int count = (int)seg_size[sg], begin = (int)seg_begin[sg];
-        for (int i = lane; i < count; i += 32) {
-            const uint2 c = reinterpret_cast<const uint2*>(cands_row + sg * p.cand_seg_stride)[i];
-            cand_l[begin + i] = c.x;
-            cand_c[begin + i] = c.y;
-        }
-    }
-    __syncthreads();
 
     PSX_MERGE_STAGE(3);
     if (p.debug_stop == 1) return;
@@ -722,25 +806,88 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
             z_rest += s.proc_tail * exp((double)temper(s.y_max, apply_t, p.temperature) - (double)x_max);
         }
     }
-    for (int i = tid; i < total; i += kMergeThreads) {
-        const float l = __uint_as_float(cand_l[i]);
-        const uint32_t cf = cand_c[i];
-        z_raw += exp((double)l - (double)raw_max);
-        const float y = processed_before_temperature(l, cf, p.penalty);
-        if (y >= keep_from) {
-            const float x = temper(y, apply_t, p.temperature);
-            const int slot = atomicAdd(&s_count, 1);
-            if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(cf & kColumnMask);
-        } else if (y > -INFINITY && !top_k_on) {
-            z_rest += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
-            dropped += 1.0;
+    // With a top-k, what reaches the largest part threshold is still several times k (every part
+    // handed on its own k).  One histogram over the values from that threshold to the row's
+    // maximum, 256 equal bins, finds a bin edge with at least k values above it: only those go on
+    // the list, usually k and a handful, and the exact k-th value is found among them later.
+    // (Any map from value to bin that never decreases as the value falls would do.)
+    const bool narrow = top_k_on && total > p.top_k;
+    const float x_low = temper(keep_from, apply_t, p.temperature);
+    const uint32_t low_key = ordered_key(x_low);
+    float bin_scale = 0.0f;  // 0: one bin, nothing is cut here
+    if (narrow && x_max - x_low > 0.0f && x_max - x_low < INFINITY) bin_scale = __fdiv_rn(255.0f, x_max - x_low);
+    auto bin_of = [&](uint32_t key) {
+        return (uint32_t)max(0, min(255, (int)__fmul_rn(__fsub_rn(x_max, from_ordered_key(key)), bin_scale)));
+    };
+    if (narrow) {
+        for (int i = tid; i < total; i += kMergeThreads) {
+            const float l = __uint_as_float(cand_l[i]);
+            const uint32_t cf = cand_c[i];
+            z_raw += exp((double)l - (double)raw_max);
+            const float y = processed_before_temperature(l, cf, p.penalty);
+            const uint32_t key = ordered_key(temper(y, apply_t, p.temperature));
+            const bool listed = y > -INFINITY && key >= low_key;
+            xkeys[i] = listed ? key : 0u;  // 0 is below every key of a number
+            if (listed) atomicAdd(&s_hist[bin_of(key)], 1u);
         }
-    }
-    {   // three sums, one barrier (which also makes s_count final); fixed order
+        hist_clean = false;
+        z_raw = warp_sum(z_raw);
+        if (lane == 0) s_d[0][warp] = z_raw;
+        __syncthreads();
+        z_raw = 0.0;
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; ++w) z_raw += s_d[0][w];
+        // lane L owns bins 8L .. 8L+7, the highest values first; where does the count reach k?
+        const uint4 a4 = reinterpret_cast<const uint4*>(s_hist)[2 * lane], b4 = reinterpret_cast<const uint4*>(s_hist)[2 * lane + 1];
+        const uint32_t bins[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
+        uint32_t local = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) local += bins[q];
+        uint32_t incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const uint32_t need = (uint32_t)p.top_k, excl = incl - local;
+        const bool here = excl < need && need <= incl;
+        int my_bin = 8 * lane;
+        if (here) {
+            uint32_t above = excl;
+#pragma unroll
+            for (int q = 0; q < 7; ++q) {
+                if (my_bin == 8 * lane + q && above + bins[q] < need) { above += bins[q]; ++my_bin; }
+            }
+        }
+        const int src = __ffs(__ballot_sync(0xFFFFFFFFu, here)) - 1;
+        const uint32_t cut_bin = src < 0 ? 255u : (uint32_t)__shfl_sync(0xFFFFFFFFu, my_bin, src);  // fewer than k: all stay
+        for (int i = tid; i < total; i += kMergeThreads) {
+            const uint32_t key = xkeys[i];
+            if (key != 0u && bin_of(key) <= cut_bin) {
+                const int slot = atomicAdd(&s_count, 1);
+                if (slot < cap) keyA[slot] = ((u64)key << 32) | (uint32_t)~(cand_c[i] & kColumnMask);
+            }
+        }
+        __syncthreads();
+    } else {
+        for (int i = tid; i < total; i += kMergeThreads) {
+            const float l = __uint_as_float(cand_l[i]);
+            const uint32_t cf = cand_c[i];
+            z_raw += exp((double)l - (double)raw_max);
+            const float y = processed_before_temperature(l, cf, p.penalty);
+            if (y >= keep_from) {
+                const float x = temper(y, apply_t, p.temperature);
+                const int slot = atomicAdd(&s_count, 1);
+                if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(cf & kColumnMask);
+            } else if (y > -INFINITY && !top_k_on) {
+                z_rest += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
+                dropped += 1.0;
+            }
+        }
+        // three sums, one barrier (which also makes s_count final); fixed order
         z_raw = warp_sum(z_raw);
         z_rest = warp_sum(z_rest);
         dropped = warp_sum(dropped);
-        __syncthreads();  // the reads of s_d above are done
         if (lane == 0) { s_d[0][warp] = z_raw; s_d[1][warp] = z_rest; s_d[2][warp] = dropped; }
         __syncthreads();
         z_raw = 0.0; z_rest = 0.0; dropped = 0.0;
@@ -760,6 +907,9 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         // temperature divide go on the list.
         for (int i = tid; i < total; i += kMergeThreads) {
             ykeys[i] = ordered_key(processed_before_temperature(__uint_as_float(cand_l[i]), cand_c[i], p.penalty));
+        }
+        if (!hist_clean) {
+            for (int i = tid; i < 4 * 256; i += kMergeThreads) s_hist[i] = 0;
         }
         if (tid == 0) s_count = 0;
         __syncthreads();
@@ -837,7 +987,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
 
     if (!decided && n <= kMergeThreads) {
         // ---- 3''. a short list (the usual case): one entry per thread, nothing sorted ---------------
-        SmallScratch w;
+        SmallScratch w;  // over the second sort array and the exp array, both idle on this path
         w.order_b = reinterpret_cast<uint32_t*>(keyB);
         w.cols = w.order_b + kMergeThreads;
         w.shared = w.cols + kMergeThreads;             // 8 words

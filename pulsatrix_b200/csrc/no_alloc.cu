@@ -6,7 +6,7 @@
 // off limits because it synchronises the whole device and stalls every other stream.  The regular
 // entry point (psx_b200_sample_rows) grows a context's scratch with cudaMalloc the first time it
 // sees a bigger batch; this one never does.  Its scratch -- the row pass's per-part records and
-// candidate segments that the survivor stage reads -- is a fixed array that is part of the loaded
+// candidate lists that the survivor stage reads -- is a fixed array that is part of the loaded
 // library image on every GPU (kStaticParts parts, about 8.1 MiB, held until the process exits).
 //
 // Consequences the caller must know:
@@ -16,8 +16,8 @@
 //   * the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //     that device current); make that first call before starting any stream capture on that device;
 //   * every call uses the same array.  Nothing in it has to start at zero: the row pass rewrites
-//     every record and every segment count of the batch before the survivor stage reads them, and
-//     segment slots beyond a count are never read, so stale contents of an earlier call are
+//     every record and every list count of the batch before the survivor stage reads them, and
+//     list slots beyond a count are never used, so stale contents of an earlier call are
 //     harmless.  But two calls that overlap on the GPU (different streams, or different host
 //     threads) race on it: keep calls stream-ordered one after another per device.
 #include <mutex>
@@ -35,8 +35,8 @@ constexpr int kMaxDevices = 64;
 
 struct StaticScratch {
     psx::PartStats stats[kStaticParts];
-    uint32_t seg_counts[kStaticParts * psx::kScanWarps];
-    uint2 candidates[(size_t)kStaticParts * psx::kScanWarps * psx::kSegCap];
+    uint32_t part_counts[kStaticParts];
+    uint2 candidates[(size_t)kStaticParts * psx::kPartCap];
     int64_t banned[kStaticBanned];
 };
 
@@ -143,7 +143,7 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
     // Shared-memory opt-ins of the two kernels (host-side function attributes, no memory): set on
     // every call, because the regular entry points adjust the same attributes to their own needs.
     PSX_STATIC_CUDA(psx::configure_scan_rows());
-    PSX_STATIC_CUDA(psx::configure_merge_rows(psx::merge_rows_shared_bytes(kSortCapacityWide, kGatherCapacityWide, 4096)));
+    PSX_STATIC_CUDA(psx::configure_merge_rows(psx::merge_rows_shared_bytes(kSortCapacityWide, kGatherCapacityWide)));
 
     // ---- the same two kernels as psx_b200_sample_rows, pointed at the built-in scratch ----------------------
     const bool top_k_on = sample && c->top_k > 0 && c->top_k < vocab;
@@ -178,23 +178,24 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
         sp.num_banned = (int32_t)c->num_eos_token_ids;
     }
     sp.stats = scratch->stats;
-    sp.seg_counts = scratch->seg_counts;
+    sp.part_counts = scratch->part_counts;
     sp.candidates = scratch->candidates;
     PSX_STATIC_CUDA(psx::launch_scan_rows(sp, nucleus, stream));
 
     psx::MergeParams mp{};
     mp.stats = sp.stats;
-    mp.seg_counts = sp.seg_counts;
+    mp.part_counts = sp.part_counts;
     mp.candidates = sp.candidates;
     mp.parts = sp.parts;
-    mp.segs_per_part = psx::kScanWarps;
-    mp.seg_cap = psx::kSegCap;
+    mp.part_cap = psx::kPartCap;
+    mp.slot_shift = psx::merge_slot_shift(sp.parts, psx::kPartCap,
+                                          sp.k_need >= psx::kPartCap ? psx::kPartCap : sp.k_need + sp.k_need / 4 + 24);
     mp.stats_part_stride = sizeof(psx::PartStats);
     mp.stats_row_stride = mp.stats_part_stride * sp.parts;
-    mp.count_seg_stride = sizeof(uint32_t);
-    mp.count_row_stride = mp.count_seg_stride * sp.parts * psx::kScanWarps;
-    mp.cand_seg_stride = sizeof(uint2) * psx::kSegCap;
-    mp.cand_row_stride = mp.cand_seg_stride * sp.parts * psx::kScanWarps;
+    mp.count_part_stride = sizeof(uint32_t);
+    mp.count_row_stride = mp.count_part_stride * sp.parts;
+    mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
+    mp.cand_row_stride = mp.cand_part_stride * sp.parts;
     mp.rows = rows;
     mp.vocab = vocab;
     mp.do_sample = sample ? 1 : 0;

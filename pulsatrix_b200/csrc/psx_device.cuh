@@ -7,6 +7,7 @@
 #include <float.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace psx {
 
@@ -15,7 +16,7 @@ constexpr int kScanThreads = 256;
 constexpr int kScanWarps = kScanThreads / 32;
 constexpr int kVecPerThread = 16;                            // float4 held in registers per thread
 constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits = 64 KB per CTA
-constexpr int kSegCap = 128;                                 // candidate slots per warp segment
+constexpr int kPartCap = 1024;                               // candidate slots per part
 constexpr int kMergeThreads = 256;
 
 // A candidate is (raw logit bits, column | flags).  The flags say how the survivor stage must
@@ -34,7 +35,7 @@ struct PartStats {
     float thr;            // every alive logit >= relax(thr) of this part is a candidate
     uint32_t nonfinite;   // 1 when the part holds a NaN or an infinity
     uint32_t alive_tail;  // non-candidates that are still alive (not banned, not padding)
-    uint32_t overflow;    // 1 when a candidate segment ran out of slots
+    uint32_t overflow;    // 1 when the part's candidate list ran out of slots
 };
 
 // ---- float operations that must round like the reference's host code ---------------------------
@@ -100,6 +101,15 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// The row pass and the survivor stage are launched so that a kernel may start while the kernel
+// before it in the stream is still running (cudaLaunchAttributeProgrammaticStreamSerialization).
+// grid_dependency_wait() returns once that earlier kernel has finished and its writes are
+// visible; a kernel calls it before it reads what the earlier kernel wrote and before it writes
+// anything the earlier kernel may still read.  Launched the ordinary way, both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- warp / block helpers ------------------------------------------------------------------------
 
@@ -179,6 +189,25 @@ __device__ __forceinline__ void block_bitonic_sort(unsigned long long* keys, int
             __syncthreads();
         }
     }
+}
+
+// Launches `kernel` so that it may begin while the kernel before it in `stream` is still running
+// (see grid_dependency_wait above); PSX_B200_NO_PDL=1 in the environment launches the ordinary way.
+template <class Params>
+inline cudaError_t launch_overlapping(void (*kernel)(Params), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                                      const Params& params) {
+    static const bool plain = [] { const char* e = getenv("PSX_B200_NO_PDL"); return e && e[0] == '1'; }();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = plain ? 0 : 1;
+    return cudaLaunchKernelEx(&config, kernel, params);
 }
 
 }  // namespace psx

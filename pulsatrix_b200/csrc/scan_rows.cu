@@ -78,9 +78,13 @@ __device__ __forceinline__ bool barrier_wait_bounded(uint64_t* bar, uint32_t par
     return false;
 }
 
-// Sets, in a bitmap with one bit per logit of this part, the columns that `ids` names.
+// Sets, in a bitmap with one bit per logit of this part, the columns that `ids` names (and the
+// same bits in `also`, when given).  Every bit that was not set before adds one to the count of
+// the warp that owns its word in the dense passes, so each warp's number of flagged logits is
+// known without anybody looking at the bitmap again.
 __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int64_t end, const ScanParams& p,
-                                         int first_pos, int part_logits, uint32_t* bitmap) {
+                                         int first_pos, int part_logits, uint32_t* bitmap, uint32_t* also,
+                                         uint32_t* warp_counts) {
     // first_pos: position of this part's first slot in the row's aligned window, minus the
     // row's misalignment, i.e. the (possibly negative) local column of data[0].
     for (int64_t i = begin + threadIdx.x; i < end; i += kScanThreads) {
@@ -89,7 +93,11 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
         const uint64_t col = (uint64_t)(id - p.col_begin);
         if (col >= (uint64_t)p.cols) continue;             // not in this GPU's columns
         const uint32_t e = (uint32_t)((int)col - first_pos);  // slot in this part, if below part_logits
-        if (e < (uint32_t)part_logits) atomicOr(&bitmap[e >> 5], 1u << (e & 31));
+        if (e < (uint32_t)part_logits) {
+            const uint32_t word = e >> 5, bit = 1u << (e & 31);
+            if (!(atomicOr(&bitmap[word], bit) & bit)) atomicAdd(&warp_counts[(word >> 2) & (kScanWarps - 1)], 1u);
+            if (also) atomicOr(&also[word], bit);
+        }
     }
 }
 
@@ -120,19 +128,18 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
 
     __shared__ __align__(8) uint64_t s_bar;
     __shared__ __align__(16) uint32_t s_bits[2 * kBitmapWords];
-    uint32_t* const s_pen = s_bits;
-    uint32_t* const s_ban = s_bits + kBitmapWords;
+    uint32_t* const s_flag = s_bits;                 // penalised or banned
+    uint32_t* const s_ban = s_bits + kBitmapWords;   // banned
     __shared__ float s_wraw[kScanWarps], s_wamax[kScanWarps], s_wymax[kScanWarps], s_wthr[kScanWarps];
     __shared__ uint32_t s_pool[kScanWarps * kPool];
     __shared__ double s_wtail[kScanWarps], s_wproc[kScanWarps];
-    __shared__ uint32_t s_wfill[kScanWarps];
+    __shared__ uint32_t s_wfill[kScanWarps], s_wflag[kScanWarps];
 
     const int part = blockIdx.x;  // grid: (parts, rows in chunks of 65535, chunks)
     const int64_t row = (int64_t)blockIdx.z * 65535 + blockIdx.y;
     if (row >= p.rows) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t part_index = (size_t)row * p.parts + part;
-    const size_t seg = part_index * kScanWarps + warp;
 
     // ---- geometry: the row as aligned float4 vectors ------------------------------------------
     const float* row_ptr = p.logits + row * p.row_stride;
@@ -142,9 +149,15 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const int v0 = part * p.vecs_per_part;
     const int v1 = min(v0 + p.vecs_per_part, nv);
     const int nvec = v1 - v0;
+    // The survivor stage that follows may be set up while this kernel runs.  This kernel reads only
+    // its caller's inputs until it has something to hand on: when the caller has promised that they
+    // are complete, it runs ahead of the kernel before it in the stream until its first write.
+    grid_dependents_may_launch();
+    if (!p.inputs_ready) grid_dependency_wait();
     if (nvec <= 0) {  // a part past the end of a row that starts on a 16-byte boundary: nothing to report
-        if (lane == 0) p.seg_counts[seg] = 0;
+        grid_dependency_wait();
         if (tid == 0) {
+            p.part_counts[part_index] = 0;
             PartStats s;
             s.raw_tail = 0.0; s.proc_tail = 0.0; s.raw_max = kPad; s.y_max = -INFINITY; s.thr = -INFINITY;
             s.nonfinite = 0; s.alive_tail = 0; s.overflow = 0;
@@ -155,6 +168,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
 
     // ---- start the copy, and build the history bitmaps while it is in flight ----------------------
     if (tid == 0) barrier_init(&s_bar, 1);
+    if (tid < kScanWarps) s_wflag[tid] = 0;
     static_assert(2 * kBitmapWords == 4 * kScanThreads, "one 16-byte store per thread clears both bitmaps");
     reinterpret_cast<uint4*>(s_bits)[tid] = make_uint4(0, 0, 0, 0);
     __syncthreads();
@@ -170,18 +184,22 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const bool use_flags = p.apply_penalty || p.num_banned > 0;
     const int first_pos = v0 * 4 - (int)misalign;
     if (p.apply_penalty && !(p.debug_skip & 16)) {
-        mark_ids(p.history_ids, p.history_offsets[row], p.history_offsets[row + 1], p, first_pos, nvec * 4, s_pen);
+        mark_ids(p.history_ids, p.history_offsets[row], p.history_offsets[row + 1], p, first_pos, nvec * 4, s_flag, nullptr,
+                 s_wflag);
     }
-    if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, first_pos, nvec * 4, s_ban);
+    if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, first_pos, nvec * 4, s_flag, s_ban, s_wflag);
     // One warp watches the copy; the others sleep in the block barrier, which also orders the
     // copied bytes before everybody's reads.
     STAGE(2);
     const bool landed = warp == 0 ? barrier_wait_bounded(&s_bar, 0) : true;
-    if (!__syncthreads_and(landed ? 1 : 0)) {
+    const bool all_landed = __syncthreads_and(landed ? 1 : 0) != 0;
+    // From here on the kernel writes scratch that an earlier survivor stage may still be reading.
+    grid_dependency_wait();
+    if (!all_landed) {
         // The copy did not complete in time: report it, give it one more bounded chance to drain
         // (shared memory must not be handed to the next CTA under a copy in flight), and leave.
-        if (lane == 0) p.seg_counts[seg] = 0;
         if (tid == 0) {
+            p.part_counts[part_index] = 0;
             PartStats s;
             s.raw_tail = 0.0; s.proc_tail = 0.0; s.raw_max = kPad; s.y_max = -INFINITY; s.thr = -INFINITY;
             s.nonfinite = 2; s.alive_tail = 0; s.overflow = 0;
@@ -212,8 +230,15 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     __syncwarp();
 
     // ---- 1. flagged logits: handed on in bitmap order, then blanked ---------------------------------
-    uint2* seg_out = p.candidates + seg * kSegCap;
-    uint32_t seg_fill = 0;  // warp-uniform
+    // The part's candidates form one list: first the flagged logits, warp after warp (each warp
+    // knows every warp's count from the marking above), then what reaches the threshold.
+    uint2* part_out = p.candidates + part_index * kPartCap;
+    uint32_t flagged_total, seg_fill;  // warp-uniform: the next free slot of this warp's run
+    {
+        const uint32_t v = lane < kScanWarps ? s_wflag[lane] : 0u;
+        flagged_total = __reduce_add_sync(0xFFFFFFFFu, v);
+        seg_fill = __reduce_add_sync(0xFFFFFFFFu, lane < warp ? v : 0u);
+    }
     const int col_base = (int)((int64_t)v0 * 4 - misalign + p.col_begin);  // global column of data[0]; fits 31 bits
     float f_raw = kPad, f_amax = 0.0f, f_y = -INFINITY;
     if (use_flags && !(p.debug_skip & 1)) {
@@ -225,7 +250,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             const int idx = r * 32 + lane;
             const int word = (kScanThreads / 8) * (idx >> 2) + 4 * warp + (idx & 3);
             const uint32_t banned_bits = s_ban[word];
-            uint32_t bits = s_pen[word] | banned_bits;
+            uint32_t bits = s_flag[word];
             const uint32_t count = __popc(bits);
             const uint32_t voters = __ballot_sync(0xFFFFFFFFu, count != 0);
             if (voters == 0) continue;
@@ -253,8 +278,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
                 f_raw = fmaxf(f_raw, l);
                 f_amax = (l != l) ? INFINITY : fmaxf(f_amax, fabsf(l));
                 f_y = fmaxf(f_y, y);
-                if (slot < (uint32_t)kSegCap) {
-                    seg_out[slot] = make_uint2(__float_as_uint(l),
+                if (slot < (uint32_t)kPartCap) {
+                    part_out[slot] = make_uint2(__float_as_uint(l),
                                                (uint32_t)(col_base + (int)e) | (banned ? kFlagBanned : kFlagPenalized));
                 }
                 ++slot;
@@ -398,9 +423,11 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         }
     }
     STAGE(8);
-    // Hand-off: slots in lane order, then trip, then component -- a fixed order.
-    if (__ballot_sync(0xFFFFFFFFu, noted != 0) != 0 && !(p.debug_skip & 2)) {
-        uint32_t count = 0;
+    // What reaches the threshold is counted now and handed on after the block has met (below): a
+    // warp's run in the part's list starts where the runs of the warps before it end.
+    uint32_t count = 0, before_mine = 0, warp_count = 0;
+    const bool any_noted = __ballot_sync(0xFFFFFFFFu, noted != 0) != 0 && !(p.debug_skip & 2);
+    if (any_noted) {
         for (uint32_t m2 = noted; m2; m2 &= m2 - 1) {
             const float4 d = data4[(__ffs(m2) - 1) * kScanThreads + tid];
             count += (d.x >= tprime ? 1u : 0u) + (d.y >= tprime ? 1u : 0u) + (d.z >= tprime ? 1u : 0u) +
@@ -412,8 +439,25 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
             const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
             if (lane >= o) incl += up;
         }
-        uint32_t slot = seg_fill + incl - count;
-        seg_fill += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        before_mine = incl - count;
+        warp_count = __shfl_sync(0xFFFFFFFFu, incl, 31);
+    }
+
+    STAGE(9);
+    // ---- block reduction in a fixed order, then the hand-off and the part's record -----------------------
+    {
+        const double wt = warp_sum((double)tail), wp = second_exp ? warp_sum((double)proc) : 0.0;
+        if (lane == 0) {
+            s_wtail[warp] = wt;
+            s_wproc[warp] = wp;
+            s_wfill[warp] = warp_count;
+        }
+    }
+    __syncthreads();
+    STAGE(10);
+    if (any_noted) {  // slots in warp order, then lane, trip, component -- a fixed order
+        uint32_t slot = flagged_total + before_mine;
+        for (int w = 0; w < warp; ++w) slot += s_wfill[w];
         for (uint32_t m2 = noted; m2; m2 &= m2 - 1) {
             const int v = (__ffs(m2) - 1) * kScanThreads + tid;
             const float4 d = data4[v];
@@ -422,36 +466,22 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 if (l[c] >= tprime) {
-                    if (slot < (uint32_t)kSegCap) seg_out[slot] = make_uint2(__float_as_uint(l[c]), col + c);
+                    if (slot < (uint32_t)kPartCap) part_out[slot] = make_uint2(__float_as_uint(l[c]), col + c);
                     ++slot;
                 }
             }
         }
     }
-
-    STAGE(9);
-    // ---- block reduction in a fixed order, then the part's record ---------------------------------------
-    {
-        const double wt = warp_sum((double)tail), wp = second_exp ? warp_sum((double)proc) : 0.0;
-        if (lane == 0) {
-            s_wtail[warp] = wt;
-            s_wproc[warp] = wp;
-            s_wfill[warp] = seg_fill;
-            p.seg_counts[seg] = min(seg_fill, (uint32_t)kSegCap);
-        }
-    }
-    __syncthreads();
-    STAGE(10);
     if (tid == 0) {
         double t = 0.0, q = 0.0;
-        uint32_t handed_on = 0, over = 0;
+        uint32_t handed_on = flagged_total;
 #pragma unroll
         for (int w = 0; w < kScanWarps; ++w) {
             t += s_wtail[w];
             q += s_wproc[w];
             handed_on += s_wfill[w];
-            over |= s_wfill[w] > (uint32_t)kSegCap ? 1u : 0u;
         }
+        p.part_counts[part_index] = min(handed_on, (uint32_t)kPartCap);
         const int64_t first = max((int64_t)v0 * 4 - (int64_t)misalign, (int64_t)0);
         const int64_t last = min((int64_t)v1 * 4 - (int64_t)misalign, p.cols);
         const uint32_t logits_here = (uint32_t)(last - first);
@@ -470,7 +500,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         s.thr = thr;
         s.nonfinite = (!(camax < INFINITY) || t != t || q != q) ? 1u : 0u;
         s.alive_tail = logits_here > handed_on ? logits_here - handed_on : 0u;
-        s.overflow = over;
+        s.overflow = handed_on > (uint32_t)kPartCap ? 1u : 0u;
         p.stats[part_index] = s;
     }
 #ifdef PSX_STAGE_CLOCKS
@@ -502,9 +532,8 @@ cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t str
     if (p.vecs_per_part > kPartVecs || p.rows > 65535ll * 65535ll) return cudaErrorInvalidConfiguration;
     const size_t shared = (size_t)((p.vecs_per_part + kScanThreads - 1) / kScanThreads * kScanThreads) * 16;
     const dim3 grid((unsigned)p.parts, (unsigned)(p.rows < 65535 ? p.rows : 65535), (unsigned)((p.rows + 65534) / 65535));
-    if (nucleus) scan_rows_kernel<true><<<grid, kScanThreads, shared, stream>>>(p);
-    else scan_rows_kernel<false><<<grid, kScanThreads, shared, stream>>>(p);
-    return cudaGetLastError();
+    return launch_overlapping(nucleus ? scan_rows_kernel<true> : scan_rows_kernel<false>, grid, dim3(kScanThreads), shared,
+                              stream, p);
 }
 
 }  // namespace psx

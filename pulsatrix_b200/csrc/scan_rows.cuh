@@ -25,11 +25,12 @@ struct ScanParams {
     int32_t k_need;                  // every part hands on at least this many logits (or all it has)
     int32_t parts;                   // CTAs per row
     int32_t vecs_per_part;           // float4 vectors per part, <= kPartVecs
+    int32_t inputs_ready;            // the inputs above are complete whatever the kernel before this one is doing
     int32_t debug_skip;              // profiling only: bit mask of kernel stages to leave out (results are then wrong)
     // output
     PartStats* stats;                // rows * parts
-    uint32_t* seg_counts;            // rows * parts * kScanWarps
-    uint2* candidates;               // rows * parts * kScanWarps * kSegCap
+    uint32_t* part_counts;           // rows * parts: candidates handed on by the part
+    uint2* candidates;               // rows * parts * kPartCap: the part's candidates, back to back
 };
 
 // nucleus: also accumulate the processed-domain tail that a full-vocabulary top-p / min-p needs.

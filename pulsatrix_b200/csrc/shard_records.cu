@@ -81,19 +81,19 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
     alive_tail = warp_sum_u32(alive_tail);
     float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
-    const int nseg = p.parts * kScanWarps;
-    const uint32_t* seg_counts = p.seg_counts + row * nseg;
-    const uint2* cands = p.candidates + (size_t)row * nseg * kSegCap;
+    const int nseg = p.parts;  // one candidate list per part
+    const uint32_t* seg_counts = p.part_counts + row * nseg;
+    const uint2* cands = p.candidates + (size_t)row * nseg * kPartCap;
 
     // The shard's own k-th largest processed value is a lower bound on the row's: nothing below
     // it (after the temperature divide's ties) can survive the merged top-k, so it need not travel.
     if (p.top_k > 0) {
         int m = 0;  // warp-uniform
         for (int s = 0; s < nseg; ++s) {
-            const int cnt = min((int)seg_counts[s], kSegCap);
+            const int cnt = min((int)seg_counts[s], kPartCap);
             for (int i = lane; i < cnt; i += 32) {
                 if (m + i < kPackKeys) {
-                    const uint2 c = cands[(size_t)s * kSegCap + i];
+                    const uint2 c = cands[(size_t)s * kPartCap + i];
                     s_keys[m + i] = ordered_key(processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty));
                 }
             }
@@ -121,13 +121,13 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
     uint2* out = reinterpret_cast<uint2*>(record + kRecordCandidatesOffset);
     uint32_t kept = 0, dropped = 0;  // warp-uniform
     for (int s = 0; s < nseg; ++s) {
-        const int cnt = min((int)seg_counts[s], kSegCap);
+        const int cnt = min((int)seg_counts[s], kPartCap);
         for (int base = 0; base < cnt; base += 32) {
             const int i = base + lane;
             bool keep = false, drop = false;
             uint2 c = make_uint2(0, 0);
             if (i < cnt) {
-                c = cands[(size_t)s * kSegCap + i];
+                c = cands[(size_t)s * kPartCap + i];
                 const float l = __uint_as_float(c.x);
                 const float y = processed_before_temperature(l, c.y, p.penalty);
                 keep = y >= keep_from;

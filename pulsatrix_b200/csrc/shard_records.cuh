@@ -26,8 +26,8 @@ __host__ __device__ inline size_t shard_record_bytes(int capacity) { return (siz
 
 struct PackParams {
     const PartStats* stats;      // rows * parts, from the row pass
-    const uint32_t* seg_counts;  // rows * parts * kScanWarps
-    const uint2* candidates;     // rows * parts * kScanWarps * kSegCap
+    const uint32_t* part_counts; // rows * parts
+    const uint2* candidates;     // rows * parts * kPartCap
     int32_t parts;
     int64_t rows;
     int32_t apply_temperature;
