@@ -137,9 +137,9 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     if (!sample) plan.k_need = 1;
     else if (top_k_on) plan.k_need = (int)std::min<int64_t>(c->top_k, 1 << 20);
     else plan.k_need = ctx->nucleus_k;
-    // A row of at most 256 vectors fits a part's candidate list whole (one vector per thread, 1024
-    // logits): hand everything on, and every filter is exact whatever the settings.
-    if (vectors <= psx::kScanThreads) plan.k_need = 1 << 30;
+    // A row of at most 256 vectors fits a part's candidate list whole (1024 logits): hand
+    // everything on, and every filter is exact whatever the settings.
+    if (vectors * 4 <= psx::kPartCap) plan.k_need = 1 << 30;
     plan.sort_capacity = plan.nucleus ? 4096 : 1024;
     plan.gather_capacity = plan.nucleus ? 8192 : 4096;
     // A part usually hands on a little over k_need logits, plus the few its share of the history flags.

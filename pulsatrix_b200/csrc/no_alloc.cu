@@ -165,7 +165,7 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
     const double log2e = 1.4426950408889634073599246810019;
     sp.log2e_over_t = (float)(apply_temperature ? log2e / (double)c->temperature : log2e);
     sp.k_need = !sample ? 1 : top_k_on ? (int)(c->top_k < (1 << 20) ? c->top_k : (1 << 20)) : 160;
-    if (vectors <= psx::kScanThreads) sp.k_need = 1 << 30;  // small rows are handed on whole
+    if (vectors * 4 <= psx::kPartCap) sp.k_need = 1 << 30;  // small rows are handed on whole
     sp.parts = (int)parts;
     sp.vecs_per_part = (int)((vectors + parts - 1) / parts);
     sp.debug_skip = 0;

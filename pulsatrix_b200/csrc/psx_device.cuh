@@ -14,8 +14,8 @@ namespace psx {
 // ---- geometry of the row pass ----------------------------------------------------------------
 constexpr int kScanThreads = 256;
 constexpr int kScanWarps = kScanThreads / 32;
-constexpr int kVecPerThread = 16;                            // float4 held in registers per thread
-constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits = 64 KB per CTA
+constexpr int kVecPerThread = 16;                            // float4 a thread looks at per pass
+constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits = 64 KB per CTA, three CTAs per SM
 constexpr int kPartCap = 1024;                               // candidate slots per part
 constexpr int kMergeThreads = 256;
 

@@ -115,7 +115,7 @@ __device__ unsigned long long g_stage_clocks[4096 * 16];
 #endif
 
 template <bool kNucleus>
-__global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanParams p) {
 #ifdef PSX_STAGE_CLOCKS
     unsigned long long clk[16];
     for (int i = 0; i < 16; ++i) clk[i] = 0;
@@ -169,8 +169,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     // ---- start the copy, and build the history bitmaps while it is in flight ----------------------
     if (tid == 0) barrier_init(&s_bar, 1);
     if (tid < kScanWarps) s_wflag[tid] = 0;
-    static_assert(2 * kBitmapWords == 4 * kScanThreads, "one 16-byte store per thread clears both bitmaps");
-    reinterpret_cast<uint4*>(s_bits)[tid] = make_uint4(0, 0, 0, 0);
+    static_assert(2 * kBitmapWords % 4 == 0, "the bitmaps are cleared 16 bytes at a time");
+    for (int i = tid; i < 2 * kBitmapWords / 4; i += kScanThreads) reinterpret_cast<uint4*>(s_bits)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     STAGE(1);
     if (tid == 0) {
@@ -246,11 +246,13 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
         // (vector v belongs to thread v % kScanThreads), so a row that is handed on whole fills every
         // warp's segment with exactly its own 128 logits.
         constexpr int kWordsPerWarp = kBitmapWords / kScanWarps;
-        for (int r = 0; r < kWordsPerWarp / 32; ++r) {
+        static_assert(kWordsPerWarp == 4 * kVecPerThread, "a warp's threads own 4 bitmap words per vector trip");
+        for (int r = 0; r < (kWordsPerWarp + 31) / 32; ++r) {
             const int idx = r * 32 + lane;
-            const int word = (kScanThreads / 8) * (idx >> 2) + 4 * warp + (idx & 3);
-            const uint32_t banned_bits = s_ban[word];
-            uint32_t bits = s_flag[word];
+            const bool owned = idx < kWordsPerWarp;
+            const int word = owned ? (kScanThreads / 8) * (idx >> 2) + 4 * warp + (idx & 3) : 0;
+            const uint32_t banned_bits = owned ? s_ban[word] : 0u;
+            uint32_t bits = owned ? s_flag[word] : 0u;
             const uint32_t count = __popc(bits);
             const uint32_t voters = __ballot_sync(0xFFFFFFFFu, count != 0);
             if (voters == 0) continue;
@@ -311,16 +313,21 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const int full_warps = live_threads >> 5;  // warps whose every thread owns a vector
     int kp = 33;  // > 32: no threshold, hand everything on
     if (full_warps > 0) kp = (p.k_need + full_warps - 1) / full_warps;
-    // Threshold: every full warp offers its kp largest per-thread maxima; the k_need-th largest
-    // of that pool (at least k_need values) is reached by at least k_need logits.  For kp <= 8
-    // the pool is kept and the surplus (fewer than 8 values) is taken away from the bottom;
-    // beyond that each warp offers only its kp-th largest and the smallest of those is used.
-    const bool pooled = kp <= kPool;
+    // Threshold: a value that at least k_need logits of the part reach (or everything, when the
+    // part has fewer).  Greedy needs the part's maximum only.  Otherwise every full warp finds
+    // its kp-th largest per-thread maximum, kp = ceil(k_need / full warps), and the smallest of
+    // those is reached by kp maxima in every full warp.  When that would overshoot k_need by
+    // only a few, the warps pool their kp largest instead and the overshoot is taken away from
+    // the bottom of the pool, which gives exactly k_need.
+    const bool single = p.k_need == 1;
+    const bool pooled = !single && kp <= kPool && full_warps * kp - p.k_need <= 4;
     {
         const float wraw = warp_max_redux(fmaxf(m, f_raw)), wamax = warp_max_redux(amax);
         const float wymax = warp_max_redux(fmaxf(m_alive, f_y));
         float wthr = -INFINITY;
-        if (pooled) {
+        if (single) {
+            wthr = warp_max_redux(m_alive);
+        } else if (pooled) {
             uint32_t offer = 0xFFFFFFFFu;  // lane i ends up with the warp's i-th largest; all ones: no entry
             if (warp < full_warps) {
                 uint32_t key = monotone_key(m_alive);
@@ -332,6 +339,8 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
                 }
             }
             if (lane < kPool) s_pool[warp * kPool + lane] = offer;
+        } else if (kp <= 8) {
+            wthr = warp_kth_largest_small(m_alive, kp, lane);
         } else if (kp <= 32) {
             wthr = warp_kth_largest(m_alive, kp, lane);
         }
@@ -350,26 +359,23 @@ __global__ void __launch_bounds__(kScanThreads) scan_rows_kernel(const ScanParam
     const float camax = warp_max_redux(lane < kScanWarps ? s_wamax[lane] : 0.0f);
     const float cymax = warp_max_redux(lane < kScanWarps ? s_wymax[lane] : -INFINITY);
     float thr = -INFINITY;
-    if (pooled) {
+    if (single) {
+        thr = warp_max_redux(lane < kScanWarps ? s_wthr[lane] : -INFINITY);
+    } else if (pooled) {
         // Lane L holds pool entries L and L + 32; the smallest entries are dropped until k_need
         // are left, whose minimum is the threshold.
         static_assert(kPool * kScanWarps == 64, "two pool entries per lane");
         uint32_t a = s_pool[lane], b2 = s_pool[lane + 32];
-        if (p.k_need == 1) {  // the largest entry
-            const uint32_t top = max(a == 0xFFFFFFFFu ? 0u : a, b2 == 0xFFFFFFFFu ? 0u : b2);
-            thr = from_ordered_key(__reduce_max_sync(0xFFFFFFFFu, top));
-        } else {
-            const int surplus = full_warps * kp - p.k_need;
-            for (int i = 0; i < surplus; ++i) {
-                const uint32_t mine = min(a, b2);
-                const uint32_t low = __reduce_min_sync(0xFFFFFFFFu, mine);
-                const uint32_t holders = __ballot_sync(0xFFFFFFFFu, mine == low);
-                if (lane == __ffs(holders) - 1) {
-                    if (a == low) a = 0xFFFFFFFFu; else b2 = 0xFFFFFFFFu;
-                }
+        const int surplus = full_warps * kp - p.k_need;
+        for (int i = 0; i < surplus; ++i) {
+            const uint32_t mine = min(a, b2);
+            const uint32_t low = __reduce_min_sync(0xFFFFFFFFu, mine);
+            const uint32_t holders = __ballot_sync(0xFFFFFFFFu, mine == low);
+            if (lane == __ffs(holders) - 1) {
+                if (a == low) a = 0xFFFFFFFFu; else b2 = 0xFFFFFFFFu;
             }
-            thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, min(a, b2)));
         }
+        thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, min(a, b2)));
     } else if (full_warps > 0 && kp <= 32) {
         const uint32_t key = lane < full_warps ? monotone_key(s_wthr[lane]) : 0xFFFFFFFFu;
         thr = from_ordered_key(__reduce_min_sync(0xFFFFFFFFu, key));
