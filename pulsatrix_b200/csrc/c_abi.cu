@@ -153,7 +153,7 @@ psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int parts) {
     if (parts > 16 * psx::kMergeThreads) {
         return fail(PSX_ERR_UNSUPPORTED, "psx_b200: rows wider than 64M logits per GPU are not supported");
     }
-    const int bytes = (int)psx::merge_rows_shared_bytes(plan.sort_capacity, plan.gather_capacity);
+    const int bytes = (int)psx::merge_rows_shared_bytes(plan.sort_capacity, plan.gather_capacity, plan.nucleus);
     if (ctx->merge_capacity_configured >= bytes) return PSX_OK;
     PSX_CUDA(psx::configure_merge_rows((size_t)bytes));
     ctx->merge_capacity_configured = bytes;
@@ -383,6 +383,12 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
     mp.cand_row_stride = mp.cand_part_stride * plan.parts;
     fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
+    if (plan.nucleus) {  // the wide plan: candidates and sort arrays share their shared memory
+        mp.logits = logits;
+        mp.logits_row_stride = row_stride;
+        mp.logits_col_begin = 0;
+        mp.overlay = 1;
+    }
 
     cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
     if (ctx->timing) {
@@ -463,6 +469,12 @@ psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream_ptr, float* logits
         fill_merge_settings(mp, config, plan, rows, vocab, /*uniforms=*/nullptr,
                             static_cast<int64_t*>(ctx->pl_tokens.ptr), static_cast<float*>(ctx->pl_log_probs.ptr), status,
                             nullptr);
+        if (plan.nucleus) {
+            mp.logits = logits;
+            mp.logits_row_stride = row_stride;
+            mp.logits_col_begin = 0;
+            mp.overlay = 1;
+        }
         mp.survivor_cols = static_cast<uint32_t*>(ctx->surv_cols.ptr);
         mp.survivor_vals = static_cast<float*>(ctx->surv_vals.ptr);
         mp.survivor_counts = static_cast<uint32_t*>(ctx->surv_counts.ptr);

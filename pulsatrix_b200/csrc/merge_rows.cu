@@ -41,8 +41,9 @@ extern "C" __attribute__((visibility("default"))) int psx_debug_merge_clocks(uns
 }
 #endif
 
-size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity) {
-    return (size_t)sort_capacity * (8 + 8 + 8 + 1) + (size_t)gather_capacity * 8 + 16;
+size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, bool overlay) {
+    const size_t list = (size_t)sort_capacity * 8, rest = (size_t)sort_capacity * (8 + 8 + 1), gathered = (size_t)gather_capacity * 8;
+    return list + (overlay ? (rest > gathered ? rest : gathered) : rest + gathered) + 16;
 }
 
 int merge_slot_shift(int parts, int part_cap, int expected) {
@@ -60,7 +61,7 @@ cudaError_t configure_merge_rows(size_t shared_bytes) {
 
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;
-    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity);
+    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, p.overlay != 0);
     return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, p);
 }
 

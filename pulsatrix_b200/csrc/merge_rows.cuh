@@ -45,9 +45,18 @@ struct MergeParams {
     int32_t survivor_cap;
     int32_t debug_stop;          // profiling only: leave the kernel after this stage (0: run everything)
     int32_t gather_capacity;     // candidates of one row held in shared memory (<= 4 * sort_capacity)
+    // Optional: the logits themselves (row r, global column c at logits[r*logits_row_stride + c -
+    // logits_col_begin]).  With them the chosen token's raw logit is read back from there, and, when
+    // `overlay` is set, the gathered candidates share their shared memory with the sort arrays that
+    // are only needed once the list is built (smaller footprint, more rows per SM).  Only for
+    // settings without a top-k.
+    const float* logits;
+    int64_t logits_row_stride;
+    int64_t logits_col_begin;
+    int32_t overlay;
 };
 
-size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity);
+size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, bool overlay);
 // The slot_shift for lists that usually hold about `expected` candidates, within the fetch budget.
 int merge_slot_shift(int parts, int part_cap, int expected);
 cudaError_t configure_merge_rows(size_t shared_bytes);

@@ -432,10 +432,97 @@ __device__ __forceinline__ double block_min_f64(double v, double* scratch) {
 // sorted, sequential replay instead.  keyA: n unsorted keys (ordered value << 32 | ~column);
 // ex[i] = exp(x_i - x_max); alive[i] is set here.
 constexpr double kExactMargin = 1e-9;
+constexpr int kMassPasses = 8;  // histograms decide_wide needs: four passes over the value, four over the column
+
+// Along ascending key (key_of(i) over the entries with in_play(i)), the first key K at which the
+// running mass start + sum of ex over keys <= K rises above `target`; 8-bit radix passes from
+// bit `top_shift` down, one barrier each: every pass adds the masses of the keys that still match
+// into its own 256-bin histogram (hist: (top_shift / 8 + 1) * 768 words, all zero on entry) and
+// every warp scans the bins for itself.  below = start + mass of the keys < K; at =
+// mass of K.  When the mass never rises above the target, K is the largest key in play.
+// Masses (all in [0, 1]) are added as fixed-point numbers of 2^-44, in three pieces of 15 bits,
+// each piece into its own 32-bit bin: integer additions give the same sums in any order, native
+// 32-bit shared-memory atomics do not mind many keys in one bin, and 2^15 entries cannot overflow
+// a piece.  What the rounding to 2^-44 loses, at most n * 2.9e-14 in all, is far inside
+// kExactMargin.
+constexpr double kMassUnit = 17592186044416.0;  // 2^44
+template <class KeyOf, class InPlay>
+__device__ inline void mass_select(KeyOf key_of, InPlay in_play, const double* ex, int n, int top_shift, double start,
+                                   double target, uint32_t* hist, uint32_t& K, double& below, double& at) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    uint32_t prefix = 0, mask = 0;
+    // the running mass is compared as an integer: units of 2^-44 above `start`
+    const double room = (target - start) * kMassUnit;
+    const u64 target_units = room <= 0.0 ? 0ull : room >= 1.8e19 ? ~0ull : (u64)room;
+    const bool already_above = !(start <= target);
+    u64 carried = 0;  // units below the current prefix
+    u64 at_units = 0;
+#pragma unroll 1
+    for (int shift = top_shift; shift >= 0; shift -= 8) {
+        uint32_t* h = hist + 768 * (shift >> 3);
+        for (int i = tid; i < n; i += kMergeThreads) {
+            if (!in_play(i)) continue;
+            const uint32_t key = key_of(i);
+            if ((key & mask) != prefix) continue;
+            const u64 units = (u64)__double2ull_rn(ex[i] * kMassUnit);  // at most 2^44
+            uint32_t* bin = h + ((key >> shift) & 255u);
+            atomicAdd(bin, (uint32_t)units & 0x7FFFu);
+            atomicAdd(bin + 256, (uint32_t)(units >> 15) & 0x7FFFu);
+            atomicAdd(bin + 512, (uint32_t)(units >> 30));
+        }
+        __syncthreads();
+        // lane L owns bins 8L .. 8L+7, ascending
+        u64 run[8];
+        u64 local = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int at_bin = 8 * lane + q;
+            local += (u64)h[at_bin] + ((u64)h[at_bin + 256] << 15) + ((u64)h[at_bin + 512] << 30);
+            run[q] = local;
+        }
+        u64 incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const u64 up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const u64 before_mine = carried + (incl - local);
+        int first = 8, last = -1;  // first bin of mine that rises above the target; last bin of mine that holds mass
+#pragma unroll
+        for (int q = 7; q >= 0; --q) {
+            if (already_above ? run[q] != (q ? run[q - 1] : 0ull) : before_mine + run[q] > target_units) first = q;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (run[q] != (q ? run[q - 1] : 0ull)) last = q;
+        }
+        const uint32_t crossing = __ballot_sync(0xFFFFFFFFu, first < 8), holding = __ballot_sync(0xFFFFFFFFu, last >= 0);
+        int src, q_src;
+        if (crossing != 0) {
+            src = __ffs(crossing) - 1;
+            q_src = __shfl_sync(0xFFFFFFFFu, first, src);
+        } else {  // never above the target: the largest key in play (holding != 0 while anything is in play)
+            src = holding != 0 ? 31 - __clz(holding) : 0;
+            q_src = max(0, __shfl_sync(0xFFFFFFFFu, last, src));
+        }
+        u64 below_bin = before_mine, mass_bin = run[0];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) {
+            if (q <= q_src) { below_bin = before_mine + run[q - 1]; mass_bin = run[q] - run[q - 1]; }
+        }
+        carried = __shfl_sync(0xFFFFFFFFu, below_bin, src);
+        at_units = __shfl_sync(0xFFFFFFFFu, mass_bin, src);
+        prefix |= (uint32_t)(8 * src + q_src) << shift;
+        mask |= 255u << shift;
+    }
+    K = prefix;
+    below = start + (double)carried / kMassUnit;
+    at = (double)at_units / kMassUnit;
+}
 
 __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const double* ex, uint8_t* alive, int n,
                             bool rest_alive, double rest, double rest_bound, double u, double* scratch,
-                            Decision& out) {
+                            uint32_t* hist /* kMassPasses * 768 words */, Decision& out) {
     const int tid = threadIdx.x;
     out.status = PSX_ROW_OK;
     out.token = -1;
@@ -453,6 +540,7 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
     for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
     top_key = block_max_u32(top_key, scratch);
     for (int i = tid; i < n; i += kMergeThreads) alive[i] = 1;
+    for (int i = tid; i < kMassPasses * 768; i += kMergeThreads) hist[i] = 0;
     __syncthreads();
 
     if (p.top_p < 1.0f) {  // src/generation.cpp:89-103
@@ -467,15 +555,12 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
             rest_alive = false;
         }
         // Smallest value key whose entries push the cumulative mass past the limit.
-        uint32_t lo = 0, hi = top_key;  // mass up to lo stays within the limit, mass up to hi (all of it) exceeds it
         if (limit >= 1.0 - 1e-12) return false;
-        while (hi - lo > 1) {
-            const uint32_t mid = lo + (hi - lo) / 2;
-            const double c = (base + masked_sum([&](int i) { return key_ord(keyA[i]) <= mid; })) / sum;
-            if (c <= limit) lo = mid; else hi = mid;
-        }
-        const uint32_t cut = hi;
-        const double below = (base + masked_sum([&](int i) { return key_ord(keyA[i]) < cut; })) / sum;
+        uint32_t cut;
+        double mass_below, mass_at;
+        mass_select([&](int i) { return key_ord(keyA[i]); }, [&](int) { return true; }, ex, n, 24, base, limit * sum, hist, cut,
+                    mass_below, mass_at);
+        const double below = mass_below / sum;
         margin = fmin(margin, fabs(below - limit));
         // Entries equal to the cut value go in ascending column order, one probability each.
         double ties = 0.0;
@@ -536,17 +621,16 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
     // src/generation.cpp:140-152: the first column whose cumulative probability exceeds u.
     if (rest_alive) { out.status = PSX_ROW_TOO_WIDE; return true; }
     const double sum = masked_sum([&](int i) { return alive[i] != 0; });
-    long long lo = -1, hi = p.vocab - 1;  // mass up to column lo is <= u, mass up to column hi (all, 1.0) is > u
-    while (hi - lo > 1) {
-        const long long mid = lo + (hi - lo) / 2;
-        const double f = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) <= mid; }) / sum;
-        if (f > u) hi = mid; else lo = mid;
-    }
-    const double before = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) < hi; }) / sum;
-    const double upto = masked_sum([&](int i) { return alive[i] != 0 && (long long)key_col(keyA[i]) <= hi; }) / sum;
+    // The first column at which the running mass rises above u * sum.
+    uint32_t hi;
+    double mass_before, mass_at;
+    const int column_shift = p.vocab <= (1 << 16) ? 8 : p.vocab <= (1 << 24) ? 16 : 24;
+    mass_select([&](int i) { return key_col(keyA[i]); }, [&](int i) { return alive[i] != 0; }, ex, n, column_shift, 0.0,
+                u * sum, hist + 4 * 768, hi, mass_before, mass_at);
+    const double before = mass_before / sum, upto = (mass_before + mass_at) / sum;
     out.draw_margin = before == 0.0 ? fabs(u - upto) : fmin(fabs(u - before), fabs(u - upto));
     if (out.draw_margin < kExactMargin) return false;
-    out.token = hi;
+    out.token = (long long)hi;
     return true;
 }
 
@@ -733,7 +817,10 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     u64* keyB = keyA + cap;
     double* ex = reinterpret_cast<double*>(keyB + cap);
     uint8_t* alive = reinterpret_cast<uint8_t*>(ex + cap);
-    uint32_t* cand_l = reinterpret_cast<uint32_t*>(alive + cap);  // raw logit bits of every candidate
+    // raw logit bits of every candidate; with `overlay` they lie over keyB / ex / alive, which nothing
+    // touches before the list in keyA is complete, and are not looked at afterwards
+    const bool overlay = p.overlay != 0 && p.logits != nullptr && !(p.do_sample && p.top_k > 0 && p.top_k < p.vocab);
+    uint32_t* cand_l = overlay ? reinterpret_cast<uint32_t*>(keyB) : reinterpret_cast<uint32_t*>(alive + cap);
     uint32_t* cand_c = cand_l + gcap;                             // column | flags
     uint32_t* ykeys = reinterpret_cast<uint32_t*>(dyn);           // scratch over the (still unused) sort arrays
     uint32_t* xkeys = reinterpret_cast<uint32_t*>(keyB);          // likewise, clear of the list itself: 4 * cap words
@@ -976,8 +1063,10 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         const bool rest_in_play = (alive_tail + dropped) > 0.0;
         const double bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_top);
         Decision wide;
-        decided = decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, u_row,
-                              s_d[0], wide);
+        // (the histograms lie over the second sort array, idle on this path: kMassPasses * 3 KB of cap * 8 bytes)
+        decided = cap * 8 >= kMassPasses * 768 * 4 &&
+                  decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, u_row, s_d[0],
+                              reinterpret_cast<uint32_t*>(keyB), wide);
         __syncthreads();
         if (decided && tid == 0) {
             s_dec = wide;
@@ -1074,9 +1163,13 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         if (tid == 0) p.survivor_counts[row] = (uint32_t)min(s_count, p.survivor_cap);
     }
     PSX_MERGE_STAGE(8);
-    if (dec.status == PSX_ROW_OK) {  // the chosen column's raw logit sits among the candidates
-        for (int i = tid; i < total; i += kMergeThreads) {
-            if ((long long)(cand_c[i] & kColumnMask) == dec.token) s_chosen_raw = cand_l[i];
+    if (dec.status == PSX_ROW_OK) {
+        if (overlay) {  // the chosen column's raw logit, from the logits themselves
+            if (tid == 0) s_chosen_raw = __float_as_uint(p.logits[row * p.logits_row_stride + (dec.token - p.logits_col_begin)]);
+        } else {        // it sits among the candidates
+            for (int i = tid; i < total; i += kMergeThreads) {
+                if ((long long)(cand_c[i] & kColumnMask) == dec.token) s_chosen_raw = cand_l[i];
+            }
         }
     }
     __syncthreads();
