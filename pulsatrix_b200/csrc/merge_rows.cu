@@ -26,7 +26,7 @@ namespace psx {
 
 namespace {
 
-__global__ void __launch_bounds__(kMergeThreads, 2) merge_rows_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const MergeParams p) {
     extern __shared__ unsigned long long dyn[];
     grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
     grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
