@@ -35,6 +35,10 @@ sys.path[:0] = [str(ROOT), str(ROOT / "tests")]
 from pulsatrix_b200.workloads import WORKLOADS  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes per algorithmic byte of the row pass, from the ncu capture of one launch on C2 that
+# profiles/scan_rows_kernel_c2.md summarises (dram read 39.09 MB + write 0 over 38.90 MB); the
+# kernel reads every logit once whatever the workload, so other workloads scale with their bytes.
+ROW_PASS_TRAFFIC_RATIO = 39087616 / 38895616
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -287,7 +291,10 @@ def run_ours(args, rank, world):
         "gpu_launches": int(launches) * world,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "scan_rows_kernel", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "traffic": int(round(w.logits_bytes * ROW_PASS_TRAFFIC_RATIO)),
+                     "traffic_note": "bytes per launch; ncu dram read+write of one C2 launch, scaled by this workload's bytes",
+                     "algorithmic_bytes": w.logits_bytes,
                      "launch_ms": scan_avg_ms, "survivor_stage_ms": merge_avg_ms,
                      "frac_of_nominal_8TBs": achieved / 8000.0,
                      "read_only_kernel_gbs": w.logits_bytes / (read_ms * 1e-3) / 1e9,
