@@ -296,13 +296,12 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     float m = kPad, amax = f_amax;
     if (!(p.debug_skip & 8)) {
         int v = tid;
-        for (; v + 3 * kScanThreads < nvec; v += 4 * kScanThreads) {  // four independent loads per trip
-            const float4 d0 = data4[v], d1 = data4[v + kScanThreads], d2 = data4[v + 2 * kScanThreads],
-                         d3 = data4[v + 3 * kScanThreads];
-            m = max_into(max_into(max_into(max_into(m, d0), d1), d2), d3);
-            amax = amax_into(amax_into(amax_into(amax_into(amax, d0), d1), d2), d3);
+        for (; v + kScanThreads < nvec; v += 2 * kScanThreads) {  // two independent loads per trip
+            const float4 d0 = data4[v], d1 = data4[v + kScanThreads];
+            m = max_into(max_into(m, d0), d1);
+            amax = amax_into(amax_into(amax, d0), d1);
         }
-        for (; v < nvec; v += kScanThreads) {
+        if (v < nvec) {
             const float4 d = data4[v];
             m = max_into(m, d);
             amax = amax_into(amax, d);
