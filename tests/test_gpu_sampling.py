@@ -215,3 +215,78 @@ def test_host_entry_point_gives_the_same_answers():
         tokens, logp, status, diag = gh.ctx().sample_rows_host(arr, hist.ravel(), offsets, gh.psx_config(cfg), u,
                                                                row_stride=stride, vocab=w.vocab)
         assert tokens.tolist() == dev[0].tolist() and logp.tobytes() == dev[1].tobytes() and (status == 0).all()
+
+
+# ---- the rarely taken paths of the survivor stage ---------------------------------------------------
+
+def test_long_histories_overflow_the_speculative_slots_and_still_match():
+    """A part whose list is several times longer than what the survivor stage fetches before it
+    knows the counts (hundreds of penalised tokens with a small top-k): the rest of the list is
+    appended afterwards."""
+    rng = np.random.RandomState(77)
+    vocab, rows, hlen = 30000, 6, 700
+    logits = (rng.randn(rows, vocab) * 3.0).astype(np.float32)
+    hist = np.stack([rng.choice(vocab, size=hlen, replace=False) for _ in range(rows)]).astype(np.int64)
+    offsets = np.arange(rows + 1, dtype=np.int64) * hlen
+    seeds = np.arange(rows, dtype=np.uint64) + 11
+    for top_k, top_p in [(5, 0.9), (1, 1.0), (40, 0.5)]:
+        cfg = ol.make_config(max_new_tokens=1, do_sample=True, temperature=0.8, top_k=top_k, top_p=top_p,
+                             repetition_penalty=1.3)
+        (tokens, logp, status, diag), want = gh.check_rows_against_oracle(logits, hist, offsets, cfg, seeds)
+        assert (status == 0).all()
+        assert (diag["survivors"] == want["survivors"]).all()
+
+
+def test_hundreds_of_ties_at_the_kth_value_take_the_sorted_path():
+    """HF semantics keep every tie at the k-th value (src/generation.cpp:85): 150 distinct large
+    logits and 400 logits equal to the 150th leave 549 survivors, more than the
+    one-entry-per-thread path holds."""
+    rng = np.random.RandomState(78)
+    vocab, rows = 20000, 4
+    logits = (rng.randn(rows, vocab) - 6.0).astype(np.float32)
+    for r in range(rows):
+        cols = rng.choice(vocab, size=549, replace=False)
+        logits[r, cols[:149]] = np.linspace(5.0, 9.0, 149).astype(np.float32) + np.float32(r) * 0.01
+        logits[r, cols[149:]] = np.float32(4.0)
+    hist = rng.randint(0, vocab, size=(rows, 32)).astype(np.int64)
+    offsets = np.arange(rows + 1, dtype=np.int64) * 32
+    seeds = np.arange(rows, dtype=np.uint64) + 5
+    for top_p, penalty in [(0.9, 1.0), (1.0, 1.0), (0.6, 1.1)]:
+        cfg = ol.make_config(max_new_tokens=1, do_sample=True, temperature=1.3, top_k=150, top_p=top_p,
+                             repetition_penalty=penalty)
+        (tokens, logp, status, diag), want = gh.check_rows_against_oracle(logits, hist, offsets, cfg, seeds)
+        assert (status == 0).all()
+        assert (diag["survivors"] == want["survivors"]).all()
+        if penalty == 1.0 and top_p == 1.0:
+            assert (diag["survivors"] == 549).all()
+
+
+def test_the_promise_of_complete_inputs_changes_no_answer():
+    """With psx_b200_ctx_inputs_are_ready a row pass runs ahead of the survivor stage of the call
+    before it: three different batches enqueued back to back give what they give one at a time."""
+    import torch
+    w = WORKLOADS["c2"]
+    cfg = gh.psx_config(workload_rows.config_of(w))
+    batches = []
+    for b in range(3):
+        logits, hist, offsets, seeds = workload_rows.build("c2", np.arange(16 * b, 16 * b + 16))
+        batches.append((torch.from_numpy(logits).cuda(), torch.from_numpy(hist.ravel().astype(np.int64)).cuda(),
+                        torch.from_numpy(offsets.astype(np.int64)).cuda(),
+                        torch.from_numpy(psx.uniforms_mt19937_64(seeds)).cuda()))
+    context = gh.ctx()
+    alone = []
+    for logits, hist, offsets, u in batches:
+        out = context.sample_rows(logits, hist, offsets, cfg, u)
+        torch.cuda.synchronize()
+        alone.append((out["tokens"].cpu().numpy(), out["log_probs"].cpu().numpy()))
+    context.inputs_are_ready(True)
+    try:
+        for _ in range(3):
+            outs = [context.sample_rows(logits, hist, offsets, cfg, u) for logits, hist, offsets, u in batches]
+            torch.cuda.synchronize()
+            for out, (tokens, logp) in zip(outs, alone):
+                assert out["status"].cpu().numpy().tolist() == [0] * 16
+                assert out["tokens"].cpu().numpy().tolist() == tokens.tolist()
+                assert out["log_probs"].cpu().numpy().tobytes() == logp.tobytes()
+    finally:
+        context.inputs_are_ready(False)
