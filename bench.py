@@ -61,7 +61,9 @@ def measured_hbm_peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of one GPU while a region runs: NVML from a thread
+    every few milliseconds (the timed regions are short), nvidia-smi when NVML cannot be loaded.
+    Reads only; changes no setting of the GPU."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -70,8 +72,38 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.lines = []
+        self.samples = []  # (sm_mhz, reasons bit mask)
+        self.thread = None
+        self.stopping = threading.Event()
+        self.max_mhz = None
+        self.nvml = None
+
+    def _poll(self, handle):
+        nvml = self.nvml
+        while not self.stopping.is_set():
+            try:
+                self.samples.append((nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM),
+                                     nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                                     if hasattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons")
+                                     else nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)))
+            except Exception:  # noqa: BLE001 - a failed sample is just a missing sample
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, args=(handle,), daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001 - fall back to the command-line tool
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
@@ -81,6 +113,20 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.nvml is not None:
+            self.stopping.set()
+            self.thread.join(timeout=2)
+            nvml = self.nvml
+            bits = {"hw_slowdown": getattr(nvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                    "hw_thermal_slowdown": getattr(nvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                    "sw_thermal_slowdown": getattr(nvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                    "sw_power_cap": getattr(nvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+            sm = [float(s[0]) for s in self.samples]
+            seen = 0
+            for _, mask in self.samples:
+                seen |= int(mask)
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(name for name, bit in bits.items() if seen & bit), "samples": len(sm)}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)

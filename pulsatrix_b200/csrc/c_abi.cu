@@ -608,9 +608,14 @@ psx_status psx_b200_sample_rows_host(psx_ctx* ctx, const float* logits, int64_t 
     if (psx_status s = reserve(ctx->h_diag, (size_t)rows * sizeof(psx_row_diag))) return s;
 
     // Rows are packed on the device (stride = vocab) whatever the host stride is.
-    PSX_CUDA(cudaMemcpy2DAsync(ctx->h_logits.ptr, (size_t)vocab * sizeof(float), logits,
-                               (size_t)row_stride * sizeof(float), (size_t)vocab * sizeof(float), (size_t)rows,
-                               cudaMemcpyHostToDevice, stream));
+    if (row_stride == vocab) {
+        PSX_CUDA(cudaMemcpyAsync(ctx->h_logits.ptr, logits, (size_t)rows * vocab * sizeof(float), cudaMemcpyHostToDevice,
+                                 stream));
+    } else {
+        PSX_CUDA(cudaMemcpy2DAsync(ctx->h_logits.ptr, (size_t)vocab * sizeof(float), logits,
+                                   (size_t)row_stride * sizeof(float), (size_t)vocab * sizeof(float), (size_t)rows,
+                                   cudaMemcpyHostToDevice, stream));
+    }
     if (with_history) {
         if (history_total > 0) {
             PSX_CUDA(cudaMemcpyAsync(ctx->h_history.ptr, history_ids, (size_t)history_total * sizeof(int64_t),
