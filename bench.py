@@ -88,7 +88,7 @@ class ClockSampler:
                                      else nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)))
             except Exception:  # noqa: BLE001 - a failed sample is just a missing sample
                 pass
-            time.sleep(0.002)
+            time.sleep(0.0005)
 
     def start(self):
         try:

@@ -247,16 +247,21 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
     const bool cut_k = top_k_on && n >= p.top_k;
 
     // Among all n: how many come before mine by (value desc, column asc) -- the keys compare that
-    // way as integers --, how many of those share my value, and how many share my value at all.
-    uint32_t counts = 0;  // three 10-bit fields
+    // way as integers --, how many of those share my value, how many share my value at all, and
+    // how many sit at lower columns.
+    uint32_t counts = 0, lower = 0;  // three 10-bit fields; one count
     if (in_range) {
         for (int j = slice; j < n; j += T) {
             const u64 other = keyA[j];
             const uint32_t before = other > mine ? 1u : 0u, same = key_ord(other) == my_ord ? 1u : 0u;
             counts += before + ((before & same) << 10) + (same << 20);
+            lower += key_col(other) < my_col ? 1u : 0u;
         }
     }
-    for (int o = T >> 1; o > 0; o >>= 1) counts += __shfl_xor_sync(0xFFFFFFFFu, counts, o);
+    for (int o = T >> 1; o > 0; o >>= 1) {
+        counts += __shfl_xor_sync(0xFFFFFFFFu, counts, o);
+        lower += __shfl_xor_sync(0xFFFFFFFFu, lower, o);
+    }
     const int place = (int)(counts & 1023u), same_before = (int)((counts >> 10) & 1023u), same = (int)(counts >> 20);
     if (have) {
         if (place == 0) { w.shared[0] = my_ord; w.shared[1] = (uint32_t)e; }  // the first maximum
@@ -267,17 +272,19 @@ __device__ inline void decide_small(const MergeParams& p, const u64* keyA, int n
     PSX_MERGE_STAGE(10);
     const uint32_t top_ord = w.shared[0], best = w.shared[1], kth = w.shared[2];
     const bool survivor = have && my_ord >= kth;  // src/generation.cpp:85: ties at the k-th value stay
-    if (survivor) w.cols[place] = my_col;         // the survivors are exactly the first ns places
+    if (have) w.cols[place] = my_col;             // the survivors are exactly the first ns places
     const int ns = __syncthreads_count(survivor ? 1 : 0);
     bool rest_alive = !top_k_on && sample && rest_in_play;
 
     // Place by ascending column among the survivors, and in the top-p walk (value ascending, then
     // column ascending): the survivors below my value, plus those of my value at lower columns.
-    int place_b = 0;
+    // Place by ascending column: the lower columns among all n, less those of the few entries
+    // beyond the survivors.
+    int place_b = (int)lower;
     const int place_w = ns - (place - same_before) - same + same_before;
     double my_ex = 0.0;
     if (survivor) {
-        for (int j = 0; j < ns; ++j) place_b += w.cols[j] < my_col ? 1 : 0;
+        for (int j = ns; j < n; ++j) place_b -= w.cols[j] < my_col ? 1 : 0;
         my_ex = exp((double)from_ordered_key(my_ord) - (double)from_ordered_key(top_ord));  // src/generation.cpp:46
         w.order_b[place_b] = (uint32_t)e;
         w.ex[place_b] = my_ex;
