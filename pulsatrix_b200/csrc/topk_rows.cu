@@ -4,6 +4,12 @@
 // its slice of the row from HBM once, turns it into order-preserving keys (NaN above every
 // number, -0.0 == +0.0, `largest == 0` mirrors the order) and keeps the keys in shared memory.
 // Everything after that works on the keys:
+//   0. while it loads, every thread notes the largest key it has seen; the k-th largest of a CTA's
+//      thread maxima is a lower bound of the k-th key of its slice (k threads hold an entry at or
+//      above it), and one sweep keeps only the entries that reach it, usually k and a few, in a
+//      short list; the lists go to the first CTA, which runs the steps below over them alone
+//      (whenever k <= 256 and no list overflows: a row of equal values still goes through the
+//      slices, by the whole cluster);
 //   1. a 4 x 8-bit radix select finds the k-th key: every CTA counts its slice's digits into a
 //      histogram of its own, the cluster meets, and every CTA adds the cluster's histograms up
 //      through distributed shared memory for itself;
@@ -36,6 +42,29 @@ __device__ __forceinline__ uint32_t rank_key(float x, bool largest) {
     return largest ? k : ~k;
 }
 
+// The kp-th largest (1-based, kp <= 32) of the 32 lanes' keys: for small kp the maximum is taken
+// away kp - 1 times, else a bitonic sort across the lanes.
+__device__ __forceinline__ uint32_t warp_kth_largest_key(uint32_t key, int kp, int lane) {
+    if (kp <= 6) {
+        for (int i = 1; i < kp; ++i) {
+            const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, key);
+            const uint32_t holders = __ballot_sync(0xFFFFFFFFu, key == top);
+            if (lane == __ffs(holders) - 1) key = 0;
+        }
+        return __reduce_max_sync(0xFFFFFFFFu, key);
+    }
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, key, j);
+            const bool descending_block = (lane & k) == 0, lower_lane = (lane & j) == 0;
+            key = (lower_lane == descending_block) ? max(key, other) : min(key, other);
+        }
+    }
+    return __shfl_sync(0xFFFFFFFFu, key, kp - 1);
+}
+
 struct TopKParams {
     const float* in;
     float* values;
@@ -47,19 +76,21 @@ struct TopKParams {
     uint32_t slice;  // entries per CTA (a multiple of 4)
     int in_shared;   // the slice's keys are kept in shared memory
     uint32_t k_pad;  // power of two >= k: slots of the collecting array
+    uint32_t list_cap;  // entries of a CTA's short list (0: no lists)
 };
 
 // The cluster's histograms of one pass, added up and scanned from the top by warp 0 of every CTA:
 // the digit at which the count from the top reaches `remaining`, the count above that digit, and
-// the count in it.  hist points at this CTA's 256 counters of the pass; the same address in every
-// CTA of the cluster.
+// the count in it.  hist points at this CTA's 256 counters of the pass (the same address in every
+// CTA of the cluster); the histograms of CTAs first_rank .. first_rank + ranks - 1 are added up.
 struct Found {
     uint32_t digit, above, inside;
 };
-__device__ __forceinline__ Found find_digit(cg::cluster_group& cluster, uint32_t* hist, int ranks, uint32_t remaining, int lane) {
+__device__ __forceinline__ Found find_digit(cg::cluster_group& cluster, uint32_t* hist, int first_rank, int ranks,
+                                            uint32_t remaining, int lane) {
     // lane L owns digits 255-8L down to 248-8L
     uint32_t bins[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < ranks; ++r) {
+    for (int r = first_rank; r < first_rank + ranks; ++r) {
         const uint4* remote = reinterpret_cast<const uint4*>(cluster.map_shared_rank(hist, r));
         const uint4 lo = remote[62 - 2 * lane], hi = remote[63 - 2 * lane];
         bins[0] += hi.w; bins[1] += hi.z; bins[2] += hi.y; bins[3] += hi.x;
@@ -96,17 +127,23 @@ __device__ __forceinline__ Found find_digit(cg::cluster_group& cluster, uint32_t
     return f;
 }
 
-__global__ void __launch_bounds__(kThreads) topk_rows_kernel(const TopKParams p) {
+__global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
-    // layout: [k_pad collected entries, 8 bytes each][slice keys, 4 bytes each (when in_shared)]
+    // layout: [k_pad collected entries][list_cap listed entries][cluster * k_pad gathered entries], 8 bytes
+    //         each, then [slice keys, 4 bytes each (when in_shared)]
     u64* collected = reinterpret_cast<u64*>(dyn);
-    uint32_t* keys = reinterpret_cast<uint32_t*>(dyn + (size_t)p.k_pad * 8);
-    __shared__ __align__(16) uint32_t s_hist[7][256];  // four passes over the key, three over the column
-    __shared__ uint32_t s_prefix, s_remaining, s_inside, s_collected;
+    u64* list = collected + p.k_pad;
+    u64* gathered = list + p.list_cap;
+    uint32_t* keys = reinterpret_cast<uint32_t*>(gathered + (size_t)p.k_pad * (p.cluster > 1 && p.list_cap != 0 ? p.cluster : 0));
+    // histograms of the long way, used in turn by its passes; a pass clears the one before it once the
+    // cluster has met again (nobody reads it any more)
+    __shared__ __align__(16) uint32_t s_hist[2][256];
+    __shared__ uint32_t s_prefix, s_remaining, s_inside, s_collected, s_listed, s_overflow;
 
     cg::cluster_group cluster = cg::this_cluster();
-    const int rank = (int)cluster.block_rank(), ranks = p.cluster;
-    const size_t row_index = blockIdx.x / (unsigned)ranks;
+    const int rank = (int)cluster.block_rank();
+    int ranks = p.cluster;  // CTAs that take part in the steps below (1 once the lists are in the first CTA)
+    const size_t row_index = blockIdx.x / (unsigned)p.cluster;
     const bool largest = p.largest != 0;
     const float* row = p.in + row_index * p.cols;
     const int tid = threadIdx.x, lane = tid & 31;
@@ -114,39 +151,147 @@ __global__ void __launch_bounds__(kThreads) topk_rows_kernel(const TopKParams p)
     const uint32_t begin = min(n, (uint32_t)rank * p.slice), end = min(n, begin + p.slice);
     const uint32_t mine = end - begin;
     const bool in_shared = p.in_shared != 0;
+    // The cluster's barrier costs about a microsecond; one CTA on its own meets with the block barrier.
+    auto meet = [&]() {
+        if (ranks > 1) cluster.sync(); else __syncthreads();
+    };
 
-    for (int i = tid; i < 7 * 256; i += kThreads) (&s_hist[0][0])[i] = 0;
-    if (tid == 0) s_collected = 0;
+    for (int i = tid; i < 2 * 256; i += kThreads) (&s_hist[0][0])[i] = 0;
+    if (tid == 0) {
+        s_collected = 0;
+        s_listed = 0;
+        s_overflow = 0;
+    }
+    uint32_t thread_max = 0;  // the largest key this thread has seen (0 is below every key of a number)
     // ---- the slice, once from HBM, as keys -----------------------------------------------------------
     if (in_shared) {
         const float* src = row + begin;
         const uint32_t head = min(mine, (uint32_t)((4 - ((reinterpret_cast<uintptr_t>(src) >> 2) & 3)) & 3));
-        for (uint32_t i = tid; i < head; i += kThreads) keys[i] = rank_key(src[i], largest);
+        // keys[head] on a 16-byte boundary, like src[head]: the array starts up to three words in
+        keys = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(keys) + 15) & ~uintptr_t(15)) + ((4 - head) & 3);
+        for (uint32_t i = tid; i < head; i += kThreads) {
+            keys[i] = rank_key(src[i], largest);
+            thread_max = max(thread_max, keys[i]);
+        }
         const uint32_t vectors = (mine - head) / 4;
         const float4* src4 = reinterpret_cast<const float4*>(src + head);
-        for (uint32_t v = tid; v < vectors; v += kThreads) {
-            const float4 d = src4[v];
-            uint32_t* to = keys + head + 4 * v;
-            to[0] = rank_key(d.x, largest); to[1] = rank_key(d.y, largest);
-            to[2] = rank_key(d.z, largest); to[3] = rank_key(d.w, largest);
+        uint4* keys4 = reinterpret_cast<uint4*>(keys + head);
+        constexpr int kBatch = 8;  // loads in flight per thread
+        for (uint32_t v0 = tid; v0 < vectors; v0 += kBatch * kThreads) {
+            float4 d[kBatch];
+#pragma unroll
+            for (int q = 0; q < kBatch; ++q) {
+                const uint32_t v = v0 + q * kThreads;
+                d[q] = v < vectors ? __ldg(src4 + v) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int q = 0; q < kBatch; ++q) {
+                const uint32_t v = v0 + q * kThreads;
+                if (v < vectors) {
+                    const uint4 key4 = make_uint4(rank_key(d[q].x, largest), rank_key(d[q].y, largest),
+                                                  rank_key(d[q].z, largest), rank_key(d[q].w, largest));
+                    keys4[v] = key4;
+                    thread_max = max(max(thread_max, max(key4.x, key4.y)), max(key4.z, key4.w));
+                }
+            }
         }
-        for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) keys[i] = rank_key(src[i], largest);
+        for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) {
+            keys[i] = rank_key(src[i], largest);
+            thread_max = max(thread_max, keys[i]);
+        }
     }
     __syncthreads();
-    auto key_at = [&](uint32_t i) { return in_shared ? keys[i] : rank_key(row[begin + i], largest); };
+    auto slice_key = [&](uint32_t i) { return in_shared ? keys[i] : rank_key(row[begin + i], largest); };
+
+    // ---- 0. the short way: this CTA's own k best are among the entries that reach a bound that k
+    //         thread maxima reach; they are listed, sorted, and the best k of every CTA meet in the first -----
+    if (in_shared && p.list_cap != 0) {  // uniform over the cluster
+        __shared__ uint32_t s_warp_bound[kThreads / 32];
+        uint32_t bound = 0;
+        if (mine > p.k) {  // else everything is listed
+            // every warp's kp-th largest thread maximum, kp = ceil(k / 8): the smallest of the eight is
+            // reached by 8 * kp >= k thread maxima (mine > k and k <= 256: enough threads hold an entry)
+            const int kp = ((int)p.k + kThreads / 32 - 1) / (kThreads / 32);
+            const uint32_t warp_bound = warp_kth_largest_key(thread_max, kp, lane);
+            if (lane == 0) s_warp_bound[tid >> 5] = warp_bound;
+            __syncthreads();
+            bound = s_warp_bound[0];
+#pragma unroll
+            for (int w = 1; w < kThreads / 32; ++w) bound = min(bound, s_warp_bound[w]);
+        }
+        for (uint32_t i = tid; i < mine; i += kThreads) {
+            const uint32_t key = keys[i];
+            if (key >= bound) {
+                const uint32_t slot = atomicAdd(&s_listed, 1u);
+                if (slot < p.list_cap) list[slot] = ((u64)key << 32) | (uint32_t)~(begin + i);
+            }
+        }
+        __syncthreads();
+        const uint32_t on_list = s_listed;
+        const bool fits = on_list <= p.list_cap;
+        uint32_t best = 0;  // entries of this CTA that can be among the row's k best
+        if (fits) {  // rank order: the key, then the lower column
+            uint32_t n_pad = 2;
+            while (n_pad < on_list) n_pad <<= 1;
+            for (uint32_t i = on_list + tid; i < n_pad; i += kThreads) list[i] = 0;
+            __syncthreads();
+            block_bitonic_sort(list, (int)n_pad, /*descending=*/true);
+            best = min(on_list, (uint32_t)p.k);
+        }
+        float* out_v = p.values + row_index * p.k;
+        float* out_i = p.indices + row_index * p.k;
+        if (ranks == 1) {
+            if (fits) {
+                for (uint32_t j = tid; j < best; j += kThreads) {
+                    const uint32_t col = ~(uint32_t)list[j];
+                    out_v[j] = row[col];
+                    out_i[j] = (float)col;
+                }
+                return;
+            }
+        } else {
+            if (tid == 0) s_overflow = fits ? 0u : 1u;
+            if (fits) {  // the best k of this CTA into its k_pad slots of the first CTA's array
+                u64* gathered0 = cluster.map_shared_rank(gathered, 0);
+                for (uint32_t j = tid; j < p.k_pad; j += kThreads) gathered0[(size_t)rank * p.k_pad + j] = j < best ? list[j] : 0;
+            }
+            cluster.sync();
+            uint32_t overflow = 0;
+            for (int r = 0; r < ranks; ++r) overflow |= *cluster.map_shared_rank(&s_overflow, r);
+            if (overflow == 0) {  // uniform over the cluster
+                cluster.sync();   // everybody has read everybody's verdict: CTAs may leave
+                if (rank != 0) return;
+                block_bitonic_sort(gathered, (int)(p.k_pad * (uint32_t)ranks), /*descending=*/true);
+                for (uint32_t j = tid; j < (uint32_t)p.k; j += kThreads) {
+                    const uint32_t col = ~(uint32_t)gathered[j];
+                    out_v[j] = row[col];
+                    out_i[j] = (float)col;
+                }
+                return;
+            }
+        }
+    }
+
+    // ---- the long way (k > 256, keys not in shared memory, or a list that overflowed: ties in the thousands):
+    //      the whole cluster, over the slices ------------------------------------------------------------------
+    const uint32_t count = mine;
+    auto key_at = [&](uint32_t i) { return slice_key(i); };
+    auto col_at = [&](uint32_t i) { return begin + i; };
+    const int first_rank = 0;
 
     // ---- 1. radix select of the k-th key ---------------------------------------------------------------
     uint32_t prefix = 0, mask = 0, remaining = (uint32_t)p.k, inside = 0;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        uint32_t* hist = s_hist[pass];
-        for (uint32_t i = tid; i < mine; i += kThreads) {
+        uint32_t* hist = s_hist[pass & 1];
+        for (uint32_t i = tid; i < count; i += kThreads) {
             const uint32_t key = key_at(i);
             if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
         }
-        cluster.sync();
+        meet();
+        if (pass > 0) s_hist[(pass - 1) & 1][tid] = 0;  // kThreads == 256 bins
         if (tid < 32) {
-            const Found f = find_digit(cluster, hist, ranks, remaining, lane);
+            const Found f = find_digit(cluster, hist, first_rank, ranks, remaining, lane);
             if (lane == 0) {
                 s_prefix = prefix | (f.digit << shift);
                 s_remaining = remaining - f.above;
@@ -168,15 +313,16 @@ __global__ void __launch_bounds__(kThreads) topk_rows_kernel(const TopKParams p)
         uint32_t cprefix = 0, cmask = 0, cremaining = ties_wanted;
         for (int pass = 0; pass < 3; ++pass) {
             const int shift = 16 - 8 * pass;
-            uint32_t* hist = s_hist[4 + pass];
-            for (uint32_t i = tid; i < mine; i += kThreads) {
+            uint32_t* hist = s_hist[pass & 1];  // the key's four passes left [0] cleared and [1] to clear
+            for (uint32_t i = tid; i < count; i += kThreads) {
                 if (key_at(i) != kth) continue;
-                const uint32_t inverted = ~(begin + i) & 0x00FFFFFFu;  // lower columns rank higher; columns are below 2^24
+                const uint32_t inverted = ~col_at(i) & 0x00FFFFFFu;  // lower columns rank higher; columns are below 2^24
                 if ((inverted & cmask) == cprefix) atomicAdd(&hist[(inverted >> shift) & 255u], 1u);
             }
-            cluster.sync();
+            meet();
+            s_hist[(pass + 1) & 1][tid] = 0;
             if (tid < 32) {
-                const Found f = find_digit(cluster, hist, ranks, cremaining, lane);
+                const Found f = find_digit(cluster, hist, first_rank, ranks, cremaining, lane);
                 if (lane == 0) {
                     s_prefix = cprefix | (f.digit << shift);
                     s_remaining = cremaining - f.above;
@@ -192,17 +338,17 @@ __global__ void __launch_bounds__(kThreads) topk_rows_kernel(const TopKParams p)
 
     // ---- 3. collect in the first CTA, sort there, write -------------------------------------------------------
     {
-        uint32_t* count0 = cluster.map_shared_rank(&s_collected, 0);
-        u64* collected0 = cluster.map_shared_rank(collected, 0);
-        for (uint32_t i = tid; i < mine; i += kThreads) {
-            const uint32_t key = key_at(i), col = begin + i;
+        uint32_t* count0 = cluster.map_shared_rank(&s_collected, first_rank);
+        u64* collected0 = cluster.map_shared_rank(collected, first_rank);
+        for (uint32_t i = tid; i < count; i += kThreads) {
+            const uint32_t key = key_at(i), col = col_at(i);
             if (key > kth || (key == kth && col <= last_tie_column)) {
                 const uint32_t slot = atomicAdd(count0, 1u);
                 if (slot < p.k_pad) collected0[slot] = ((u64)key << 32) | (uint32_t)~col;
             }
         }
     }
-    cluster.sync();  // nobody touches another CTA's shared memory after this
+    meet();  // nobody touches another CTA's shared memory after this
     if (rank != 0) return;
     const uint32_t taken = min(s_collected, (uint32_t)p.k);  // == k
     for (uint32_t i = taken + tid; i < p.k_pad; i += kThreads) collected[i] = 0;
@@ -233,9 +379,13 @@ cudaError_t launch_topk_rows(const float* in, float* values, float* indices, siz
     p.slice = (uint32_t)(((cols + p.cluster - 1) / p.cluster + 3) / 4 * 4);
     p.k_pad = 1;
     while (p.k_pad < k) p.k_pad <<= 1;
-    // keys in shared memory when they fit beside the collecting array and the histograms
-    p.in_shared = p.slice <= (uint32_t)kSliceMax && (size_t)p.k_pad * 8 + (size_t)p.slice * 4 + 8192 <= 227 * 1024 ? 1 : 0;
-    const size_t shared = (size_t)p.k_pad * 8 + (p.in_shared ? (size_t)p.slice * 4 : 0);
+    // short lists when each of a CTA's k best can be the maximum of a thread of its own
+    p.list_cap = k <= (size_t)kThreads ? 4 * (p.k_pad < 64 ? 64 : p.k_pad) : 0;
+    const size_t entries = p.k_pad + p.list_cap + (p.cluster > 1 && p.list_cap != 0 ? (size_t)p.cluster * p.k_pad : 0);
+    // keys in shared memory when they fit beside those arrays and the histograms
+    p.in_shared = p.slice <= (uint32_t)kSliceMax && entries * 8 + (size_t)p.slice * 4 + 4096 <= 227 * 1024 ? 1 : 0;
+    if (!p.in_shared) p.list_cap = 0;
+    const size_t shared = (p.in_shared ? entries * 8 + (size_t)p.slice * 4 + 32 : (size_t)p.k_pad * 8);
     if (rows * (size_t)p.cluster > 0x7FFFFFFFull) return cudaErrorInvalidConfiguration;
     if (shared > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(topk_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -252,7 +402,7 @@ cudaError_t launch_topk_rows(const float* in, float* values, float* indices, siz
     attribute[0].val.clusterDim.y = 1;
     attribute[0].val.clusterDim.z = 1;
     config.attrs = attribute;
-    config.numAttrs = 1;
+    config.numAttrs = p.cluster > 1 ? 1 : 0;  // a row of one CTA is an ordinary launch
     return cudaLaunchKernelEx(&config, topk_rows_kernel, p);
 }
 
