@@ -127,6 +127,7 @@ __device__ __forceinline__ Found find_digit(cg::cluster_group& cluster, uint32_t
     return f;
 }
 
+template <bool kLargest>
 __global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
     // layout: [k_pad collected entries][list_cap listed entries][cluster * k_pad gathered entries], 8 bytes
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams
     const int rank = (int)cluster.block_rank();
     int ranks = p.cluster;  // CTAs that take part in the steps below (1 once the lists are in the first CTA)
     const size_t row_index = blockIdx.x / (unsigned)p.cluster;
-    const bool largest = p.largest != 0;
+    constexpr bool largest = kLargest;
     const float* row = p.in + row_index * p.cols;
     const int tid = threadIdx.x, lane = tid & 31;
     const uint32_t n = (uint32_t)p.cols;
@@ -162,51 +163,47 @@ __global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams
         s_listed = 0;
         s_overflow = 0;
     }
-    uint32_t thread_max = 0;  // the largest key this thread has seen (0 is below every key of a number)
-    // ---- the slice, once from HBM, as keys -----------------------------------------------------------
-    if (in_shared) {
+    __syncthreads();
+    float* out_v = p.values + row_index * p.k;
+    float* out_i = p.indices + row_index * p.k;
+
+    // ---- 0. the short way (k <= 256): two sweeps over the slice as floats, the second one out of L2.
+    //      Sweep one notes every thread's best entry; a bound that k of those reach is a lower bound of
+    //      the slice's k-th best.  Sweep two lists what reaches the bound, usually k and a few; the list
+    //      is put in rank order by counting, and the best k of every CTA meet in the first CTA. ----------
+    if (p.list_cap != 0) {  // uniform over the cluster
+        __shared__ uint32_t s_warp_bound[kThreads / 32];
         const float* src = row + begin;
         const uint32_t head = min(mine, (uint32_t)((4 - ((reinterpret_cast<uintptr_t>(src) >> 2) & 3)) & 3));
-        // keys[head] on a 16-byte boundary, like src[head]: the array starts up to three words in
-        keys = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(keys) + 15) & ~uintptr_t(15)) + ((4 - head) & 3);
-        for (uint32_t i = tid; i < head; i += kThreads) {
-            keys[i] = rank_key(src[i], largest);
-            thread_max = max(thread_max, keys[i]);
-        }
         const uint32_t vectors = (mine - head) / 4;
         const float4* src4 = reinterpret_cast<const float4*>(src + head);
-        uint4* keys4 = reinterpret_cast<uint4*>(keys + head);
         constexpr int kBatch = 8;  // loads in flight per thread
+        // sweep one: the extreme number this thread sees (fmaxf / fminf pass NaN by), and whether it saw a NaN
+        float extreme = largest ? -INFINITY : INFINITY;
+        bool saw_nan = false;
+        auto note = [&](float x) {
+            saw_nan |= x != x;
+            extreme = largest ? fmaxf(extreme, x) : fminf(extreme, x);
+        };
+        for (uint32_t i = tid; i < head; i += kThreads) note(src[i]);
         for (uint32_t v0 = tid; v0 < vectors; v0 += kBatch * kThreads) {
             float4 d[kBatch];
 #pragma unroll
             for (int q = 0; q < kBatch; ++q) {
                 const uint32_t v = v0 + q * kThreads;
-                d[q] = v < vectors ? __ldg(src4 + v) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                d[q] = v < vectors ? __ldg(src4 + v) : make_float4(extreme, extreme, extreme, extreme);
             }
 #pragma unroll
-            for (int q = 0; q < kBatch; ++q) {
-                const uint32_t v = v0 + q * kThreads;
-                if (v < vectors) {
-                    const uint4 key4 = make_uint4(rank_key(d[q].x, largest), rank_key(d[q].y, largest),
-                                                  rank_key(d[q].z, largest), rank_key(d[q].w, largest));
-                    keys4[v] = key4;
-                    thread_max = max(max(thread_max, max(key4.x, key4.y)), max(key4.z, key4.w));
-                }
-            }
+            for (int q = 0; q < kBatch; ++q) { note(d[q].x); note(d[q].y); note(d[q].z); note(d[q].w); }
         }
-        for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) {
-            keys[i] = rank_key(src[i], largest);
-            thread_max = max(thread_max, keys[i]);
-        }
-    }
-    __syncthreads();
-    auto slice_key = [&](uint32_t i) { return in_shared ? keys[i] : rank_key(row[begin + i], largest); };
+        for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) note(src[i]);
+        // The thread's best key, never overstated: a NaN is the best key when the largest are wanted
+        // and the worst (0) otherwise; a thread that saw nothing, or only NaN, offers 0.
+        const bool saw_any = (uint32_t)tid < head || (uint32_t)tid < vectors || head + 4 * vectors + tid < mine;
+        uint32_t thread_max = 0;
+        if (largest) thread_max = saw_nan ? 0xFFFFFFFFu : (saw_any ? rank_key(extreme, true) : 0u);
+        else thread_max = (saw_any && !(saw_nan && extreme == INFINITY)) ? rank_key(extreme, false) : 0u;
 
-    // ---- 0. the short way: this CTA's own k best are among the entries that reach a bound that k
-    //         thread maxima reach; they are listed, sorted, and the best k of every CTA meet in the first -----
-    if (in_shared && p.list_cap != 0) {  // uniform over the cluster
-        __shared__ uint32_t s_warp_bound[kThreads / 32];
         uint32_t bound = 0;
         if (mine > p.k) {  // else everything is listed
             // every warp's kp-th largest thread maximum, kp = ceil(k / 8): the smallest of the eight is
@@ -219,42 +216,92 @@ __global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams
 #pragma unroll
             for (int w = 1; w < kThreads / 32; ++w) bound = min(bound, s_warp_bound[w]);
         }
-        for (uint32_t i = tid; i < mine; i += kThreads) {
-            const uint32_t key = keys[i];
-            if (key >= bound) {
-                const uint32_t slot = atomicAdd(&s_listed, 1u);
-                if (slot < p.list_cap) list[slot] = ((u64)key << 32) | (uint32_t)~(begin + i);
+        // sweep two: key >= bound, decided on the float itself: with the largest wanted, x is NaN or
+        // x >= the bound's float; with the smallest wanted, x <= the mirrored bound's float.  A bound of
+        // 0 lists everything; a bound that only NaN reaches is left to the long way.
+        const bool everything = bound == 0, only_nan = largest && bound == 0xFFFFFFFFu;
+        const float edge = largest ? from_ordered_key(bound) : from_ordered_key(~bound);
+        auto reaches = [&](float x) { return largest ? !(x < edge) : x <= edge; };
+        auto put = [&](float x, uint32_t col) {
+            const uint32_t slot = atomicAdd(&s_listed, 1u);
+            if (slot < p.list_cap) list[slot] = ((u64)rank_key(x, largest) << 32) | (uint32_t)~col;
+        };
+        if (everything) {
+            if (mine <= p.list_cap) {
+                for (uint32_t i = tid; i < mine; i += kThreads) put(src[i], begin + i);
+            } else if (tid == 0) {
+                s_listed = p.list_cap + 1;  // does not fit
+            }
+        } else if (only_nan) {
+            if (tid == 0) s_listed = p.list_cap + 1;
+        } else {
+            for (uint32_t i = tid; i < head; i += kThreads) {
+                if (reaches(src[i])) put(src[i], begin + i);
+            }
+            for (uint32_t v0 = tid; v0 < vectors; v0 += kBatch * kThreads) {
+                float4 d[kBatch];
+#pragma unroll
+                for (int q = 0; q < kBatch; ++q) {
+                    const uint32_t v = v0 + q * kThreads;
+                    // beyond the slice: a value that does not reach the bound
+                    d[q] = v < vectors ? __ldg(src4 + v) : (largest ? make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY)
+                                                                   : make_float4(INFINITY, INFINITY, INFINITY, INFINITY));
+                }
+#pragma unroll
+                for (int q = 0; q < kBatch; ++q) {
+                    const float best4 = largest ? fmaxf(fmaxf(d[q].x, d[q].y), fmaxf(d[q].z, d[q].w))
+                                                : fminf(fminf(d[q].x, d[q].y), fminf(d[q].z, d[q].w));
+                    const bool any_nan = largest && (d[q].x != d[q].x || d[q].y != d[q].y || d[q].z != d[q].z || d[q].w != d[q].w);
+                    if ((reaches(best4) || any_nan) && v0 + q * kThreads < vectors) {  // rare
+                        const uint32_t col = begin + head + 4 * (v0 + q * kThreads);
+                        if (reaches(d[q].x)) put(d[q].x, col);
+                        if (reaches(d[q].y)) put(d[q].y, col + 1);
+                        if (reaches(d[q].z)) put(d[q].z, col + 2);
+                        if (reaches(d[q].w)) put(d[q].w, col + 3);
+                    }
+                }
+            }
+            for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) {
+                if (reaches(src[i])) put(src[i], begin + i);
             }
         }
         __syncthreads();
         const uint32_t on_list = s_listed;
         const bool fits = on_list <= p.list_cap;
-        uint32_t best = 0;  // entries of this CTA that can be among the row's k best
-        if (fits) {  // rank order: the key, then the lower column
-            uint32_t n_pad = 2;
-            while (n_pad < on_list) n_pad <<= 1;
-            for (uint32_t i = on_list + tid; i < n_pad; i += kThreads) list[i] = 0;
-            __syncthreads();
-            block_bitonic_sort(list, (int)n_pad, /*descending=*/true);
-            best = min(on_list, (uint32_t)p.k);
-        }
-        float* out_v = p.values + row_index * p.k;
-        float* out_i = p.indices + row_index * p.k;
-        if (ranks == 1) {
-            if (fits) {
-                for (uint32_t j = tid; j < best; j += kThreads) {
-                    const uint32_t col = ~(uint32_t)list[j];
-                    out_v[j] = row[col];
-                    out_i[j] = (float)col;
+        const uint32_t best = min(on_list, (uint32_t)p.k);  // entries of this CTA that can be among the row's k best
+        // Where the best entries go: straight out (one CTA), or into this CTA's k_pad slots of the
+        // first CTA's array.  An entry's place is the number of entries that rank before it.
+        u64* gathered0 = ranks > 1 ? cluster.map_shared_rank(gathered, 0) + (size_t)rank * p.k_pad : nullptr;
+        if (fits) {
+            if (on_list > (uint32_t)kThreads) {  // a long list: sort it
+                uint32_t n_pad = 2;
+                while (n_pad < on_list) n_pad <<= 1;
+                for (uint32_t i = on_list + tid; i < n_pad; i += kThreads) list[i] = 0;
+                __syncthreads();
+                block_bitonic_sort(list, (int)n_pad, /*descending=*/true);
+            }
+            for (uint32_t i = tid; i < on_list; i += kThreads) {
+                const u64 entry = list[i];
+                uint32_t place = i;
+                if (on_list <= (uint32_t)kThreads) {
+                    place = 0;
+                    for (uint32_t j = 0; j < on_list; ++j) place += list[j] > entry ? 1u : 0u;
                 }
-                return;
+                if (place < best) {
+                    if (ranks == 1) {
+                        const uint32_t col = ~(uint32_t)entry;
+                        out_v[place] = row[col];
+                        out_i[place] = (float)col;
+                    } else {
+                        gathered0[place] = entry;
+                    }
+                }
             }
-        } else {
+            if (ranks == 1) return;
+            for (uint32_t j = best + tid; j < p.k_pad; j += kThreads) gathered0[j] = 0;
+        }
+        if (ranks > 1) {
             if (tid == 0) s_overflow = fits ? 0u : 1u;
-            if (fits) {  // the best k of this CTA into its k_pad slots of the first CTA's array
-                u64* gathered0 = cluster.map_shared_rank(gathered, 0);
-                for (uint32_t j = tid; j < p.k_pad; j += kThreads) gathered0[(size_t)rank * p.k_pad + j] = j < best ? list[j] : 0;
-            }
             cluster.sync();
             uint32_t overflow = 0;
             for (int r = 0; r < ranks; ++r) overflow |= *cluster.map_shared_rank(&s_overflow, r);
@@ -270,7 +317,41 @@ __global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams
                 return;
             }
         }
+        if (tid == 0) s_listed = 0;
+        __syncthreads();
     }
+
+    // ---- the slice as keys in shared memory, for the long way ----------------------------------------------
+    if (in_shared) {
+        const float* src = row + begin;
+        const uint32_t head = min(mine, (uint32_t)((4 - ((reinterpret_cast<uintptr_t>(src) >> 2) & 3)) & 3));
+        // keys[head] on a 16-byte boundary, like src[head]: the array starts up to three words in
+        keys = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(keys) + 15) & ~uintptr_t(15)) + ((4 - head) & 3);
+        for (uint32_t i = tid; i < head; i += kThreads) keys[i] = rank_key(src[i], largest);
+        const uint32_t vectors = (mine - head) / 4;
+        const float4* src4 = reinterpret_cast<const float4*>(src + head);
+        uint4* keys4 = reinterpret_cast<uint4*>(keys + head);
+        constexpr int kBatch = 8;  // loads in flight per thread
+        for (uint32_t v0 = tid; v0 < vectors; v0 += kBatch * kThreads) {
+            float4 d[kBatch];
+#pragma unroll
+            for (int q = 0; q < kBatch; ++q) {
+                const uint32_t v = v0 + q * kThreads;
+                d[q] = v < vectors ? __ldg(src4 + v) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int q = 0; q < kBatch; ++q) {
+                const uint32_t v = v0 + q * kThreads;
+                if (v < vectors) {
+                    keys4[v] = make_uint4(rank_key(d[q].x, largest), rank_key(d[q].y, largest), rank_key(d[q].z, largest),
+                                          rank_key(d[q].w, largest));
+                }
+            }
+        }
+        for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) keys[i] = rank_key(src[i], largest);
+    }
+    __syncthreads();
+    auto slice_key = [&](uint32_t i) { return in_shared ? keys[i] : rank_key(row[begin + i], largest); };
 
     // ---- the long way (k > 256, keys not in shared memory, or a list that overflowed: ties in the thousands):
     //      the whole cluster, over the slices ------------------------------------------------------------------
@@ -354,8 +435,6 @@ __global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams
     for (uint32_t i = taken + tid; i < p.k_pad; i += kThreads) collected[i] = 0;
     __syncthreads();
     if (p.k_pad > 1) block_bitonic_sort(collected, (int)p.k_pad, /*descending=*/true);
-    float* out_v = p.values + row_index * p.k;
-    float* out_i = p.indices + row_index * p.k;
     for (uint32_t j = tid; j < taken; j += kThreads) {
         const uint32_t col = ~(uint32_t)collected[j];
         out_v[j] = row[col];
@@ -379,16 +458,17 @@ cudaError_t launch_topk_rows(const float* in, float* values, float* indices, siz
     p.slice = (uint32_t)(((cols + p.cluster - 1) / p.cluster + 3) / 4 * 4);
     p.k_pad = 1;
     while (p.k_pad < k) p.k_pad <<= 1;
-    // short lists when each of a CTA's k best can be the maximum of a thread of its own
+    // The short way (k <= 256) needs no keys in shared memory; if one of its lists overflows, the
+    // long way sweeps global memory.  Otherwise the keys are kept when they fit.
     p.list_cap = k <= (size_t)kThreads ? 4 * (p.k_pad < 64 ? 64 : p.k_pad) : 0;
     const size_t entries = p.k_pad + p.list_cap + (p.cluster > 1 && p.list_cap != 0 ? (size_t)p.cluster * p.k_pad : 0);
-    // keys in shared memory when they fit beside those arrays and the histograms
-    p.in_shared = p.slice <= (uint32_t)kSliceMax && entries * 8 + (size_t)p.slice * 4 + 4096 <= 227 * 1024 ? 1 : 0;
-    if (!p.in_shared) p.list_cap = 0;
-    const size_t shared = (p.in_shared ? entries * 8 + (size_t)p.slice * 4 + 32 : (size_t)p.k_pad * 8);
+    p.in_shared = p.list_cap == 0 && p.slice <= (uint32_t)kSliceMax &&
+                  entries * 8 + (size_t)p.slice * 4 + 4096 <= 227 * 1024 ? 1 : 0;
+    const size_t shared = entries * 8 + (p.in_shared ? (size_t)p.slice * 4 + 32 : 0);
     if (rows * (size_t)p.cluster > 0x7FFFFFFFull) return cudaErrorInvalidConfiguration;
     if (shared > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(topk_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        const cudaError_t e = largest ? cudaFuncSetAttribute(topk_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared)
+                                      : cudaFuncSetAttribute(topk_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t config = {};
@@ -403,7 +483,7 @@ cudaError_t launch_topk_rows(const float* in, float* values, float* indices, siz
     attribute[0].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = p.cluster > 1 ? 1 : 0;  // a row of one CTA is an ordinary launch
-    return cudaLaunchKernelEx(&config, topk_rows_kernel, p);
+    return largest ? cudaLaunchKernelEx(&config, topk_rows_kernel<true>, p) : cudaLaunchKernelEx(&config, topk_rows_kernel<false>, p);
 }
 
 }  // namespace psx
