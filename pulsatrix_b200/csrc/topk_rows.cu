@@ -128,7 +128,7 @@ __device__ __forceinline__ Found find_digit(cg::cluster_group& cluster, uint32_t
 }
 
 template <bool kLargest>
-__global__ void __launch_bounds__(kThreads, 3) topk_rows_kernel(const TopKParams p) {
+__global__ void __launch_bounds__(kThreads, 4) topk_rows_kernel(const TopKParams p) {
     extern __shared__ __align__(16) unsigned char dyn[];
     // layout: [k_pad collected entries][list_cap listed entries][cluster * k_pad gathered entries], 8 bytes
     //         each, then [slice keys, 4 bytes each (when in_shared)]
