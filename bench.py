@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
+    ap.add_argument("--top-k", action="store_true",
+                    help="time psx_b200_top_k_rows on a few shapes instead (one GPU; prints its own JSON line)")
     return ap.parse_args()
 
 
@@ -388,10 +390,47 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+TOP_K_SHAPES = [(4096, 16384, 64), (1024, 65536, 32), (64, 151936, 20), (8192, 4096, 16), (256, 128256, 1024)]
+
+
+def run_top_k(args):
+    """The selection primitive alone (DeviceBackend::top_k_rows): rows/s and input GB/s per shape,
+    inputs rotating over more than L2, CUDA events on the launching stream."""
+    import torch
+    import pulsatrix_b200 as psx
+
+    ctx = psx.Context(0)
+    results = []
+    for rows, cols, k in TOP_K_SHAPES:
+        count = max(2, (2 * L2_BYTES) // (rows * cols * 4) + 1)
+        xs = [torch.randn(rows, cols, device="cuda") for _ in range(count)]
+        for i in range(max(args.warmup, 3)):
+            ctx.top_k_rows(xs[i % count], k)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = max(3, min(args.steps, 50))
+        begin.record()
+        for i in range(steps):
+            ctx.top_k_rows(xs[i % count], k)
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        results.append({"rows": rows, "cols": cols, "k": k, "us": ms * 1e3, "rows_per_s": rows / (ms * 1e-3),
+                        "input_gbs": rows * cols * 4 / (ms * 1e-3) / 1e9})
+        del xs
+    peak, peak_kind = measured_hbm_peak()
+    print(json.dumps({"metric": "top_k_rows rows/s", "unit": "rows/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
+                      "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results}))
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.top_k:
+        if rank == 0:
+            run_top_k(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

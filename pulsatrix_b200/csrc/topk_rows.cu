@@ -42,6 +42,19 @@ __device__ __forceinline__ uint32_t rank_key(float x, bool largest) {
     return largest ? k : ~k;
 }
 
+// Three-input maximum / minimum in one instruction (sm_100); the .NaN forms return NaN when any
+// operand is NaN, the plain forms pass NaN operands by.
+__device__ __forceinline__ float max3_nan(float a, float b, float c) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // The kp-th largest (1-based, kp <= 32) of the 32 lanes' keys: for small kp the maximum is taken
 // away kp - 1 times, else a bitonic sort across the lanes.
 __device__ __forceinline__ uint32_t warp_kth_largest_key(uint32_t key, int kp, int lane) {
@@ -178,12 +191,13 @@ __global__ void __launch_bounds__(kThreads, 4) topk_rows_kernel(const TopKParams
         const uint32_t vectors = (mine - head) / 4;
         const float4* src4 = reinterpret_cast<const float4*>(src + head);
         constexpr int kBatch = 8;  // loads in flight per thread
-        // sweep one: the extreme number this thread sees (fmaxf / fminf pass NaN by), and whether it saw a NaN
+        // sweep one: the extreme entry this thread sees.  With the largest wanted a NaN is the best
+        // there is, and the maximum that returns NaN for a NaN operand finds it; with the smallest
+        // wanted a NaN is the worst, and the plain minimum passes it by.
         float extreme = largest ? -INFINITY : INFINITY;
-        bool saw_nan = false;
-        auto note = [&](float x) {
-            saw_nan |= x != x;
-            extreme = largest ? fmaxf(extreme, x) : fminf(extreme, x);
+        auto note = [&](float x) { extreme = largest ? max3_nan(extreme, x, x) : fminf(extreme, x); };
+        auto note4 = [&](const float4& d) {
+            extreme = largest ? max3_nan(max3_nan(d.x, d.y, d.z), d.w, extreme) : min3(min3(d.x, d.y, d.z), d.w, extreme);
         };
         for (uint32_t i = tid; i < head; i += kThreads) note(src[i]);
         for (uint32_t v0 = tid; v0 < vectors; v0 += kBatch * kThreads) {
@@ -194,15 +208,14 @@ __global__ void __launch_bounds__(kThreads, 4) topk_rows_kernel(const TopKParams
                 d[q] = v < vectors ? __ldg(src4 + v) : make_float4(extreme, extreme, extreme, extreme);
             }
 #pragma unroll
-            for (int q = 0; q < kBatch; ++q) { note(d[q].x); note(d[q].y); note(d[q].z); note(d[q].w); }
+            for (int q = 0; q < kBatch; ++q) note4(d[q]);
         }
         for (uint32_t i = head + 4 * vectors + tid; i < mine; i += kThreads) note(src[i]);
-        // The thread's best key, never overstated: a NaN is the best key when the largest are wanted
-        // and the worst (0) otherwise; a thread that saw nothing, or only NaN, offers 0.
+        // The thread's best key, never overstated: a thread that saw nothing offers 0, and so does one
+        // whose minimum is still +inf when the smallest are wanted (it may have seen nothing but NaN).
         const bool saw_any = (uint32_t)tid < head || (uint32_t)tid < vectors || head + 4 * vectors + tid < mine;
-        uint32_t thread_max = 0;
-        if (largest) thread_max = saw_nan ? 0xFFFFFFFFu : (saw_any ? rank_key(extreme, true) : 0u);
-        else thread_max = (saw_any && !(saw_nan && extreme == INFINITY)) ? rank_key(extreme, false) : 0u;
+        uint32_t thread_max = saw_any ? rank_key(extreme, largest) : 0u;
+        if (!largest && extreme == INFINITY) thread_max = 0;
 
         uint32_t bound = 0;
         if (mine > p.k) {  // else everything is listed
@@ -249,10 +262,10 @@ __global__ void __launch_bounds__(kThreads, 4) topk_rows_kernel(const TopKParams
                 }
 #pragma unroll
                 for (int q = 0; q < kBatch; ++q) {
-                    const float best4 = largest ? fmaxf(fmaxf(d[q].x, d[q].y), fmaxf(d[q].z, d[q].w))
-                                                : fminf(fminf(d[q].x, d[q].y), fminf(d[q].z, d[q].w));
-                    const bool any_nan = largest && (d[q].x != d[q].x || d[q].y != d[q].y || d[q].z != d[q].z || d[q].w != d[q].w);
-                    if ((reaches(best4) || any_nan) && v0 + q * kThreads < vectors) {  // rare
+                    // (a NaN among the four makes best4 NaN when the largest are wanted, and NaN reaches)
+                    const float best4 = largest ? max3_nan(max3_nan(d[q].x, d[q].y, d[q].z), d[q].w, d[q].w)
+                                                : min3(min3(d[q].x, d[q].y, d[q].z), d[q].w, d[q].w);
+                    if (reaches(best4) && v0 + q * kThreads < vectors) {  // rare
                         const uint32_t col = begin + head + 4 * (v0 + q * kThreads);
                         if (reaches(d[q].x)) put(d[q].x, col);
                         if (reaches(d[q].y)) put(d[q].y, col + 1);
