@@ -142,8 +142,19 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     if (vectors * 4 <= psx::kPartCap) plan.k_need = 1 << 30;
     plan.sort_capacity = plan.nucleus ? 4096 : 1024;
     plan.gather_capacity = plan.nucleus ? 8192 : 4096;
+    if (!plan.nucleus && plan.k_need < psx::kPartCap) {
+        // A large k over many parts: a part whose threshold is a warp's 25th of 32 thread maxima hands
+        // on about twice k, and the row's candidates no longer fit 4096 slots.
+        const int64_t estimate = (int64_t)plan.parts * (2 * plan.k_need + 32) + 256;
+        if (estimate > 3500) {
+            plan.sort_capacity = 2048;
+            plan.gather_capacity = estimate > 5600 ? 8192 : 6144;
+        }
+    }
     // A part usually hands on a little over k_need logits, plus the few its share of the history flags.
-    const int expected = plan.k_need >= psx::kPartCap ? psx::kPartCap : plan.k_need + plan.k_need / 4 + 24;
+    const int expected = plan.k_need >= psx::kPartCap ? psx::kPartCap
+                         : plan.k_need > 64         ? 2 * plan.k_need + 24
+                                                    : plan.k_need + plan.k_need / 4 + 24;
     plan.slot_shift = psx::merge_slot_shift(plan.parts, psx::kPartCap, expected);
     return plan;
 }

@@ -1,15 +1,18 @@
 // top_k_rows: the k best entries of every row in rank order, with their columns as floats.
 //
-// A row belongs to a thread-block cluster of 1, 2, 4 or 8 CTAs (by its length); each CTA reads
-// its slice of the row from HBM once, turns it into order-preserving keys (NaN above every
-// number, -0.0 == +0.0, `largest == 0` mirrors the order) and keeps the keys in shared memory.
-// Everything after that works on the keys:
-//   0. while it loads, every thread notes the largest key it has seen; the k-th largest of a CTA's
-//      thread maxima is a lower bound of the k-th key of its slice (k threads hold an entry at or
-//      above it), and one sweep keeps only the entries that reach it, usually k and a few, in a
-//      short list; the lists go to the first CTA, which runs the steps below over them alone
-//      (whenever k <= 256 and no list overflows: a row of equal values still goes through the
-//      slices, by the whole cluster);
+// A row belongs to a thread-block cluster of 1, 2, 4 or 8 CTAs (by its length), a slice of the
+// row per CTA.  Entries are compared as order-preserving keys: NaN above every number,
+// -0.0 == +0.0, `largest == 0` mirrors the order.
+//
+// The short way (k <= 256): two sweeps over the slice as floats, straight from global memory, the
+// second one out of L2.  Sweep one notes every thread's best entry; the smallest over the warps of
+// the kp-th best of those (kp = ceil(k / 8)) is a bound that k entries of the slice reach.  Sweep
+// two lists what reaches the bound, usually k and a few; the list is put in rank order by
+// counting, and with several CTAs per row the best k of each meet in the first CTA's shared memory
+// (distributed shared memory, two cluster barriers), where they are sorted and written out.
+//
+// The long way (larger k, or a list that overflowed: thousands of ties): the slice becomes keys in
+// shared memory (or is swept from global memory when it does not fit), and
 //   1. a 4 x 8-bit radix select finds the k-th key: every CTA counts its slice's digits into a
 //      histogram of its own, the cluster meets, and every CTA adds the cluster's histograms up
 //      through distributed shared memory for itself;
@@ -17,12 +20,11 @@
 //      columns of the tying entries, finds the column up to which they are taken (the reference
 //      keeps the lowest columns, src/top_k_math.hpp:19-47);
 //   3. the entries above the k-th key and the chosen ties are collected in the first CTA's shared
-//      memory (remote atomics and stores), sorted there by (key, ~column) -- rank order, equal
-//      values by ascending column -- and written out; the values are copied from the input, so
-//      that their bits (the sign of zero, NaN payloads) are the input's.
-// Pure selection: nothing is computed, so the result equals the host reference bit for bit.
-// HBM-bound in design: the row is read once, and k values again at the end.  Rows too long for
-// the cluster's shared memory (more than 8 x 48K entries) are swept from global memory instead.
+//      memory (remote atomics and stores) and sorted there by (key, ~column) -- rank order, equal
+//      values by ascending column.
+// The values written are copied from the input, so that their bits (the sign of zero, NaN
+// payloads) are the input's.  Pure selection: nothing is computed, so the result equals the host
+// reference bit for bit.
 #include <cooperative_groups.h>
 
 #include "topk_rows.cuh"
