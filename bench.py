@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--contexts", type=int, default=3,
+                    help="sampler contexts in flight per GPU (one stream and one scratch each; steps go round-robin)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
     ap.add_argument("--top-k", action="store_true",
                     help="time psx_b200_top_k_rows on a few shapes instead (one GPU; prints its own JSON line)")
@@ -222,21 +224,24 @@ def run_ours(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    ctx = psx.Context(local)
-    # Every batch is complete in HBM before the first timed call: the row pass of a step may start
+    # One context (stream + scratch) per batch in flight, the way a server that decodes several
+    # batches at once would hold them: step i runs on context i % M, so the row pass of one batch
+    # overlaps the survivor stage of another.  Every batch is complete in HBM before the first timed
+    # call, which each context is told, so inside a context too the row pass of a step may start
     # reading while the survivor stage of the step before it is still running.
-    ctx.inputs_are_ready(True)
+    m_ctx = max(1, args.contexts)
+    ctxs = [psx.Context(local) for _ in range(m_ctx)]
+    for c in ctxs:
+        c.inputs_are_ready(True)
+    ctx = ctxs[0]
     cfg = workload_config(w)
     n_batches = max(2, (2 * L2_BYTES) // w.logits_bytes + 2)
     batches, offsets = build_batches(w, device, n_batches, seed=1234 + rank)
     seeds = np.arange(w.rows, dtype=np.uint64)
     uniforms = torch.from_numpy(psx.uniforms_mt19937_64(seeds)).to(device)
-    out = ctx.alloc_outputs(w.rows)
+    outs = [c.alloc_outputs(w.rows) for c in ctxs]
     stream = torch.cuda.current_stream(device)
-
-    def step(i):
-        logits, hist = batches[i % n_batches]
-        ctx.sample_rows(logits, hist, offsets, cfg, uniforms, out=out, stream=stream.cuda_stream)
+    side = [torch.cuda.Stream(device) for _ in range(m_ctx)]
 
     def barrier():
         torch.cuda.synchronize()
@@ -244,50 +249,58 @@ def run_ours(args, rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    barrier()
-    status = out["status"].cpu().numpy()
-    failed = int((status != 0).sum())
+    def timed(launch, m, steps, warmup):
+        """Milliseconds for `steps` calls of launch(i, context index, stream) spread round-robin over
+        the first m contexts, each on its own stream: the begin event is recorded on the current
+        stream and every side stream waits for it; the end event is recorded on the current stream
+        after it has waited for the last work of every side stream."""
+        for i in range(warmup):
+            launch(i, i % m, side[i % m])
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        for s in side[:m]:
+            s.wait_event(begin)
+        for i in range(steps):
+            launch(i, i % m, side[i % m])
+        for s in side[:m]:
+            done = torch.cuda.Event()
+            done.record(s)
+            stream.wait_event(done)
+        end.record(stream)
+        barrier()
+        return begin.elapsed_time(end)
 
-    # ---- value: K steps, device-resident inputs, CUDA events on the launching stream ----
+    def full_step(i, c, s):
+        logits, hist = batches[i % n_batches]
+        ctxs[c].sample_rows(logits, hist, offsets, cfg, uniforms, out=outs[c], stream=s.cuda_stream)
+
+    def row_pass(i, c, s):
+        logits, hist = batches[i % n_batches]
+        ctxs[c].row_pass_only(logits, hist, offsets, cfg, stream=s.cuda_stream)
+
+    def read_only(i, c, s):
+        psx.read_only_pass(batches[i % n_batches][0], sink, stream=s.cuda_stream)
+
+    warm = max(args.warmup, 3)
+    sink = torch.zeros(1, dtype=torch.float32, device=device)
+    timed(full_step, m_ctx, 0, warm * m_ctx)
+    failed = sum(int((o["status"].cpu().numpy() != 0).sum()) for o in outs)
+
     sampler = ClockSampler(local)
     sampler.start()
-    launches0 = ctx.launches
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    begin.record(stream)
-    for i in range(args.steps):
-        step(i)
-    end.record(stream)
-    barrier()
-    elapsed_ms = begin.elapsed_time(end)
-    launches = ctx.launches - launches0
-
-    # ---- roofline: the row pass alone, K back-to-back launches over the rotating batches ----
-    for i in range(3):
-        ctx.row_pass_only(batches[i % n_batches][0], batches[i % n_batches][1], offsets, cfg, stream=stream.cuda_stream)
-    barrier()
-    begin.record(stream)
-    for i in range(args.steps):
-        logits, hist = batches[i % n_batches]
-        ctx.row_pass_only(logits, hist, offsets, cfg, stream=stream.cuda_stream)
-    end.record(stream)
-    barrier()
-    scan_ms, calls = begin.elapsed_time(end), args.steps
+    # ---- value: K steps, device-resident inputs, CUDA events, M contexts in flight ----
+    launches0 = sum(c.launches for c in ctxs)
+    elapsed_ms = timed(full_step, m_ctx, args.steps, m_ctx)
+    launches = sum(c.launches for c in ctxs) - launches0
+    # ---- roofline: the row pass alone, K launches over the rotating batches, same M streams ----
+    scan_ms, calls = timed(row_pass, m_ctx, args.steps, 3 * m_ctx), args.steps
     merge_ms = max(elapsed_ms - scan_ms, 0.0)
-
+    # ---- the same two with one context, every launch on one stream ----
+    one_ms = timed(full_step, 1, args.steps, 3)
+    one_scan_ms = timed(row_pass, 1, args.steps, 3)
     # ---- the practical ceiling: a kernel that only reads the same batches, same cadence ----
-    sink = torch.zeros(1, dtype=torch.float32, device=device)
-    for i in range(3):
-        psx.read_only_pass(batches[i % n_batches][0], sink, stream=stream.cuda_stream)
-    barrier()
-    begin.record(stream)
-    for i in range(args.steps):
-        psx.read_only_pass(batches[i % n_batches][0], sink, stream=stream.cuda_stream)
-    end.record(stream)
-    barrier()
-    read_ms = begin.elapsed_time(end) / args.steps
+    read_ms = timed(read_only, 1, args.steps, 3) / args.steps
     clocks = sampler.stop()
 
     # ---- e2e: the host-buffer entry point, pinned inputs, copies inside the timed region ----
@@ -306,11 +319,11 @@ def run_ours(args, rank, world):
     h2d = h_logits.numel() * 4 + h_hist.numel() * 8 + h_off.numel() * 8 + (h_u.numel() * 8 if w.do_sample else 0)
     d2h = w.rows * (8 + 4 + 4 + 24)
 
-    times = torch.tensor([elapsed_ms, e2e_s * 1e3, scan_ms / max(calls, 1), merge_ms / max(calls, 1), read_ms],
-                         dtype=torch.float64, device=device)
+    times = torch.tensor([elapsed_ms, e2e_s * 1e3, scan_ms / max(calls, 1), merge_ms / max(calls, 1), read_ms,
+                          one_ms, one_scan_ms / max(calls, 1)], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, scan_avg_ms, merge_avg_ms, read_ms = times.tolist()
+    elapsed_ms, e2e_ms, scan_avg_ms, merge_avg_ms, read_ms, one_ms, one_scan_avg_ms = times.tolist()
     if rank != 0:
         return
 
@@ -333,6 +346,7 @@ def run_ours(args, rank, world):
                                f"penalty={w.repetition_penalty}, T={w.temperature}, top_k={w.top_k}, top_p={w.top_p}, "
                                f"do_sample={w.do_sample}",
                    "parallelism": f"rows split over {world} GPU(s), no data-path collective",
+                   "contexts_in_flight": m_ctx,
                    "l2": f"inputs rotate over {n_batches} batches = {n_batches * w.logits_bytes / 2**20:.0f} MiB > L2"},
         "e2e": {"value": w.rows * world * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps},
@@ -343,10 +357,13 @@ def run_ours(args, rank, world):
                      "traffic": int(round(w.logits_bytes * ROW_PASS_TRAFFIC_RATIO)),
                      "traffic_note": "bytes per launch; ncu dram read+write of one C2 launch, scaled by this workload's bytes",
                      "algorithmic_bytes": w.logits_bytes,
-                     "launch_ms": scan_avg_ms, "survivor_stage_ms": merge_avg_ms,
+                     "launch_ms": scan_avg_ms, "step_minus_row_pass_ms": merge_avg_ms,
                      "frac_of_nominal_8TBs": achieved / 8000.0,
                      "read_only_kernel_gbs": w.logits_bytes / (read_ms * 1e-3) / 1e9,
                      "frac_of_read_only_kernel": read_ms / scan_avg_ms},
+        "single_context": {"value": w.rows * world * args.steps / (one_ms * 1e-3), "unit": "rows/s",
+                           "ms_per_step": one_ms / args.steps, "row_pass_launch_ms": one_scan_avg_ms,
+                           "roofline_frac": w.logits_bytes / (one_scan_avg_ms * 1e-3) / 1e9 / peak},
         "failed_rows": failed,
     }
     if world == 1:

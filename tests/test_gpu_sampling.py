@@ -290,3 +290,39 @@ def test_the_promise_of_complete_inputs_changes_no_answer():
                 assert out["log_probs"].cpu().numpy().tobytes() == logp.tobytes()
     finally:
         context.inputs_are_ready(False)
+
+
+def test_contexts_in_flight_on_their_own_streams_change_no_answer():
+    """Three contexts, each with its own stream, scratch and outputs, fed round-robin the way the
+    benchmark feeds them: the row pass of one batch overlaps the survivor stage of another, and every
+    batch gets what it gets alone (checked against the restatement too)."""
+    import torch
+    w = WORKLOADS["c2"]
+    config = workload_rows.config_of(w)
+    cfg = gh.psx_config(config)
+    batches, expected = [], []
+    for b in range(6):
+        logits, hist, offsets, seeds = workload_rows.build("c2", np.arange(8 * b, 8 * b + 8))
+        expected.append(ol.rows("oracle", logits, hist.ravel(), offsets, config, seeds))
+        batches.append((torch.from_numpy(logits).cuda(), torch.from_numpy(hist.ravel().astype(np.int64)).cuda(),
+                        torch.from_numpy(offsets.astype(np.int64)).cuda(),
+                        torch.from_numpy(psx.uniforms_mt19937_64(seeds)).cuda()))
+    torch.cuda.synchronize()
+    contexts = [psx.Context(0) for _ in range(3)]
+    streams = [torch.cuda.Stream() for _ in contexts]
+    try:
+        for c in contexts:
+            c.inputs_are_ready(True)
+        for _ in range(3):
+            outs = []
+            for i, (logits, hist, offsets, u) in enumerate(batches):
+                c = i % len(contexts)
+                outs.append(contexts[c].sample_rows(logits, hist, offsets, cfg, u, stream=streams[c].cuda_stream))
+            torch.cuda.synchronize()
+            for out, want in zip(outs, expected):
+                assert out["status"].cpu().numpy().tolist() == [0] * 8
+                assert out["tokens"].cpu().numpy().tolist() == want["token"].tolist()
+                np.testing.assert_allclose(out["log_probs"].cpu().numpy(), want["log_prob"], rtol=1e-5)
+    finally:
+        for c in contexts:
+            c.close()
