@@ -393,60 +393,74 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     // Per-lane float sums of at most 16 four-element sums each; they go to double in the reduction.
     float tail = 0.0f, proc = 0.0f;
 
-    // The part was padded to whole 256-vector trips, so the loop is branch-free but for the rare
-    // vector that reaches the threshold; those are only noted here (one bit per trip) and handed
-    // on after the loop, which lets the compiler keep several trips in flight.
+    // The part was padded to whole 256-vector trips and the loop is branch-free: a vector that
+    // reaches the threshold (rare) is only noted, one bit per trip, and its sums are left out; after
+    // the loop its components below the threshold are summed again and what reaches it is counted.
     const int trips = (nvec + kScanThreads - 1) / kScanThreads;
     uint32_t noted = 0;
+    auto exps_of = [&](const float4& d, float& e0, float& e1, float& e2, float& e3, float& q0, float& q1, float& q2,
+                       float& q3) {
+        float x0 = __fmaf_rn(d.x, kLog2e, -c_l2), x1 = __fmaf_rn(d.y, kLog2e, -c_l2);
+        float x2 = __fmaf_rn(d.z, kLog2e, -c_l2), x3 = __fmaf_rn(d.w, kLog2e, -c_l2);
+        if (kNucleus) {
+            x0 = __fmaf_rn(x0, kLog2eRel, x0); x1 = __fmaf_rn(x1, kLog2eRel, x1);
+            x2 = __fmaf_rn(x2, kLog2eRel, x2); x3 = __fmaf_rn(x3, kLog2eRel, x3);
+        }
+        e0 = ex2_approx(x0); e1 = ex2_approx(x1); e2 = ex2_approx(x2); e3 = ex2_approx(x3);
+        q0 = q1 = q2 = q3 = 0.0f;
+        if (second_exp) {
+            float y0 = __fmaf_rn(d.x, p.log2e_over_t, -pc_l2), y1 = __fmaf_rn(d.y, p.log2e_over_t, -pc_l2);
+            float y2 = __fmaf_rn(d.z, p.log2e_over_t, -pc_l2), y3 = __fmaf_rn(d.w, p.log2e_over_t, -pc_l2);
+            q0 = ex2_approx(__fmaf_rn(y0, kLog2eRel, y0)); q1 = ex2_approx(__fmaf_rn(y1, kLog2eRel, y1));
+            q2 = ex2_approx(__fmaf_rn(y2, kLog2eRel, y2)); q3 = ex2_approx(__fmaf_rn(y3, kLog2eRel, y3));
+        }
+    };
     if (!(p.debug_skip & 4)) {
 #pragma unroll 4
         for (int t = 0; t < trips; ++t) {
             const float4 d = data4[t * kScanThreads + tid];
-            float x0 = __fmaf_rn(d.x, kLog2e, -c_l2), x1 = __fmaf_rn(d.y, kLog2e, -c_l2);
-            float x2 = __fmaf_rn(d.z, kLog2e, -c_l2), x3 = __fmaf_rn(d.w, kLog2e, -c_l2);
-            if (kNucleus) {
-                x0 = __fmaf_rn(x0, kLog2eRel, x0); x1 = __fmaf_rn(x1, kLog2eRel, x1);
-                x2 = __fmaf_rn(x2, kLog2eRel, x2); x3 = __fmaf_rn(x3, kLog2eRel, x3);
-            }
-            float e0 = ex2_approx(x0), e1 = ex2_approx(x1), e2 = ex2_approx(x2), e3 = ex2_approx(x3);
-            float q0 = 0.0f, q1 = 0.0f, q2 = 0.0f, q3 = 0.0f;
+            float e0, e1, e2, e3, q0, q1, q2, q3;
+            exps_of(d, e0, e1, e2, e3, q0, q1, q2, q3);
+            const bool hit = fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime;
+            const float s = (e0 + e1) + (e2 + e3);
+            tail += hit ? 0.0f : s;
             if (second_exp) {
-                float y0 = __fmaf_rn(d.x, p.log2e_over_t, -pc_l2), y1 = __fmaf_rn(d.y, p.log2e_over_t, -pc_l2);
-                float y2 = __fmaf_rn(d.z, p.log2e_over_t, -pc_l2), y3 = __fmaf_rn(d.w, p.log2e_over_t, -pc_l2);
-                q0 = ex2_approx(__fmaf_rn(y0, kLog2eRel, y0)); q1 = ex2_approx(__fmaf_rn(y1, kLog2eRel, y1));
-                q2 = ex2_approx(__fmaf_rn(y2, kLog2eRel, y2)); q3 = ex2_approx(__fmaf_rn(y3, kLog2eRel, y3));
+                const float q = (q0 + q1) + (q2 + q3);
+                proc += hit ? 0.0f : q;
             }
-            if (fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime) {
-                // What is handed on leaves the sums (its exp is taken in double by the survivor stage).
-                if (d.x >= tprime) { e0 = 0.0f; q0 = 0.0f; }
-                if (d.y >= tprime) { e1 = 0.0f; q1 = 0.0f; }
-                if (d.z >= tprime) { e2 = 0.0f; q2 = 0.0f; }
-                if (d.w >= tprime) { e3 = 0.0f; q3 = 0.0f; }
-                noted |= 1u << t;
-            }
-            tail += (e0 + e1) + (e2 + e3);
-            if (second_exp) proc += (q0 + q1) + (q2 + q3);
+            noted |= hit ? (1u << t) : 0u;
         }
     }
     STAGE(8);
     // What reaches the threshold is counted now and handed on after the block has met (below): a
-    // warp's run in the part's list starts where the runs of the warps before it end.
+    // warp's run in the part's list starts where the runs of the warps before it end.  It leaves
+    // the sums (its exp is taken in double by the survivor stage); its neighbours in the vector stay.
     uint32_t count = 0, before_mine = 0, warp_count = 0;
     const bool any_noted = __ballot_sync(0xFFFFFFFFu, noted != 0) != 0 && !(p.debug_skip & 2);
     if (any_noted) {
         for (uint32_t m2 = noted; m2; m2 &= m2 - 1) {
             const float4 d = data4[(__ffs(m2) - 1) * kScanThreads + tid];
-            count += (d.x >= tprime ? 1u : 0u) + (d.y >= tprime ? 1u : 0u) + (d.z >= tprime ? 1u : 0u) +
-                     (d.w >= tprime ? 1u : 0u);
+            float e0, e1, e2, e3, q0, q1, q2, q3;
+            exps_of(d, e0, e1, e2, e3, q0, q1, q2, q3);
+            const bool h0 = d.x >= tprime, h1 = d.y >= tprime, h2 = d.z >= tprime, h3 = d.w >= tprime;
+            count += (h0 ? 1u : 0u) + (h1 ? 1u : 0u) + (h2 ? 1u : 0u) + (h3 ? 1u : 0u);
+            tail += ((h0 ? 0.0f : e0) + (h1 ? 0.0f : e1)) + ((h2 ? 0.0f : e2) + (h3 ? 0.0f : e3));
+            if (second_exp) proc += ((h0 ? 0.0f : q0) + (h1 ? 0.0f : q1)) + ((h2 ? 0.0f : q2) + (h3 ? 0.0f : q3));
         }
-        uint32_t incl = count;
+        // Slots in lane order.  Usually a lane hands on one logit; otherwise scan the counts.
+        const uint32_t voters = __ballot_sync(0xFFFFFFFFu, count != 0);
+        before_mine = __popc(voters & ((1u << lane) - 1u));
+        warp_count = __popc(voters);
+        if (__ballot_sync(0xFFFFFFFFu, count > 1) != 0) {
+            uint32_t incl = count;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-            if (lane >= o) incl += up;
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            before_mine = incl - count;
+            warp_count = __shfl_sync(0xFFFFFFFFu, incl, 31);
         }
-        before_mine = incl - count;
-        warp_count = __shfl_sync(0xFFFFFFFFu, incl, 31);
     }
 
     STAGE(9);
