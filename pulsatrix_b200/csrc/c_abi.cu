@@ -53,7 +53,7 @@ struct psx_ctx {
     cudaStream_t stream = nullptr;
     int sm_count = 0;
     uint64_t launches = 0;
-    int merge_capacity_configured = 0;
+    bool merge_configured = false;
     bool scan_configured = false;
     int nucleus_k = 160;  // logits every part hands on when no top-k bounds the survivors
     // row-pass scratch
@@ -164,16 +164,20 @@ psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int parts) {
     if (parts > 16 * psx::kMergeThreads) {
         return fail(PSX_ERR_UNSUPPORTED, "psx_b200: rows wider than 64M logits per GPU are not supported");
     }
-    const int bytes = (int)psx::merge_rows_shared_bytes(plan.sort_capacity, plan.gather_capacity, plan.nucleus);
-    if (ctx->merge_capacity_configured >= bytes) return PSX_OK;
-    PSX_CUDA(psx::configure_merge_rows((size_t)bytes));
-    ctx->merge_capacity_configured = bytes;
+    (void)plan;
+    if (ctx->merge_configured) return PSX_OK;
+    PSX_CUDA(psx::configure_merge_rows());
+    ctx->merge_configured = true;
     return PSX_OK;
 }
 
 // Fills the part of ScanParams that depends on the settings; uploads the banned ids.
 psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_config* c, const Plan& plan,
                         psx::ScanParams& sp) {
+    if (!ctx->scan_configured) {  // a part is more shared memory than a kernel gets without asking
+        PSX_CUDA(psx::configure_scan_rows());
+        ctx->scan_configured = true;
+    }
     sp.apply_penalty = c->repetition_penalty != 1.0f ? 1 : 0;  // src/generation.cpp:59
     sp.penalty = c->repetition_penalty;
     sp.apply_temperature = plan.apply_temperature ? 1 : 0;
@@ -330,10 +334,6 @@ psx_status plan_row_pass(psx_ctx* ctx, cudaStream_t stream, const float* logits,
     sp.vocab = vocab;
     sp.history_ids = history_ids;
     sp.history_offsets = history_offsets;
-    if (!ctx->scan_configured) {
-        PSX_CUDA(psx::configure_scan_rows());
-        ctx->scan_configured = true;
-    }
     if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
     return reserve_scan_scratch(ctx, rows, plan, sp);
 }

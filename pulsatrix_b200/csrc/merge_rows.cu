@@ -55,9 +55,7 @@ int merge_slot_shift(int parts, int part_cap, int expected) {
     return shift;
 }
 
-cudaError_t configure_merge_rows(size_t shared_bytes) {
-    return cudaFuncSetAttribute(merge_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes);
-}
+cudaError_t configure_merge_rows() { return allow_all_dynamic_shared(merge_rows_kernel); }
 
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;

@@ -59,7 +59,7 @@ struct MergeParams {
 size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, bool overlay);
 // The slot_shift for lists that usually hold about `expected` candidates, within the fetch budget.
 int merge_slot_shift(int parts, int part_cap, int expected);
-cudaError_t configure_merge_rows(size_t shared_bytes);
+cudaError_t configure_merge_rows();  // once per device: lifts the kernel's dynamic shared-memory limit to the device's
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream);
 
 }  // namespace psx

@@ -143,7 +143,7 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
     // Shared-memory opt-ins of the two kernels (host-side function attributes, no memory): set on
     // every call, because the regular entry points adjust the same attributes to their own needs.
     PSX_STATIC_CUDA(psx::configure_scan_rows());
-    PSX_STATIC_CUDA(psx::configure_merge_rows(psx::merge_rows_shared_bytes(kSortCapacityWide, kGatherCapacityWide, false)));
+    PSX_STATIC_CUDA(psx::configure_merge_rows());
 
     // ---- the same two kernels as psx_b200_sample_rows, pointed at the built-in scratch ----------------------
     const bool top_k_on = sample && c->top_k > 0 && c->top_k < vocab;

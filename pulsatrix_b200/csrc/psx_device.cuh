@@ -191,6 +191,23 @@ __device__ __forceinline__ void block_bitonic_sort(unsigned long long* keys, int
     }
 }
 
+// Lets `kernel` be launched with as much dynamic shared memory as the current device gives a block.
+// The limit belongs to the kernel and the device, not to a caller: contexts and host threads that
+// need different amounts must not lower it under one another, so it is raised to the most, once.
+template <class Kernel>
+inline cudaError_t allow_all_dynamic_shared(Kernel kernel) {
+    int device = 0, most = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&most, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    if (e != cudaSuccess) return e;
+    cudaFuncAttributes attributes;
+    e = cudaFuncGetAttributes(&attributes, kernel);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                most - (int)attributes.sharedSizeBytes);
+}
+
 // Launches `kernel` so that it may begin while the kernel before it in `stream` is still running
 // (see grid_dependency_wait above); PSX_B200_NO_PDL=1 in the environment launches the ordinary way.
 template <class Params>

@@ -541,10 +541,9 @@ extern "C" __attribute__((visibility("default"))) int psx_debug_stage_clocks(uns
 #endif
 
 cudaError_t configure_scan_rows() {
-    cudaError_t e = cudaFuncSetAttribute(scan_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kPartVecs * 16);
+    const cudaError_t e = allow_all_dynamic_shared(scan_rows_kernel<true>);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(scan_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPartVecs * 16);
+    return allow_all_dynamic_shared(scan_rows_kernel<false>);
 }
 
 cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t stream) {

@@ -482,9 +482,18 @@ cudaError_t launch_topk_rows(const float* in, float* values, float* indices, siz
     const size_t shared = entries * 8 + (p.in_shared ? (size_t)p.slice * 4 + 32 : 0);
     if (rows * (size_t)p.cluster > 0x7FFFFFFFull) return cudaErrorInvalidConfiguration;
     if (shared > 48 * 1024) {
-        const cudaError_t e = largest ? cudaFuncSetAttribute(topk_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared)
-                                      : cudaFuncSetAttribute(topk_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        if (e != cudaSuccess) return e;
+        // Once per device and direction (the call sets the same value every time, so two host threads
+        // that both find the flag clear do no harm).
+        static bool lifted[2][64] = {};
+        int device = 0;
+        if (cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return e;
+        bool& done = lifted[largest ? 1 : 0][device & 63];
+        if (!done) {
+            const cudaError_t e = largest ? allow_all_dynamic_shared(topk_rows_kernel<true>)
+                                          : allow_all_dynamic_shared(topk_rows_kernel<false>);
+            if (e != cudaSuccess) return e;
+            done = true;
+        }
     }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)(rows * p.cluster));

@@ -26,9 +26,9 @@ def psx_config(cfg, num_new_tokens=0):
                                    eos_token_ids=eos)
 
 
-def sample_on_gpu(logits, hist_flat, offsets, cfg, uniforms, num_new_tokens=0, pad_columns=0, shift=0):
+def sample_on_gpu(logits, hist_flat, offsets, cfg, uniforms, num_new_tokens=0, pad_columns=0, shift=0, context=None):
     """Device-resident call.  pad_columns widens the row stride, shift offsets the base pointer by
-    that many floats, so rows need not start on a 16-byte boundary."""
+    that many floats, so rows need not start on a 16-byte boundary; context: the shared one if None."""
     import torch
     rows, vocab = logits.shape
     stride = vocab + pad_columns
@@ -38,7 +38,7 @@ def sample_on_gpu(logits, hist_flat, offsets, cfg, uniforms, num_new_tokens=0, p
     d_hist = torch.from_numpy(np.ascontiguousarray(hist_flat, dtype=np.int64)).cuda() if hist_flat is not None else None
     d_off = torch.from_numpy(np.ascontiguousarray(offsets, dtype=np.int64)).cuda() if offsets is not None else None
     d_u = torch.from_numpy(np.ascontiguousarray(uniforms, dtype=np.float64)).cuda() if uniforms is not None else None
-    out = ctx().sample_rows(view, d_hist, d_off, psx_config(cfg, num_new_tokens), d_u, vocab=vocab)
+    out = (context or ctx()).sample_rows(view, d_hist, d_off, psx_config(cfg, num_new_tokens), d_u, vocab=vocab)
     torch.cuda.synchronize()
     return (out["tokens"].cpu().numpy(), out["log_probs"].cpu().numpy(), out["status"].cpu().numpy(),
             psx.Context.diag_to_numpy(out["diag"]))

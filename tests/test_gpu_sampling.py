@@ -326,3 +326,26 @@ def test_contexts_in_flight_on_their_own_streams_change_no_answer():
     finally:
         for c in contexts:
             c.close()
+
+
+def test_contexts_with_different_plans_do_not_lower_each_others_limits():
+    """A full-vocabulary top-p (large survivor-stage shared memory) in one context, a small top-k in a
+    context created after it, then the first again: the kernels' limits belong to the process."""
+    w = WORKLOADS["c3"]
+    logits, hist, offsets, seeds = workload_rows.build("c3", np.arange(6))
+    wide = workload_rows.config_of(w)
+    narrow = ol.make_config(max_new_tokens=1, do_sample=True, top_k=5, temperature=0.9)
+    u = psx.uniforms_mt19937_64(seeds)
+    first, second = psx.Context(0), None
+    try:
+        a = gh.sample_on_gpu(logits, hist.ravel(), offsets, wide, u, context=first)
+        second = psx.Context(0)
+        b = gh.sample_on_gpu(logits, hist.ravel(), offsets, narrow, u, context=second)
+        again = gh.sample_on_gpu(logits, hist.ravel(), offsets, wide, u, context=first)
+    finally:
+        first.close()
+        if second is not None:
+            second.close()
+    assert a[0].tolist() == ol.rows("oracle", logits, hist.ravel(), offsets, wide, seeds)["token"].tolist()
+    assert b[0].tolist() == ol.rows("oracle", logits, hist.ravel(), offsets, narrow, seeds)["token"].tolist()
+    assert again[0].tolist() == a[0].tolist() and again[1].tobytes() == a[1].tobytes()

@@ -69,3 +69,14 @@ def test_sharded_equals_unsharded_for_greedy_and_top_k(world):
         assert (status == 0).all()
         assert tokens.tolist() == want["token"].tolist()
         assert (np.abs(logp - want["log_prob"]) <= 1e-5 * np.abs(want["log_prob"]) + 1e-9).all()
+
+
+def test_a_shard_scan_may_be_the_first_call_of_a_process():
+    """The kernels' shared-memory limits are lifted by whichever entry point runs first: a fresh
+    process whose first call is psx_b200_shard_scan must work like any other."""
+    import subprocess
+    import sys
+    done = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-p", "no:cacheprovider",
+                           f"{Path(__file__).resolve()}::test_c5_in_eight_shards_matches_the_reference_fixture"],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
