@@ -1,6 +1,6 @@
 """Benchmark of the token-sampling hot path: sampled rows/s and logits-read HBM GB/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--contexts M] [--impl ours|reference]
 
 A step is one pass of the sampling path (row pass + survivor stage) over one batch of the
 workload on every GPU: each rank owns its own batch (rows split across GPUs, no collective on
@@ -10,6 +10,12 @@ than fit in L2.  `value` is timed with CUDA events around exactly K steps with d
 inputs; `e2e` is the same metric through the host-buffer entry point, copies included;
 `roofline` is the row pass alone (algorithmic bytes = 4 * rows * vocab per launch) against the
 measured HBM peak; `cpu_baseline` is the reference's CPU sampler on this box's host cores.
+
+Steps go round-robin to M sampler contexts (default 3), each with its own stream and scratch, the
+way a server holds one context per batch in flight; the same loops with one context are timed too
+and reported under `single_context`.  `--workload c5` is the vocabulary-sharded mode instead: the
+batch is fixed, every rank holds rows x (vocab / N) logits, and a step is shard scan, one NCCL
+all-gather of the per-row records, survivor stage (strong scaling, one context).
 
 `--impl reference` times the reference's own CPU sampler (compiled from its sources into
 oracle/_ref, or the plain-C restatement when that is absent) on a bounded sample of the same
@@ -497,7 +503,7 @@ def run_sharded(args, rank, world):
                 "d2h_bytes_per_step": w.rows * 8, "steps": e2e_steps},
         "gpu_launches": int(launches) * world,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "scan_rows_kernel (+ pack_shard_records_kernel)", "achieved": achieved,
+        "roofline": {"bound": "hbm", "kernel": "scan_rows_kernel (+ pack_records_kernel)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": int(round(shard_bytes * ROW_PASS_TRAFFIC_RATIO)),
                      "traffic_note": "bytes per launch; ncu dram read+write of one C2 launch, scaled by this shard's bytes",

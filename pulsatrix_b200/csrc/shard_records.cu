@@ -1,67 +1,74 @@
 // Packs one GPU's row-pass output into one record per row for the all-gather of the
 // vocabulary-sharded path: the shard's parts are joined into a single PartStats (max, tail
 // sum-exp against that max, threshold = the largest part threshold) and only the candidates at
-// or above that threshold are kept, in a fixed order; the others' mass moves into the tail.
-// One warp per row; a few KB read and about a KB written per row.
+// or above that threshold are kept, in a fixed order (part, then place in the part's list); the
+// others' mass moves into the tail.  One block of eight warps per row; a warp takes whole parts.
 #include "shard_records.cuh"
 
 namespace psx {
 
 namespace {
 
-constexpr int kPackKeys = 4096;  // candidates of one row the exact local selection can look at
+constexpr int kPackThreads = 256;
+constexpr int kPackWarps = kPackThreads / 32;
+constexpr int kPackKeys = 4096;  // candidates of one row the exact local selection can look at;
+                                 // afterwards the same words hold one kept-count per part
 
-// The k-th largest (1-based, k <= m) of m keys in shared memory, by one warp: four 8-bit radix
-// passes, most significant digit first.
-__device__ uint32_t warp_select_kth(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, int lane) {
+// The k-th largest (1-based, k <= m) of m keys in shared memory, by the whole block: four 8-bit
+// radix passes, most significant digit first; the first warp finds the digit.  `pick` is two
+// shared words for its answer.
+__device__ uint32_t block_select_kth_key(const uint32_t* keys, int m, uint32_t k, uint32_t* hist, uint32_t* pick) {
+    const int tid = threadIdx.x, lane = tid & 31;
     uint32_t prefix = 0, mask = 0, remaining = k;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int b = lane; b < 256; b += 32) hist[b] = 0;
-        __syncwarp();
-        for (int i = lane; i < m; i += 32) {
+        hist[tid] = 0;  // kPackThreads == 256 bins
+        __syncthreads();
+        for (int i = tid; i < m; i += kPackThreads) {
             const uint32_t key = keys[i];
             if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
         }
-        __syncwarp();
-        uint32_t local = 0;  // lane L owns digits 255-8L down to 248-8L
-        for (int b = 0; b < 8; ++b) local += hist[255 - 8 * lane - b];
-        uint32_t incl = local;
+        __syncthreads();
+        if (tid < 32) {
+            uint32_t local = 0;  // lane L owns digits 255-8L down to 248-8L
+            for (int b = 0; b < 8; ++b) local += hist[255 - 8 * lane - b];
+            uint32_t incl = local;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-            if (lane >= o) incl += up;
-        }
-        const uint32_t excl = incl - local;
-        const bool here = excl < remaining && remaining <= incl;
-        uint32_t digit = 0, above = 0;
-        if (here) {
-            above = excl;
-            int d = 255 - 8 * lane;
-            for (int b = 0; b < 8; ++b, --d) {
-                if (above + hist[d] >= remaining) break;
-                above += hist[d];
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += up;
             }
-            digit = (uint32_t)d;
+            const uint32_t excl = incl - local;
+            if (excl < remaining && remaining <= incl) {  // exactly one lane
+                uint32_t above = excl;
+                int d = 255 - 8 * lane;
+                for (int b = 0; b < 8; ++b, --d) {
+                    if (above + hist[d] >= remaining) break;
+                    above += hist[d];
+                }
+                pick[0] = (uint32_t)d;
+                pick[1] = above;
+            }
         }
-        const int owner = __ffs(__ballot_sync(0xFFFFFFFFu, here)) - 1;
-        digit = __shfl_sync(0xFFFFFFFFu, digit, owner);
-        above = __shfl_sync(0xFFFFFFFFu, above, owner);
-        prefix |= digit << shift;
-        remaining -= above;
+        __syncthreads();
+        prefix |= pick[0] << shift;
+        remaining -= pick[1];
         mask |= 255u << shift;
-        __syncwarp();
     }
     return prefix;
 }
 
-__global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
+__global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackParams p) {
     __shared__ uint32_t s_keys[kPackKeys];
     __shared__ uint32_t s_hist[256];
+    __shared__ uint32_t s_pick[2];
+    __shared__ double s_sum[2][kPackWarps];
+    __shared__ uint32_t s_dropped[kPackWarps];
     const int64_t row = blockIdx.x;
-    const int lane = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool apply_t = p.apply_temperature != 0;
     const PartStats* stats = p.stats + row * p.parts;
 
+    // Every warp joins the parts' records for itself (a few dozen small loads out of L2).
     float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
     uint32_t nonfinite = 0, overflow = 0, alive_tail = 0;
     for (int i = lane; i < p.parts; i += 32) {
@@ -81,17 +88,17 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
     alive_tail = warp_sum_u32(alive_tail);
     float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
-    const int nseg = p.parts;  // one candidate list per part
+    const int nseg = p.parts;  // one candidate list per part; at most kPackKeys parts (checked by the host)
     const uint32_t* seg_counts = p.part_counts + row * nseg;
     const uint2* cands = p.candidates + (size_t)row * nseg * kPartCap;
 
     // The shard's own k-th largest processed value is a lower bound on the row's: nothing below
     // it (after the temperature divide's ties) can survive the merged top-k, so it need not travel.
     if (p.top_k > 0) {
-        int m = 0;  // warp-uniform
+        int m = 0;  // block-uniform
         for (int s = 0; s < nseg; ++s) {
             const int cnt = min((int)seg_counts[s], kPartCap);
-            for (int i = lane; i < cnt; i += 32) {
+            for (int i = tid; i < cnt; i += kPackThreads) {
                 if (m + i < kPackKeys) {
                     const uint2 c = cands[(size_t)s * kPartCap + i];
                     s_keys[m + i] = ordered_key(processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty));
@@ -99,17 +106,19 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
             }
             m += cnt;
         }
-        __syncwarp();
+        __syncthreads();
         if (m <= kPackKeys && m > p.top_k) {
-            const uint32_t kth = warp_select_kth(s_keys, m, (uint32_t)p.top_k, s_hist, lane);
+            const uint32_t kth = block_select_kth_key(s_keys, m, (uint32_t)p.top_k, s_hist, s_pick);
             keep_from = fmaxf(keep_from, relax_threshold(from_ordered_key(kth), apply_t, p.temperature));
         }
+        __syncthreads();  // the keys are done with: their words now hold the parts' kept counts
     } else if (!p.do_sample) {
         keep_from = fmaxf(y_max, -FLT_MAX);  // greedy: the maximum and its ties
     }
 
+    // Tails of the parts: thread t takes parts t, t + 256, ...
     double raw_tail = 0.0, proc_tail = 0.0;
-    for (int i = lane; i < p.parts; i += 32) {
+    for (int i = tid; i < p.parts; i += kPackThreads) {
         const PartStats s = stats[i];
         raw_tail += s.raw_tail * exp((double)s.raw_max - (double)raw_max);
         if (s.y_max > -INFINITY && s.proc_tail > 0.0) {
@@ -117,48 +126,82 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
         }
     }
 
-    char* record = static_cast<char*>(p.records) + row * (int64_t)shard_record_bytes(p.capacity);
-    uint2* out = reinterpret_cast<uint2*>(record + kRecordCandidatesOffset);
-    uint32_t kept = 0, dropped = 0;  // warp-uniform
-    for (int s = 0; s < nseg; ++s) {
+    // First sweep: warp w takes parts w, w + 8, ...; counts what each keeps, and moves the mass of
+    // what it drops into the tails.
+    uint32_t* s_kept = s_keys;
+    uint32_t dropped = 0;  // warp-uniform
+    for (int s = warp; s < nseg; s += kPackWarps) {
         const int cnt = min((int)seg_counts[s], kPartCap);
+        uint32_t kept = 0;
         for (int base = 0; base < cnt; base += 32) {
             const int i = base + lane;
-            bool keep = false, drop = false;
-            uint2 c = make_uint2(0, 0);
+            bool keep = false;
             if (i < cnt) {
-                c = cands[(size_t)s * kPartCap + i];
+                const uint2 c = cands[(size_t)s * kPartCap + i];
                 const float l = __uint_as_float(c.x);
                 const float y = processed_before_temperature(l, c.y, p.penalty);
                 keep = y >= keep_from;
-                drop = !keep;
-                if (drop) {
+                if (!keep) {
                     raw_tail += exp((double)l - (double)raw_max);
-                    if (y > -INFINITY) {
-                        proc_tail += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
-                    }
+                    if (y > -INFINITY) proc_tail += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
                 }
             }
-            const uint32_t votes = __ballot_sync(0xFFFFFFFFu, keep);
-            if (keep) {
-                const uint32_t slot = kept + __popc(votes & ((1u << lane) - 1u));
-                if (slot < (uint32_t)p.capacity) out[slot] = c;
-            }
-            kept += __popc(votes);
-            dropped += __popc(__ballot_sync(0xFFFFFFFFu, drop));
+            kept += __popc(__ballot_sync(0xFFFFFFFFu, keep));
         }
+        dropped += (uint32_t)cnt - kept;
+        if (lane == 0) s_kept[s] = kept;
     }
     raw_tail = warp_sum(raw_tail);
     proc_tail = warp_sum(proc_tail);
     if (lane == 0) {
+        s_sum[0][warp] = raw_tail;
+        s_sum[1][warp] = proc_tail;
+        s_dropped[warp] = dropped;
+    }
+    __syncthreads();
+
+    // Second sweep: a part's kept candidates go where the parts before it end.
+    char* record = static_cast<char*>(p.records) + row * (int64_t)shard_record_bytes(p.capacity);
+    uint2* out = reinterpret_cast<uint2*>(record + kRecordCandidatesOffset);
+    for (int s = warp; s < nseg; s += kPackWarps) {
+        uint32_t before = 0;
+        for (int j = lane; j < s; j += 32) before += s_kept[j];
+        before = warp_sum_u32(before);
+        if (s_kept[s] == 0) continue;
+        const int cnt = min((int)seg_counts[s], kPartCap);
+        for (int base = 0; base < cnt; base += 32) {
+            const int i = base + lane;
+            bool keep = false;
+            uint2 c = make_uint2(0, 0);
+            if (i < cnt) {
+                c = cands[(size_t)s * kPartCap + i];
+                keep = processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty) >= keep_from;
+            }
+            const uint32_t votes = __ballot_sync(0xFFFFFFFFu, keep);
+            if (keep) {
+                const uint32_t slot = before + __popc(votes & ((1u << lane) - 1u));
+                if (slot < (uint32_t)p.capacity) out[slot] = c;
+            }
+            before += __popc(votes);
+        }
+    }
+    if (tid == 0) {
+        uint32_t kept = 0, all_dropped = 0;
+        for (int s = 0; s < nseg; ++s) kept += s_kept[s];
+        double t = 0.0, q = 0.0;
+        for (int w = 0; w < kPackWarps; ++w) {  // a fixed order
+            t += s_sum[0][w];
+            q += s_sum[1][w];
+            all_dropped += s_dropped[w];
+        }
         PartStats s;
-        s.raw_tail = raw_tail;
-        s.proc_tail = proc_tail;
+        s.raw_tail = t;
+        s.proc_tail = q;
         s.raw_max = raw_max;
         s.y_max = y_max;
         s.thr = thr;
         s.nonfinite = nonfinite;
-        s.alive_tail = alive_tail + dropped;
+        s.alive_tail = alive_tail + all_dropped;
         s.overflow = (overflow || kept > (uint32_t)p.capacity) ? 1u : 0u;
         *reinterpret_cast<PartStats*>(record + kRecordStatsOffset) = s;
         *reinterpret_cast<uint32_t*>(record + kRecordCountOffset) = min(kept, (uint32_t)p.capacity);
@@ -170,7 +213,8 @@ __global__ void __launch_bounds__(32) pack_records_kernel(const PackParams p) {
 
 cudaError_t launch_pack_records(const PackParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;
-    pack_records_kernel<<<(unsigned)p.rows, 32, 0, stream>>>(p);
+    if (p.parts > kPackKeys) return cudaErrorInvalidConfiguration;
+    pack_records_kernel<<<(unsigned)p.rows, kPackThreads, 0, stream>>>(p);
     return cudaGetLastError();
 }
 
