@@ -236,6 +236,51 @@ class Context:
             _dptr(out["log_probs"]), _dptr(out["status"]), _dptr(out["diag"])))
         return out
 
+    def bind_sample_rows(self, logits, history_ids, history_offsets, config, uniforms, out=None, stream=None,
+                         vocab=None):
+        """sample_rows with its arguments converted once: returns a function of no arguments that
+        enqueues the same call again (same buffers, same stream) and returns the output dict.  For
+        loops over fixed buffers, where building the argument list costs as much as the launches."""
+        rows = logits.shape[0]
+        vocab = logits.shape[1] if vocab is None else vocab
+        assert logits.stride(1) == 1 or rows == 0
+        out = out or self.alloc_outputs(rows)
+        if stream is None:
+            import torch
+            stream = torch.cuda.current_stream(logits.device).cuda_stream
+        args = (self._ctx, C.c_void_p(stream), _dptr(logits), C.c_int64(rows), C.c_int64(vocab),
+                C.c_int64(logits.stride(0) if rows else vocab), _dptr(history_ids), _dptr(history_offsets),
+                C.c_void_p(C.addressof(config)), _dptr(uniforms), _dptr(out["tokens"]), _dptr(out["log_probs"]),
+                _dptr(out["status"]), _dptr(out["diag"]))
+        fn = self._lib.psx_b200_sample_rows
+        keep = (logits, history_ids, history_offsets, config, uniforms, out)  # the buffers live as long as the call
+
+        def call(fn=fn, args=args, out=out, keep=keep):
+            status = fn(*args)
+            if status:
+                _check(status)
+            return out
+        return call
+
+    def bind_row_pass_only(self, logits, history_ids, history_offsets, config, stream=None, vocab=None):
+        """row_pass_only with its arguments converted once (see bind_sample_rows)."""
+        rows = logits.shape[0]
+        vocab = logits.shape[1] if vocab is None else vocab
+        if stream is None:
+            import torch
+            stream = torch.cuda.current_stream(logits.device).cuda_stream
+        args = (self._ctx, C.c_void_p(stream), _dptr(logits), C.c_int64(rows), C.c_int64(vocab),
+                C.c_int64(logits.stride(0) if rows else vocab), _dptr(history_ids), _dptr(history_offsets),
+                C.c_void_p(C.addressof(config)))
+        fn = self._lib.psx_b200_row_pass_only
+        keep = (logits, history_ids, history_offsets, config)
+
+        def call(fn=fn, args=args, keep=keep):
+            status = fn(*args)
+            if status:
+                _check(status)
+        return call
+
     def process_logits_host(self, logits, history_ids, history_offsets, config):
         """ProcessLogits on host rows (numpy float32 (rows, vocab), modified in place).  Returns the
         per-row status array; raises when the device path declines a row."""

@@ -124,10 +124,10 @@ Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t ro
     Plan plan;
     const bool aligned = (reinterpret_cast<uintptr_t>(logits) % 16 == 0) && (row_stride % 4 == 0);
     const int64_t vectors = (cols + 3 + (aligned ? 0 : 3)) / 4;  // most float4 a row can span
-    int part_vecs = psx::kPartVecs;
-    if (const char* env = std::getenv("PSX_B200_PART_VECS")) {  // tuning knob: vectors per CTA, 256..4096
-        part_vecs = std::max(256, std::min(psx::kPartVecs, std::atoi(env)));
-    }
+    static const int part_vecs = [] {  // tuning knob, read once: vectors per CTA, 256..4096
+        const char* env = std::getenv("PSX_B200_PART_VECS");
+        return env ? std::max(256, std::min(psx::kPartVecs, std::atoi(env))) : psx::kPartVecs;
+    }();
     plan.parts = (int)((vectors + part_vecs - 1) / part_vecs);
     plan.vecs_per_part = (int)((vectors + plan.parts - 1) / plan.parts);
     const bool sample = c->do_sample != 0;
@@ -187,10 +187,11 @@ psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_co
     sp.k_need = plan.k_need;
     sp.parts = plan.parts;
     sp.vecs_per_part = plan.vecs_per_part;
-    {
-        const char* skip = std::getenv("PSX_B200_DEBUG_SKIP");  // profiling only
-        sp.debug_skip = skip ? std::atoi(skip) : 0;
-    }
+    static const int debug_skip = [] {  // profiling only, read once
+        const char* skip = std::getenv("PSX_B200_DEBUG_SKIP");
+        return skip ? std::atoi(skip) : 0;
+    }();
+    sp.debug_skip = debug_skip;
     sp.inputs_ready = ctx->inputs_ready ? 1 : 0;
     sp.num_banned = 0;
     sp.banned_ids = nullptr;
@@ -234,10 +235,11 @@ void fill_merge_settings(psx::MergeParams& mp, const psx_sampling_config* c, con
     mp.row_status = row_status;
     mp.diag = diag;
     mp.sort_capacity = plan.sort_capacity;
-    {
-        const char* stop = std::getenv("PSX_B200_DEBUG_MERGE_STOP");  // profiling only
-        mp.debug_stop = stop ? std::atoi(stop) : 0;
-    }
+    static const int debug_stop = [] {  // profiling only, read once
+        const char* stop = std::getenv("PSX_B200_DEBUG_MERGE_STOP");
+        return stop ? std::atoi(stop) : 0;
+    }();
+    mp.debug_stop = debug_stop;
     mp.gather_capacity = plan.gather_capacity;
 }
 
