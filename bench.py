@@ -11,7 +11,7 @@ inputs; `e2e` is the same metric through the host-buffer entry point, copies inc
 `roofline` is the row pass alone (algorithmic bytes = 4 * rows * vocab per launch) against the
 measured HBM peak; `cpu_baseline` is the reference's CPU sampler on this box's host cores.
 
-Steps go round-robin to M sampler contexts (default 3), each with its own stream and scratch, the
+Steps go round-robin to M sampler contexts (default 4), each with its own stream and scratch, the
 way a server holds one context per batch in flight; the same loops with one context are timed too
 and reported under `single_context`.  `--workload c5` is the vocabulary-sharded mode instead: the
 batch is fixed, every rank holds rows x (vocab / N) logits, and a step is shard scan, one NCCL
@@ -55,7 +55,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--contexts", type=int, default=3,
+    ap.add_argument("--contexts", type=int, default=4,
                     help="sampler contexts in flight per GPU (one stream and one scratch each; steps go round-robin)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
     ap.add_argument("--top-k", action="store_true",

@@ -59,7 +59,9 @@ cudaError_t configure_merge_rows() { return allow_all_dynamic_shared(merge_rows_
 
 cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;
-    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, p.overlay != 0);
+    // The same condition as the kernel's: the overlaid layout is for plans without a top-k.
+    const bool overlay = p.overlay != 0 && p.logits != nullptr && !(p.do_sample && p.top_k > 0 && p.top_k < p.vocab);
+    const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, overlay);
     return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, p);
 }
 

@@ -349,3 +349,33 @@ def test_contexts_with_different_plans_do_not_lower_each_others_limits():
     assert a[0].tolist() == ol.rows("oracle", logits, hist.ravel(), offsets, wide, seeds)["token"].tolist()
     assert b[0].tolist() == ol.rows("oracle", logits, hist.ravel(), offsets, narrow, seeds)["token"].tolist()
     assert again[0].tolist() == a[0].tolist() and again[1].tobytes() == a[1].tobytes()
+
+
+def test_a_prepared_call_enqueues_the_same_call_again():
+    """Context.bind_sample_rows converts the arguments once; calling the result twice gives what
+    sample_rows gives, and new contents of the same buffers are seen by the next call."""
+    import torch
+    w = WORKLOADS["c1"]
+    cfg = workload_rows.config_of(w)
+    logits, hist, offsets, seeds = workload_rows.build("c1", np.arange(10))
+    other = workload_rows.build("c1", np.arange(10, 20))[0]
+    d_logits = torch.from_numpy(logits).cuda()
+    d_hist = torch.from_numpy(hist.ravel().astype(np.int64)).cuda()
+    d_off = torch.from_numpy(offsets.astype(np.int64)).cuda()
+    d_u = torch.from_numpy(psx.uniforms_mt19937_64(seeds)).cuda()
+    context = gh.ctx()
+    config = gh.psx_config(cfg)
+    plain = context.sample_rows(d_logits, d_hist, d_off, config, d_u)
+    torch.cuda.synchronize()
+    want = plain["tokens"].cpu().numpy().tolist()
+    call = context.bind_sample_rows(d_logits, d_hist, d_off, config, d_u)
+    for _ in range(2):
+        out = call()
+        torch.cuda.synchronize()
+        assert out["tokens"].cpu().numpy().tolist() == want
+        assert out["log_probs"].cpu().numpy().tobytes() == plain["log_probs"].cpu().numpy().tobytes()
+    d_logits.copy_(torch.from_numpy(other))
+    out = call()
+    torch.cuda.synchronize()
+    expect = ol.rows("oracle", other, hist.ravel(), offsets, cfg, seeds)
+    assert out["tokens"].cpu().numpy().tolist() == expect["token"].tolist()
