@@ -86,14 +86,19 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
                                          int first_pos, int part_logits, uint32_t* bitmap, uint32_t* also,
                                          uint32_t* warp_counts) {
     // first_pos: position of this part's first slot in the row's aligned window, minus the
-    // row's misalignment, i.e. the (possibly negative) local column of data[0].
+    // row's misalignment, i.e. the (possibly negative) local column of data[0].  The ids this part
+    // cares about are one interval: its slots, cut to this GPU's columns [0, cols).  Those lie inside
+    // the vocabulary (src/generation.cpp:62 ignores ids outside it), so one unsigned comparison
+    // of the distance from the interval's first id decides.
+    const int lo = max(first_pos, 0);
+    const int64_t hi = min((int64_t)first_pos + part_logits, p.cols);
+    const int64_t first_id = p.col_begin + lo;
+    const uint64_t span = hi > lo ? (uint64_t)(hi - lo) : 0u;
+    const uint32_t shift = (uint32_t)(lo - first_pos);
     for (int64_t i = begin + threadIdx.x; i < end; i += kScanThreads) {
-        const int64_t id = ids[i];
-        if ((uint64_t)id >= (uint64_t)p.vocab) continue;  // src/generation.cpp:62: ids outside the vocabulary are ignored
-        const uint64_t col = (uint64_t)(id - p.col_begin);
-        if (col >= (uint64_t)p.cols) continue;             // not in this GPU's columns
-        const uint32_t e = (uint32_t)((int)col - first_pos);  // slot in this part, if below part_logits
-        if (e < (uint32_t)part_logits) {
+        const uint64_t rel = (uint64_t)ids[i] - (uint64_t)first_id;  // wraps for ids before the interval
+        if (rel < span) {
+            const uint32_t e = (uint32_t)rel + shift;  // slot in this part
             const uint32_t word = e >> 5, bit = 1u << (e & 31);
             if (!(atomicOr(&bitmap[word], bit) & bit)) atomicAdd(&warp_counts[(word >> 2) & (kScanWarps - 1)], 1u);
             if (also) atomicOr(&also[word], bit);
@@ -312,7 +317,8 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     const int live_threads = min(kScanThreads, nvec);
     const int full_warps = live_threads >> 5;  // warps whose every thread owns a vector
     int kp = 33;  // > 32: no threshold, hand everything on
-    if (full_warps > 0) kp = (p.k_need + full_warps - 1) / full_warps;
+    if (full_warps == kScanWarps) kp = (p.k_need + kScanWarps - 1) / kScanWarps;  // the usual case: a shift
+    else if (full_warps > 0) kp = (p.k_need + full_warps - 1) / full_warps;
     // Threshold: a value that at least k_need logits of the part reach (or everything, when the
     // part has fewer).  Greedy needs the part's maximum only.  Otherwise every full warp finds
     // its kp-th largest per-thread maximum, kp = ceil(k_need / full warps), and the smallest of
