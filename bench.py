@@ -48,6 +48,27 @@ ROW_PASS_TRAFFIC_RATIO = 39087616 / 38895616
 FALLBACK_HBM_GBS = 6650.0
 
 
+# The one JSON line goes to the process's original standard output; everything else a library prints
+# there while the benchmark runs (NCCL announces its version on it) is sent to standard error.
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(result):
+    line = (json.dumps(result) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, line)
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -392,7 +413,7 @@ def run_ours(args, rank, world):
         sample = host_sample(w, batches[0], offsets, 64)
         value, kind, cores, text = cpu_rows_per_second(w, *sample, args.cpu_seconds)
         result["cpu_baseline"] = {"value": value, "unit": "rows/s", "cores": cores, "kind": kind, "sample": text}
-    print(json.dumps(result), flush=True)
+    emit(result)
 
 
 def run_sharded(args, rank, world):
@@ -527,7 +548,7 @@ def run_sharded(args, rank, world):
                      "algorithmic_bytes": shard_bytes, "launch_ms": scan_avg_ms},
         "failed_rows": failed, "every_rank_drew_the_same_tokens": same_everywhere,
     }
-    print(json.dumps(result), flush=True)
+    emit(result)
 
 def run_reference(args, rank, world):
     if rank != 0:
@@ -551,7 +572,7 @@ def run_reference(args, rank, world):
     elapsed = time.perf_counter() - t0
     value = rows * steps / elapsed
     text = f"{rows} rows of {w.name} per step, {cores} threads"
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": "sampled rows/sec and logits-read HBM GB/s vs B200 peak", "value": value,
         "unit": "rows/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 1),
         "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -560,7 +581,7 @@ def run_reference(args, rank, world):
                    "parallelism": "host threads, one row each"},
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": kind, "sample": text},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+    })
 
 
 TOP_K_SHAPES = [(4096, 16384, 64), (1024, 65536, 32), (64, 151936, 20), (8192, 4096, 16), (256, 128256, 1024)]
@@ -592,12 +613,13 @@ def run_top_k(args):
                         "input_gbs": rows * cols * 4 / (ms * 1e-3) / 1e9})
         del xs
     peak, peak_kind = measured_hbm_peak()
-    print(json.dumps({"metric": "top_k_rows rows/s", "unit": "rows/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
-                      "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results}))
+    emit({"metric": "top_k_rows rows/s", "unit": "rows/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
+          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
 
 
 def main():
     args = parse_args()
+    keep_stdout_for_the_result()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.top_k:
