@@ -299,15 +299,11 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
 
     // ---- 2. per-thread maxima, then the part's raw max and selection threshold -------------------------
     float m = kPad, amax = f_amax;
+    const int trips = (nvec + kScanThreads - 1) / kScanThreads;  // the part is padded to whole trips
     if (!(p.debug_skip & 8)) {
-        int v = tid;
-        for (; v + kScanThreads < nvec; v += 2 * kScanThreads) {  // two independent loads per trip
-            const float4 d0 = data4[v], d1 = data4[v + kScanThreads];
-            m = max_into(max_into(m, d0), d1);
-            amax = amax_into(amax_into(amax, d0), d1);
-        }
-        if (v < nvec) {
-            const float4 d = data4[v];
+#pragma unroll 4
+        for (int t = 0; t < trips; ++t) {
+            const float4 d = data4[t * kScanThreads + tid];
             m = max_into(m, d);
             amax = amax_into(amax, d);
         }
@@ -402,7 +398,6 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     // The part was padded to whole 256-vector trips and the loop is branch-free: a vector that
     // reaches the threshold (rare) is only noted, one bit per trip, and its sums are left out; after
     // the loop its components below the threshold are summed again and what reaches it is counted.
-    const int trips = (nvec + kScanThreads - 1) / kScanThreads;
     uint32_t noted = 0;
     auto exps_of = [&](const float4& d, float& e0, float& e1, float& e2, float& e3, float& q0, float& q1, float& q2,
                        float& q3) {
