@@ -60,22 +60,29 @@ __device__ __forceinline__ void bulk_copy_to_shared(void* dst, const void* src, 
                  : "memory");
 }
 
-// Waits for phase `parity` of the barrier, but not for ever: gives up after about a second.
+__device__ __forceinline__ unsigned long long global_nanoseconds() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for phase `parity` of the barrier, but not for ever: every try may sleep in the hardware for
+// up to the hinted microsecond, and a second after the first try the wait gives up.
 __device__ __forceinline__ bool barrier_wait_bounded(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_address(bar);
-    for (uint32_t tries = 0; tries < (1u << 22); ++tries) {
+    const unsigned long long started = global_nanoseconds();
+    for (;;) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(1000u)
             : "memory");
         if (done) return true;
-        __nanosleep(tries < 64 ? 100 : 400);
+        if (global_nanoseconds() - started > 1000000000ull) return false;
     }
-    return false;
 }
 
 // Sets, in a bitmap with one bit per logit of this part, the columns that `ids` names (and the
