@@ -17,6 +17,13 @@ and reported under `single_context`.  `--workload c5` is the vocabulary-sharded 
 batch is fixed, every rank holds rows x (vocab / N) logits, and a step is shard scan, one NCCL
 all-gather of the per-row records, survivor stage (strong scaling, one context).
 
+The driver's K (`--steps`) stays the unit: a region of exactly K steps is timed with CUDA events
+between barriers, and the region is repeated until at least 50 ms of GPU time have been timed;
+`ms_per_step` is the median over the repeats, with p10, p90 and the number of repeats beside it
+(the reference's own benchmark schema reports the same three).  With more than one GPU the line
+also carries a `sharded` record: workload C5 with its vocabulary split over the ranks, a few timed
+steps and a check of the first 48 rows against the reference fixture.
+
 `--impl reference` times the reference's own CPU sampler (compiled from its sources into
 oracle/_ref, or the plain-C restatement when that is absent) on a bounded sample of the same
 workload, rank 0 only.
@@ -41,11 +48,12 @@ sys.path[:0] = [str(ROOT), str(ROOT / "tests")]
 from pulsatrix_b200.workloads import WORKLOADS  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
-# DRAM bytes per algorithmic byte of the row pass, from the ncu capture of one launch on C2 that
-# profiles/scan_rows_kernel_c2.md summarises (dram read 39.09 MB + write 0 over 38.90 MB); the
-# kernel reads every logit once whatever the workload, so other workloads scale with their bytes.
-ROW_PASS_TRAFFIC_RATIO = 39087616 / 38895616
+# DRAM bytes (read + write) of one row-pass launch as ncu counted them, per workload that has been
+# captured; workloads without a capture report no traffic figure.
+ROW_PASS_TRAFFIC = {"c2": 39087616}
 FALLBACK_HBM_GBS = 6650.0
+MIN_TIMED_MS = 50.0   # a K-step region is repeated until this much GPU time has been timed
+MAX_REPEATS = 400
 
 
 # The one JSON line goes to the process's original standard output; everything else a library prints
@@ -208,6 +216,19 @@ def build_batches(w, device, count, seed):
     return batches, offsets
 
 
+def workload_text(w):
+    """The same words in both arms' config.workload."""
+    return (f"{w.name}: batch={w.rows} rows per GPU, vocab={w.vocab}, history={w.history}, penalty={w.repetition_penalty}, "
+            f"T={w.temperature}, top_k={w.top_k}, top_p={w.top_p}, do_sample={w.do_sample}")
+
+
+def spread(per_step_ms):
+    """median, p10, p90 of a list of per-step times."""
+    a = np.sort(np.asarray(per_step_ms, dtype=np.float64))
+    pick = lambda q: float(a[min(len(a) - 1, max(0, int(round(q * (len(a) - 1)))))])  # noqa: E731
+    return {"median": float(np.median(a)), "p10": pick(0.10), "p90": pick(0.90), "repeats": int(len(a))}
+
+
 def workload_config(w):
     import pulsatrix_b200 as psx
     return psx.SamplingConfig.make(do_sample=w.do_sample, temperature=w.temperature, top_k=w.top_k, top_p=w.top_p,
@@ -276,13 +297,11 @@ def run_ours(args, rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(launch, m, steps, warmup):
-        """Milliseconds for `steps` calls of launch(i, context index, stream) spread round-robin over
-        the first m contexts, each on its own stream: the begin event is recorded on the current
-        stream and every side stream waits for it; the end event is recorded on the current stream
-        after it has waited for the last work of every side stream."""
-        for i in range(warmup):
-            launch(i, i % m, side[i % m])
+    def region(launch, m, steps):
+        """Milliseconds for exactly `steps` calls of launch(i, context index, stream) spread round-robin
+        over the first m contexts, each on its own stream, between two barriers: the begin event is
+        recorded on the current stream and every side stream waits for it; the end event is recorded
+        on the current stream after it has waited for the last work of every side stream."""
         barrier()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record(stream)
@@ -297,6 +316,25 @@ def run_ours(args, rank, world):
         end.record(stream)
         barrier()
         return begin.elapsed_time(end)
+
+    def timed(launch, m, steps, warmup):
+        """Per-step milliseconds of every repeat of the K-step region (the max over the ranks of each
+        repeat): warm-up calls first, then the region again and again until MIN_TIMED_MS of GPU time
+        have been timed.  Every rank makes the same number of repeats (it follows from the first
+        region's time, agreed on by all)."""
+        for i in range(warmup):
+            launch(i, i % m, side[i % m])
+        if steps <= 0:
+            barrier()
+            return []
+        first = torch.tensor([region(launch, m, steps)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(first, op=dist.ReduceOp.MAX)
+        repeats = int(min(MAX_REPEATS, max(3, np.ceil(MIN_TIMED_MS / max(float(first.item()), 1e-3)))))
+        times = torch.tensor([region(launch, m, steps) for _ in range(repeats)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        return (times / steps).tolist()
 
     # The loops run over fixed buffers: each (context, batch) pair's call is prepared once
     # (Context.bind_*), so a step costs the host one foreign call, not the conversion of 14 arguments.
@@ -334,17 +372,23 @@ def run_ours(args, rank, world):
         sampler.start()
     # ---- value: K steps, device-resident inputs, CUDA events, M contexts in flight ----
     launches0 = sum(c.launches for c in ctxs)
-    elapsed_ms = timed(full_step, m_ctx, args.steps, m_ctx)
-    launches = sum(c.launches for c in ctxs) - launches0
+    step_ms = timed(full_step, m_ctx, args.steps, m_ctx)
+    launches = (sum(c.launches for c in ctxs) - launches0 - 2 * m_ctx) // (len(step_ms) + 1)  # per K-step region
     # ---- roofline: the row pass alone, K launches over the rotating batches, same M streams ----
-    scan_ms, calls = timed(row_pass, m_ctx, args.steps, max(3, n_batches) * m_ctx), args.steps
-    merge_ms = max(elapsed_ms - scan_ms, 0.0)
+    scan_ms = timed(row_pass, m_ctx, args.steps, max(3, n_batches) * m_ctx)
     # ---- the same two with one context, every launch on one stream ----
     one_ms = timed(full_step, 1, args.steps, max(3, n_batches))
     one_scan_ms = timed(row_pass, 1, args.steps, max(3, n_batches))
     # ---- the practical ceiling: a kernel that only reads the same batches, same cadence ----
-    read_ms = timed(read_only, m_ctx, args.steps, 3 * m_ctx) / args.steps
-    one_read_ms = timed(read_only, 1, args.steps, 3) / args.steps
+    read_ms = timed(read_only, m_ctx, args.steps, 3 * m_ctx)
+    one_read_ms = timed(read_only, 1, args.steps, 3)
+    # ---- what one Generate() sees: a single row per call, device-resident, one context ----
+    single_row = None
+    if w.name == "c1":
+        row_calls = [ctx.bind_sample_rows(batches[0][0][r:r + 1], batches[0][1][r * w.history:(r + 1) * w.history],
+                                          offsets[:2], cfg, uniforms[r:r + 1], out=ctx.alloc_outputs(1), stream=side[0].cuda_stream)
+                     for r in range(64)]
+        single_row = spread(timed(lambda i, c, s: row_calls[i % 64](), 1, min(args.steps, 200), 64))
     clocks = sampler.stop() if sampler else None
 
     # ---- e2e: the host-buffer entry point, pinned inputs, copies inside the timed region ----
@@ -363,34 +407,36 @@ def run_ours(args, rank, world):
     h2d = h_logits.numel() * 4 + h_hist.numel() * 8 + h_off.numel() * 8 + (h_u.numel() * 8 if w.do_sample else 0)
     d2h = w.rows * (8 + 4 + 4 + 24)
 
-    times = torch.tensor([elapsed_ms, e2e_s * 1e3, scan_ms / max(calls, 1), merge_ms / max(calls, 1), read_ms,
-                          one_ms, one_scan_ms / max(calls, 1), one_read_ms], dtype=torch.float64, device=device)
+    e2e_ms = torch.tensor([e2e_s * 1e3], dtype=torch.float64, device=device)
     if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, scan_avg_ms, merge_avg_ms, read_ms, one_ms, one_scan_avg_ms, one_read_ms = times.tolist()
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_ms.item())
+    sharded = sharded_record(args, rank, world, local) if world > 1 else None
     if rank != 0:
         return
 
     peak, peak_kind = measured_hbm_peak()
-    achieved = w.logits_bytes / (scan_avg_ms * 1e-3) / 1e9
+    step, scan, one, one_scan = spread(step_ms), spread(scan_ms), spread(one_ms), spread(one_scan_ms)
+    read_med, one_read_med = spread(read_ms)["median"], spread(one_read_ms)["median"]
+    achieved = w.logits_bytes / (scan["median"] * 1e-3) / 1e9
     result = {
         "metric": "sampled rows/sec and logits-read HBM GB/s vs B200 peak",
-        "value": w.rows * world * args.steps / (elapsed_ms * 1e-3),
+        "value": w.rows * world / (step["median"] * 1e-3),
         "unit": "rows/s",
         "n_gpus": world,
         "steps": args.steps,
         "warmup": max(args.warmup, 3),
-        "ms_per_step": elapsed_ms / args.steps,
+        "ms_per_step": step["median"],
+        "p10_ms_per_step": step["p10"], "p90_ms_per_step": step["p90"], "repeats": step["repeats"],
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "f32 logits; f64 survivor stage",
         "data": "synthetic",
-        "config": {"workload": f"{w.name}: batch={w.rows} rows per GPU, vocab={w.vocab}, history={w.history}, "
-                               f"penalty={w.repetition_penalty}, T={w.temperature}, top_k={w.top_k}, top_p={w.top_p}, "
-                               f"do_sample={w.do_sample}",
+        "config": {"workload": workload_text(w),
                    "parallelism": f"rows split over {world} GPU(s), no data-path collective",
                    "contexts_in_flight": m_ctx,
+                   "timing": f"a region of {args.steps} steps between barriers, repeated {step['repeats']} times; medians",
                    "l2": f"inputs rotate over {n_batches} batches = {n_batches * w.logits_bytes / 2**20:.0f} MiB > L2"},
         "e2e": {"value": w.rows * world * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps},
@@ -398,19 +444,27 @@ def run_ours(args, rank, world):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "scan_rows_kernel", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": int(round(w.logits_bytes * ROW_PASS_TRAFFIC_RATIO)),
-                     "traffic_note": "bytes per launch; ncu dram read+write of one C2 launch, scaled by this workload's bytes",
+                     "traffic": ROW_PASS_TRAFFIC.get(w.name),
+                     "traffic_note": "dram read + write bytes of one launch from an ncu capture of this workload; null: not captured",
                      "algorithmic_bytes": w.logits_bytes,
-                     "launch_ms": scan_avg_ms, "step_minus_row_pass_ms": merge_avg_ms,
+                     "launch_ms": scan["median"], "launch_ms_p10": scan["p10"], "launch_ms_p90": scan["p90"],
+                     "step_minus_row_pass_ms": max(step["median"] - scan["median"], 0.0),
                      "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "read_only_kernel_gbs": w.logits_bytes / (read_ms * 1e-3) / 1e9,
-                     "frac_of_read_only_kernel": read_ms / scan_avg_ms},
-        "single_context": {"value": w.rows * world * args.steps / (one_ms * 1e-3), "unit": "rows/s",
-                           "ms_per_step": one_ms / args.steps, "row_pass_launch_ms": one_scan_avg_ms,
-                           "roofline_frac": w.logits_bytes / (one_scan_avg_ms * 1e-3) / 1e9 / peak,
-                           "read_only_kernel_gbs": w.logits_bytes / (one_read_ms * 1e-3) / 1e9},
+                     "read_only_kernel_gbs": w.logits_bytes / (read_med * 1e-3) / 1e9,
+                     "frac_of_read_only_kernel": read_med / scan["median"]},
+        "single_context": {"value": w.rows * world / (one["median"] * 1e-3), "unit": "rows/s",
+                           "ms_per_step": one["median"], "p10_ms_per_step": one["p10"], "p90_ms_per_step": one["p90"],
+                           "row_pass_launch_ms": one_scan["median"],
+                           "roofline_frac": w.logits_bytes / (one_scan["median"] * 1e-3) / 1e9 / peak,
+                           "read_only_kernel_gbs": w.logits_bytes / (one_read_med * 1e-3) / 1e9},
         "failed_rows": failed,
     }
+    if single_row is not None:
+        result["single_row_call"] = {"us_per_call": single_row["median"] * 1e3, "p10_us": single_row["p10"] * 1e3,
+                                     "p90_us": single_row["p90"] * 1e3,
+                                     "note": "one row of the workload per call, device-resident, one context"}
+    if sharded is not None:
+        result["sharded"] = sharded
     if world == 1:
         sample = host_sample(w, batches[0], offsets, 64)
         value, kind, cores, text = cpu_rows_per_second(w, *sample, args.cpu_seconds)
@@ -418,28 +472,21 @@ def run_ours(args, rank, world):
     emit(result)
 
 
-def run_sharded(args, rank, world):
-    """Workloads whose vocabulary is split over the GPUs (C5): the batch is the same whatever N is, every
-    rank holds rows x (vocab / N) logits, scans them, and one NCCL all-gather of the per-row records lets
-    every rank finish the draw.  Strong scaling: the rows are fixed, the columns per GPU shrink with N."""
+def sharded_setup(w, device, rank, world, n_batches_for, fixture_rows=48):
+    """This rank's column shards of `w` (rotating batches), the shared histories, and a ShardedSampler.
+    The first `fixture_rows` rows of batch 0 are the reference fixture's rows (built by the CPU
+    checker's generator), so that a step over batch 0 can be compared with tests/golden."""
     import torch
-    import torch.distributed as dist
     import pulsatrix_b200 as psx
-    from pulsatrix_b200.sharded import sample_rows_sharded, shard_bounds
+    from pulsatrix_b200.sharded import ShardedSampler, shard_bounds
+    import workload_rows
 
-    w = WORKLOADS[args.workload]
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world == 1:  # the all-gather of one rank still goes through torch.distributed
-        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29591", rank=0, world_size=1,
-                                device_id=device)
-    ctx = psx.Context(local)
+    ctx = psx.Context(device.index)
     ctx.inputs_are_ready(True)
     cfg = workload_config(w)
     begin_col, cols = shard_bounds(w.vocab, world, rank)
     shard_bytes = 4 * w.rows * cols
-    n_batches = max(2, (2 * L2_BYTES) // shard_bytes + 2)
+    n_batches = n_batches_for(shard_bytes)
     gen = torch.Generator(device=device)
     gen.manual_seed(4321 + rank)
     shards = []
@@ -452,14 +499,39 @@ def run_sharded(args, rank, world):
     same = torch.Generator(device=device)
     same.manual_seed(99)  # every rank holds the same histories
     hist = torch.randint(0, w.vocab, (w.rows * w.history,), generator=same, device=device, dtype=torch.int64)
+    fixture_rows = min(fixture_rows, w.rows)
+    f_logits, f_hist, _, _ = workload_rows.build(w.name, np.arange(fixture_rows))
+    shards[0][:fixture_rows] = torch.from_numpy(np.ascontiguousarray(f_logits[:, begin_col: begin_col + cols])).to(device)
+    hist[: fixture_rows * w.history] = torch.from_numpy(f_hist.reshape(-1).astype(np.int64)).to(device)
     offsets = torch.arange(w.rows + 1, device=device, dtype=torch.int64) * w.history
     uniforms = torch.from_numpy(psx.uniforms_mt19937_64(np.arange(w.rows, dtype=np.uint64))).to(device)
-    out = ctx.alloc_outputs(w.rows)
-    record = ctx.shard_record_bytes(cfg)
-    mine = torch.empty(w.rows * record, dtype=torch.uint8, device=device)
-    stream = torch.cuda.current_stream(device)
+    sampler = ShardedSampler(ctx, w.rows, w.vocab, cfg, device)
+    return ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, fixture_rows
 
-    def barrier():
+
+def fixture_rows_matched(w, sampler, fixture_rows):
+    """Rows of the last step (over batch 0) whose token equals the reference fixture's, on this rank."""
+    gold = np.load(ROOT / "tests" / "golden" / f"workload_{w.name}.npz")
+    got = sampler.flat()
+    tokens = got["tokens"][:fixture_rows].cpu().numpy()
+    status = got["status"][:fixture_rows].cpu().numpy()
+    return int(((tokens == gold["token"][:fixture_rows]) & (status == 0)).sum())
+
+
+def sharded_record(args, rank, world, local):
+    """Workload C5 with its vocabulary split over the ranks of this run: shard scan, one NCCL
+    all-gather of the per-row records, the rows shared out for the draw, one small all-gather of
+    the results.  A few timed steps and a check of the first 48 rows against the reference fixture."""
+    import torch
+    import torch.distributed as dist
+
+    w = WORKLOADS["c5"]
+    device = torch.device("cuda", local)
+    stream = torch.cuda.current_stream(device)
+    ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, n_fix = sharded_setup(
+        w, device, rank, world, lambda nbytes: max(2, (2 * L2_BYTES) // nbytes + 2))
+
+    def sync_all():
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
@@ -467,6 +539,62 @@ def run_sharded(args, rank, world):
     def timed(fn, steps, warmup):
         for i in range(warmup):
             fn(i)
+        sync_all()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        for i in range(steps):
+            fn(i)
+        end.record(stream)
+        sync_all()
+        return begin.elapsed_time(end) / steps
+
+    steps = max(3, min(args.steps, 50))
+    sampler.step(shards[0], hist, offsets, uniforms)
+    sync_all()
+    matched = fixture_rows_matched(w, sampler, n_fix)
+    failed = int((sampler.flat()["status"].cpu().numpy() != 0).sum())
+    step_ms = timed(lambda i: sampler.step(shards[i % len(shards)], hist, offsets, uniforms), steps, 3)
+    scan_ms = timed(lambda i: ctx.shard_scan(shards[i % len(shards)], begin_col, w.vocab, hist, offsets, cfg, sampler.mine), steps, 3)
+    stats = torch.tensor([step_ms, scan_ms, -float(matched), float(failed)], dtype=torch.float64, device=device)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    step_ms, scan_ms, neg_matched, failed = stats.tolist()
+    peak, _ = measured_hbm_peak()
+    records_bytes, results_bytes = sampler.allgather_bytes
+    return {"workload": f"c5: batch={w.rows} rows, vocab={w.vocab} in {world} column shard(s), history={w.history}, "
+                        f"top_k={w.top_k}, top_p={w.top_p}",
+            "step_us": step_ms * 1e3, "rows_per_s": w.rows / (step_ms * 1e-3), "steps": steps,
+            "shard_scan_us": scan_ms * 1e3, "scan_frac": shard_bytes / (scan_ms * 1e-3) / 1e9 / peak,
+            "allgather_bytes": records_bytes, "results_allgather_bytes": results_bytes,
+            "fixture_rows": n_fix, "fixture_rows_matched": int(-neg_matched), "failed_rows": int(failed),
+            "note": "max over ranks of the times; fixture_rows_matched is the fewest over the ranks"}
+
+
+def run_sharded(args, rank, world):
+    """Workloads whose vocabulary is split over the GPUs (C5): the batch is the same whatever N is, every
+    rank holds rows x (vocab / N) logits, scans them, one NCCL all-gather of the per-row records brings
+    the candidates together, the ranks share the rows out for the draw and a second, small all-gather
+    spreads the results.  Strong scaling: the rows are fixed, the columns per GPU shrink with N."""
+    import torch
+    import torch.distributed as dist
+
+    w = WORKLOADS[args.workload]
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world == 1:  # the all-gathers of one rank still go through torch.distributed
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29591", rank=0, world_size=1,
+                                device_id=device)
+    ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, n_fix = sharded_setup(
+        w, device, rank, world, lambda nbytes: max(2, (2 * L2_BYTES) // nbytes + 2))
+    n_batches = len(shards)
+    stream = torch.cuda.current_stream(device)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def region(fn, steps):
         barrier()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record(stream)
@@ -476,33 +604,45 @@ def run_sharded(args, rank, world):
         barrier()
         return begin.elapsed_time(end)
 
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        first = torch.tensor([region(fn, steps)], dtype=torch.float64, device=device)
+        dist.all_reduce(first, op=dist.ReduceOp.MAX)
+        repeats = int(min(MAX_REPEATS, max(3, np.ceil(MIN_TIMED_MS / max(float(first.item()), 1e-3)))))
+        times = torch.tensor([region(fn, steps) for _ in range(repeats)], dtype=torch.float64, device=device)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        return (times / steps).tolist()
+
     def full_step(i):
-        sample_rows_sharded(ctx, shards[i % n_batches], w.vocab, hist, offsets, cfg, uniforms, out=out)
+        sampler.step(shards[i % n_batches], hist, offsets, uniforms)
 
     def scan_only(i):
-        ctx.shard_scan(shards[i % n_batches], begin_col, w.vocab, hist, offsets, cfg, mine)
+        ctx.shard_scan(shards[i % n_batches], begin_col, w.vocab, hist, offsets, cfg, sampler.mine)
 
     warm = max(args.warmup, 3)
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
+    sampler.step(shards[0], hist, offsets, uniforms)
+    barrier()
+    matched = fixture_rows_matched(w, sampler, n_fix)
+    failed = int((sampler.flat()["status"].cpu().numpy() != 0).sum())
+    clock_sampler = ClockSampler(local) if rank == 0 else None
+    if clock_sampler:
+        clock_sampler.start()
     launches0 = ctx.launches
-    elapsed_ms = timed(full_step, args.steps, warm)
-    launches = (ctx.launches - launches0) * args.steps // (args.steps + warm)
-    failed = int((out["status"].cpu().numpy() != 0).sum())
-    tokens = out["tokens"].clone()
+    step_ms = timed(full_step, args.steps, warm)
+    launches = (ctx.launches - launches0) * args.steps // (warm + (len(step_ms) + 1) * args.steps)
     scan_ms = timed(scan_only, args.steps, 3)
-    clocks = sampler.stop() if sampler else None
+    clocks = clock_sampler.stop() if clock_sampler else None
 
     # ---- e2e: this rank's shard comes from pinned host memory every step, the tokens go back ----
     h_shard = shards[0].cpu().pin_memory()
-    h_tokens = torch.empty(w.rows, dtype=torch.int64).pin_memory()
+    h_tokens = torch.empty((sampler.world, sampler.per), dtype=torch.int64).pin_memory()
     staged = torch.empty_like(shards[0])
     e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step(i):
         staged.copy_(h_shard, non_blocking=True)
-        o = sample_rows_sharded(ctx, staged, w.vocab, hist, offsets, cfg, uniforms, out=out)
+        o = sampler.step(staged, hist, offsets, uniforms)
         h_tokens.copy_(o["tokens"], non_blocking=True)
         stream.synchronize()
 
@@ -516,27 +656,26 @@ def run_sharded(args, rank, world):
     barrier()
     e2e_s = time.perf_counter() - t0
 
-    lo, hi = tokens.clone(), tokens.clone()
-    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-    same_everywhere = bool((lo == hi).all().item())
-    times = torch.tensor([elapsed_ms, e2e_s * 1e3, scan_ms / args.steps], dtype=torch.float64, device=device)
-    dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, scan_avg_ms = times.tolist()
+    stats = torch.tensor([e2e_s * 1e3, -float(matched), float(failed)], dtype=torch.float64, device=device)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    e2e_ms, neg_matched, failed = stats.tolist()
     if rank != 0:
         return
     peak, peak_kind = measured_hbm_peak()
-    achieved = shard_bytes / (scan_avg_ms * 1e-3) / 1e9
+    step, scan = spread(step_ms), spread(scan_ms)
+    achieved = shard_bytes / (scan["median"] * 1e-3) / 1e9
+    records_bytes, results_bytes = sampler.allgather_bytes
     result = {
         "metric": "sampled rows/sec and logits-read HBM GB/s vs B200 peak",
-        "value": w.rows * args.steps / (elapsed_ms * 1e-3), "unit": "rows/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warm, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "value": w.rows / (step["median"] * 1e-3), "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": step["median"], "p10_ms_per_step": step["p10"], "p90_ms_per_step": step["p90"],
+        "repeats": step["repeats"], "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 logits; f64 survivor stage", "data": "synthetic",
         "config": {"workload": f"{w.name}: batch={w.rows} rows, vocab={w.vocab} in {world} column shard(s), "
                                f"history={w.history}, penalty={w.repetition_penalty}, T={w.temperature}, "
                                f"top_k={w.top_k}, top_p={w.top_p}",
-                   "parallelism": f"vocabulary split over {world} GPU(s); one NCCL all-gather of "
-                                  f"{w.rows * record} bytes per rank per step",
+                   "parallelism": f"vocabulary split over {world} GPU(s); per step one NCCL all-gather of "
+                                  f"{records_bytes} bytes per rank (records) and one of {results_bytes} (results)",
                    "contexts_in_flight": 1,
                    "l2": f"shards rotate over {n_batches} batches = {n_batches * shard_bytes / 2**20:.0f} MiB > L2"},
         "e2e": {"value": w.rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": shard_bytes,
@@ -545,12 +684,12 @@ def run_sharded(args, rank, world):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "scan_rows_kernel (+ pack_records_kernel)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": int(round(shard_bytes * ROW_PASS_TRAFFIC_RATIO)),
-                     "traffic_note": "bytes per launch; ncu dram read+write of one C2 launch, scaled by this shard's bytes",
-                     "algorithmic_bytes": shard_bytes, "launch_ms": scan_avg_ms},
-        "failed_rows": failed, "every_rank_drew_the_same_tokens": same_everywhere,
+                     "traffic": None, "traffic_note": "not captured for this workload",
+                     "algorithmic_bytes": shard_bytes, "launch_ms": scan["median"]},
+        "failed_rows": int(failed), "fixture_rows": n_fix, "fixture_rows_matched": int(-neg_matched),
     }
     emit(result)
+
 
 def run_reference(args, rank, world):
     if rank != 0:
@@ -579,8 +718,8 @@ def run_reference(args, rank, world):
         "unit": "rows/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 1),
         "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 logits; f64 softmax", "data": "synthetic",
-        "config": {"workload": f"{w.name}: vocab={w.vocab}, history={w.history}, top_k={w.top_k}, top_p={w.top_p}",
-                   "parallelism": "host threads, one row each"},
+        "config": {"workload": workload_text(w), "parallelism": "host threads, one row each",
+                   "sample": text},
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": kind, "sample": text},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     })

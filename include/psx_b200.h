@@ -47,8 +47,8 @@ typedef enum psx_row_status {
     PSX_ROW_ALL_REMOVED = 5, /* "Generate: every token was removed" (src/generation.cpp:136-138) */
     PSX_ROW_TOO_WIDE = 16,   /* more tokens survive the filters (or tie at a cut) than the device
                                 path holds; nothing was drawn for this row */
-    PSX_ROW_DEVICE_TIMEOUT = 32 /* a bounded device-side wait (the bulk copy of the row into shared
-                                memory) ran out; nothing was drawn for this row */
+    PSX_ROW_DEVICE_TIMEOUT = 32 /* a bounded device-side wait (a bulk copy of a piece of the row into
+                                shared memory) ran out; nothing was drawn for this row */
 } psx_row_status;
 
 /* GenerationConfig (include/pulsatrix/generation.hpp:29-52) without the loop fields, plus the
@@ -111,6 +111,17 @@ PSX_API psx_status psx_b200_ctx_read_timing(psx_ctx* ctx, double* row_pass_ms, d
  * Without the promise it waits for the kernel before it first.  No counterpart in the reference. */
 PSX_API psx_status psx_b200_ctx_inputs_are_ready(psx_ctx* ctx, int ready);
 
+/* How long a kernel of this context waits for one of its own asynchronous copies (a chunk of a row
+ * on its way into shared memory) before it gives up: default one second.  A row whose wait ran out
+ * reports PSX_ROW_DEVICE_TIMEOUT, nothing is drawn for it, and the context stays usable.  No
+ * counterpart in the reference. */
+PSX_API psx_status psx_b200_ctx_set_wait_limit(psx_ctx* ctx, uint64_t nanoseconds);
+/* Test hook, never set it in production: while enabled, the row pass announces 16 bytes more per
+ * copy than the copy delivers, so that its wait for the copy runs out (with no copy in flight)
+ * and every row reports PSX_ROW_DEVICE_TIMEOUT.  It exists so that the give-up path of the bounded
+ * wait can be tested without a fault.  No counterpart in the reference. */
+PSX_API psx_status psx_b200_test_short_copy(psx_ctx* ctx, int enable);
+
 /* Batched sampling step on device-resident logits: for every row, what one iteration of
  * Generate()'s loop computes (src/generation.cpp:124-156) -- finite check, raw log-softmax,
  * ProcessLogits (src/generation.cpp:55-112: repetition penalty, EOS ban, temperature, top-k,
@@ -155,8 +166,11 @@ PSX_API psx_status psx_b200_read_only_pass(void* stream, const void* data, size_
  * device-wide synchronisation.  It takes no context and calls no cudaMalloc / cudaFree: the
  * scratch between its two kernels is a fixed array inside the library image on every GPU (about
  * 8.1 MiB).  Limits: rows * ceil(vocab / 16384) <= 1024 and at most 256 banned EOS ids, else
- * PSX_ERR_UNSUPPORTED.  The first call on a device looks up that array's address and should come
- * before any stream capture on that device.  All calls share the array: calls that overlap on
+ * PSX_ERR_UNSUPPORTED.  The
+ * first call on a device looks up that array's address and sets the kernels up: make it at
+ * start-up, before any stream capture on that device and before the host process's own pool
+ * takes the rest of the GPU's memory (the array and the kernels' code are placed on the device
+ * when the first call loads them).  All calls share the array: calls that overlap on
  * the GPU race, so keep them stream-ordered per device.  Same inputs, outputs and statuses as
  * psx_b200_sample_rows (no diagnostics).  This entry point has no counterpart in the reference. */
 PSX_API psx_status psx_b200_sample_rows_static(void* stream, const float* logits, int64_t rows, int64_t vocab,
@@ -209,6 +223,15 @@ PSX_API psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream, const void* 
                                 int64_t rows, int64_t vocab, const psx_sampling_config* config,
                                 const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
                                 psx_row_diag* diag);
+
+/* Part 2 for a subset of the rows: merges rows row_begin .. row_begin + row_count - 1 only, so that
+ * the ranks can share the rows out among themselves and exchange the 16 bytes per row of results
+ * afterwards.  `gathered` and `uniforms` are indexed by the absolute row as above; the outputs hold
+ * the merged rows only, row_begin's at index 0.  No counterpart in the reference. */
+PSX_API psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream, const void* gathered, int32_t num_shards,
+                                     int64_t rows, int64_t row_begin, int64_t row_count, int64_t vocab,
+                                     const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
+                                     float* log_probs, int32_t* row_status, psx_row_diag* diag);
 
 /* Replaces DeviceBackend::top_k_rows (include/pulsatrix/device_backend.hpp:828-837; CUDA
  * implementation src/cuda_backend.cu:851-860, kernel src/gpu_kernels.cuh:1256-1262): per row of

@@ -9,13 +9,15 @@ from pathlib import Path
 import numpy as np
 
 PACKAGE = Path(__file__).resolve().parent
-ROW_OK, ROW_NON_FINITE, ROW_ALL_REMOVED, ROW_TOO_WIDE = 0, 4, 5, 16
+ROW_OK, ROW_NON_FINITE, ROW_ALL_REMOVED, ROW_TOO_WIDE, ROW_DEVICE_TIMEOUT = 0, 4, 5, 16, 32
 OK, ERR_BAD_ARGUMENT, ERR_CUDA, ERR_ROW_FAILED, ERR_UNSUPPORTED = range(5)
 
 EXPORTS = [
     "psx_b200_version", "psx_b200_last_error", "psx_b200_ctx_create", "psx_b200_ctx_destroy", "psx_b200_ctx_stream",
-    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
-    "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_top_k_rows",
+    "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready",
+    "psx_b200_ctx_set_wait_limit", "psx_b200_test_short_copy", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
+    "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_shard_merge_rows",
+    "psx_b200_top_k_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
 
@@ -69,6 +71,8 @@ _lib = None
 
 
 def library_path() -> Path:
+    if os.environ.get("PSX_B200_LIBRARY"):  # a variant build (see build.py)
+        return Path(os.environ["PSX_B200_LIBRARY"])
     if os.environ.get("PSX_B200_STAGE_CLOCKS") == "1":  # the profiling build (see build.py)
         return PACKAGE / "libpsx_b200_clocks.so"
     return PACKAGE / "libpsx_b200.so"
@@ -95,6 +99,8 @@ def library():
         lib.psx_b200_sync.argtypes = [C.c_void_p, C.c_void_p]
         lib.psx_b200_ctx_enable_timing.argtypes = [C.c_void_p, C.c_int]
         lib.psx_b200_ctx_inputs_are_ready.argtypes = [C.c_void_p, C.c_int]
+        lib.psx_b200_ctx_set_wait_limit.argtypes = [C.c_void_p, C.c_uint64]
+        lib.psx_b200_test_short_copy.argtypes = [C.c_void_p, C.c_int]
         lib.psx_b200_ctx_read_timing.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         ptr, i64 = C.c_void_p, C.c_int64
         lib.psx_b200_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
@@ -106,6 +112,7 @@ def library():
         lib.psx_b200_sample_rows_host.argtypes = [ptr, ptr, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_scan.argtypes = [ptr, ptr, ptr, i64, i64, i64, i64, i64, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_merge.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_shard_merge_rows.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_top_k_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int]
         lib.psx_uniforms_mt19937_64.argtypes = [ptr, i64, ptr]
         lib.psx_uniforms_portable.argtypes = [ptr, i64, ptr]
@@ -194,6 +201,14 @@ class Context:
         """Promise that the inputs of the calls that follow are complete before each call is made
         (see psx_b200_ctx_inputs_are_ready): the row pass then overlaps the kernel before it."""
         _check(self._lib.psx_b200_ctx_inputs_are_ready(self._ctx, int(ready)))
+
+    def set_wait_limit(self, nanoseconds):
+        """How long a kernel waits for one of its own copies before the row reports ROW_DEVICE_TIMEOUT."""
+        _check(self._lib.psx_b200_ctx_set_wait_limit(self._ctx, int(nanoseconds)))
+
+    def test_short_copy(self, on=True):
+        """Test hook (psx_b200_test_short_copy): the row pass's waits for its chunks run out."""
+        _check(self._lib.psx_b200_test_short_copy(self._ctx, int(on)))
 
     def enable_timing(self, on=True):
         _check(self._lib.psx_b200_ctx_enable_timing(self._ctx, int(on)))
@@ -361,12 +376,17 @@ class Context:
                                              shard_logits.stride(0), shard_begin, vocab, _dptr(history_ids),
                                              _dptr(history_offsets), C.addressof(config), _dptr(records)))
 
-    def shard_merge(self, gathered, num_shards, rows, vocab, config, uniforms, out=None, stream=None):
+    def shard_merge(self, gathered, num_shards, rows, vocab, config, uniforms, out=None, stream=None, row_begin=0,
+                    row_count=None):
+        """Merges rows row_begin .. row_begin + row_count - 1 (all of them by default); `out` holds
+        the merged rows only, the first of them at index 0."""
         import torch
-        out = out or self.alloc_outputs(rows)
+        row_count = rows - row_begin if row_count is None else row_count
+        out = out or self.alloc_outputs(row_count)
         if stream is None:
             stream = torch.cuda.current_stream(gathered.device).cuda_stream
-        _check(self._lib.psx_b200_shard_merge(self._ctx, C.c_void_p(stream), _dptr(gathered), num_shards, rows, vocab,
-                                              C.addressof(config), _dptr(uniforms), _dptr(out["tokens"]),
-                                              _dptr(out["log_probs"]), _dptr(out["status"]), _dptr(out["diag"])))
+        _check(self._lib.psx_b200_shard_merge_rows(self._ctx, C.c_void_p(stream), _dptr(gathered), num_shards, rows,
+                                                   row_begin, row_count, vocab, C.addressof(config), _dptr(uniforms),
+                                                   _dptr(out["tokens"]), _dptr(out["log_probs"]), _dptr(out["status"]),
+                                                   _dptr(out.get("diag"))))
         return out

@@ -38,18 +38,24 @@ def _stale() -> bool:
     return any(p.stat().st_mtime > built for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, defines=(), output: Path | None = None) -> Path:
+    """defines / output: a variant library for experiments (e.g. defines=["PSX_STREAM_RING=4"]), written to
+    `output` and loaded by pointing PSX_B200_LIBRARY at it; the default library is not touched."""
     profiling = _profiling()
     library = PACKAGE / "libpsx_b200_clocks.so" if profiling else LIBRARY
-    if not force and not profiling and not _stale():
+    variant = output is not None
+    if variant:
+        library = Path(output)
+    if not force and not profiling and not variant and not _stale():
         return LIBRARY
     objects = []
-    build_dir = PACKAGE / ("build_clocks" if profiling else "build")
+    build_dir = PACKAGE / ("build_clocks" if profiling else "build_" + library.stem if variant else "build")
     build_dir.mkdir(exist_ok=True)
     procs = []
     for src in SOURCES:
         obj = build_dir / (src + ".o")
-        cmd = ["nvcc", *NVCC_FLAGS, *(["-DPSX_STAGE_CLOCKS"] if profiling else []), *(["-Xptxas", "-v"] if verbose else []),
+        cmd = ["nvcc", *NVCC_FLAGS, *(["-DPSX_STAGE_CLOCKS"] if profiling else []), *[f"-D{d}" for d in defines],
+               *(["-Xptxas", "-v"] if verbose else []),
                "-c", str(CSRC / src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objects.append(str(obj))
@@ -67,7 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
     subprocess.run(["nvcc", "-arch=sm_100a", "-shared", "-o", str(library), *objects, "-lcudart"], check=True)
-    if not profiling:
+    if not profiling and not variant:
         build_cpp_test()
     return library
 
@@ -83,4 +89,6 @@ def build_cpp_test() -> Path:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    extra = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
+    out = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--output=")]
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, defines=extra, output=Path(out[0]) if out else None))

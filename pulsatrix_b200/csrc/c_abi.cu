@@ -13,6 +13,7 @@
 
 #include "merge_rows.cuh"
 #include "process_rows.cuh"
+#include "sample_plan.cuh"
 #include "scan_rows.cuh"
 #include "shard_records.cuh"
 #include "topk_rows.cuh"
@@ -55,7 +56,6 @@ struct psx_ctx {
     uint64_t launches = 0;
     bool merge_configured = false;
     bool scan_configured = false;
-    int nucleus_k = 160;  // logits every part hands on when no top-k bounds the survivors
     // row-pass scratch
     Buffer stats, part_counts, candidates, banned;
     // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
@@ -68,6 +68,8 @@ struct psx_ctx {
     bool timing = false;
     std::vector<cudaEvent_t> timing_events;
     bool inputs_ready = false;  // psx_b200_ctx_inputs_are_ready
+    uint64_t wait_limit_ns = psx::kDefaultWaitLimitNs;  // psx_b200_ctx_set_wait_limit
+    bool test_short_copy = false;                       // psx_b200_test_short_copy
 };
 
 namespace {
@@ -108,56 +110,7 @@ psx_status check_config(const psx_sampling_config* c) {
     return PSX_OK;
 }
 
-struct Plan {
-    int parts = 1;
-    int vecs_per_part = 1;
-    int k_need = 1;
-    bool nucleus = false;  // sampling without a top-k: the processed tail mass is needed too
-    bool apply_temperature = false;
-    int sort_capacity = 1024;
-    int gather_capacity = 4096;
-    int slot_shift = 0;    // the survivor stage fetches 2^slot_shift slots of every part's list at once
-};
-
-Plan make_plan(const psx_ctx* ctx, const float* logits, int64_t cols, int64_t row_stride, int64_t vocab,
-               const psx_sampling_config* c) {
-    Plan plan;
-    const bool aligned = (reinterpret_cast<uintptr_t>(logits) % 16 == 0) && (row_stride % 4 == 0);
-    const int64_t vectors = (cols + 3 + (aligned ? 0 : 3)) / 4;  // most float4 a row can span
-    static const int part_vecs = [] {  // tuning knob, read once: vectors per CTA, 256..4096
-        const char* env = std::getenv("PSX_B200_PART_VECS");
-        return env ? std::max(256, std::min(psx::kPartVecs, std::atoi(env))) : psx::kPartVecs;
-    }();
-    plan.parts = (int)((vectors + part_vecs - 1) / part_vecs);
-    plan.vecs_per_part = (int)((vectors + plan.parts - 1) / plan.parts);
-    const bool sample = c->do_sample != 0;
-    const bool top_k_on = sample && c->top_k > 0 && c->top_k < vocab;
-    plan.apply_temperature = sample && c->temperature != 1.0f;  // src/generation.cpp:77
-    plan.nucleus = sample && !top_k_on;
-    if (!sample) plan.k_need = 1;
-    else if (top_k_on) plan.k_need = (int)std::min<int64_t>(c->top_k, 1 << 20);
-    else plan.k_need = ctx->nucleus_k;
-    // A row of at most 256 vectors fits a part's candidate list whole (1024 logits): hand
-    // everything on, and every filter is exact whatever the settings.
-    if (vectors * 4 <= psx::kPartCap) plan.k_need = 1 << 30;
-    plan.sort_capacity = plan.nucleus ? 4096 : 1024;
-    plan.gather_capacity = plan.nucleus ? 8192 : 4096;
-    if (!plan.nucleus && plan.k_need < psx::kPartCap) {
-        // A large k over many parts: a part whose threshold is a warp's 25th of 32 thread maxima hands
-        // on about twice k, and the row's candidates no longer fit 4096 slots.
-        const int64_t estimate = (int64_t)plan.parts * (2 * plan.k_need + 32) + 256;
-        if (estimate > 3500) {
-            plan.sort_capacity = 2048;
-            plan.gather_capacity = estimate > 5600 ? 8192 : 6144;
-        }
-    }
-    // A part usually hands on a little over k_need logits, plus the few its share of the history flags.
-    const int expected = plan.k_need >= psx::kPartCap ? psx::kPartCap
-                         : plan.k_need > 64         ? 2 * plan.k_need + 24
-                                                    : plan.k_need + plan.k_need / 4 + 24;
-    plan.slot_shift = psx::merge_slot_shift(plan.parts, psx::kPartCap, expected);
-    return plan;
-}
+using psx::Plan;
 
 // The survivor stage holds one row's candidates in shared memory.
 psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int parts) {
@@ -174,27 +127,14 @@ psx_status configure_merge(psx_ctx* ctx, const Plan& plan, int parts) {
 // Fills the part of ScanParams that depends on the settings; uploads the banned ids.
 psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_config* c, const Plan& plan,
                         psx::ScanParams& sp) {
-    if (!ctx->scan_configured) {  // a part is more shared memory than a kernel gets without asking
+    if (!ctx->scan_configured) {  // a part's ring is more shared memory than a kernel gets without asking
         PSX_CUDA(psx::configure_scan_rows());
         ctx->scan_configured = true;
     }
-    sp.apply_penalty = c->repetition_penalty != 1.0f ? 1 : 0;  // src/generation.cpp:59
-    sp.penalty = c->repetition_penalty;
-    sp.apply_temperature = plan.apply_temperature ? 1 : 0;
-    sp.temperature = c->temperature;
-    const double log2e = 1.4426950408889634073599246810019;
-    sp.log2e_over_t = (float)(plan.apply_temperature ? log2e / (double)c->temperature : log2e);
-    sp.k_need = plan.k_need;
-    sp.parts = plan.parts;
-    sp.vecs_per_part = plan.vecs_per_part;
-    static const int debug_skip = [] {  // profiling only, read once
-        const char* skip = std::getenv("PSX_B200_DEBUG_SKIP");
-        return skip ? std::atoi(skip) : 0;
-    }();
-    sp.debug_skip = debug_skip;
+    psx::fill_scan_settings(sp, c, plan);
     sp.inputs_ready = ctx->inputs_ready ? 1 : 0;
-    sp.num_banned = 0;
-    sp.banned_ids = nullptr;
+    sp.wait_limit_ns = ctx->wait_limit_ns;
+    sp.test_short_copy = ctx->test_short_copy ? 1 : 0;
     if (c->num_new_tokens < c->min_new_tokens && c->num_eos_token_ids > 0) {  // src/generation.cpp:69
         if (c->num_eos_token_ids > (1 << 20)) return fail(PSX_ERR_UNSUPPORTED, "psx_b200: too many eos ids");
         const size_t bytes = (size_t)c->num_eos_token_ids * sizeof(int64_t);
@@ -217,30 +157,14 @@ psx_status reserve_scan_scratch(psx_ctx* ctx, int64_t rows, const Plan& plan, ps
     return PSX_OK;
 }
 
-void fill_merge_settings(psx::MergeParams& mp, const psx_sampling_config* c, const Plan& plan, int64_t rows,
-                         int64_t vocab, const double* uniforms, int64_t* tokens, float* log_probs,
-                         int32_t* row_status, psx_row_diag* diag) {
-    mp.rows = rows;
-    mp.vocab = vocab;
-    mp.do_sample = c->do_sample != 0;
-    mp.apply_temperature = plan.apply_temperature ? 1 : 0;
-    mp.temperature = c->temperature;
-    mp.penalty = c->repetition_penalty;
-    mp.top_k = c->top_k;
-    mp.top_p = c->top_p;
-    mp.min_p = c->min_p;
-    mp.uniforms = uniforms;
-    mp.tokens = tokens;
-    mp.log_probs = log_probs;
-    mp.row_status = row_status;
-    mp.diag = diag;
-    mp.sort_capacity = plan.sort_capacity;
-    static const int debug_stop = [] {  // profiling only, read once
-        const char* stop = std::getenv("PSX_B200_DEBUG_MERGE_STOP");
-        return stop ? std::atoi(stop) : 0;
-    }();
-    mp.debug_stop = debug_stop;
-    mp.gather_capacity = plan.gather_capacity;
+// What a failed row means, in the reference's words where it has them (src/generation.cpp:130,137).
+const char* row_failure_text(int32_t status) {
+    switch (status) {
+        case PSX_ROW_NON_FINITE: return "Generate: the model returned a non-finite logit";
+        case PSX_ROW_ALL_REMOVED: return "Generate: every token was removed";
+        case PSX_ROW_DEVICE_TIMEOUT: return "psx_b200: a device-side wait for a copy of the row ran out";
+        default: return "psx_b200: too many tokens survive the filters for the device path";
+    }
 }
 
 psx_status check_common(psx_ctx* ctx, const psx_sampling_config* config, int64_t rows, int64_t cols,
@@ -326,7 +250,7 @@ psx_status plan_row_pass(psx_ctx* ctx, cudaStream_t stream, const float* logits,
                          int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
                          const psx_sampling_config* config, Plan& plan, psx::ScanParams& sp) {
     PSX_CUDA(cudaSetDevice(ctx->device));
-    plan = make_plan(ctx, logits, vocab, row_stride, vocab, config);
+    plan = psx::make_plan(logits, vocab, row_stride, vocab, config);
     sp = psx::ScanParams{};
     sp.logits = logits;
     sp.row_stride = row_stride;
@@ -383,25 +307,7 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     if (psx_status s = configure_merge(ctx, plan, plan.parts)) return s;
 
     psx::MergeParams mp{};
-    mp.stats = sp.stats;
-    mp.part_counts = sp.part_counts;
-    mp.candidates = sp.candidates;
-    mp.parts = plan.parts;
-    mp.part_cap = psx::kPartCap;
-    mp.slot_shift = plan.slot_shift;
-    mp.stats_part_stride = sizeof(psx::PartStats);
-    mp.stats_row_stride = mp.stats_part_stride * plan.parts;
-    mp.count_part_stride = sizeof(uint32_t);
-    mp.count_row_stride = mp.count_part_stride * plan.parts;
-    mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
-    mp.cand_row_stride = mp.cand_part_stride * plan.parts;
-    fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
-    if (plan.nucleus) {  // the wide plan: candidates and sort arrays share their shared memory
-        mp.logits = logits;
-        mp.logits_row_stride = row_stride;
-        mp.logits_col_begin = 0;
-        mp.overlay = 1;
-    }
+    psx::fill_merge_params(mp, sp, plan, config, rows, vocab, uniforms, tokens, log_probs, row_status, diag, logits, row_stride);
 
     cudaEvent_t marks[3] = {nullptr, nullptr, nullptr};
     if (ctx->timing) {
@@ -467,27 +373,9 @@ psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream_ptr, float* logits
         PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
         ++ctx->launches;
         psx::MergeParams mp{};
-        mp.stats = sp.stats;
-        mp.part_counts = sp.part_counts;
-        mp.candidates = sp.candidates;
-        mp.parts = plan.parts;
-        mp.part_cap = psx::kPartCap;
-        mp.slot_shift = plan.slot_shift;
-        mp.stats_part_stride = sizeof(psx::PartStats);
-        mp.stats_row_stride = mp.stats_part_stride * plan.parts;
-        mp.count_part_stride = sizeof(uint32_t);
-        mp.count_row_stride = mp.count_part_stride * plan.parts;
-        mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
-        mp.cand_row_stride = mp.cand_part_stride * plan.parts;
-        fill_merge_settings(mp, config, plan, rows, vocab, /*uniforms=*/nullptr,
-                            static_cast<int64_t*>(ctx->pl_tokens.ptr), static_cast<float*>(ctx->pl_log_probs.ptr), status,
-                            nullptr);
-        if (plan.nucleus) {
-            mp.logits = logits;
-            mp.logits_row_stride = row_stride;
-            mp.logits_col_begin = 0;
-            mp.overlay = 1;
-        }
+        psx::fill_merge_params(mp, sp, plan, config, rows, vocab, /*uniforms=*/nullptr,
+                               static_cast<int64_t*>(ctx->pl_tokens.ptr), static_cast<float*>(ctx->pl_log_probs.ptr), status,
+                               nullptr, logits, row_stride);
         mp.survivor_cols = static_cast<uint32_t*>(ctx->surv_cols.ptr);
         mp.survivor_vals = static_cast<float*>(ctx->surv_vals.ptr);
         mp.survivor_counts = static_cast<uint32_t*>(ctx->surv_counts.ptr);
@@ -551,11 +439,7 @@ psx_status psx_b200_process_logits_host(psx_ctx* ctx, float* logits, int64_t row
     PSX_CUDA(cudaStreamSynchronize(stream));
     for (int64_t r = 0; r < rows; ++r) {
         if (out_status[r] != PSX_ROW_OK && out_status[r] != PSX_ROW_ALL_REMOVED) {
-            return fail(PSX_ERR_ROW_FAILED,
-                        std::string(out_status[r] == PSX_ROW_NON_FINITE
-                                        ? "psx_b200: a logit is not finite"
-                                        : "psx_b200: too many tokens survive the filters for the device path") +
-                            " (row " + std::to_string(r) + ")");
+            return fail(PSX_ERR_ROW_FAILED, std::string(row_failure_text(out_status[r])) + " (row " + std::to_string(r) + ")");
         }
     }
     return PSX_OK;
@@ -570,6 +454,19 @@ psx_status psx_b200_ctx_enable_timing(psx_ctx* ctx, int enable) {
 psx_status psx_b200_ctx_inputs_are_ready(psx_ctx* ctx, int ready) {
     if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
     ctx->inputs_ready = ready != 0;
+    return PSX_OK;
+}
+
+psx_status psx_b200_ctx_set_wait_limit(psx_ctx* ctx, uint64_t nanoseconds) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (nanoseconds == 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the wait limit must be positive");
+    ctx->wait_limit_ns = nanoseconds;
+    return PSX_OK;
+}
+
+psx_status psx_b200_test_short_copy(psx_ctx* ctx, int enable) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    ctx->test_short_copy = enable != 0;
     return PSX_OK;
 }
 
@@ -669,10 +566,7 @@ psx_status psx_b200_sample_rows_host(psx_ctx* ctx, const float* logits, int64_t 
     PSX_CUDA(cudaStreamSynchronize(stream));
     for (int64_t r = 0; r < rows; ++r) {
         if (row_status[r] != PSX_ROW_OK) {
-            const char* what = row_status[r] == PSX_ROW_NON_FINITE    ? "Generate: the model returned a non-finite logit"
-                               : row_status[r] == PSX_ROW_ALL_REMOVED ? "Generate: every token was removed"
-                                                                      : "psx_b200: too many tokens survive the filters "
-                                                                        "for the device path";
+            const char* what = row_failure_text(row_status[r]);
             return fail(PSX_ERR_ROW_FAILED, std::string(what) + " (row " + std::to_string(r) + ")");
         }
     }
@@ -704,7 +598,7 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
 
-    const Plan plan = make_plan(ctx, shard_logits, shard_cols, row_stride, vocab, config);
+    const Plan plan = psx::make_plan(shard_logits, shard_cols, row_stride, vocab, config);
     psx::ScanParams sp{};
     sp.logits = shard_logits;
     sp.row_stride = row_stride;
@@ -737,14 +631,17 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
     return PSX_OK;
 }
 
-psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gathered, int32_t num_shards,
-                                int64_t rows, int64_t vocab, const psx_sampling_config* config,
-                                const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
-                                psx_row_diag* diag) {
+psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream_ptr, const void* gathered, int32_t num_shards,
+                                     int64_t rows, int64_t row_begin, int64_t row_count, int64_t vocab,
+                                     const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
+                                     float* log_probs, int32_t* row_status, psx_row_diag* diag) {
     if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
     if (psx_status s = check_config(config)) return s;
     if (rows < 0 || num_shards < 1 || vocab <= 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: bad sizes");
-    if (rows == 0) return PSX_OK;
+    if (row_begin < 0 || row_count < 0 || row_begin + row_count > rows) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the rows to merge do not lie inside the batch");
+    }
+    if (rows == 0 || row_count == 0) return PSX_OK;
     if (!gathered || !tokens || !log_probs || !row_status) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
     const bool sample = config->do_sample != 0;
     if (sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
@@ -771,10 +668,34 @@ psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gath
     mp.slot_shift = psx::merge_slot_shift(num_shards, capacity, capacity / 2);
     mp.stats_row_stride = mp.count_row_stride = mp.cand_row_stride = record;
     mp.stats_part_stride = mp.count_part_stride = mp.cand_part_stride = record * rows;
-    fill_merge_settings(mp, config, plan, rows, vocab, uniforms, tokens, log_probs, row_status, diag);
+    mp.rows = row_count;
+    mp.row_begin = row_begin;
+    mp.vocab = vocab;
+    mp.do_sample = sample ? 1 : 0;
+    mp.apply_temperature = plan.apply_temperature ? 1 : 0;
+    mp.temperature = config->temperature;
+    mp.penalty = config->repetition_penalty;
+    mp.top_k = config->top_k;
+    mp.top_p = config->top_p;
+    mp.min_p = config->min_p;
+    mp.uniforms = uniforms;  // by absolute row; the outputs hold the merged rows only, the first of them at [0]
+    mp.tokens = tokens - row_begin;
+    mp.log_probs = log_probs - row_begin;
+    mp.row_status = row_status - row_begin;
+    mp.diag = diag ? diag - row_begin : nullptr;
+    mp.sort_capacity = plan.sort_capacity;
+    mp.gather_capacity = plan.gather_capacity;
     PSX_CUDA(psx::launch_merge_rows(mp, stream));
     ++ctx->launches;
     return PSX_OK;
+}
+
+psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gathered, int32_t num_shards,
+                                int64_t rows, int64_t vocab, const psx_sampling_config* config,
+                                const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
+                                psx_row_diag* diag) {
+    return psx_b200_shard_merge_rows(ctx, stream_ptr, gathered, num_shards, rows, 0, rows < 0 ? 0 : rows, vocab, config,
+                                     uniforms, tokens, log_probs, row_status, diag);
 }
 
 psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream_ptr, const float* in, float* values, float* indices,

@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const Merg
     extern __shared__ unsigned long long dyn[];
     grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
     grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
-    survivor::merge_row(p, blockIdx.x, dyn);
+    survivor::merge_row(p, p.row_begin + blockIdx.x, dyn);
 }
 
 }  // namespace

@@ -21,7 +21,8 @@ struct MergeParams {
     int32_t part_cap;            // slots of a part's list
     int32_t slot_shift;          // 2^slot_shift slots of every list are fetched before the counts are known;
                                  // parts << slot_shift <= 16 * kMergeThreads
-    int64_t rows;
+    int64_t rows;                // rows this launch decides: row_begin .. row_begin + rows - 1
+    int64_t row_begin;           // (every array below and above is indexed by the absolute row)
     int64_t vocab;               // global vocabulary size
     // settings (GenerationConfig, already validated)
     int32_t do_sample;
@@ -43,7 +44,6 @@ struct MergeParams {
     float* survivor_vals;        // their processed logits
     uint32_t* survivor_counts;   // rows
     int32_t survivor_cap;
-    int32_t debug_stop;          // profiling only: leave the kernel after this stage (0: run everything)
     int32_t gather_capacity;     // candidates of one row held in shared memory (<= 4 * sort_capacity)
     // Optional: the logits themselves (row r, global column c at logits[r*logits_row_stride + c -
     // logits_col_begin]).  With them the chosen token's raw logit is read back from there, and, when

@@ -700,7 +700,7 @@ __device__ inline uint32_t block_select_kth(KeyAt key_at, int m, uint32_t k, uin
 // What the parts of a row say together, and how many candidates the row has.
 struct Joined {
     float raw_max, y_max, thr;
-    uint32_t bad_bits;  // bit 0..7: a non-finite logit; 8..15: a copy that timed out; 16..: a list that overflowed
+    uint32_t bad_bits;  // bit 0: a non-finite logit; bit 1: a copy that timed out; bit 2: a list that overflowed
     double alive_tail;
     int total;          // candidates of the row (they are in shared memory when it is <= gather_capacity)
 };
@@ -732,13 +732,14 @@ __device__ __forceinline__ Joined join_and_gather(const MergeParams& p, const ch
         }
     }
     float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
-    double bad = 0.0, alive_tail = 0.0;
+    uint32_t bad = 0;  // bit 0: a non-finite logit; bit 1: a copy that timed out; bit 2: a list that overflowed
+    double alive_tail = 0.0;
     for (int i = tid; i < p.parts; i += kMergeThreads) {
         const PartStats s = *reinterpret_cast<const PartStats*>(stats_row + i * p.stats_part_stride);
         raw_max = fmaxf(raw_max, s.raw_max);
         y_max = fmaxf(y_max, s.y_max);
         thr = fmaxf(thr, s.thr);
-        bad += (double)((s.nonfinite & 1u) + (s.nonfinite >> 1) * 256u + s.overflow * 65536u);
+        bad |= (s.nonfinite & 3u) | (s.overflow ? 4u : 0u);
         alive_tail += (double)s.alive_tail;
     }
     uint32_t warp_total = 0, beyond = 0;
@@ -753,23 +754,23 @@ __device__ __forceinline__ Joined join_and_gather(const MergeParams& p, const ch
         raw_max = warp_max(raw_max);
         y_max = warp_max(y_max);
         thr = warp_max(thr);
-        bad = warp_sum(bad);
+        bad = __reduce_or_sync(0xFFFFFFFFu, bad);
         alive_tail = warp_sum(alive_tail);
         if (lane == 0) {
             s_f[0][warp] = raw_max; s_f[1][warp] = y_max; s_f[2][warp] = thr;
-            s_d[0][warp] = bad; s_d[1][warp] = alive_tail;
-            s_u[0][warp] = warp_total; s_u[1][warp] = beyond;
+            s_d[1][warp] = alive_tail;
+            s_u[0][warp] = warp_total; s_u[1][warp] = beyond; s_u[2][warp] = bad;
         }
         __syncthreads();
         raw_max = s_f[0][0]; y_max = s_f[1][0]; thr = s_f[2][0];
-        bad = 0.0; alive_tail = 0.0;
+        bad = 0; alive_tail = 0.0;
         warp_total = 0; beyond = 0;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
             raw_max = fmaxf(raw_max, s_f[0][w]);
             y_max = fmaxf(y_max, s_f[1][w]);
             thr = fmaxf(thr, s_f[2][w]);
-            bad += s_d[0][w];
+            bad |= s_u[2][w];
             alive_tail += s_d[1][w];
             beyond += s_u[1][w];
         }
@@ -783,7 +784,7 @@ __device__ __forceinline__ Joined join_and_gather(const MergeParams& p, const ch
     }
     Joined j;
     j.raw_max = raw_max; j.y_max = y_max; j.thr = thr;
-    j.bad_bits = (uint32_t)bad;
+    j.bad_bits = bad;
     j.alive_tail = alive_tail;
     j.total = (int)(fetched_total + beyond);
     if (j.bad_bits != 0 || j.total > p.gather_capacity) return j;
@@ -834,7 +835,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
 
     __shared__ float s_f[3][kMergeThreads / 32];
     __shared__ double s_d[3][kMergeThreads / 32];
-    __shared__ uint32_t s_u[2][kMergeThreads / 32];
+    __shared__ uint32_t s_u[3][kMergeThreads / 32];
     __shared__ int s_count;
     __shared__ int s_ns;
     __shared__ uint32_t s_chosen_raw;
@@ -870,15 +871,14 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         if (tid == 0) {
             p.tokens[row] = -1;
             p.log_probs[row] = 0.0f;
-            p.row_status[row] = (joined.bad_bits & 0xFF00u) ? PSX_ROW_DEVICE_TIMEOUT
-                                : (joined.bad_bits & 0xFFu) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
+            p.row_status[row] = (joined.bad_bits & 2u) ? PSX_ROW_DEVICE_TIMEOUT
+                                : (joined.bad_bits & 1u) ? PSX_ROW_NON_FINITE : PSX_ROW_TOO_WIDE;
             if (p.diag) p.diag[row] = psx_row_diag{total, 0, INFINITY, INFINITY};
         }
         return;
     }
 
     PSX_MERGE_STAGE(3);
-    if (p.debug_stop == 1) return;
     float keep_from = relax_threshold(thr, apply_t, p.temperature);
     const float x_max = temper(y_max, apply_t, p.temperature);
     const bool top_k_on = p.do_sample && p.top_k > 0 && p.top_k < p.vocab;  // src/generation.cpp:80
@@ -890,7 +890,6 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     if (!p.do_sample) keep_from = fmaxf(y_max, -FLT_MAX);
 
     PSX_MERGE_STAGE(4);
-    if (p.debug_stop == 2) return;
     // ---- 2. raw sum-exp over everything; the list of those that can survive ------------------------
     double z_raw = 0.0, z_rest = 0.0, dropped = 0.0;
     for (int i = tid; i < p.parts; i += kMergeThreads) {
@@ -1055,7 +1054,6 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         __syncthreads();
     }
     PSX_MERGE_STAGE(6);
-    if (p.debug_stop == 3) return;
     // ---- 3'. a long list without a top-k: decided by the whole block, without sorting --------------
     bool decided = false;
     if (p.do_sample && !top_k_on && n > kMergeThreads) {
@@ -1152,7 +1150,6 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     }  // !decided
     __syncthreads();
     PSX_MERGE_STAGE(7);
-    if (p.debug_stop == 4) return;
     Decision dec = s_dec;
     if (p.survivor_cols != nullptr && dec.status == PSX_ROW_OK) {  // hand the surviving set itself out
         if (tid == 0) s_count = 0;

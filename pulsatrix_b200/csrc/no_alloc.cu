@@ -14,7 +14,10 @@
 //     64 x 151,936 batch is 640 parts); bigger batches and more than kStaticBanned EOS ids are
 //     refused with PSX_ERR_UNSUPPORTED, nothing is launched;
 //   * the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-//     that device current); make that first call before starting any stream capture on that device;
+//     that device current) and lifts the two kernels' shared-memory limits; make that first call
+//     at start-up: before any stream capture on that device, and before the host process's own
+//     pool takes the rest of the GPU's memory -- under CUDA's lazy module loading the array's
+//     8.1 MiB and the kernels' code are placed on the device when the first call loads them;
 //   * every call uses the same array.  Nothing in it has to start at zero: the row pass rewrites
 //     every record and every list count of the batch before the survivor stage reads them, and
 //     list slots beyond a count are never used, so stale contents of an earlier call are
@@ -25,6 +28,7 @@
 
 #include "../../include/psx_b200.h"
 #include "merge_rows.cuh"
+#include "sample_plan.cuh"
 #include "scan_rows.cuh"
 
 namespace {
@@ -50,9 +54,6 @@ struct DeviceSetup {
 };
 DeviceSetup g_setup[kMaxDevices];
 std::mutex g_setup_mutex;
-
-constexpr int kSortCapacity = 1024, kGatherCapacity = 4096;          // as the regular top-k / greedy plan
-constexpr int kSortCapacityWide = 4096, kGatherCapacityWide = 8192;  // sampling without a top-k
 
 }  // namespace
 
@@ -108,22 +109,7 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
         return set_error(PSX_ERR_BAD_ARGUMENT, "psx_b200: eos_token_ids is null");
     }
 
-    // ---- the fixed limits ------------------------------------------------------------------------------
-    const bool aligned = (reinterpret_cast<uintptr_t>(logits) % 16 == 0) && (row_stride % 4 == 0);
-    const int64_t vectors = (vocab + 3 + (aligned ? 0 : 3)) / 4;
-    const int64_t parts = (vectors + psx::kPartVecs - 1) / psx::kPartVecs;
-    if (rows * parts > kStaticParts) {
-        return set_error(PSX_ERR_UNSUPPORTED,
-                         "psx_b200_sample_rows_static: the batch needs " + std::to_string(rows * parts) +
-                             " parts (rows x ceil(vocab / 16384)); the built-in scratch holds " +
-                             std::to_string(kStaticParts) + " -- use psx_b200_sample_rows or a smaller batch");
-    }
-    if (ban && c->num_eos_token_ids > kStaticBanned) {
-        return set_error(PSX_ERR_UNSUPPORTED, "psx_b200_sample_rows_static: at most " + std::to_string(kStaticBanned) +
-                                                  " EOS ids can be banned");
-    }
-
-    // ---- once per device: the array's device address, the kernels' shared-memory opt-ins -------------------
+    // ---- once per device: the array's device address, the SM count, the kernels' shared-memory opt-ins --------
     int device = 0;
     PSX_STATIC_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= kMaxDevices) return set_error(PSX_ERR_UNSUPPORTED, "psx_b200: device index too large");
@@ -134,21 +120,30 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
         if (!setup.done) {
             void* address = nullptr;
             PSX_STATIC_CUDA(cudaGetSymbolAddress(&address, g_scratch));  // for the device that is current
+            // Host-side function attributes, no memory: the limits are lifted to the device's maximum
+            // once, and nobody lowers them again.
+            PSX_STATIC_CUDA(psx::configure_scan_rows());
+            PSX_STATIC_CUDA(psx::configure_merge_rows());
             setup.scratch = static_cast<StaticScratch*>(address);
             setup.done = true;
         }
         scratch = setup.scratch;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-    // Shared-memory opt-ins of the two kernels (host-side function attributes, no memory): set on
-    // every call, because the regular entry points adjust the same attributes to their own needs.
-    PSX_STATIC_CUDA(psx::configure_scan_rows());
-    PSX_STATIC_CUDA(psx::configure_merge_rows());
+
+    // ---- the same plan as psx_b200_sample_rows, within the fixed limits ----------------------------------------
+    const psx::Plan plan = psx::make_plan(logits, vocab, row_stride, vocab, c);
+    if (rows * plan.parts > kStaticParts) {
+        return set_error(PSX_ERR_UNSUPPORTED,
+                         "psx_b200_sample_rows_static: the batch needs " + std::to_string(rows * plan.parts) +
+                             " parts (rows x ceil(vocab / 16384)); the built-in scratch holds " + std::to_string(kStaticParts) + " -- use psx_b200_sample_rows or a smaller batch");
+    }
+    if (ban && c->num_eos_token_ids > kStaticBanned) {
+        return set_error(PSX_ERR_UNSUPPORTED, "psx_b200_sample_rows_static: at most " + std::to_string(kStaticBanned) +
+                                                  " EOS ids can be banned");
+    }
 
     // ---- the same two kernels as psx_b200_sample_rows, pointed at the built-in scratch ----------------------
-    const bool top_k_on = sample && c->top_k > 0 && c->top_k < vocab;
-    const bool apply_temperature = sample && c->temperature != 1.0f;
-    const bool nucleus = sample && !top_k_on;
     psx::ScanParams sp{};
     sp.logits = logits;
     sp.row_stride = row_stride;
@@ -158,19 +153,7 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
     sp.vocab = vocab;
     sp.history_ids = history_ids;
     sp.history_offsets = history_offsets;
-    sp.apply_penalty = penalty ? 1 : 0;
-    sp.penalty = c->repetition_penalty;
-    sp.apply_temperature = apply_temperature ? 1 : 0;
-    sp.temperature = c->temperature;
-    const double log2e = 1.4426950408889634073599246810019;
-    sp.log2e_over_t = (float)(apply_temperature ? log2e / (double)c->temperature : log2e);
-    sp.k_need = !sample ? 1 : top_k_on ? (int)(c->top_k < (1 << 20) ? c->top_k : (1 << 20)) : 160;
-    if (vectors * 4 <= psx::kPartCap) sp.k_need = 1 << 30;  // small rows are handed on whole
-    sp.parts = (int)parts;
-    sp.vecs_per_part = (int)((vectors + parts - 1) / parts);
-    sp.debug_skip = 0;
-    sp.num_banned = 0;
-    sp.banned_ids = nullptr;
+    psx::fill_scan_settings(sp, c, plan);
     if (ban) {
         PSX_STATIC_CUDA(cudaMemcpyAsync(scratch->banned, c->eos_token_ids, (size_t)c->num_eos_token_ids * sizeof(int64_t),
                                         cudaMemcpyHostToDevice, stream));
@@ -180,38 +163,10 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
     sp.stats = scratch->stats;
     sp.part_counts = scratch->part_counts;
     sp.candidates = scratch->candidates;
-    PSX_STATIC_CUDA(psx::launch_scan_rows(sp, nucleus, stream));
+    PSX_STATIC_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
 
     psx::MergeParams mp{};
-    mp.stats = sp.stats;
-    mp.part_counts = sp.part_counts;
-    mp.candidates = sp.candidates;
-    mp.parts = sp.parts;
-    mp.part_cap = psx::kPartCap;
-    mp.slot_shift = psx::merge_slot_shift(sp.parts, psx::kPartCap,
-                                          sp.k_need >= psx::kPartCap ? psx::kPartCap : sp.k_need + sp.k_need / 4 + 24);
-    mp.stats_part_stride = sizeof(psx::PartStats);
-    mp.stats_row_stride = mp.stats_part_stride * sp.parts;
-    mp.count_part_stride = sizeof(uint32_t);
-    mp.count_row_stride = mp.count_part_stride * sp.parts;
-    mp.cand_part_stride = sizeof(uint2) * psx::kPartCap;
-    mp.cand_row_stride = mp.cand_part_stride * sp.parts;
-    mp.rows = rows;
-    mp.vocab = vocab;
-    mp.do_sample = sample ? 1 : 0;
-    mp.apply_temperature = apply_temperature ? 1 : 0;
-    mp.temperature = c->temperature;
-    mp.penalty = c->repetition_penalty;
-    mp.top_k = c->top_k;
-    mp.top_p = c->top_p;
-    mp.min_p = c->min_p;
-    mp.uniforms = uniforms;
-    mp.tokens = tokens;
-    mp.log_probs = log_probs;
-    mp.row_status = row_status;
-    mp.diag = nullptr;
-    mp.sort_capacity = nucleus ? kSortCapacityWide : kSortCapacity;
-    mp.gather_capacity = nucleus ? kGatherCapacityWide : kGatherCapacity;
+    psx::fill_merge_params(mp, sp, plan, c, rows, vocab, uniforms, tokens, log_probs, row_status, nullptr, logits, row_stride);
     PSX_STATIC_CUDA(psx::launch_merge_rows(mp, stream));
     return PSX_OK;
 }

@@ -1,10 +1,11 @@
 // The row pass: the one kernel that reads the logits from HBM.
 //
 // Each CTA owns one "part" of one row: up to 4096 aligned float4 vectors (16384 logits, 64 KB).
-// One thread asks the TMA unit for the whole part with bulk asynchronous copies
-// (cp.async.bulk global -> shared, completion on an mbarrier; no multicast), so the bytes stream
-// from HBM into shared memory without passing through registers while the other threads turn
-// the row's token history into a bitmap.  Everything after that reads shared memory:
+// One thread asks the TMA unit for the whole part with four bulk asynchronous copies of 16 KB
+// (cp.async.bulk global -> shared, each completing on an mbarrier of its own; no multicast), so the
+// bytes stream from HBM into shared memory without passing through registers while the other
+// threads turn the row's token history into a bitmap; a warp starts on a quarter of the part as
+// soon as that quarter has landed.  Everything after that reads shared memory:
 //   1. the few logits the history (repetition penalty, src/generation.cpp:59-68) or the EOS ban
 //      (:69-73) names are handed on as candidates whatever their value, in a fixed order, and
 //      blanked in shared memory, so the dense passes below never look at a flag;
@@ -20,6 +21,7 @@
 // the divide can merge (relax_threshold).
 //
 // HBM bound: 4 bytes per logit, read once; what is written is a few hundred bytes per part.
+#include "psx_async.cuh"
 #include "scan_rows.cuh"
 
 namespace psx {
@@ -31,58 +33,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLog2eRel = (float)(1.4426950408889634073599246810019 / (double)1.4426950408889634f - 1.0);
 constexpr float kPad = -FLT_MAX;  // stands for "no logit here": finite, never above a real logit
 constexpr int kBitmapWords = kPartVecs * 4 / 32;  // one bit per logit of a part
-constexpr uint32_t kCopyChunk = 16384;            // bytes per bulk copy
+constexpr uint32_t kCopyChunk = 16384;            // bytes per bulk copy; every copy completes on a barrier of its own
+constexpr int kCopies = kPartVecs * 16 / kCopyChunk;
 
 // acc = max(acc, all four) in two three-input instructions.
 __device__ __forceinline__ float max_into(float acc, const float4& v) { return fmax3(fmax3(v.x, v.y, v.z), v.w, acc); }
 __device__ __forceinline__ float amax_into(float acc, const float4& v) {
     return fmax3(fmax3(fabsf(v.x), fabsf(v.y), fabsf(v.z)), fabsf(v.w), acc);
-}
-
-// ---- mbarrier + bulk copy (PTX; the destination and the barrier are this CTA's shared memory) ----
-
-__device__ __forceinline__ uint32_t smem_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void barrier_init(uint64_t* bar, uint32_t arrivals) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)), "r"(arrivals) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-
-__device__ __forceinline__ void barrier_expect_bytes(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ void bulk_copy_to_shared(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_address(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_address(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ unsigned long long global_nanoseconds() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Waits for phase `parity` of the barrier, but not for ever: every try may sleep in the hardware for
-// up to the hinted microsecond, and a second after the first try the wait gives up.
-__device__ __forceinline__ bool barrier_wait_bounded(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_address(bar);
-    const unsigned long long started = global_nanoseconds();
-    for (;;) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity), "r"(1000u)
-            : "memory");
-        if (done) return true;
-        if (global_nanoseconds() - started > 1000000000ull) return false;
-    }
 }
 
 // Sets, in a bitmap with one bit per logit of this part, the columns that `ids` names (and the
@@ -138,7 +95,7 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     float* data = reinterpret_cast<float*>(dyn_smem);
     const float4* data4 = reinterpret_cast<const float4*>(dyn_smem);
 
-    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ __align__(8) uint64_t s_bar[kCopies];
     __shared__ __align__(16) uint32_t s_bits[2 * kBitmapWords];
     uint32_t* const s_flag = s_bits;                 // penalised or banned
     uint32_t* const s_ban = s_bits + kBitmapWords;   // banned
@@ -179,7 +136,10 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     }
 
     // ---- start the copy, and build the history bitmaps while it is in flight ----------------------
-    if (tid == 0) barrier_init(&s_bar, 1);
+    if (tid == 0) {
+        for (int i = 0; i < kCopies; ++i) barrier_init(&s_bar[i], 1);
+        barrier_init_fence();
+    }
     if (tid < kScanWarps) s_wflag[tid] = 0;
     static_assert(2 * kBitmapWords % 4 == 0, "the bitmaps are cleared 16 bytes at a time");
     for (int i = tid; i < 2 * kBitmapWords / 4; i += kScanThreads) reinterpret_cast<uint4*>(s_bits)[i] = make_uint4(0, 0, 0, 0);
@@ -188,60 +148,35 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     if (tid == 0) {
         const uint32_t bytes = (uint32_t)nvec * 16u;
         const char* src = reinterpret_cast<const char*>(vbase + v0);
-        barrier_expect_bytes(&s_bar, bytes);
-        for (uint32_t off = 0; off < bytes; off += kCopyChunk) {
-            bulk_copy_to_shared(dyn_smem + off, src + off, min(kCopyChunk, bytes - off), &s_bar);
+        for (uint32_t off = 0, i = 0; off < bytes; off += kCopyChunk, ++i) {
+            const uint32_t piece = min(kCopyChunk, bytes - off);
+            // (test hook: announcing more bytes than the copy delivers leaves the barrier open with
+            // nothing in flight, which is how the bounded wait is exercised)
+            barrier_expect_bytes(&s_bar[i], piece + (p.test_short_copy ? 16u : 0u));
+            bulk_copy_to_shared(dyn_smem + off, src + off, piece, &s_bar[i]);
         }
     }
     const bool use_flags = p.apply_penalty || p.num_banned > 0;
     const int first_pos = v0 * 4 - (int)misalign;
-    if (p.apply_penalty && !(p.debug_skip & 16)) {
+    if (p.apply_penalty) {
         mark_ids(p.history_ids, p.history_offsets[row], p.history_offsets[row + 1], p, first_pos, nvec * 4, s_flag, nullptr,
                  s_wflag);
     }
     if (p.num_banned > 0) mark_ids(p.banned_ids, 0, p.num_banned, p, first_pos, nvec * 4, s_flag, s_ban, s_wflag);
-    // One warp watches the copy; the others sleep in the block barrier, which also orders the
-    // copied bytes before everybody's reads.
+    __syncthreads();  // the bitmaps are complete
     STAGE(2);
-    const bool landed = warp == 0 ? barrier_wait_bounded(&s_bar, 0) : true;
-    const bool all_landed = __syncthreads_and(landed ? 1 : 0) != 0;
-    // From here on the kernel writes scratch that an earlier survivor stage may still be reading.
-    grid_dependency_wait();
-    if (!all_landed) {
-        // The copy did not complete in time: report it, give it one more bounded chance to drain
-        // (shared memory must not be handed to the next CTA under a copy in flight), and leave.
-        if (tid == 0) {
-            p.part_counts[part_index] = 0;
-            PartStats s;
-            s.raw_tail = 0.0; s.proc_tail = 0.0; s.raw_max = kPad; s.y_max = -INFINITY; s.thr = -INFINITY;
-            s.nonfinite = 2; s.alive_tail = 0; s.overflow = 0;
-            p.stats[part_index] = s;
-        }
-        if (warp == 0) barrier_wait_bounded(&s_bar, 0);
-        return;
-    }
-
-    STAGE(3);
-    // Pad the part to whole 256-vector trips (at most one vector per thread).
+    const int copies = (nvec * 16 + (int)kCopyChunk - 1) / (int)kCopyChunk;
+    const int trips = (nvec + kScanThreads - 1) / kScanThreads;  // the part is padded to whole trips
+    // Pad the part to whole 256-vector trips (at most one vector per thread).  The padding lies
+    // behind the copied bytes, so it need not wait for them.
     {
         // Every shared-memory write from here on is made by the thread that owns the vector in the
         // dense passes (vector v belongs to thread v % kScanThreads) or by a thread of its warp, so
         // warp-level ordering is enough and the warps run on without meeting again until the
         // threshold.
-        const int padded = (nvec + kScanThreads - 1) / kScanThreads * kScanThreads;
-        const int v = padded - kScanThreads + tid;
+        const int v = (trips - 1) * kScanThreads + tid;
         if (v >= nvec) reinterpret_cast<float4*>(dyn_smem)[v] = make_float4(kPad, kPad, kPad, kPad);
     }
-    // Components of the first and last vector that lie outside the row are blanked.
-    if (v0 == 0 && tid == 0) {
-        for (uint32_t c = 0; c < misalign; ++c) data[c] = kPad;
-    }
-    if (v1 == nv && tid == ((nvec - 1) & (kScanThreads - 1))) {
-        for (int64_t pos = (int64_t)misalign + p.cols; pos < (int64_t)nv * 4; ++pos) data[pos - (int64_t)v0 * 4] = kPad;
-    }
-    __syncwarp();
-
-    // ---- 1. flagged logits: handed on in bitmap order, then blanked ---------------------------------
     // The part's candidates form one list: first the flagged logits, warp after warp (each warp
     // knows every warp's count from the marking above), then what reaches the threshold.
     uint2* part_out = p.candidates + part_index * kPartCap;
@@ -253,68 +188,88 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     }
     const int col_base = (int)((int64_t)v0 * 4 - misalign + p.col_begin);  // global column of data[0]; fits 31 bits
     float f_raw = kPad, f_amax = 0.0f, f_y = -INFINITY;
-    if (use_flags && !(p.debug_skip & 1)) {
-        // A warp takes the bitmap words of the logits its own threads own in the dense passes
-        // (vector v belongs to thread v % kScanThreads), so a row that is handed on whole fills every
-        // warp's segment with exactly its own 128 logits.
-        constexpr int kWordsPerWarp = kBitmapWords / kScanWarps;
-        static_assert(kWordsPerWarp == 4 * kVecPerThread, "a warp's threads own 4 bitmap words per vector trip");
-        for (int r = 0; r < (kWordsPerWarp + 31) / 32; ++r) {
-            const int idx = r * 32 + lane;
-            const bool owned = idx < kWordsPerWarp;
-            const int word = owned ? (kScanThreads / 8) * (idx >> 2) + 4 * warp + (idx & 3) : 0;
-            const uint32_t banned_bits = owned ? s_ban[word] : 0u;
-            uint32_t bits = owned ? s_flag[word] : 0u;
+    float m = kPad, amax = 0.0f;
+    bool landed = true;  // (a wait that ran out is dealt with where the block meets next)
+
+    // The part in two halves of 32 KB (two copies, eight trips each): a warp waits for a half itself
+    // -- the wait also orders the copied bytes before the warp's reads --, hands on the half's
+    // flagged logits and takes its maxima while the other half is still landing.
+    constexpr int kWordsPerWarp = kBitmapWords / kScanWarps;
+    static_assert(kCopies == 4 && kVecPerThread == 16 && kWordsPerWarp == 64, "two halves of two copies, eight trips, 32 bitmap words per warp");
+    for (int half = 0; half < 2 && 2 * half < copies; ++half) {
+        for (int i = 2 * half; i < min(copies, 2 * half + 2); ++i) {
+            landed = barrier_wait_bounded(&s_bar[i], 0, p.wait_limit_ns) && landed;
+        }
+        // From here on the kernel writes scratch that an earlier survivor stage may still be reading.
+        if (half == 0) grid_dependency_wait();
+        // Components of the first and last vector that lie outside the row are blanked.
+        if (half == 0 && v0 == 0 && tid == 0) {
+            for (uint32_t c = 0; c < misalign; ++c) data[c] = kPad;
+        }
+        if (2 * half + 2 >= copies && v1 == nv && tid == ((nvec - 1) & (kScanThreads - 1))) {
+            for (int64_t pos = (int64_t)misalign + p.cols; pos < (int64_t)nv * 4; ++pos) data[pos - (int64_t)v0 * 4] = kPad;
+        }
+        __syncwarp();
+        STAGE(3);
+
+        // ---- 1. flagged logits: handed on in bitmap order, then blanked -------------------------------
+        if (use_flags) {
+            // A warp takes the bitmap words of the logits its own threads own in the dense passes
+            // (vector v belongs to thread v % kScanThreads), so a row that is handed on whole fills every
+            // warp's segment with exactly its own 128 logits.  Lane L: trip 8 * half + L / 4, quarter L % 4.
+            const int idx = half * 32 + lane;
+            const int word = (kScanThreads / 8) * (idx >> 2) + 4 * warp + (idx & 3);
+            const uint32_t banned_bits = s_ban[word];
+            uint32_t bits = s_flag[word];
             const uint32_t count = __popc(bits);
             const uint32_t voters = __ballot_sync(0xFFFFFFFFu, count != 0);
-            if (voters == 0) continue;
-            // Slots in lane order.  Usually a lane flags one logit; otherwise scan the counts.
-            uint32_t slot = seg_fill + __popc(voters & ((1u << lane) - 1u));
-            uint32_t total = __popc(voters);
-            if (__ballot_sync(0xFFFFFFFFu, count > 1) != 0) {
-                uint32_t incl = count;
+            if (voters != 0) {
+                // Slots in lane order.  Usually a lane flags one logit; otherwise scan the counts.
+                uint32_t slot = seg_fill + __popc(voters & ((1u << lane) - 1u));
+                uint32_t total = __popc(voters);
+                if (__ballot_sync(0xFFFFFFFFu, count > 1) != 0) {
+                    uint32_t incl = count;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                    if (lane >= o) incl += up;
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                        if (lane >= o) incl += up;
+                    }
+                    slot = seg_fill + incl - count;
+                    total = __shfl_sync(0xFFFFFFFFu, incl, 31);
                 }
-                slot = seg_fill + incl - count;
-                total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-            }
-            seg_fill += total;
-            while (bits) {
-                const int b = __ffs(bits) - 1;
-                bits &= bits - 1;
-                const uint32_t e = (uint32_t)word * 32u + (uint32_t)b;
-                const float l = data[e];
-                const bool banned = (banned_bits >> b) & 1u;
-                const float y = banned ? -INFINITY : penalize(l, p.penalty);
-                f_raw = fmaxf(f_raw, l);
-                f_amax = (l != l) ? INFINITY : fmaxf(f_amax, fabsf(l));
-                f_y = fmaxf(f_y, y);
-                if (slot < (uint32_t)kPartCap) {
-                    part_out[slot] = make_uint2(__float_as_uint(l),
-                                               (uint32_t)(col_base + (int)e) | (banned ? kFlagBanned : kFlagPenalized));
+                seg_fill += total;
+                while (bits) {
+                    const int b = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    const uint32_t e = (uint32_t)word * 32u + (uint32_t)b;
+                    const float l = data[e];
+                    const bool banned = (banned_bits >> b) & 1u;
+                    const float y = banned ? -INFINITY : penalize(l, p.penalty);
+                    f_raw = fmaxf(f_raw, l);
+                    f_amax = (l != l) ? INFINITY : fmaxf(f_amax, fabsf(l));
+                    f_y = fmaxf(f_y, y);
+                    if (slot < (uint32_t)kPartCap) {
+                        part_out[slot] = make_uint2(__float_as_uint(l),
+                                                   (uint32_t)(col_base + (int)e) | (banned ? kFlagBanned : kFlagPenalized));
+                    }
+                    ++slot;
+                    data[e] = kPad;
                 }
-                ++slot;
-                data[e] = kPad;
             }
+            __syncwarp();
         }
-    }
-    __syncwarp();
-    STAGE(4);
+        STAGE(4);
 
-    // ---- 2. per-thread maxima, then the part's raw max and selection threshold -------------------------
-    float m = kPad, amax = f_amax;
-    const int trips = (nvec + kScanThreads - 1) / kScanThreads;  // the part is padded to whole trips
-    if (!(p.debug_skip & 8)) {
+        // ---- 2. per-thread maxima (the part's raw max and selection threshold follow) ------------------
+        const int t_end = min(trips, 8 * half + 8);
 #pragma unroll 4
-        for (int t = 0; t < trips; ++t) {
+        for (int t = 8 * half; t < t_end; ++t) {
             const float4 d = data4[t * kScanThreads + tid];
             m = max_into(m, d);
             amax = amax_into(amax, d);
         }
     }
+    amax = fmaxf(amax, f_amax);
     STAGE(5);
     const float m_alive = (m == kPad) ? -INFINITY : m;  // a thread without logits takes no part in the selection
     const int live_threads = min(kScanThreads, nvec);
@@ -360,7 +315,21 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
             s_wthr[warp] = wthr;
         }
     }
-    __syncthreads();
+    if (__syncthreads_or(landed ? 0 : 1) != 0) {
+        // A copy did not complete in time: report it, give the copies one more bounded chance to
+        // drain (shared memory must not be handed to the next CTA under a copy in flight), and leave.
+        if (tid == 0) {
+            p.part_counts[part_index] = 0;
+            PartStats s;
+            s.raw_tail = 0.0; s.proc_tail = 0.0; s.raw_max = kPad; s.y_max = -INFINITY; s.thr = -INFINITY;
+            s.nonfinite = 2; s.alive_tail = 0; s.overflow = 0;
+            p.stats[part_index] = s;
+        }
+        if (warp == 0) {
+            for (int i = 0; i < copies; ++i) barrier_wait_bounded(&s_bar[i], 0, p.wait_limit_ns);
+        }
+        return;
+    }
     STAGE(6);
 
     // ---- every warp joins the warps' results and works out the part's constants for itself --------------
@@ -423,28 +392,26 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
             q2 = ex2_approx(__fmaf_rn(y2, kLog2eRel, y2)); q3 = ex2_approx(__fmaf_rn(y3, kLog2eRel, y3));
         }
     };
-    if (!(p.debug_skip & 4)) {
 #pragma unroll 4
-        for (int t = 0; t < trips; ++t) {
-            const float4 d = data4[t * kScanThreads + tid];
-            float e0, e1, e2, e3, q0, q1, q2, q3;
-            exps_of(d, e0, e1, e2, e3, q0, q1, q2, q3);
-            const bool hit = fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime;
-            const float s = (e0 + e1) + (e2 + e3);
-            tail += hit ? 0.0f : s;
-            if (second_exp) {
-                const float q = (q0 + q1) + (q2 + q3);
-                proc += hit ? 0.0f : q;
-            }
-            noted |= hit ? (1u << t) : 0u;
+    for (int t = 0; t < trips; ++t) {
+        const float4 d = data4[t * kScanThreads + tid];
+        float e0, e1, e2, e3, q0, q1, q2, q3;
+        exps_of(d, e0, e1, e2, e3, q0, q1, q2, q3);
+        const bool hit = fmax3(fmax3(d.x, d.y, d.z), d.w, kPad) >= tprime;
+        const float s = (e0 + e1) + (e2 + e3);
+        tail += hit ? 0.0f : s;
+        if (second_exp) {
+            const float q = (q0 + q1) + (q2 + q3);
+            proc += hit ? 0.0f : q;
         }
+        noted |= hit ? (1u << t) : 0u;
     }
     STAGE(8);
     // What reaches the threshold is counted now and handed on after the block has met (below): a
     // warp's run in the part's list starts where the runs of the warps before it end.  It leaves
     // the sums (its exp is taken in double by the survivor stage); its neighbours in the vector stay.
     uint32_t count = 0, before_mine = 0, warp_count = 0;
-    const bool any_noted = __ballot_sync(0xFFFFFFFFu, noted != 0) != 0 && !(p.debug_skip & 2);
+    const bool any_noted = __ballot_sync(0xFFFFFFFFu, noted != 0) != 0;
     if (any_noted) {
         for (uint32_t m2 = noted; m2; m2 &= m2 - 1) {
             const float4 d = data4[(__ffs(m2) - 1) * kScanThreads + tid];

@@ -26,15 +26,18 @@ struct ScanParams {
     int32_t parts;                   // CTAs per row
     int32_t vecs_per_part;           // float4 vectors per part, <= kPartVecs
     int32_t inputs_ready;            // the inputs above are complete whatever the kernel before this one is doing
-    int32_t debug_skip;              // profiling only: bit mask of kernel stages to leave out (results are then wrong)
+    uint64_t wait_limit_ns;          // a wait for a copy gives up after this long (the part then reports a time-out)
+    int32_t test_short_copy;         // tests only: the copies deliver less than was announced, so that a wait runs out
     // output
     PartStats* stats;                // rows * parts
     uint32_t* part_counts;           // rows * parts: candidates handed on by the part
     uint2* candidates;               // rows * parts * kPartCap: the part's candidates, back to back
 };
 
+constexpr uint64_t kDefaultWaitLimitNs = 1000000000ull;
+
 // nucleus: also accumulate the processed-domain tail that a full-vocabulary top-p / min-p needs.
-// Opts the kernel in to 64 KB of dynamic shared memory; once per device, before the first launch.
+// configure: once per device, before the first launch (lifts the kernels' dynamic shared-memory limit).
 cudaError_t configure_scan_rows();
 cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t stream);
 

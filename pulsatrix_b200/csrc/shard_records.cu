@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     raw_max = warp_max(raw_max);
     y_max = warp_max(y_max);
     thr = warp_max(thr);
-    nonfinite = __any_sync(0xFFFFFFFFu, nonfinite != 0) ? 1u : 0u;
+    nonfinite = __reduce_or_sync(0xFFFFFFFFu, nonfinite);  // bit 0: a non-finite logit; bit 1: a copy that timed out
     overflow = __any_sync(0xFFFFFFFFu, overflow != 0) ? 1u : 0u;
     alive_tail = warp_sum_u32(alive_tail);
     float keep_from = relax_threshold(thr, apply_t, p.temperature);

@@ -16,7 +16,8 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent.parent
 ORACLE_DIR = ROOT / "oracle"
-REFERENCE_CHECKOUT = Path(os.environ.get("PSX_REFERENCE_DIR", "/root/reference"))
+# The reference checkout: PSX_REFERENCE_DIR, else a directory named `reference` beside this repository.
+REFERENCE_CHECKOUT = Path(os.environ.get("PSX_REFERENCE_DIR") or ROOT.parent / "reference")
 
 OK, BAD_CONFIG, EMPTY_PROMPT, EMPTY_LOGITS, NON_FINITE, ALL_REMOVED = range(6)
 

@@ -11,14 +11,15 @@ import gpu_harness as gh
 import oracle_lib as ol
 import pulsatrix_b200 as psx
 import workload_rows
-from pulsatrix_b200.sharded import gathered_layout, shard_bounds
+from pulsatrix_b200.sharded import gathered_layout, row_bounds, shard_bounds
 from pulsatrix_b200.workloads import WORKLOADS
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-def run_sharded(logits, hist_flat, offsets, cfg, uniforms, world):
+def run_sharded(logits, hist_flat, offsets, cfg, uniforms, world, merge_blocks=1):
+    """merge_blocks > 1: the rows are decided block by block, as that many ranks would share them out."""
     import torch
     rows, vocab = logits.shape
     ctx = gh.ctx()
@@ -34,9 +35,19 @@ def run_sharded(logits, hist_flat, offsets, cfg, uniforms, world):
         shard = d_logits[:, begin: begin + cols]  # a strided view: row stride stays the full vocabulary
         ctx.shard_scan(shard, begin, vocab, d_hist, d_off, config, gathered[layout[s]: layout[s] + per])
     d_u = torch.from_numpy(uniforms).cuda() if uniforms is not None else None
-    out = ctx.shard_merge(gathered, world, rows, vocab, config, d_u)
-    torch.cuda.synchronize()
-    return out["tokens"].cpu().numpy(), out["log_probs"].cpu().numpy(), out["status"].cpu().numpy()
+    if merge_blocks == 1:
+        out = ctx.shard_merge(gathered, world, rows, vocab, config, d_u)
+        torch.cuda.synchronize()
+        return out["tokens"].cpu().numpy(), out["log_probs"].cpu().numpy(), out["status"].cpu().numpy()
+    pieces = []
+    for b in range(merge_blocks):
+        begin, count, _ = row_bounds(rows, merge_blocks, b)
+        if count == 0:
+            continue
+        out = ctx.shard_merge(gathered, world, rows, vocab, config, d_u, row_begin=begin, row_count=count)
+        torch.cuda.synchronize()
+        pieces.append([out[k].cpu().numpy() for k in ("tokens", "log_probs", "status")])
+    return tuple(np.concatenate([p[i] for p in pieces]) for i in range(3))
 
 
 def test_c5_in_eight_shards_matches_the_reference_fixture():
@@ -48,6 +59,17 @@ def test_c5_in_eight_shards_matches_the_reference_fixture():
     tokens, logp, status = run_sharded(logits, hist.ravel(), offsets, cfg, psx.uniforms_mt19937_64(seeds), w.shards)
     assert (status == 0).all(), status
     assert tokens.tolist() == gold["token"][ids].tolist()
+    assert (np.abs(logp - gold["log_prob"][ids]) <= 1e-5 * np.abs(gold["log_prob"][ids]) + 1e-9).all()
+
+
+def test_rows_shared_out_among_the_ranks_give_the_same_answers():
+    w = WORKLOADS["c5"]
+    gold = np.load(GOLDEN / "workload_c5.npz")
+    ids = np.arange(96, 133)  # 37 rows in 8 blocks: the last blocks are short or empty
+    logits, hist, offsets, seeds = workload_rows.build("c5", ids)
+    tokens, logp, status = run_sharded(logits, hist.ravel(), offsets, workload_rows.config_of(w),
+                                       psx.uniforms_mt19937_64(seeds), w.shards, merge_blocks=8)
+    assert (status == 0).all() and tokens.tolist() == gold["token"][ids].tolist()
     assert (np.abs(logp - gold["log_prob"][ids]) <= 1e-5 * np.abs(gold["log_prob"][ids]) + 1e-9).all()
 
 

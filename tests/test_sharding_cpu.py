@@ -9,7 +9,7 @@ from pathlib import Path
 
 import pytest
 
-from pulsatrix_b200.sharded import gathered_layout, shard_bounds
+from pulsatrix_b200.sharded import gathered_layout, row_bounds, shard_bounds
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -25,6 +25,17 @@ def test_shards_tile_the_vocabulary(vocab, world):
     assert covered == vocab
     with pytest.raises(ValueError):
         shard_bounds(vocab, world, world)
+
+
+@pytest.mark.parametrize("rows,world", [(512, 8), (48, 8), (13, 4), (3, 8), (1, 2), (64, 1)])
+def test_row_blocks_tile_the_rows(rows, world):
+    covered, sizes = 0, set()
+    for rank in range(world):
+        begin, count, per = row_bounds(rows, world, rank)
+        assert begin == covered and 0 <= count <= per
+        covered += count
+        sizes.add(per)
+    assert covered == rows and len(sizes) == 1 and sizes.pop() * world >= rows
 
 
 def test_gathered_layout_is_shard_major():
@@ -58,6 +69,23 @@ WORKER = textwrap.dedent("""
     begin, cols = shard_bounds(1000, world, rank)
     width = torch.tensor([cols]); dist.all_reduce(width)
     assert int(width) == 1000
+    # the second collective: every rank's block of results (tokens | log-probs | status), all-gathered,
+    # read back through the views ShardedSampler hands out
+    from pulsatrix_b200.sharded import row_bounds
+    rows = 7
+    row_begin, count, per = row_bounds(rows, world, rank)
+    block = torch.zeros(16 * per, dtype=torch.uint8)
+    block[: 8 * per].view(torch.int64)[:count] = torch.arange(row_begin, row_begin + count) * 10
+    block[8 * per: 12 * per].view(torch.float32)[:count] = -torch.arange(row_begin, row_begin + count).float()
+    block[12 * per:].view(torch.int32)[:count] = 5
+    results = torch.zeros(world * 16 * per, dtype=torch.uint8)
+    dist.all_gather_into_tensor(results, block)
+    by_rank = results.view(world, 16 * per)
+    tokens = by_rank[:, : 8 * per].view(torch.int64).reshape(-1)[:rows]
+    logp = by_rank[:, 8 * per: 12 * per].view(torch.float32).reshape(-1)[:rows]
+    status = by_rank[:, 12 * per:].view(torch.int32).reshape(-1)[:rows]
+    assert tokens.tolist() == [10 * r for r in range(rows)]
+    assert logp.tolist() == [-float(r) for r in range(rows)] and (status == 5).all()
     dist.destroy_process_group()
     print("ok", rank)
 """)
