@@ -87,6 +87,8 @@ def parse_args():
     ap.add_argument("--contexts", type=int, default=4,
                     help="sampler contexts in flight per GPU (one stream and one scratch each; steps go round-robin)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
+    ap.add_argument("--softmax", action="store_true",
+                    help="time psx_b200_softmax_rows / logsumexp_rows on a few shapes instead (one GPU; prints its own JSON line)")
     ap.add_argument("--top-k", action="store_true",
                     help="time psx_b200_top_k_rows on a few shapes instead (one GPU; prints its own JSON line)")
     return ap.parse_args()
@@ -758,14 +760,53 @@ def run_top_k(args):
           "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
 
 
+SOFTMAX_SHAPES = [(65536, 128), (8192, 4096), (1024, 49152), (256, 128256), (64, 151936), (512, 262144)]
+
+
+def run_softmax(args):
+    """The row primitives beside the path (DeviceBackend::softmax_rows / logsumexp_rows): GB/s against
+    8 bytes per element (read + write) for softmax and 4 (read) for logsumexp, inputs rotating over more
+    than L2, CUDA events on the launching stream."""
+    import torch
+    import pulsatrix_b200 as psx
+
+    ctx = psx.Context(0)
+    results = []
+    for rows, cols in SOFTMAX_SHAPES:
+        count = max(2, (2 * L2_BYTES) // (rows * cols * 4) + 1)
+        xs = [torch.randn(rows, cols, device="cuda") * 3 for _ in range(count)]
+        out = torch.empty_like(xs[0])
+        entry = {"rows": rows, "cols": cols}
+        for name, fn, bytes_per in (("softmax", lambda x: ctx.softmax_rows(x, out=out), 8),
+                                    ("logsumexp", lambda x: ctx.logsumexp_rows(x), 4)):
+            for i in range(max(args.warmup, 3)):
+                fn(xs[i % count])
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            steps = max(3, min(args.steps, 50))
+            begin.record()
+            for i in range(steps):
+                fn(xs[i % count])
+            end.record()
+            torch.cuda.synchronize()
+            ms = begin.elapsed_time(end) / steps
+            entry[name + "_us"] = ms * 1e3
+            entry[name + "_gbs"] = rows * cols * bytes_per / (ms * 1e-3) / 1e9
+        results.append(entry)
+        del xs, out
+    peak, peak_kind = measured_hbm_peak()
+    emit({"metric": "softmax_rows / logsumexp_rows GB/s", "unit": "GB/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
+          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
+
+
 def main():
     args = parse_args()
     keep_stdout_for_the_result()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.top_k:
+    if args.top_k or args.softmax:
         if rank == 0:
-            run_top_k(args)
+            (run_top_k if args.top_k else run_softmax)(args)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)

@@ -242,6 +242,19 @@ PSX_API psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream, const v
 PSX_API psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream, const float* in, float* values, float* indices,
                                size_t rows, size_t cols, size_t k, int largest);
 
+/* Replace DeviceBackend::softmax_rows, logsumexp_rows and gather_rows
+ * (include/pulsatrix/device_backend.hpp:456,465,596; CUDA implementations src/cuda_backend.cu with
+ * the kernels src/gpu_kernels.cuh:315-365,665; CPU semantics src/cpu_backend.cpp:292-338,459-466)
+ * for row-major device matrices.  softmax: out[r][j] = exp(in[r][j] - max_r) / sum, out may alias
+ * in; logsumexp: out[r] = max_r + log(sum_j exp(in[r][j] - max_r)); both in float like the
+ * reference (sums in a fixed tree: equal to the reference's sequential sums to rounding, its own
+ * CPU/GPU tolerance is 1e-4).  gather: out[i][:] = table[indices[i]][:] with whole-number float
+ * indices, bit-exact.  Asynchronous on `stream`. */
+PSX_API psx_status psx_b200_softmax_rows(psx_ctx* ctx, void* stream, const float* in, float* out, size_t rows, size_t cols);
+PSX_API psx_status psx_b200_logsumexp_rows(psx_ctx* ctx, void* stream, const float* in, float* out, size_t rows, size_t cols);
+PSX_API psx_status psx_b200_gather_rows(psx_ctx* ctx, void* stream, const float* table, const float* indices, float* out,
+                                        size_t count, size_t dim);
+
 /* Host helpers: the uniform streams the reference draws from.
  * psx_uniforms_mt19937_64: out[i] = (std::mt19937_64(seeds[i])() >> 11) * 2^-53, the first draw
  * of Generate() for that seed (src/generation.cpp:120,143).

@@ -1,8 +1,11 @@
 /** @file device_backend.hpp
  *  The part of the reference's DeviceBackend interface (include/pulsatrix/device_backend.hpp:248-838)
- *  that the selection path touches: memory, copies and top_k_rows (:828-837), plus the minimal
- *  Shape/Tensor that top_k() takes.  Same names and argument meaning; everything else of the
- *  reference's ~100 virtuals belongs to the model side and is not rebuilt here.
+ *  that the selection path and its neighbours touch: memory, copies, top_k_rows (:828-837),
+ *  softmax_rows (:456), logsumexp_rows (:465) and gather_rows (:596), plus the minimal Shape/Tensor
+ *  that top_k() takes.  Same names and argument meaning; everything else of the reference's ~100
+ *  virtuals belongs to the model side and is not rebuilt here, so this class is not
+ *  layout-compatible with the reference's: a program written against these headers links against
+ *  this library, one compiled against the reference's header does not.
  */
 #pragma once
 
@@ -33,6 +36,12 @@ public:
      *  the lower column first.  Preconditions (checked by top_k()): 1 <= k <= cols <= 2^24. */
     virtual void top_k_rows(const float* in, float* values, float* indices, size_t rows, size_t cols, size_t k,
                             bool largest) = 0;
+    /** Row-wise softmax of a (rows x cols) matrix, max-subtracted. out may alias in. */
+    virtual void softmax_rows(const float* in, float* out, size_t rows, size_t cols) = 0;
+    /** Per-row log-sum-exp, max-subtracted: out[i] = log sum_j exp(in[i][j]). */
+    virtual void logsumexp_rows(const float* in, float* out, size_t rows, size_t cols) = 0;
+    /** out[i][:] = table[indices[i]][:] for count rows of width dim. */
+    virtual void gather_rows(const float* table, const float* indices, float* out, size_t count, size_t dim) = 0;
 };
 
 /** The B200 backend: owns a psx_ctx (stream + scratch); every call synchronises before returning,
@@ -49,6 +58,9 @@ public:
     void copy(void* dst, const void* src, size_t bytes, CopyDirection dir) override;
     void top_k_rows(const float* in, float* values, float* indices, size_t rows, size_t cols, size_t k,
                     bool largest) override;
+    void softmax_rows(const float* in, float* out, size_t rows, size_t cols) override;
+    void logsumexp_rows(const float* in, float* out, size_t rows, size_t cols) override;
+    void gather_rows(const float* table, const float* indices, float* out, size_t count, size_t dim) override;
     /** The underlying C context, for the generation entry points. */
     [[nodiscard]] psx_ctx* context() const noexcept { return ctx_; }
 

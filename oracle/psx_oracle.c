@@ -376,6 +376,41 @@ void psxo_top_k_rows(const float* in, float* values, float* indices, int64_t row
     free(items);
 }
 
+/* ---- src/cpu_backend.cpp:292-310 (softmax_rows), :325-338 (logsumexp_rows), :459-466 (gather_rows) ---- */
+void psxo_softmax_rows(const float* in, float* out, int64_t rows, int64_t cols) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* x = in + r * cols;
+        float* y = out + r * cols;
+        float row_max = x[0];
+        for (int64_t j = 1; j < cols; ++j) row_max = x[j] > row_max ? x[j] : row_max; /* std::max(a, b): b when a < b */
+        float exp_sum = 0.0f;
+        for (int64_t j = 0; j < cols; ++j) {
+            const float e = expf(x[j] - row_max);
+            y[j] = e;
+            exp_sum += e;
+        }
+        for (int64_t j = 0; j < cols; ++j) y[j] /= exp_sum;
+    }
+}
+
+void psxo_logsumexp_rows(const float* in, float* out, int64_t rows, int64_t cols) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* x = in + r * cols;
+        float row_max = x[0];
+        for (int64_t j = 1; j < cols; ++j) row_max = x[j] > row_max ? x[j] : row_max;
+        float exp_sum = 0.0f;
+        for (int64_t j = 0; j < cols; ++j) exp_sum += expf(x[j] - row_max);
+        out[r] = row_max + logf(exp_sum);
+    }
+}
+
+void psxo_gather_rows(const float* table, const float* indices, float* out, int64_t count, int64_t dim) {
+    for (int64_t i = 0; i < count; ++i) {
+        const float* row = table + (size_t)indices[i] * (size_t)dim;
+        for (int64_t d = 0; d < dim; ++d) out[i * dim + d] = row[d];
+    }
+}
+
 /* ---- src/determinism.cpp:14-34 --------------------------------------------------------------- */
 static uint64_t g_seed = 0, g_counter = 0;
 

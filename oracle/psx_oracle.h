@@ -97,6 +97,11 @@ int psxo_rows(const float* logits, int64_t rows, int64_t vocab, int64_t row_stri
 void psxo_top_k_rows(const float* in, float* values, float* indices, int64_t rows, int64_t cols, int64_t k,
                      int largest);
 
+/* src/cpu_backend.cpp:292-310,325-338,459-466: the float row primitives beside the path. */
+void psxo_softmax_rows(const float* in, float* out, int64_t rows, int64_t cols);
+void psxo_logsumexp_rows(const float* in, float* out, int64_t rows, int64_t cols);
+void psxo_gather_rows(const float* table, const float* indices, float* out, int64_t count, int64_t dim);
+
 /* src/determinism.cpp:24-34: the global seed stream. */
 void psxo_set_seed(uint64_t seed);
 uint64_t psxo_next_seed(void);

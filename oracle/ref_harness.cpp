@@ -143,6 +143,21 @@ void psxref_top_k_rows(const float* in, float* values, float* indices, int64_t r
                    static_cast<size_t>(k), largest != 0);
 }
 
+void psxref_softmax_rows(const float* in, float* out, int64_t rows, int64_t cols) {
+    pulsatrix::CPUBackend cpu;
+    cpu.softmax_rows(in, out, static_cast<size_t>(rows), static_cast<size_t>(cols));
+}
+
+void psxref_logsumexp_rows(const float* in, float* out, int64_t rows, int64_t cols) {
+    pulsatrix::CPUBackend cpu;
+    cpu.logsumexp_rows(in, out, static_cast<size_t>(rows), static_cast<size_t>(cols));
+}
+
+void psxref_gather_rows(const float* table, const float* indices, float* out, int64_t count, int64_t dim) {
+    pulsatrix::CPUBackend cpu;
+    cpu.gather_rows(table, indices, out, static_cast<size_t>(count), static_cast<size_t>(dim));
+}
+
 // top_k() on a (rows, cols) CPU tensor: 0 on success, 1 when it throws std::invalid_argument.
 int psxref_top_k(const float* in, float* values, float* indices, int64_t rows, int64_t cols, int64_t k,
                  int largest) {

@@ -17,7 +17,7 @@ EXPORTS = [
     "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready",
     "psx_b200_ctx_set_wait_limit", "psx_b200_test_short_copy", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_shard_merge_rows",
-    "psx_b200_top_k_rows",
+    "psx_b200_top_k_rows", "psx_b200_softmax_rows", "psx_b200_logsumexp_rows", "psx_b200_gather_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
 
@@ -114,6 +114,9 @@ def library():
         lib.psx_b200_shard_merge.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_merge_rows.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_top_k_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int]
+        lib.psx_b200_softmax_rows.argtypes = [ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
+        lib.psx_b200_logsumexp_rows.argtypes = [ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
+        lib.psx_b200_gather_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
         lib.psx_uniforms_mt19937_64.argtypes = [ptr, i64, ptr]
         lib.psx_uniforms_portable.argtypes = [ptr, i64, ptr]
         _lib = lib
@@ -362,6 +365,34 @@ class Context:
         _check(self._lib.psx_b200_top_k_rows(self._ctx, C.c_void_p(stream), _dptr(x), _dptr(values), _dptr(indices),
                                              rows, cols, k if k >= 0 else 0, int(largest)))
         return values, indices
+
+    # ---- row primitives ---------------------------------------------------------------------------------
+    def softmax_rows(self, x, out=None, stream=None):
+        """x: cuda float32 contiguous (rows, cols); out may be x itself."""
+        import torch
+        out = torch.empty_like(x) if out is None else out
+        if stream is None:
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+        _check(self._lib.psx_b200_softmax_rows(self._ctx, C.c_void_p(stream), _dptr(x), _dptr(out), x.shape[0], x.shape[1]))
+        return out
+
+    def logsumexp_rows(self, x, stream=None):
+        import torch
+        out = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+        if stream is None:
+            stream = torch.cuda.current_stream(x.device).cuda_stream
+        _check(self._lib.psx_b200_logsumexp_rows(self._ctx, C.c_void_p(stream), _dptr(x), _dptr(out), x.shape[0], x.shape[1]))
+        return out
+
+    def gather_rows(self, table, indices, stream=None):
+        """table: cuda float32 (n, dim); indices: cuda float32 whole numbers (count,)."""
+        import torch
+        out = torch.empty((indices.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+        if stream is None:
+            stream = torch.cuda.current_stream(table.device).cuda_stream
+        _check(self._lib.psx_b200_gather_rows(self._ctx, C.c_void_p(stream), _dptr(table), _dptr(indices), _dptr(out),
+                                              indices.shape[0], table.shape[1]))
+        return out
 
     # ---- vocabulary-sharded -----------------------------------------------------------------------------
     def shard_record_bytes(self, config) -> int:

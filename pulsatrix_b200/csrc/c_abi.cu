@@ -13,6 +13,7 @@
 
 #include "merge_rows.cuh"
 #include "process_rows.cuh"
+#include "row_ops.cuh"
 #include "sample_plan.cuh"
 #include "scan_rows.cuh"
 #include "shard_records.cuh"
@@ -719,6 +720,37 @@ psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream_ptr, const float* in, 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
     PSX_CUDA(psx::launch_topk_rows(in, values, indices, rows, cols, k, largest != 0, stream));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_softmax_rows(psx_ctx* ctx, void* stream_ptr, const float* in, float* out, size_t rows, size_t cols) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (rows == 0 || cols == 0) return PSX_OK;  // src/cuda_backend.cu: every op returns early on an empty size
+    if (!in || !out) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    PSX_CUDA(psx::launch_softmax_rows(in, out, rows, cols, static_cast<cudaStream_t>(stream_ptr)));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_logsumexp_rows(psx_ctx* ctx, void* stream_ptr, const float* in, float* out, size_t rows, size_t cols) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (rows == 0 || cols == 0) return PSX_OK;
+    if (!in || !out) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    PSX_CUDA(psx::launch_logsumexp_rows(in, out, rows, cols, static_cast<cudaStream_t>(stream_ptr)));
+    ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_gather_rows(psx_ctx* ctx, void* stream_ptr, const float* table, const float* indices, float* out,
+                                size_t count, size_t dim) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (count == 0 || dim == 0) return PSX_OK;
+    if (!table || !indices || !out) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    PSX_CUDA(psx::launch_gather_rows(table, indices, out, count, dim, static_cast<cudaStream_t>(stream_ptr)));
     ++ctx->launches;
     return PSX_OK;
 }

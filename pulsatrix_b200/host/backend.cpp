@@ -59,6 +59,24 @@ void CUDABackend::top_k_rows(const float* in, float* values, float* indices, siz
     check_status(psx_b200_sync(ctx_, stream));
 }
 
+void CUDABackend::softmax_rows(const float* in, float* out, size_t rows, size_t cols) {
+    void* stream = psx_b200_ctx_stream(ctx_);
+    check_status(psx_b200_softmax_rows(ctx_, stream, in, out, rows, cols));
+    check_status(psx_b200_sync(ctx_, stream));
+}
+
+void CUDABackend::logsumexp_rows(const float* in, float* out, size_t rows, size_t cols) {
+    void* stream = psx_b200_ctx_stream(ctx_);
+    check_status(psx_b200_logsumexp_rows(ctx_, stream, in, out, rows, cols));
+    check_status(psx_b200_sync(ctx_, stream));
+}
+
+void CUDABackend::gather_rows(const float* table, const float* indices, float* out, size_t count, size_t dim) {
+    void* stream = psx_b200_ctx_stream(ctx_);
+    check_status(psx_b200_gather_rows(ctx_, stream, table, indices, out, count, dim));
+    check_status(psx_b200_sync(ctx_, stream));
+}
+
 Tensor::Tensor(Shape shape, DeviceBackend* backend) : shape_(std::move(shape)), backend_(backend) {
     data_ = static_cast<float*>(backend_->allocate(static_cast<size_t>(shape_.numel()) * sizeof(float)));
 }

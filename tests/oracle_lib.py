@@ -182,6 +182,23 @@ def top_k_rows(lib_kind, x, k, largest=True):
     return values, indices
 
 
+def row_primitive(lib_kind, name, *arrays):
+    """softmax_rows / logsumexp_rows (x) or gather_rows (table, indices) through a CPU checker."""
+    lib = oracle() if lib_kind == "oracle" else reference()
+    prefix = "psxo_" if lib_kind == "oracle" else "psxref_"
+    fn = getattr(lib, prefix + name)
+    if name == "gather_rows":
+        table, indices = (np.ascontiguousarray(a, dtype=np.float32) for a in arrays)
+        out = np.empty((indices.shape[0], table.shape[1]), dtype=np.float32)
+        fn(_ptr(table, C.c_float), _ptr(indices, C.c_float), _ptr(out, C.c_float), C.c_int64(indices.shape[0]),
+           C.c_int64(table.shape[1]))
+        return out
+    x = np.ascontiguousarray(arrays[0], dtype=np.float32)
+    out = np.empty_like(x) if name == "softmax_rows" else np.empty(x.shape[0], dtype=np.float32)
+    fn(_ptr(x, C.c_float), _ptr(out, C.c_float), C.c_int64(x.shape[0]), C.c_int64(x.shape[1]))
+    return out
+
+
 def mt_uniforms(seeds):
     """First uniform of std::mt19937_64(seed) for each seed: (engine() >> 11) * 2^-53."""
     lib = oracle()

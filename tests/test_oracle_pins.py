@@ -298,3 +298,33 @@ def test_restatement_reproduces_the_golden_rows(name):
     assert got["survivors"].tolist() == gold["survivors"][ids].tolist()
     if w.do_sample:
         assert np.allclose(got["u"], ol.mt_uniforms(seeds), rtol=0, atol=0)
+
+
+# ---- the float row primitives beside the path (src/cpu_backend.cpp:292-338,459-466) ---------------------
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_row_primitives_known_answers(kind):
+    x = np.array([[0.0, 0.0, 0.0, 0.0], [1.0, 2.0, 3.0, 4.0], [-1e30, 5.0, 5.0, -np.inf]], dtype=np.float32)
+    y = ol.row_primitive(kind, "softmax_rows", x)
+    assert y[0].tolist() == [0.25] * 4
+    e = np.exp(x[1].astype(np.float64) - 4.0)
+    assert np.allclose(y[1], e / e.sum(), rtol=1e-6)
+    assert y[2].tolist() == [0.0, 0.5, 0.5, 0.0]
+    lse = ol.row_primitive(kind, "logsumexp_rows", x)
+    assert np.allclose(lse, [np.log(4.0), 4.0 + np.log(e.sum()), 5.0 + np.log(2.0)], rtol=1e-6)
+    table = np.arange(12, dtype=np.float32).reshape(4, 3)
+    got = ol.row_primitive(kind, "gather_rows", table, np.array([3.0, 0.0, 3.0, 1.0], dtype=np.float32))
+    assert got.tolist() == table[[3, 0, 3, 1]].tolist()
+
+
+@needs_reference
+def test_row_primitive_restatements_equal_the_reference_bit_for_bit():
+    rng = np.random.RandomState(5)
+    for rows, cols in [(3, 1), (5, 17), (2, 1000), (4, 4097)]:
+        x = (rng.randn(rows, cols) * 4).astype(np.float32)
+        for name in ("softmax_rows", "logsumexp_rows"):
+            assert ol.row_primitive("oracle", name, x).tobytes() == ol.row_primitive("reference", name, x).tobytes()
+    table = rng.randn(50, 7).astype(np.float32)
+    idx = rng.randint(0, 50, size=31).astype(np.float32)
+    assert ol.row_primitive("oracle", "gather_rows", table, idx).tobytes() == \
+        ol.row_primitive("reference", "gather_rows", table, idx).tobytes()
