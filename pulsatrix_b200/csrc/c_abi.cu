@@ -315,8 +315,10 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
         for (cudaEvent_t& e : marks) PSX_CUDA(cudaEventCreate(&e));
         PSX_CUDA(cudaEventRecord(marks[0], stream));
     }
-    PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
-    ++ctx->launches;
+    if (!plan.lists_cannot_bound) {
+        PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+        ++ctx->launches;
+    }
     if (ctx->timing) PSX_CUDA(cudaEventRecord(marks[1], stream));
     PSX_CUDA(psx::launch_merge_rows(mp, stream));
     ++ctx->launches;
@@ -371,12 +373,15 @@ psx_status psx_b200_process_logits(psx_ctx* ctx, void* stream_ptr, float* logits
         if (psx_status s = reserve(ctx->surv_counts, (size_t)rows * sizeof(uint32_t))) return s;
         if (psx_status s = reserve(ctx->pl_tokens, (size_t)rows * sizeof(int64_t))) return s;
         if (psx_status s = reserve(ctx->pl_log_probs, (size_t)rows * sizeof(float))) return s;
-        PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
-        ++ctx->launches;
+        if (!plan.lists_cannot_bound) {
+            PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+            ++ctx->launches;
+        }
         psx::MergeParams mp{};
         psx::fill_merge_params(mp, sp, plan, config, rows, vocab, /*uniforms=*/nullptr,
                                static_cast<int64_t*>(ctx->pl_tokens.ptr), static_cast<float*>(ctx->pl_log_probs.ptr), status,
                                nullptr, logits, row_stride);
+        mp.process_out = logits;  // a row that is decided from the row itself is rewritten in place right there
         mp.survivor_cols = static_cast<uint32_t*>(ctx->surv_cols.ptr);
         mp.survivor_vals = static_cast<float*>(ctx->surv_vals.ptr);
         mp.survivor_counts = static_cast<uint32_t*>(ctx->surv_counts.ptr);

@@ -13,13 +13,16 @@
 //      maximum, the inverse-CDF walk in column order against the row's uniform -- all in double;
 //   4. writes the token, float(log(exp(l - M) / Z)) of the raw logits (src/generation.cpp:156),
 //      a row status and the distances of the two decisions from their boundaries.
-// Reads a few KB per row; never touches the logits.
+// Reads a few KB per row and never touches the logits -- except for a row that does not fit the
+// lists (more survivors or ties than they hold): that row is decided from the logits themselves
+// by the same CTA (general_row_impl.cuh).
 #ifdef PSX_STAGE_CLOCKS
 // Profiling build only: thread 0 of each row's CTA stamps the SM clock at the stage boundaries.
 __device__ unsigned long long g_merge_clocks[1024 * 16];
 #define PSX_MERGE_STAGE(i) \
     do { if (threadIdx.x == 0) g_merge_clocks[(size_t)(blockIdx.x & 1023) * 16 + (i)] = clock64(); } while (0)
 #endif
+#include "general_row_impl.cuh"
 #include "merge_rows_impl.cuh"
 
 namespace psx {
@@ -30,7 +33,13 @@ __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const Merg
     extern __shared__ unsigned long long dyn[];
     grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
     grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
-    survivor::merge_row(p, p.row_begin + blockIdx.x, dyn);
+    const int64_t row = p.row_begin + blockIdx.x;
+    if (p.general != 2) survivor::merge_row(p, row, dyn);
+    if (p.general != 0 && p.logits != nullptr) {
+        // A row the candidate lists could not decide is decided from the row itself.
+        __syncthreads();
+        if (p.general == 2 || p.row_status[row] == PSX_ROW_TOO_WIDE) survivor::general_row(p, row, dyn);
+    }
 }
 
 }  // namespace
@@ -62,7 +71,9 @@ cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
     // The same condition as the kernel's: the overlaid layout is for plans without a top-k.
     const bool overlay = p.overlay != 0 && p.logits != nullptr && !(p.do_sample && p.top_k > 0 && p.top_k < p.vocab);
     const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, overlay);
-    return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, p);
+    MergeParams with_size = p;
+    with_size.dyn_bytes = (int32_t)shared;
+    return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, with_size);
 }
 
 }  // namespace psx

@@ -54,7 +54,21 @@ struct MergeParams {
     int64_t logits_row_stride;
     int64_t logits_col_begin;
     int32_t overlay;
+    // Optional: what it takes to decide a row from the row itself (general_row), for the rows the
+    // candidate lists cannot decide -- more survivors, or more ties at a cut, than they hold.
+    // Needs `logits` (with logits_col_begin == 0: the whole vocabulary on this GPU).
+    const int64_t* history_ids;      // as the row pass got them; null: no repetition penalty
+    const int64_t* history_offsets;
+    const int64_t* banned_ids;
+    int32_t num_banned;
+    int32_t general;                 // 0: off; 1: for rows the lists declined; 2: for every row (the lists are not looked at)
+    float* process_out;              // ProcessLogits: general_row rewrites the row in place instead of drawing
+    int32_t dyn_bytes;               // dynamic shared memory of the launch (filled in by launch_merge_rows)
 };
+
+// Row status between the survivor stage and ProcessLogits' write-back: general_row has already
+// rewritten the row in place.  Never leaves the library.
+constexpr int kRowDoneInPlace = 64;
 
 size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, bool overlay);
 // The slot_shift for lists that usually hold about `expected` candidates, within the fetch budget.

@@ -453,8 +453,8 @@ constexpr int kMassPasses = 8;  // histograms decide_wide needs: four passes ove
 // a piece.  What the rounding to 2^-44 loses, at most n * 2.9e-14 in all, is far inside
 // kExactMargin.
 constexpr double kMassUnit = 17592186044416.0;  // 2^44
-template <class KeyOf, class InPlay>
-__device__ inline void mass_select(KeyOf key_of, InPlay in_play, const double* ex, int n, int top_shift, double start,
+template <class KeyOf, class InPlay, class MassOf>
+__device__ inline void mass_select(KeyOf key_of, InPlay in_play, MassOf mass_of, int n, int top_shift, double start,
                                    double target, uint32_t* hist, uint32_t& K, double& below, double& at) {
     const int tid = threadIdx.x, lane = tid & 31;
     uint32_t prefix = 0, mask = 0;
@@ -471,7 +471,7 @@ __device__ inline void mass_select(KeyOf key_of, InPlay in_play, const double* e
             if (!in_play(i)) continue;
             const uint32_t key = key_of(i);
             if ((key & mask) != prefix) continue;
-            const u64 units = (u64)__double2ull_rn(ex[i] * kMassUnit);  // at most 2^44
+            const u64 units = (u64)__double2ull_rn(mass_of(i) * kMassUnit);  // at most 2^44
             uint32_t* bin = h + ((key >> shift) & 255u);
             atomicAdd(bin, (uint32_t)units & 0x7FFFu);
             atomicAdd(bin + 256, (uint32_t)(units >> 15) & 0x7FFFu);
@@ -565,8 +565,8 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
         if (limit >= 1.0 - 1e-12) return false;
         uint32_t cut;
         double mass_below, mass_at;
-        mass_select([&](int i) { return key_ord(keyA[i]); }, [&](int) { return true; }, ex, n, 24, base, limit * sum, hist, cut,
-                    mass_below, mass_at);
+        mass_select([&](int i) { return key_ord(keyA[i]); }, [&](int) { return true; }, [&](int i) { return ex[i]; }, n, 24, base,
+                    limit * sum, hist, cut, mass_below, mass_at);
         const double below = mass_below / sum;
         margin = fmin(margin, fabs(below - limit));
         // Entries equal to the cut value go in ascending column order, one probability each.
@@ -632,8 +632,8 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
     uint32_t hi;
     double mass_before, mass_at;
     const int column_shift = p.vocab <= (1 << 16) ? 8 : p.vocab <= (1 << 24) ? 16 : 24;
-    mass_select([&](int i) { return key_col(keyA[i]); }, [&](int i) { return alive[i] != 0; }, ex, n, column_shift, 0.0,
-                u * sum, hist + 4 * 768, hi, mass_before, mass_at);
+    mass_select([&](int i) { return key_col(keyA[i]); }, [&](int i) { return alive[i] != 0; }, [&](int i) { return ex[i]; }, n,
+                column_shift, 0.0, u * sum, hist + 4 * 768, hi, mass_before, mass_at);
     const double before = mass_before / sum, upto = (mass_before + mass_at) / sum;
     out.draw_margin = before == 0.0 ? fabs(u - upto) : fmin(fabs(u - before), fabs(u - upto));
     if (out.draw_margin < kExactMargin) return false;

@@ -163,7 +163,7 @@ extern "C" psx_status psx_b200_sample_rows_static(void* stream_ptr, const float*
     sp.stats = scratch->stats;
     sp.part_counts = scratch->part_counts;
     sp.candidates = scratch->candidates;
-    PSX_STATIC_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
+    if (!plan.lists_cannot_bound) PSX_STATIC_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
 
     psx::MergeParams mp{};
     psx::fill_merge_params(mp, sp, plan, c, rows, vocab, uniforms, tokens, log_probs, row_status, nullptr, logits, row_stride);

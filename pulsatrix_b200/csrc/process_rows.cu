@@ -57,7 +57,12 @@ __global__ void __launch_bounds__(kThreads) process_rows_kernel(const ProcessPar
 
 __global__ void __launch_bounds__(kThreads) scatter_survivors_kernel(const ProcessParams p) {
     const int64_t row = blockIdx.x;
-    if (p.row_status[row] != PSX_ROW_OK) return;
+    const int status = p.row_status[row];
+    if (status == kRowDoneInPlace) {  // the survivor stage has rewritten this row itself
+        if (threadIdx.x == 0) p.row_status[row] = PSX_ROW_OK;
+        return;
+    }
+    if (status != PSX_ROW_OK) return;
     const int count = (int)p.survivor_counts[row];
     float* out = p.logits + row * p.row_stride;
     for (int i = threadIdx.x; i < count; i += kThreads) {

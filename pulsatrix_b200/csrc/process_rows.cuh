@@ -2,6 +2,7 @@
 #pragma once
 
 #include "../../include/psx_b200.h"
+#include "merge_rows.cuh"
 #include "psx_device.cuh"
 
 namespace psx {
@@ -18,7 +19,7 @@ struct ProcessParams {
     int32_t apply_temperature;
     float temperature;
     int32_t filters_on;              // 1: blank the row, then write the survivors below back
-    const int32_t* row_status;       // device, rows: what the survivor stage said (filters_on only)
+    int32_t* row_status;             // device, rows: what the survivor stage said (filters_on only)
     const uint32_t* survivor_cols;   // rows * survivor_cap
     const float* survivor_vals;
     const uint32_t* survivor_counts; // rows

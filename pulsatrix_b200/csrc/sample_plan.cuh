@@ -21,6 +21,7 @@ struct Plan {
     int sort_capacity = 1024;
     int gather_capacity = 4096;
     int slot_shift = 0;    // the survivor stage fetches 2^slot_shift slots of every part's list at once
+    bool lists_cannot_bound = false;  // no candidate list can hold what may survive: rows are decided from the row itself
 };
 
 constexpr int kNucleusNeed = 160;  // logits every part hands on when no top-k bounds the survivors
@@ -46,6 +47,10 @@ inline Plan make_plan(const float* logits, int64_t cols, int64_t row_stride, int
     // A row of at most 256 vectors fits a part's candidate list whole (1024 logits): hand
     // everything on, and every filter is exact whatever the settings.
     if (vectors * 4 <= kPartCap) plan.k_need = 1 << 30;
+    // Sampling with no filter at all keeps every token, and a part can bound a top-k of at most one
+    // logit per thread: such rows skip the row pass and are decided from the row itself.
+    plan.lists_cannot_bound = vectors * 4 > kPartCap &&
+                              ((plan.nucleus && !(c->top_p < 1.0f) && !(c->min_p > 0.0f)) || (top_k_on && plan.k_need > kScanThreads));
     plan.sort_capacity = plan.nucleus ? 4096 : 1024;
     plan.gather_capacity = plan.nucleus ? 8192 : 4096;
     if (!plan.nucleus && plan.k_need < kPartCap) {
@@ -83,7 +88,8 @@ inline void fill_scan_settings(ScanParams& sp, const psx_sampling_config* c, con
 }
 
 // The survivor stage over what a row pass with `sp` leaves behind.  `logits` (with its stride) lets a
-// plan without a top-k overlay its shared-memory arrays; pass nullptr to keep them apart.
+// plan without a top-k overlay its shared-memory arrays, and lets any plan decide from the row itself
+// the rows its candidate lists cannot; pass nullptr when the whole row is not on this GPU.
 inline void fill_merge_params(MergeParams& mp, const ScanParams& sp, const Plan& plan, const psx_sampling_config* c,
                               int64_t rows, int64_t vocab, const double* uniforms, int64_t* tokens, float* log_probs,
                               int32_t* row_status, psx_row_diag* diag, const float* logits, int64_t row_stride) {
@@ -115,11 +121,17 @@ inline void fill_merge_params(MergeParams& mp, const ScanParams& sp, const Plan&
     mp.diag = diag;
     mp.sort_capacity = plan.sort_capacity;
     mp.gather_capacity = plan.gather_capacity;
-    if (plan.nucleus && logits != nullptr) {  // the wide plan: candidates and sort arrays share their shared memory
+    if (logits != nullptr) {
         mp.logits = logits;
         mp.logits_row_stride = row_stride;
         mp.logits_col_begin = 0;
-        mp.overlay = 1;
+        mp.overlay = plan.nucleus ? 1 : 0;  // the wide plan: candidates and sort arrays share their shared memory
+        // what it takes to decide a row from the row itself, should the lists not do
+        mp.history_ids = sp.apply_penalty ? sp.history_ids : nullptr;
+        mp.history_offsets = sp.history_offsets;
+        mp.banned_ids = sp.banned_ids;
+        mp.num_banned = sp.num_banned;
+        mp.general = plan.lists_cannot_bound ? 2 : 1;
     }
 }
 
