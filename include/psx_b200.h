@@ -238,7 +238,9 @@ PSX_API psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream, const v
  * a row-major (rows, cols) device matrix, the k largest (or smallest) values in rank order and
  * their column indices as whole-number floats.  NaN ranks above every number; equal values keep
  * the lower column first.  Requires 1 <= k <= cols <= 2^24 (top_k() validates the same,
- * src/top_k.cpp:10-21).  Asynchronous on `stream`. */
+ * src/top_k.cpp:10-21).  Up to k = 4096 the k winners are selected and sorted in shared memory;
+ * beyond that the rows are sorted whole in the context's scratch memory.  Asynchronous on
+ * `stream`. */
 PSX_API psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream, const float* in, float* values, float* indices,
                                size_t rows, size_t cols, size_t k, int largest);
 

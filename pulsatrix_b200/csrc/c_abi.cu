@@ -58,7 +58,7 @@ struct psx_ctx {
     bool merge_configured = false;
     bool scan_configured = false;
     // row-pass scratch
-    Buffer stats, part_counts, candidates, banned;
+    Buffer stats, part_counts, candidates, banned, sort_keys;
     // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
     Buffer surv_cols, surv_vals, surv_counts, pl_tokens, pl_log_probs, pl_status;
     // staging of the host entry point
@@ -221,7 +221,7 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (Buffer* b : {&ctx->stats, &ctx->part_counts, &ctx->candidates, &ctx->banned, &ctx->surv_cols, &ctx->surv_vals,
+    for (Buffer* b : {&ctx->stats, &ctx->part_counts, &ctx->candidates, &ctx->banned, &ctx->sort_keys, &ctx->surv_cols, &ctx->surv_vals,
                       &ctx->surv_counts, &ctx->pl_tokens, &ctx->pl_log_probs, &ctx->pl_status, &ctx->h_logits, &ctx->h_history,
                       &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
@@ -716,14 +716,17 @@ psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream_ptr, const float* in, 
     if (cols > (size_t(1) << 24)) {  // src/top_k.cpp:19-21
         return fail(PSX_ERR_BAD_ARGUMENT, "top_k: last dimension exceeds 2^24, beyond exact float indices");
     }
-    if (k > (size_t)psx::kTopKMax) {
-        return fail(PSX_ERR_UNSUPPORTED, "psx_b200: top_k_rows holds at most " + std::to_string(psx::kTopKMax) +
-                                             " entries per row on the device");
-    }
     if (rows > 0x7FFFFFFFull) return fail(PSX_ERR_UNSUPPORTED, "psx_b200: too many rows for one launch");
     if (!in || !values || !indices) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
+    if (k > (size_t)psx::kTopKMax) {  // more than one CTA sorts in shared memory: the rows are sorted whole, in scratch
+        size_t batch = 0;
+        if (psx_status s = reserve(ctx->sort_keys, psx::sort_rows_scratch_bytes(rows, cols, &batch))) return s;
+        PSX_CUDA(psx::launch_sort_rows(in, values, indices, rows, cols, k, largest != 0, ctx->sort_keys.ptr, stream));
+        ctx->launches += (rows + batch - 1) / batch;
+        return PSX_OK;
+    }
     PSX_CUDA(psx::launch_topk_rows(in, values, indices, rows, cols, k, largest != 0, stream));
     ++ctx->launches;
     return PSX_OK;

@@ -457,7 +457,124 @@ __global__ void __launch_bounds__(kThreads, 4) topk_rows_kernel(const TopKParams
     }
 }
 
+// ---- k beyond what one CTA's shared memory sorts: the whole row is sorted in global memory -----------
+// One CTA of 1024 threads per row: the row becomes 64-bit keys (rank key, ~column), padded to a power
+// of two with keys below every real one, in scratch memory; a bitonic network sorts them, descending --
+// steps that reach across more than 4096 keys run over global memory, all the others over one tile of
+// 4096 keys at a time in shared memory --, and the first k keys are the answer, in rank order: equal
+// values keep the lower column first because ~column is part of the key.
+constexpr int kSortThreads = 1024;
+constexpr int kSortTile = 4096;
+
+__device__ __forceinline__ void tile_steps(u64* tile, uint32_t tile_base, uint32_t k2, uint32_t j_from) {
+    for (uint32_t j = j_from; j > 0; j >>= 1) {
+        for (uint32_t q = threadIdx.x; q < kSortTile / 2; q += kSortThreads) {
+            const uint32_t i = ((q & ~(j - 1)) << 1) | (q & (j - 1)), l = i | j;
+            const bool descending = ((tile_base + i) & k2) == 0;
+            const u64 a = tile[i], b = tile[l];
+            if (descending ? a < b : a > b) {
+                tile[i] = b;
+                tile[l] = a;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <bool kLargest>
+__global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const float* __restrict__ in, float* values, float* indices,
+                                                                 u64* scratch, size_t cols, size_t k, uint32_t n_pad,
+                                                                 size_t first_row) {
+    __shared__ u64 tile[kSortTile];
+    const size_t row = first_row + blockIdx.x;
+    const float* x = in + row * cols;
+    u64* keys = scratch + (size_t)blockIdx.x * n_pad;
+    const uint32_t tile_len = min((uint32_t)kSortTile, n_pad);
+    // every tile on its own: keys from the row, all steps up to the tile's length
+    for (uint32_t base = 0; base < n_pad; base += kSortTile) {
+        for (uint32_t t = threadIdx.x; t < tile_len; t += kSortThreads) {
+            const size_t i = (size_t)base + t;
+            tile[t] = i < cols ? (((u64)rank_key(x[i], kLargest) << 32) | (uint32_t)~(uint32_t)i) : 0ull;
+        }
+        __syncthreads();
+        for (uint32_t k2 = 2; k2 <= tile_len; k2 <<= 1) {
+            for (uint32_t j = k2 >> 1; j > 0; j >>= 1) {
+                for (uint32_t q = threadIdx.x; q < tile_len / 2; q += kSortThreads) {
+                    const uint32_t i = ((q & ~(j - 1)) << 1) | (q & (j - 1)), l = i | j;
+                    const bool descending = ((base + i) & k2) == 0;
+                    const u64 a = tile[i], b = tile[l];
+                    if (descending ? a < b : a > b) {
+                        tile[i] = b;
+                        tile[l] = a;
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        for (uint32_t t = threadIdx.x; t < tile_len; t += kSortThreads) keys[base + t] = tile[t];
+        __syncthreads();
+    }
+    // the longer steps over global memory, the rest of each merge over the tiles again
+    for (uint32_t k2 = 2 * kSortTile; k2 <= n_pad && k2 != 0; k2 <<= 1) {
+        for (uint32_t j = k2 >> 1; j >= (uint32_t)kSortTile; j >>= 1) {
+            for (uint32_t q = threadIdx.x; q < n_pad / 2; q += kSortThreads) {
+                const uint32_t i = ((q & ~(j - 1)) << 1) | (q & (j - 1)), l = i | j;
+                const bool descending = (i & k2) == 0;
+                const u64 a = keys[i], b = keys[l];
+                if (descending ? a < b : a > b) {
+                    keys[i] = b;
+                    keys[l] = a;
+                }
+            }
+            __syncthreads();  // (orders this block's global writes before its next reads)
+        }
+        for (uint32_t base = 0; base < n_pad; base += kSortTile) {
+            for (uint32_t t = threadIdx.x; t < kSortTile; t += kSortThreads) tile[t] = keys[base + t];
+            __syncthreads();
+            tile_steps(tile, base, k2, kSortTile / 2);
+            for (uint32_t t = threadIdx.x; t < kSortTile; t += kSortThreads) keys[base + t] = tile[t];
+            __syncthreads();
+        }
+    }
+    for (size_t jj = threadIdx.x; jj < k; jj += kSortThreads) {
+        const uint32_t col = ~(uint32_t)keys[jj];
+        values[row * k + jj] = x[col];
+        indices[row * k + jj] = (float)col;
+    }
+}
+
 }  // namespace
+
+size_t sort_rows_scratch_bytes(size_t rows, size_t cols, size_t* rows_per_launch) {
+    size_t n_pad = 1;
+    while (n_pad < cols) n_pad <<= 1;
+    const size_t budget = (size_t)256 << 20;  // scratch of one launch
+    size_t batch = budget / (n_pad * 8);
+    batch = batch < 1 ? 1 : batch > rows ? rows : batch;
+    if (rows_per_launch) *rows_per_launch = batch;
+    return batch * n_pad * 8;
+}
+
+cudaError_t launch_sort_rows(const float* in, float* values, float* indices, size_t rows, size_t cols, size_t k, bool largest,
+                             void* scratch, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    size_t batch = 0;
+    sort_rows_scratch_bytes(rows, cols, &batch);
+    uint32_t n_pad = 1;
+    while (n_pad < cols) n_pad <<= 1;
+    for (size_t first = 0; first < rows; first += batch) {
+        const unsigned blocks = (unsigned)(rows - first < batch ? rows - first : batch);
+        if (largest) {
+            sort_rows_kernel<true><<<blocks, kSortThreads, 0, stream>>>(in, values, indices, static_cast<u64*>(scratch), cols, k,
+                                                                       n_pad, first);
+        } else {
+            sort_rows_kernel<false><<<blocks, kSortThreads, 0, stream>>>(in, values, indices, static_cast<u64*>(scratch), cols, k,
+                                                                        n_pad, first);
+        }
+        if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
 
 cudaError_t launch_topk_rows(const float* in, float* values, float* indices, size_t rows, size_t cols, size_t k,
                              bool largest, cudaStream_t stream) {
