@@ -736,8 +736,14 @@ def run_top_k(args):
     import torch
     import pulsatrix_b200 as psx
 
+    import ctypes as C
     ctx = psx.Context(0)
     results = []
+    harness = ROOT / "oracle" / "_ref" / "libpsx_refcuda.so"  # the reference's own CUDA backend, compiled in place
+    reference = None
+    if harness.exists():
+        reference = C.CDLL(str(harness))
+        reference.psxrefcuda_time_top_k_rows.restype = C.c_double
     for rows, cols, k in TOP_K_SHAPES:
         count = max(2, (2 * L2_BYTES) // (rows * cols * 4) + 1)
         xs = [torch.randn(rows, cols, device="cuda") for _ in range(count)]
@@ -752,8 +758,15 @@ def run_top_k(args):
         end.record()
         torch.cuda.synchronize()
         ms = begin.elapsed_time(end) / steps
-        results.append({"rows": rows, "cols": cols, "k": k, "us": ms * 1e3, "rows_per_s": rows / (ms * 1e-3),
-                        "input_gbs": rows * cols * 4 / (ms * 1e-3) / 1e9})
+        entry = {"rows": rows, "cols": cols, "k": k, "us": ms * 1e3, "rows_per_s": rows / (ms * 1e-3),
+                 "input_gbs": rows * cols * 4 / (ms * 1e-3) / 1e9}
+        if reference is not None and rows <= 4096:
+            # the reference's unmodified CUDABackend::top_k_rows on this GPU (one thread per row), each
+            # call synchronised as its backend does; beside it the same call through the override
+            entry["reference_cuda_us"] = reference.psxrefcuda_time_top_k_rows(None, C.c_int64(rows), C.c_int64(cols), C.c_int64(k), C.c_int(2))
+            entry["through_override_us"] = reference.psxrefcuda_time_top_k_rows(str(psx.library_path()).encode(), C.c_int64(rows),
+                                                                               C.c_int64(cols), C.c_int64(k), C.c_int(5))
+        results.append(entry)
         del xs
     peak, peak_kind = measured_hbm_peak()
     emit({"metric": "top_k_rows rows/s", "unit": "rows/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
