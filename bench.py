@@ -87,6 +87,8 @@ def parse_args():
     ap.add_argument("--contexts", type=int, default=4,
                     help="sampler contexts in flight per GPU (one stream and one scratch each; steps go round-robin)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
+    ap.add_argument("--lm-head", action="store_true",
+                    help="time the device head + sampling step on decode-sized batches instead (one GPU; prints its own JSON line)")
     ap.add_argument("--softmax", action="store_true",
                     help="time psx_b200_softmax_rows / logsumexp_rows on a few shapes instead (one GPU; prints its own JSON line)")
     ap.add_argument("--top-k", action="store_true",
@@ -812,14 +814,62 @@ def run_softmax(args):
           "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
 
 
+LM_HEAD_SHAPES = [(1, 2048, 151936), (8, 2048, 151936), (64, 2048, 151936), (1, 576, 49152), (8, 4096, 128256)]
+
+
+def run_lm_head(args):
+    """Head and sampling in one call (psx_b200_lm_head_sample_rows) on decode-sized batches: the weight
+    matrix (vocab x d, fp32) is the traffic, 4 * vocab * d bytes per call; beside it the same step with
+    the logits coming from the host as the reference's adapter hands them over (src/generation.cpp:248-256)."""
+    import torch
+    import pulsatrix_b200 as psx
+
+    ctx = psx.Context(0)
+    results = []
+    peak, peak_kind = measured_hbm_peak()
+    for rows, d, vocab in LM_HEAD_SHAPES:
+        weight = torch.randn((vocab, d), device="cuda") * 0.05
+        hidden = torch.randn((rows, d), device="cuda")
+        hist = torch.randint(0, vocab, (rows * 64,), device="cuda", dtype=torch.int64)
+        offsets = torch.arange(rows + 1, device="cuda", dtype=torch.int64) * 64
+        cfg = psx.SamplingConfig.make(do_sample=True, temperature=0.8, top_k=50, top_p=0.9, repetition_penalty=1.1)
+        u = torch.from_numpy(psx.uniforms_mt19937_64(np.arange(rows, dtype=np.uint64))).cuda()
+        out = ctx.alloc_outputs(rows)
+        for _ in range(max(args.warmup, 3)):
+            ctx.lm_head_sample_rows(hidden, weight, hist, offsets, cfg, u, out=out)
+        torch.cuda.synchronize()
+        steps = max(3, min(args.steps, 30))
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(steps):
+            ctx.lm_head_sample_rows(hidden, weight, hist, offsets, cfg, u, out=out)
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        # the reference's hand-over: logits on the host, every step
+        logits = ctx.lm_head_logits(hidden, weight).cpu().pin_memory()
+        h_hist, h_off, h_u = hist.cpu().pin_memory(), offsets.cpu().pin_memory(), u.cpu().pin_memory()
+        ctx.sample_rows_host(logits, h_hist, h_off, cfg, h_u)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            ctx.sample_rows_host(logits, h_hist, h_off, cfg, h_u)
+        host_ms = (time.perf_counter() - t0) * 1e3 / steps
+        results.append({"rows": rows, "d_model": d, "vocab": vocab, "us": ms * 1e3, "rows_per_s": rows / (ms * 1e-3),
+                        "weight_gbs": 4 * vocab * d / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": 4 * vocab * d / (ms * 1e-3) / 1e9 / peak,
+                        "sampling_from_host_logits_us": host_ms * 1e3})
+        del weight
+    emit({"metric": "lm head + sampling step", "unit": "us per call", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
+          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
+
+
 def main():
     args = parse_args()
     keep_stdout_for_the_result()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.top_k or args.softmax:
+    if args.top_k or args.softmax or args.lm_head:
         if rank == 0:
-            (run_top_k if args.top_k else run_softmax)(args)
+            (run_top_k if args.top_k else run_softmax if args.softmax else run_lm_head)(args)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)

@@ -244,6 +244,28 @@ PSX_API psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream, const v
 PSX_API psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream, const float* in, float* values, float* indices,
                                size_t rows, size_t cols, size_t k, int largest);
 
+/* The language-model head on the device: logits[m][j] = sum_p hidden[m][p] * w_j[p], what
+ * TiedLMHeadModule::forward computes with gemm_ex(hidden, E^T) (src/tied_lm_head_module.cpp:31-53;
+ * an untied head is a bias-free Linear: gemm(hidden, W), src/linear_module.cpp) right before
+ * Generate() samples (src/generation.cpp:251-256 -- where the reference copies the row to the host).
+ * hidden: device, rows x d fp32, contiguous.  weight: device fp32, vocab x d (PSX_HEAD_VOCAB_BY_D, the
+ * tied embedding) or d x vocab (PSX_HEAD_D_BY_VOCAB, a Linear's weight).  Every logit is one float
+ * accumulator that takes its products in ascending p, product and sum each rounded, as the
+ * reference's CPU backend forms it (src/cpu_backend.cpp:188-196): the logits are the reference's bit
+ * for bit.  psx_b200_lm_head_logits writes them to `logits` (row m at logits + m * row_stride);
+ * psx_b200_lm_head_sample_rows keeps them in the context's scratch and samples them at once with
+ * psx_b200_sample_rows (same remaining arguments, same outputs): the row never leaves the device. */
+enum { PSX_HEAD_VOCAB_BY_D = 0, PSX_HEAD_D_BY_VOCAB = 1 };
+PSX_API psx_status psx_b200_lm_head_logits(psx_ctx* ctx, void* stream, const float* hidden, int64_t rows, int64_t d,
+                                           const float* weight, int64_t vocab, int32_t weight_layout, float* logits,
+                                           int64_t row_stride);
+PSX_API psx_status psx_b200_lm_head_sample_rows(psx_ctx* ctx, void* stream, const float* hidden, int64_t rows, int64_t d,
+                                                const float* weight, int64_t vocab, int32_t weight_layout,
+                                                const int64_t* history_ids, const int64_t* history_offsets,
+                                                const psx_sampling_config* config, const double* uniforms,
+                                                int64_t* tokens, float* log_probs, int32_t* row_status,
+                                                psx_row_diag* diag);
+
 /* Replace DeviceBackend::softmax_rows, logsumexp_rows and gather_rows
  * (include/pulsatrix/device_backend.hpp:456,465,596; CUDA implementations src/cuda_backend.cu with
  * the kernels src/gpu_kernels.cuh:315-365,665; CPU semantics src/cpu_backend.cpp:292-338,459-466)

@@ -9,6 +9,7 @@
 
 #include <cstdint>
 #include <functional>
+#include <memory>
 #include <optional>
 #include <vector>
 
@@ -20,10 +21,16 @@ namespace pulsatrix {
 using NextTokenLogitsFn = std::function<std::vector<float>(const std::vector<int64_t>& tokens)>;
 
 /** The same for a model whose logits stay on the GPU: returns a device pointer to `vocab` floats
- *  that stays valid until the next call.  Not in the reference (its adapter copies to the host). */
+ *  that stays valid until the next call.  Not in the reference (its adapter copies to the host).
+ *  `stream` is the CUDA stream (a cudaStream_t) the model produced the logits on: Generate() orders
+ *  its kernels after everything the model has enqueued there, so the model need not wait for its
+ *  own head.  nullptr says the logits are complete when the model returns (the legacy default
+ *  stream, which synchronises with every blocking stream, is not meant by it).  The logits must live
+ *  on the device that was current when the calling thread first used this library. */
 struct DeviceLogits {
     const float* data = nullptr;
     int64_t vocab = 0;
+    void* stream = nullptr;
 };
 using DeviceNextTokenLogitsFn = std::function<DeviceLogits(const std::vector<int64_t>& tokens)>;
 
@@ -68,5 +75,43 @@ PULSATRIX_API void ProcessLogits(std::vector<float>& logits, const std::vector<i
 [[nodiscard]] PULSATRIX_API GenerationResult Generate(const DeviceNextTokenLogitsFn& model,
                                                       const std::vector<int64_t>& prompt,
                                                       const GenerationConfig& config = {});
+
+/** The language-model head on the GPU: logits = hidden . W^T, what TiedLMHeadModule::forward
+ *  (src/tied_lm_head_module.cpp:31-53) or an untied Linear head computes, with the weights resident
+ *  on the device and the logits left there.  Every logit is accumulated in ascending feature order
+ *  with product and sum each rounded to float, as the reference's CPU backend does
+ *  (src/cpu_backend.cpp:188-196): the logits equal the reference's bit for bit.  Not in the
+ *  reference as a class of its own (there the head is a Module of the model). */
+class PULSATRIX_API DeviceLmHead {
+public:
+    /** @param weight vocab x d_model row-major when @p tied (the embedding table), else d_model x vocab
+     *         (a Linear's weight).
+     *  @throws std::invalid_argument when the sizes do not match. */
+    DeviceLmHead(const std::vector<float>& weight, int64_t vocab, int64_t d_model, bool tied);
+    ~DeviceLmHead();
+    DeviceLmHead(const DeviceLmHead&) = delete;
+    DeviceLmHead& operator=(const DeviceLmHead&) = delete;
+    [[nodiscard]] int64_t vocab() const { return vocab_; }
+    [[nodiscard]] int64_t d_model() const { return d_model_; }
+    /** The logits of one hidden state (d_model floats, host): copied to the device, multiplied there;
+     *  the result stays on the device, on the calling thread's context stream. */
+    [[nodiscard]] DeviceLogits logits(const std::vector<float>& hidden);
+
+private:
+    int64_t vocab_, d_model_;
+    bool tied_;
+    float* weight_ = nullptr;
+    float* hidden_ = nullptr;
+    float* logits_ = nullptr;
+};
+
+/** The model up to the head as generation sees it: token sequence in, the final norm's output at
+ *  the last position out (d_model floats). */
+using HiddenStateFn = std::function<std::vector<float>(const std::vector<int64_t>& tokens)>;
+
+/** A DeviceNextTokenLogitsFn made of a model body and a device head: what replaces the last two
+ *  steps of the reference's cached adapter, head and copy to the host (src/generation.cpp:251-256).
+ *  The logits never leave the GPU; per token only d_model floats go up and a token id comes back. */
+[[nodiscard]] PULSATRIX_API DeviceNextTokenLogitsFn MakeDeviceLmHeadLogits(HiddenStateFn body, std::shared_ptr<DeviceLmHead> head);
 
 }  // namespace pulsatrix

@@ -16,6 +16,7 @@
 
 #include "portable_random.hpp"  // private header of the reference, reached with -I<ref>/src
 #include "psx_oracle.h"         // the shared C structs (psxo_config, psxo_step_info, status codes)
+#include "pulsatrix/causal_lm.hpp"
 #include "pulsatrix/cpu_backend.hpp"
 #include "pulsatrix/determinism.hpp"
 #include "pulsatrix/generation.hpp"
@@ -156,6 +157,64 @@ void psxref_logsumexp_rows(const float* in, float* out, int64_t rows, int64_t co
 void psxref_gather_rows(const float* table, const float* indices, float* out, int64_t count, int64_t dim) {
     pulsatrix::CPUBackend cpu;
     cpu.gather_rows(table, indices, out, static_cast<size_t>(count), static_cast<size_t>(dim));
+}
+
+// A tiny Hugging Face model of the reference's own fixtures (tests/fixtures/hf_tiny/<name>), decoded
+// greedily for `steps` tokens after `prompt`: per step the input of the language-model head (the
+// final norm's output at the last position, d floats), the logits the reference's head makes of it
+// (vocab floats) and the token; the head's weight matrix (vocab x d when tied to the embedding, else
+// the Linear's d x vocab); and what Generate() with the KV cache generates (`generated`, the tokens
+// CausalLMTest.GreedyGenerationMatchesTransformers pins).  Buffers are the caller's; 0 on success.
+int psxref_tiny_lm(const char* directory, const int64_t* prompt, int64_t prompt_len, int64_t steps, int64_t* d_out,
+                   int64_t* vocab_out, int32_t* tied_out, float* weight, int64_t weight_capacity, float* hidden,
+                   float* logits, int64_t* tokens, int64_t* generated) {
+    try {
+        pulsatrix::CPUBackend cpu;
+        std::unique_ptr<pulsatrix::CausalLM> model = pulsatrix::LoadCausalLM(directory, &cpu);
+        const int64_t d = model->config().hidden_size, vocab = model->config().vocab_size;
+        *d_out = d;
+        *vocab_out = vocab;
+        const bool tied = model->lm_head() == nullptr;
+        *tied_out = tied ? 1 : 0;
+        pulsatrix::Tensor* w = tied ? model->embed_tokens().named_parameters().front().ref.value
+                                    : model->lm_head()->named_parameters().front().ref.value;
+        const std::vector<float> w_host = w->to_host_vector();
+        if (static_cast<int64_t>(w_host.size()) != d * vocab || d * vocab > weight_capacity) return 3;
+        std::memcpy(weight, w_host.data(), w_host.size() * sizeof(float));
+
+        std::vector<int64_t> sequence(prompt, prompt + prompt_len);
+        const int64_t last_layer = model->num_layers();
+        for (int64_t s = 0; s < steps; ++s) {
+            const int64_t length = static_cast<int64_t>(sequence.size());
+            std::vector<float> last_hidden;
+            model->set_hidden_state_hook([&](int64_t position, const pulsatrix::Tensor& x) {
+                if (position == last_layer) {
+                    const std::vector<float> all = x.to_host_vector();
+                    last_hidden.assign(all.end() - d, all.end());
+                }
+                return x;
+            });
+            const std::vector<float> ids(sequence.begin(), sequence.end());
+            const std::vector<float> out = model->forward(pulsatrix::Tensor(pulsatrix::Shape({1, length}), &cpu, ids)).to_host_vector();
+            model->set_hidden_state_hook({});
+            const float* row = out.data() + (length - 1) * vocab;
+            std::memcpy(logits + s * vocab, row, static_cast<size_t>(vocab) * sizeof(float));
+            const std::vector<float> normed =
+                model->norm().forward(pulsatrix::Tensor(pulsatrix::Shape({1, d}), &cpu, last_hidden)).to_host_vector();
+            std::memcpy(hidden + s * d, normed.data(), static_cast<size_t>(d) * sizeof(float));
+            const int64_t token = std::max_element(row, row + vocab) - row;  // the first maximum
+            tokens[s] = token;
+            sequence.push_back(token);
+        }
+        pulsatrix::GenerationConfig g;
+        g.max_new_tokens = steps;
+        const pulsatrix::GenerationResult r =
+            pulsatrix::Generate(model->next_token_logits(prompt_len + steps + 8), std::vector<int64_t>(prompt, prompt + prompt_len), g);
+        for (int64_t s = 0; s < steps; ++s) generated[s] = s < static_cast<int64_t>(r.new_tokens.size()) ? r.new_tokens[s] : -1;
+        return 0;
+    } catch (const std::exception&) {
+        return 2;
+    }
 }
 
 // top_k() on a (rows, cols) CPU tensor: 0 on success, 1 when it throws std::invalid_argument.

@@ -17,7 +17,7 @@ EXPORTS = [
     "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready",
     "psx_b200_ctx_set_wait_limit", "psx_b200_test_short_copy", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_shard_merge_rows",
-    "psx_b200_top_k_rows", "psx_b200_softmax_rows", "psx_b200_logsumexp_rows", "psx_b200_gather_rows",
+    "psx_b200_top_k_rows", "psx_b200_lm_head_logits", "psx_b200_lm_head_sample_rows", "psx_b200_softmax_rows", "psx_b200_logsumexp_rows", "psx_b200_gather_rows",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
 
@@ -114,6 +114,9 @@ def library():
         lib.psx_b200_shard_merge.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_merge_rows.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_top_k_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int]
+        lib.psx_b200_lm_head_logits.argtypes = [ptr, ptr, ptr, i64, i64, ptr, i64, C.c_int32, ptr, i64]
+        lib.psx_b200_lm_head_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, ptr, i64, C.c_int32, ptr, ptr, ptr, ptr, ptr, ptr,
+                                                     ptr, ptr]
         lib.psx_b200_softmax_rows.argtypes = [ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
         lib.psx_b200_logsumexp_rows.argtypes = [ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
         lib.psx_b200_gather_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
@@ -365,6 +368,34 @@ class Context:
         _check(self._lib.psx_b200_top_k_rows(self._ctx, C.c_void_p(stream), _dptr(x), _dptr(values), _dptr(indices),
                                              rows, cols, k if k >= 0 else 0, int(largest)))
         return values, indices
+
+    # ---- the language-model head -------------------------------------------------------------------------
+    def lm_head_logits(self, hidden, weight, vocab_by_d=True, out=None, stream=None):
+        """hidden: cuda float32 (rows, d); weight: (vocab, d) when vocab_by_d else (d, vocab).  Returns (rows, vocab)."""
+        import torch
+        rows, d = hidden.shape
+        vocab = weight.shape[0] if vocab_by_d else weight.shape[1]
+        out = torch.empty((rows, vocab), dtype=torch.float32, device=hidden.device) if out is None else out
+        if stream is None:
+            stream = torch.cuda.current_stream(hidden.device).cuda_stream
+        _check(self._lib.psx_b200_lm_head_logits(self._ctx, C.c_void_p(stream), _dptr(hidden), rows, d, _dptr(weight), vocab,
+                                                 0 if vocab_by_d else 1, _dptr(out), out.stride(0)))
+        return out
+
+    def lm_head_sample_rows(self, hidden, weight, history_ids, history_offsets, config, uniforms, vocab_by_d=True, out=None,
+                            stream=None):
+        """The head and the sampling step in one call: the logits stay in the context's scratch."""
+        import torch
+        rows, d = hidden.shape
+        vocab = weight.shape[0] if vocab_by_d else weight.shape[1]
+        out = out or self.alloc_outputs(rows)
+        if stream is None:
+            stream = torch.cuda.current_stream(hidden.device).cuda_stream
+        _check(self._lib.psx_b200_lm_head_sample_rows(
+            self._ctx, C.c_void_p(stream), _dptr(hidden), rows, d, _dptr(weight), vocab, 0 if vocab_by_d else 1,
+            _dptr(history_ids), _dptr(history_offsets), C.addressof(config), _dptr(uniforms), _dptr(out["tokens"]),
+            _dptr(out["log_probs"]), _dptr(out["status"]), _dptr(out["diag"])))
+        return out
 
     # ---- row primitives ---------------------------------------------------------------------------------
     def softmax_rows(self, x, out=None, stream=None):

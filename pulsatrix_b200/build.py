@@ -15,7 +15,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libpsx_b200.so"
-SOURCES = ["c_abi.cu", "scan_rows.cu", "merge_rows.cu", "topk_rows.cu", "shard_records.cu", "no_alloc.cu", "read_floor.cu", "process_rows.cu", "row_ops.cu"]
+SOURCES = ["c_abi.cu", "scan_rows.cu", "merge_rows.cu", "topk_rows.cu", "shard_records.cu", "no_alloc.cu", "read_floor.cu", "process_rows.cu", "row_ops.cu", "lm_head.cu"]
 HOST_SOURCES = ["determinism.cpp", "sampler.cpp", "backend.cpp", "generation.cpp"]  # the C++ API over the C ABI
 CPP_TEST = PACKAGE.parent / "tests" / "cpp" / "host_api_test"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=true",
@@ -82,8 +82,10 @@ def build_cpp_test() -> Path:
     """The C++ test program of the host API (tests/cpp/host_api_test.cpp), linked against the library."""
     source = CPP_TEST.with_suffix(".cpp")
     if source.exists():
-        subprocess.run(["g++", "-std=c++17", "-O1", "-I", str(PACKAGE.parent / "include"), str(source), "-o", str(CPP_TEST),
-                        "-L", str(PACKAGE), "-lpsx_b200", f"-Wl,-rpath,{PACKAGE}", "-Wl,-rpath,$ORIGIN/../../pulsatrix_b200"],
+        cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+        subprocess.run(["g++", "-std=c++17", "-O1", "-ffp-contract=off", "-I", str(PACKAGE.parent / "include"),
+                        "-I", str(cuda / "include"), str(source), "-o", str(CPP_TEST), "-L", str(PACKAGE), "-lpsx_b200",
+                        "-L", str(cuda / "lib64"), "-lcudart", f"-Wl,-rpath,{PACKAGE}", "-Wl,-rpath,$ORIGIN/../../pulsatrix_b200"],
                        check=True)
     return CPP_TEST
 

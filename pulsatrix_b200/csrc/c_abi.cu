@@ -11,6 +11,7 @@
 #include <string>
 #include <vector>
 
+#include "lm_head.cuh"
 #include "merge_rows.cuh"
 #include "process_rows.cuh"
 #include "row_ops.cuh"
@@ -58,7 +59,7 @@ struct psx_ctx {
     bool merge_configured = false;
     bool scan_configured = false;
     // row-pass scratch
-    Buffer stats, part_counts, candidates, banned, sort_keys;
+    Buffer stats, part_counts, candidates, banned, sort_keys, head_logits;
     // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
     Buffer surv_cols, surv_vals, surv_counts, pl_tokens, pl_log_probs, pl_status;
     // staging of the host entry point
@@ -221,7 +222,7 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (Buffer* b : {&ctx->stats, &ctx->part_counts, &ctx->candidates, &ctx->banned, &ctx->sort_keys, &ctx->surv_cols, &ctx->surv_vals,
+    for (Buffer* b : {&ctx->stats, &ctx->part_counts, &ctx->candidates, &ctx->banned, &ctx->sort_keys, &ctx->head_logits, &ctx->surv_cols, &ctx->surv_vals,
                       &ctx->surv_counts, &ctx->pl_tokens, &ctx->pl_log_probs, &ctx->pl_status, &ctx->h_logits, &ctx->h_history,
                       &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
@@ -730,6 +731,60 @@ psx_status psx_b200_top_k_rows(psx_ctx* ctx, void* stream_ptr, const float* in, 
     PSX_CUDA(psx::launch_topk_rows(in, values, indices, rows, cols, k, largest != 0, stream));
     ++ctx->launches;
     return PSX_OK;
+}
+
+namespace {
+psx_status check_head(psx_ctx* ctx, const float* hidden, int64_t rows, int64_t d, const float* weight, int64_t vocab,
+                      int32_t weight_layout) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (rows < 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: rows must not be negative");
+    if (d <= 0 || vocab <= 0) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the head needs d_model > 0 and vocab > 0");
+    if (weight_layout != PSX_HEAD_VOCAB_BY_D && weight_layout != PSX_HEAD_D_BY_VOCAB) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: unknown weight layout");
+    }
+    if (rows > 0 && (!hidden || !weight)) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    return PSX_OK;
+}
+}  // namespace
+
+psx_status psx_b200_lm_head_logits(psx_ctx* ctx, void* stream_ptr, const float* hidden, int64_t rows, int64_t d,
+                                   const float* weight, int64_t vocab, int32_t weight_layout, float* logits,
+                                   int64_t row_stride) {
+    if (psx_status s = check_head(ctx, hidden, rows, d, weight, vocab, weight_layout)) return s;
+    if (rows == 0) return PSX_OK;
+    if (!logits || row_stride < vocab) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: logits is null or row_stride is smaller than the row");
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    PSX_CUDA(psx::launch_lm_head(hidden, rows, d, weight, vocab, weight_layout == PSX_HEAD_VOCAB_BY_D, logits, row_stride,
+                                 static_cast<cudaStream_t>(stream_ptr)));
+    ctx->launches += (uint64_t)((rows + 63) / 64);
+    return PSX_OK;
+}
+
+psx_status psx_b200_lm_head_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* hidden, int64_t rows, int64_t d,
+                                        const float* weight, int64_t vocab, int32_t weight_layout,
+                                        const int64_t* history_ids, const int64_t* history_offsets,
+                                        const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
+                                        float* log_probs, int32_t* row_status, psx_row_diag* diag) {
+    if (psx_status s = check_head(ctx, hidden, rows, d, weight, vocab, weight_layout)) return s;
+    if (psx_status s = check_config(config)) return s;
+    if (rows == 0) return PSX_OK;
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    const int64_t stride = (vocab + 3) / 4 * 4;  // rows of the scratch start on 16-byte boundaries
+    if (psx_status s = reserve(ctx->head_logits, (size_t)rows * stride * sizeof(float))) return s;
+    float* logits = static_cast<float*>(ctx->head_logits.ptr);
+    PSX_CUDA(psx::launch_lm_head(hidden, rows, d, weight, vocab, weight_layout == PSX_HEAD_VOCAB_BY_D, logits, stride,
+                                 static_cast<cudaStream_t>(stream_ptr)));
+    ctx->launches += (uint64_t)((rows + 63) / 64);
+    // The logits were written by the kernel just enqueued: the row pass must wait for it whatever the
+    // caller promised about its own inputs.
+    struct RestorePromise {
+        psx_ctx* ctx;
+        bool saved;
+        ~RestorePromise() { ctx->inputs_ready = saved; }
+    } restore{ctx, ctx->inputs_ready};
+    ctx->inputs_ready = false;
+    return psx_b200_sample_rows(ctx, stream_ptr, logits, rows, vocab, stride, history_ids, history_offsets, config, uniforms,
+                                tokens, log_probs, row_status, diag);
 }
 
 psx_status psx_b200_softmax_rows(psx_ctx* ctx, void* stream_ptr, const float* in, float* out, size_t rows, size_t cols) {

@@ -26,7 +26,9 @@ struct ContextHolder {
     float* log_prob = nullptr;
     int32_t* status = nullptr;
     int64_t* offsets = nullptr;
+    cudaEvent_t produced = nullptr;  // marks what a model has enqueued on its own stream
     ~ContextHolder() {
+        if (produced) cudaEventDestroy(produced);
         for (void* p : {(void*)history, (void*)uniform, (void*)token, (void*)log_prob, (void*)status, (void*)offsets}) {
             if (p) cudaFree(p);
         }
@@ -157,6 +159,19 @@ GenerationResult Generate(const DeviceNextTokenLogitsFn& model, const std::vecto
     return run_loop(prompt, config, [&](const std::vector<int64_t>& tokens, int64_t n, double u, int64_t& token, float& log_prob) {
         const DeviceLogits logits = model(tokens);
         if (!logits.data || logits.vocab <= 0) throw std::invalid_argument("Generate: the model returned no logits");
+        if (n == 0) {  // the row must live on this thread's device
+            cudaPointerAttributes where{};
+            int device = -1;
+            if (cudaPointerGetAttributes(&where, logits.data) == cudaSuccess && cudaGetDevice(&device) == cudaSuccess &&
+                where.type == cudaMemoryTypeDevice && where.device != device) {
+                throw std::invalid_argument("Generate: the logits live on another device than this thread's");
+            }
+        }
+        if (logits.stream && logits.stream != static_cast<void*>(stream)) {  // after whatever the model enqueued there
+            if (!holder.produced) cuda(cudaEventCreateWithFlags(&holder.produced, cudaEventDisableTiming));
+            cuda(cudaEventRecord(holder.produced, static_cast<cudaStream_t>(logits.stream)));
+            cuda(cudaStreamWaitEvent(stream, holder.produced, 0));
+        }
         if (tokens.size() > holder.history_capacity) {  // grow and start over
             if (holder.history) cuda(cudaFree(holder.history));
             holder.history_capacity = std::max<size_t>(2 * tokens.size(), 1024);
@@ -183,6 +198,50 @@ GenerationResult Generate(const DeviceNextTokenLogitsFn& model, const std::vecto
         if (status == PSX_ROW_ALL_REMOVED) throw std::invalid_argument("Generate: every token was removed");
         if (status != PSX_ROW_OK) throw std::runtime_error("psx_b200: the device path declined the row (status " + std::to_string(status) + ")");
     });
+}
+
+DeviceLmHead::DeviceLmHead(const std::vector<float>& weight, int64_t vocab, int64_t d_model, bool tied)
+    : vocab_(vocab), d_model_(d_model), tied_(tied) {
+    if (vocab <= 0 || d_model <= 0 || static_cast<int64_t>(weight.size()) != vocab * d_model) {
+        throw std::invalid_argument("DeviceLmHead: the weight must hold vocab * d_model values");
+    }
+    thread_context();  // (sets up the device's context)
+    auto cuda = [](cudaError_t e) {
+        if (e != cudaSuccess) throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(e));
+    };
+    cuda(cudaMalloc(&weight_, weight.size() * sizeof(float)));
+    cuda(cudaMalloc(&hidden_, static_cast<size_t>(d_model) * sizeof(float)));
+    cuda(cudaMalloc(&logits_, static_cast<size_t>((vocab + 3) / 4 * 4) * sizeof(float)));
+    cuda(cudaMemcpy(weight_, weight.data(), weight.size() * sizeof(float), cudaMemcpyHostToDevice));
+}
+
+DeviceLmHead::~DeviceLmHead() {
+    for (float* p : {weight_, hidden_, logits_}) {
+        if (p) cudaFree(p);
+    }
+}
+
+DeviceLogits DeviceLmHead::logits(const std::vector<float>& hidden) {
+    if (static_cast<int64_t>(hidden.size()) != d_model_) {
+        throw std::invalid_argument("DeviceLmHead: the hidden state must hold d_model values");
+    }
+    ContextHolder& holder = thread_context();
+    cudaStream_t stream = static_cast<cudaStream_t>(psx_b200_ctx_stream(holder.ctx));
+    // (the copy reads pageable host memory: it has left `hidden` when the call returns)
+    if (cudaMemcpyAsync(hidden_, hidden.data(), hidden.size() * sizeof(float), cudaMemcpyHostToDevice, stream) != cudaSuccess) {
+        throw std::runtime_error("CUDA error: copying the hidden state");
+    }
+    const psx_status s = psx_b200_lm_head_logits(holder.ctx, stream, hidden_, 1, d_model_, weight_, vocab_,
+                                                 tied_ ? PSX_HEAD_VOCAB_BY_D : PSX_HEAD_D_BY_VOCAB, logits_, vocab_);
+    if (s != PSX_OK) raise(s);
+    return DeviceLogits{logits_, vocab_, stream};
+}
+
+DeviceNextTokenLogitsFn MakeDeviceLmHeadLogits(HiddenStateFn body, std::shared_ptr<DeviceLmHead> head) {
+    if (!body || !head) throw std::invalid_argument("MakeDeviceLmHeadLogits: the body and the head must not be empty");
+    return [body = std::move(body), head = std::move(head)](const std::vector<int64_t>& tokens) {
+        return head->logits(body(tokens));
+    };
 }
 
 }  // namespace pulsatrix

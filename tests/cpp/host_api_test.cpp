@@ -2,7 +2,10 @@
 // (tests/generation_test.cpp:66-245, tests/top_k_test.cpp:49-144, tests/sampler_test.cpp:20-77,
 // tests/determinism_test.cpp:41-53 of the reference).  No test framework is available offline,
 // so a few macros stand in.  `host_api_test --host-only` runs what needs no GPU.
+#include <cuda_runtime.h>
+
 #include <algorithm>
+#include <memory>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -280,6 +283,87 @@ static void test_device_logits_overload_matches(CUDABackend& gpu) {
     CHECK(a.log_probs == b.log_probs);
 }
 
+// A model that produces its logits asynchronously on a stream of its own and does not wait for them:
+// Generate() must order its kernels after that stream's work (DeviceLogits::stream).
+static void test_device_logits_from_another_stream(CUDABackend& gpu) {
+    const int64_t vocab = 200000;  // a copy long enough to still be in flight when the model returns
+    float* pinned = nullptr;
+    CHECK(cudaMallocHost(&pinned, static_cast<size_t>(vocab) * sizeof(float)) == cudaSuccess);
+    cudaStream_t producer = nullptr;
+    CHECK(cudaStreamCreateWithFlags(&producer, cudaStreamNonBlocking) == cudaSuccess);
+    Tensor row(Shape({vocab}), &gpu, std::vector<float>(static_cast<size_t>(vocab), -50.0f));  // stale contents
+    auto fill = [&](const std::vector<int64_t>& t) {
+        for (int64_t i = 0; i < vocab; ++i) pinned[i] = static_cast<float>((i * 7919 + t.back() * 104729) % 1000) * 0.01f;
+    };
+    NextTokenLogitsFn host_model = [&](const std::vector<int64_t>& t) {
+        fill(t);
+        return std::vector<float>(pinned, pinned + vocab);
+    };
+    DeviceNextTokenLogitsFn device_model = [&](const std::vector<int64_t>& t) {
+        cudaStreamSynchronize(producer);  // (the pinned buffer is free again)
+        fill(t);
+        cudaMemcpyAsync(row.data(), pinned, static_cast<size_t>(vocab) * sizeof(float), cudaMemcpyHostToDevice, producer);
+        return DeviceLogits{row.data(), vocab, producer};  // not waited for
+    };
+    GenerationConfig c;
+    c.max_new_tokens = 12;
+    c.repetition_penalty = 1.5f;
+    const GenerationResult a = Generate(host_model, {5, 6}, c), b = Generate(device_model, {5, 6}, c);
+    CHECK(a.new_tokens == b.new_tokens);
+    CHECK(a.log_probs == b.log_probs);
+    cudaStreamSynchronize(producer);
+    cudaStreamDestroy(producer);
+    cudaFreeHost(pinned);
+}
+
+// The head on the device: Generate(MakeDeviceLmHeadLogits(body, head)) gives the tokens and log-probs
+// of a host model whose head is the reference's loop (one float accumulator per logit, ascending
+// feature order, product and sum each rounded: src/cpu_backend.cpp:188-196).
+static void test_device_lm_head(bool tied) {
+    const int64_t vocab = 3001, d = 97;
+    std::vector<float> weight(static_cast<size_t>(vocab * d));
+    uint32_t s = tied ? 11u : 23u;
+    for (auto& x : weight) { s = s * 1664525u + 1013904223u; x = static_cast<float>(static_cast<int>((s >> 9) % 2001) - 1000) * 0.001f; }
+    HiddenStateFn body = [&](const std::vector<int64_t>& t) {
+        std::vector<float> h(static_cast<size_t>(d));
+        uint32_t r = static_cast<uint32_t>(t.back() * 2654435761u + t.size() * 40503u);
+        for (auto& x : h) { r = r * 1664525u + 1013904223u; x = static_cast<float>(static_cast<int>((r >> 10) % 4001) - 2000) * 0.002f; }
+        return h;
+    };
+    NextTokenLogitsFn host_model = [&](const std::vector<int64_t>& t) {
+        const std::vector<float> h = body(t);
+        std::vector<float> logits(static_cast<size_t>(vocab));
+        for (int64_t j = 0; j < vocab; ++j) {
+            volatile float acc = 0.0f;  // (volatile: every product and every sum is rounded to float, never fused)
+            for (int64_t p = 0; p < d; ++p) {
+                const float w = tied ? weight[static_cast<size_t>(j * d + p)] : weight[static_cast<size_t>(p * vocab + j)];
+                volatile float product = h[static_cast<size_t>(p)] * w;
+                acc = acc + product;
+            }
+            logits[static_cast<size_t>(j)] = acc;
+        }
+        return logits;
+    };
+    auto head = std::make_shared<DeviceLmHead>(weight, vocab, d, tied);
+    const DeviceNextTokenLogitsFn device_model = MakeDeviceLmHeadLogits(body, head);
+    GenerationConfig greedy;
+    greedy.max_new_tokens = 24;
+    greedy.repetition_penalty = 1.2f;
+    GenerationConfig sampled = greedy;
+    sampled.do_sample = true;
+    sampled.temperature = 0.7f;
+    sampled.top_k = 30;
+    sampled.top_p = 0.9f;
+    sampled.seed = 9;
+    for (const GenerationConfig& c : {greedy, sampled}) {
+        const GenerationResult a = Generate(host_model, {3, 1, 4}, c), b = Generate(device_model, {3, 1, 4}, c);
+        CHECK(a.new_tokens == b.new_tokens);
+        CHECK(a.log_probs == b.log_probs);
+    }
+    CHECK_THROWS(DeviceLmHead(weight, vocab, d + 1, tied), std::invalid_argument);
+    CHECK_THROWS((void)head->logits(std::vector<float>(5)), std::invalid_argument);
+}
+
 // ---- top-k -------------------------------------------------------------------------------------------
 
 static std::vector<float> tie_heavy_values(size_t n, uint32_t seed) {  // coarse values: ties are common
@@ -397,6 +481,9 @@ int main(int argc, char** argv) {
             test_sampling_is_seeded_and_follows_the_distribution(draws);
             test_rejects_bad_input();
             test_device_logits_overload_matches(gpu);
+            test_device_logits_from_another_stream(gpu);
+            test_device_lm_head(true);
+            test_device_lm_head(false);
             test_top_k(gpu);
         } catch (const std::exception& e) {
             ++g_failures;
