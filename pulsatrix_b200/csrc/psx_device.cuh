@@ -67,14 +67,23 @@ __device__ __forceinline__ float next_below(float q) {
 // A value t' <= t such that y < t' implies y / T < t / T after rounding: dividing by the
 // temperature can map neighbouring floats to the same quotient, and every logit whose quotient
 // ties with the threshold's must be kept as a candidate.  Never below -FLT_MAX, so that -inf
-// (banned) entries never pass `y >= t'`.
+// (banned) entries never pass `y >= t'`.  Non-decreasing in t, and one definition for the row pass
+// and the survivor stage: a part's relaxed threshold never exceeds the relaxed largest threshold.
 __device__ __forceinline__ float relax_threshold(float t, bool apply_temp, float temperature) {
     float r = t;
     if (apply_temp && t > -INFINITY) {
-        const float q = __fdiv_rn(t, temperature);
-        const float below = next_below(q);
-        r = __fmul_rd(temperature, below);
-        if (!(r <= t)) r = (r != r) ? -INFINITY : t;
+        // With y < t - (|t| 2^-21 + T 2^-147) the exact quotients y / T and t / T are more than
+        // |t / T| 2^-21 + 2^-147 apart, which is more than their two rounding errors (2^-24 relative or
+        // 2^-150 absolute each): the rounded ones differ too.  No divide needed.
+        r = __fsub_rn(t, __fmaf_rn(fabsf(t), 0x1p-21f, __fmul_rn(temperature, 0x1p-147f)));
+        if (!(fabsf(t) <= __fmul_rn(temperature, 1e37f))) {
+            // Quotients near t / T may overflow, where the argument above ends: take the neighbour of
+            // the rounded quotient back through the multiplication as well, and the lower of the two.
+            const float q = __fdiv_rn(t, temperature);
+            float e = __fmul_rd(temperature, next_below(q));
+            if (!(e <= t)) e = (e != e) ? -INFINITY : t;
+            r = fminf(r, e);
+        }
     }
     return fmaxf(r, -FLT_MAX);
 }
