@@ -58,8 +58,12 @@ struct psx_ctx {
     uint64_t launches = 0;
     bool merge_configured = false;
     bool scan_configured = false;
-    // row-pass scratch
-    Buffer stats, part_counts, candidates, banned, sort_keys, head_logits;
+    // Row-pass scratch, twice: successive sampling calls alternate between the two sets, so that the row
+    // pass of one call never writes what the survivor stage of the call before it is still reading
+    // (see ScanParams::wait_before_writes).
+    Buffer stats[2], part_counts[2], candidates[2];
+    int scratch_set = 0;
+    Buffer banned, sort_keys, head_logits;
     // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
     Buffer surv_cols, surv_vals, surv_counts, pl_tokens, pl_log_probs, pl_status;
     // staging of the host entry point
@@ -148,14 +152,14 @@ psx_status prepare_scan(psx_ctx* ctx, cudaStream_t stream, const psx_sampling_co
     return PSX_OK;
 }
 
-psx_status reserve_scan_scratch(psx_ctx* ctx, int64_t rows, const Plan& plan, psx::ScanParams& sp) {
+psx_status reserve_scan_scratch(psx_ctx* ctx, int64_t rows, const Plan& plan, psx::ScanParams& sp, int set = 0) {
     const size_t parts = (size_t)rows * plan.parts;
-    if (psx_status s = reserve(ctx->stats, parts * sizeof(psx::PartStats))) return s;
-    if (psx_status s = reserve(ctx->part_counts, parts * sizeof(uint32_t))) return s;
-    if (psx_status s = reserve(ctx->candidates, parts * psx::kPartCap * sizeof(uint2))) return s;
-    sp.stats = static_cast<psx::PartStats*>(ctx->stats.ptr);
-    sp.part_counts = static_cast<uint32_t*>(ctx->part_counts.ptr);
-    sp.candidates = static_cast<uint2*>(ctx->candidates.ptr);
+    if (psx_status s = reserve(ctx->stats[set], parts * sizeof(psx::PartStats))) return s;
+    if (psx_status s = reserve(ctx->part_counts[set], parts * sizeof(uint32_t))) return s;
+    if (psx_status s = reserve(ctx->candidates[set], parts * psx::kPartCap * sizeof(uint2))) return s;
+    sp.stats = static_cast<psx::PartStats*>(ctx->stats[set].ptr);
+    sp.part_counts = static_cast<uint32_t*>(ctx->part_counts[set].ptr);
+    sp.candidates = static_cast<uint2*>(ctx->candidates[set].ptr);
     return PSX_OK;
 }
 
@@ -222,7 +226,7 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (Buffer* b : {&ctx->stats, &ctx->part_counts, &ctx->candidates, &ctx->banned, &ctx->sort_keys, &ctx->head_logits, &ctx->surv_cols, &ctx->surv_vals,
+    for (Buffer* b : {&ctx->stats[0], &ctx->stats[1], &ctx->part_counts[0], &ctx->part_counts[1], &ctx->candidates[0], &ctx->candidates[1], &ctx->banned, &ctx->sort_keys, &ctx->head_logits, &ctx->surv_cols, &ctx->surv_vals,
                       &ctx->surv_counts, &ctx->pl_tokens, &ctx->pl_log_probs, &ctx->pl_status, &ctx->h_logits, &ctx->h_history,
                       &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
@@ -250,7 +254,7 @@ namespace {
 // Argument checks, plan, scratch and parameters shared by the sampling entry points.
 psx_status plan_row_pass(psx_ctx* ctx, cudaStream_t stream, const float* logits, int64_t rows, int64_t vocab,
                          int64_t row_stride, const int64_t* history_ids, const int64_t* history_offsets,
-                         const psx_sampling_config* config, Plan& plan, psx::ScanParams& sp) {
+                         const psx_sampling_config* config, Plan& plan, psx::ScanParams& sp, bool alternate = false) {
     PSX_CUDA(cudaSetDevice(ctx->device));
     plan = psx::make_plan(logits, vocab, row_stride, vocab, config);
     sp = psx::ScanParams{};
@@ -263,7 +267,12 @@ psx_status plan_row_pass(psx_ctx* ctx, cudaStream_t stream, const float* logits,
     sp.history_ids = history_ids;
     sp.history_offsets = history_offsets;
     if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
-    return reserve_scan_scratch(ctx, rows, plan, sp);
+    if (!alternate) return reserve_scan_scratch(ctx, rows, plan, sp);
+    // A row pass followed by a survivor stage, call after call on one stream: this call's scratch is the set
+    // that the call before it did not use, and only the row pass's last CTA waits for the kernel before it.
+    ctx->scratch_set ^= 1;
+    sp.wait_before_writes = 0;
+    return reserve_scan_scratch(ctx, rows, plan, sp, ctx->scratch_set);
 }
 
 }  // namespace
@@ -303,7 +312,7 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
     Plan plan;
     psx::ScanParams sp;
     if (psx_status s = plan_row_pass(ctx, stream, logits, rows, vocab, row_stride, history_ids, history_offsets, config,
-                                     plan, sp)) {
+                                     plan, sp, /*alternate=*/true)) {
         return s;
     }
     if (psx_status s = configure_merge(ctx, plan, plan.parts)) return s;

@@ -21,6 +21,13 @@
 __device__ unsigned long long g_merge_clocks[1024 * 16];
 #define PSX_MERGE_STAGE(i) \
     do { if (threadIdx.x == 0) g_merge_clocks[(size_t)(blockIdx.x & 1023) * 16 + (i)] = clock64(); } while (0)
+// wall-clock (globaltimer) stamps of each CTA: entry, after the wait for the row pass, exit
+__device__ unsigned long long g_merge_times[1024 * 4];
+#define PSX_MERGE_TIME(i) \
+    do { if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+         g_merge_times[(size_t)(blockIdx.x & 1023) * 4 + (i)] = t_; } } while (0)
+#else
+#define PSX_MERGE_TIME(i) do {} while (0)
 #endif
 #include "general_row_impl.cuh"
 #include "merge_rows_impl.cuh"
@@ -31,8 +38,10 @@ namespace {
 
 __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const MergeParams p) {
     extern __shared__ unsigned long long dyn[];
+    PSX_MERGE_TIME(0);
     grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
     grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
+    PSX_MERGE_TIME(1);
     const int64_t row = p.row_begin + blockIdx.x;
     if (p.general != 2) survivor::merge_row(p, row, dyn);
     if (p.general != 0 && p.logits != nullptr) {
@@ -40,6 +49,7 @@ __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const Merg
         __syncthreads();
         if (p.general == 2 || p.row_status[row] == PSX_ROW_TOO_WIDE) survivor::general_row(p, row, dyn);
     }
+    PSX_MERGE_TIME(2);
 }
 
 }  // namespace
@@ -47,6 +57,9 @@ __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const Merg
 #ifdef PSX_STAGE_CLOCKS
 extern "C" __attribute__((visibility("default"))) int psx_debug_merge_clocks(unsigned long long* out, int n) {
     return (int)cudaMemcpyFromSymbol(out, g_merge_clocks, sizeof(unsigned long long) * n);
+}
+extern "C" __attribute__((visibility("default"))) int psx_debug_merge_times(unsigned long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, g_merge_times, sizeof(unsigned long long) * n);
 }
 #endif
 

@@ -83,6 +83,7 @@ inline void fill_scan_settings(ScanParams& sp, const psx_sampling_config* c, con
     sp.vecs_per_part = plan.vecs_per_part;
     sp.wait_limit_ns = kDefaultWaitLimitNs;
     sp.test_short_copy = 0;
+    sp.wait_before_writes = 1;
     sp.num_banned = 0;
     sp.banned_ids = nullptr;
 }

@@ -136,11 +136,8 @@ __device__ unsigned long long g_stage_clocks[4096 * 24];
 //          when a flag can only lower a logit (penalty >= 1: l / p or l * p <= l; a ban gives -inf) and no
 //          processed tail is wanted: a flagged logit whose processed value reaches the threshold then
 //          reaches it raw as well, and the rest belong to the raw tail with their raw value.
-#ifndef PSX_SCAN_CTAS
-#define PSX_SCAN_CTAS 3
-#endif
 template <bool kNucleus, bool kRestore>
-__global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanParams p) {
     static_assert(!(kNucleus && kRestore), "the processed tail needs the flagged logits out of the sums");
 #ifdef PSX_STAGE_CLOCKS
     unsigned long long clk[24];
@@ -165,7 +162,13 @@ __global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(
 
     const int part = blockIdx.x;  // grid: (parts, rows in chunks of 65535, chunks)
     const int64_t row = (int64_t)blockIdx.z * 65535 + blockIdx.y;
-    if (row >= p.rows) return;
+    // (see ScanParams::wait_before_writes: the last CTA of the grid keeps the kernel from finishing early)
+    const bool ends_the_grid = !p.wait_before_writes && blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 &&
+                               blockIdx.z == gridDim.z - 1;
+    if (row >= p.rows) {
+        if (ends_the_grid) grid_dependency_wait();
+        return;
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t part_index = (size_t)row * p.parts + part;
 
@@ -183,7 +186,7 @@ __global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(
     grid_dependents_may_launch();
     if (!p.inputs_ready) grid_dependency_wait();
     if (nvec <= 0) {  // a part past the end of a row that starts on a 16-byte boundary: nothing to report
-        grid_dependency_wait();
+        if (p.wait_before_writes || ends_the_grid) grid_dependency_wait();
         if (tid == 0) {
             p.part_counts[part_index] = 0;
             PartStats s;
@@ -276,7 +279,7 @@ __global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(
         }
         STAGE(16 + half);
         // Without kRestore the kernel now writes scratch that an earlier survivor stage may still be reading.
-        if (!kRestore && half == 0) grid_dependency_wait();
+        if (!kRestore && half == 0 && p.wait_before_writes) grid_dependency_wait();
         // Components of the first and last vector that lie outside the row are blanked.
         if (half == 0 && v0 == 0 && tid == 0) {
             for (uint32_t c = 0; c < misalign; ++c) data[c] = kPad;
@@ -420,7 +423,7 @@ __global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(
     if (__syncthreads_or(landed ? 0 : 1) != 0) {
         // A copy did not complete in time: report it, give the copies one more bounded chance to
         // drain (shared memory must not be handed to the next CTA under a copy in flight), and leave.
-        grid_dependency_wait();
+        if (p.wait_before_writes || ends_the_grid) grid_dependency_wait();
         if (tid == 0) {
             p.part_counts[part_index] = 0;
             PartStats s;
@@ -597,7 +600,10 @@ __global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(
     }
     __syncthreads();
     STAGE(10);
-    if (kRestore) grid_dependency_wait();  // the first write to scratch that an earlier survivor stage may still be reading
+    if (kRestore && p.wait_before_writes) grid_dependency_wait();  // the first write to scratch that the kernel before this one may still be reading
+#ifdef PSX_STAGE_CLOCKS
+    if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); clk[15] = t_; }
+#endif
     STAGE(18);
     // The part's record, by three warps side by side, each ahead of its share of the hand-off.
     PartStats* const record = p.stats + part_index;
@@ -669,6 +675,7 @@ __global__ void __launch_bounds__(kScanThreads, PSX_SCAN_CTAS) scan_rows_kernel(
             }
         }
     }
+    if (ends_the_grid) grid_dependency_wait();
 #ifdef PSX_STAGE_CLOCKS
     STAGE(11);
     if (tid == 0 && part_index < 4096) {

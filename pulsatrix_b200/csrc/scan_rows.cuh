@@ -28,6 +28,13 @@ struct ScanParams {
     int32_t inputs_ready;            // the inputs above are complete whatever the kernel before this one is doing
     uint64_t wait_limit_ns;          // a wait for a copy gives up after this long (the part then reports a time-out)
     int32_t test_short_copy;         // tests only: the copies deliver less than was announced, so that a wait runs out
+    // The kernel before this one in the stream (launched so that the two may overlap) may still be reading the
+    // scratch below.  1: every CTA waits for it to finish before its first write.  0: the caller alternates
+    // between two sets of scratch and launches row pass and survivor stage in turn; then the set written here
+    // was last read two kernels back, and it is enough that this kernel does not finish before the kernel
+    // before it has (only the last CTA waits, just before it ends): the survivor stage that waits for this
+    // kernel thereby starts after the survivor stage before it has finished, and so on down the stream.
+    int32_t wait_before_writes;
     // output
     PartStats* stats;                // rows * parts
     uint32_t* part_counts;           // rows * parts: candidates handed on by the part
