@@ -330,8 +330,7 @@ psx_status psx_b200_sample_rows(psx_ctx* ctx, void* stream_ptr, const float* log
         ++ctx->launches;
     }
     if (ctx->timing) PSX_CUDA(cudaEventRecord(marks[1], stream));
-    PSX_CUDA(psx::launch_merge_rows(mp, stream));
-    ++ctx->launches;
+    PSX_CUDA(psx::launch_merge_rows(mp, stream, &ctx->launches));
     if (ctx->timing) {
         PSX_CUDA(cudaEventRecord(marks[2], stream));
         ctx->timing_events.insert(ctx->timing_events.end(), marks, marks + 3);
@@ -701,8 +700,7 @@ psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream_ptr, const void*
     mp.diag = diag ? diag - row_begin : nullptr;
     mp.sort_capacity = plan.sort_capacity;
     mp.gather_capacity = plan.gather_capacity;
-    PSX_CUDA(psx::launch_merge_rows(mp, stream));
-    ++ctx->launches;
+    PSX_CUDA(psx::launch_merge_rows(mp, stream, &ctx->launches));
     return PSX_OK;
 }
 

@@ -31,25 +31,65 @@ __device__ unsigned long long g_merge_times[1024 * 4];
 #endif
 #include "general_row_impl.cuh"
 #include "merge_rows_impl.cuh"
+#include "merge_rows_warp_impl.cuh"
 
 namespace psx {
 
 namespace {
 
-__global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const MergeParams p) {
-    extern __shared__ unsigned long long dyn[];
-    PSX_MERGE_TIME(0);
-    grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
-    grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
-    PSX_MERGE_TIME(1);
-    const int64_t row = p.row_begin + blockIdx.x;
+__device__ __forceinline__ void decide_row(const MergeParams& p, const int64_t row, unsigned long long* dyn) {
     if (p.general != 2) survivor::merge_row(p, row, dyn);
     if (p.general != 0 && p.logits != nullptr) {
         // A row the candidate lists could not decide is decided from the row itself.
         __syncthreads();
         if (p.general == 2 || p.row_status[row] == PSX_ROW_TOO_WIDE) survivor::general_row(p, row, dyn);
     }
+}
+
+__global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const MergeParams p) {
+    extern __shared__ unsigned long long dyn[];
+    PSX_MERGE_TIME(0);
+    if (p.only_undecided) {
+        // After a launch by warps: a few CTAs look through the rows for what the warps left undecided
+        // (usually nothing).  The kernel after this one may start at once: it waits for this one where it must.
+        grid_dependents_may_launch();
+        grid_dependency_wait();
+        __shared__ int s_found[kMergeThreads];
+        __shared__ int s_n;
+        const int64_t per_cta = (p.rows + gridDim.x - 1) / gridDim.x;
+        const int64_t begin = p.row_begin + (int64_t)blockIdx.x * per_cta, end = min(begin + per_cta, p.row_begin + p.rows);
+        for (int64_t r0 = begin; r0 < end; r0 += kMergeThreads) {
+            if (threadIdx.x == 0) s_n = 0;
+            __syncthreads();
+            const int64_t r = r0 + threadIdx.x;
+            if (r < end && p.row_status[r] == kRowUndecided) s_found[atomicAdd(&s_n, 1)] = (int)(r - r0);
+            __syncthreads();
+            const int found = s_n;
+            for (int i = 0; i < found; ++i) {  // (in any order: rows do not depend on one another)
+                const int64_t row = r0 + s_found[i];
+                __syncthreads();
+                decide_row(p, row, dyn);
+                __syncthreads();
+            }
+        }
+        return;
+    }
+    grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
+    grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
+    PSX_MERGE_TIME(1);
+    decide_row(p, p.row_begin + blockIdx.x, dyn);
     PSX_MERGE_TIME(2);
+}
+
+template <int N>
+__global__ void __launch_bounds__(kMergeThreads) merge_rows_warp_kernel(const MergeParams p) {
+    extern __shared__ unsigned long long dyn[];
+    grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
+    grid_dependents_may_launch();
+    const int warp = threadIdx.x >> 5;
+    const int64_t row = p.row_begin + (int64_t)blockIdx.x * survivor::kRowsPerCta + warp;
+    if (row >= p.row_begin + p.rows) return;  // (no barrier in this kernel: a warp may leave)
+    survivor::warp_merge_row<N>(p, row, reinterpret_cast<unsigned char*>(dyn) + (size_t)warp * survivor::warp_arena_bytes(p.warp_list_cap));
 }
 
 }  // namespace
@@ -79,14 +119,49 @@ int merge_slot_shift(int parts, int part_cap, int expected) {
 
 cudaError_t configure_merge_rows() { return allow_all_dynamic_shared(merge_rows_kernel); }
 
-cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream) {
+bool plan_merge_by_warp(MergeParams& p, int k_need, bool greedy, int expected) {
+    p.by_warp = 0;
+    if (!greedy && k_need > 64) return false;
+    int shift = 0;
+    while ((1 << shift) < expected && (2 << shift) <= p.part_cap) ++shift;
+    while (shift > 0 && ((long long)p.parts << shift) > 512) --shift;
+    if (((long long)p.parts << shift) > 512) return false;
+    p.by_warp = 1;
+    p.warp_slot_shift = shift;
+    p.warp_list_cap = (greedy || k_need <= 32) ? 64 : 128;
+    return true;
+}
+
+cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream, uint64_t* launched) {
     if (p.rows <= 0) return cudaSuccess;
     // The same condition as the kernel's: the overlaid layout is for plans without a top-k.
     const bool overlay = p.overlay != 0 && p.logits != nullptr && !(p.do_sample && p.top_k > 0 && p.top_k < p.vocab);
     const size_t shared = merge_rows_shared_bytes(p.sort_capacity, p.gather_capacity, overlay);
     MergeParams with_size = p;
     with_size.dyn_bytes = (int32_t)shared;
-    return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, with_size);
+    with_size.only_undecided = 0;
+    // By warps from 256 rows on: a warp takes longer over a row than a block does (about 13 us against 7 on
+    // 64 rows of 152 K logits), so few rows are answered sooner by blocks; many rows get through faster by
+    // warps (1000 x 49 K, top-k 50: 70 -> 59 us per step; 1024 greedy rows: 47 -> 37 us).
+    const bool by_warp = p.by_warp != 0 && p.general != 2 && p.survivor_cols == nullptr && p.rows >= kRowsByWarpFrom;
+    if (launched != nullptr) *launched += by_warp ? 2 : 1;
+    if (!by_warp) {
+        return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, with_size);
+    }
+    // One warp per row, eight rows per CTA; then the block-per-row kernel over what the warps left undecided.
+    const int fetches = (int)((((long long)p.parts << p.warp_slot_shift) + 31) / 32);
+    const size_t warp_shared = survivor::warp_arena_bytes(p.warp_list_cap) * survivor::kRowsPerCta;
+    const dim3 grid((unsigned)((p.rows + survivor::kRowsPerCta - 1) / survivor::kRowsPerCta));
+    cudaError_t e;
+    if (fetches <= 1) e = launch_overlapping(merge_rows_warp_kernel<1>, grid, dim3(kMergeThreads), warp_shared, stream, with_size);
+    else if (fetches <= 2) e = launch_overlapping(merge_rows_warp_kernel<2>, grid, dim3(kMergeThreads), warp_shared, stream, with_size);
+    else if (fetches <= 4) e = launch_overlapping(merge_rows_warp_kernel<4>, grid, dim3(kMergeThreads), warp_shared, stream, with_size);
+    else if (fetches <= 8) e = launch_overlapping(merge_rows_warp_kernel<8>, grid, dim3(kMergeThreads), warp_shared, stream, with_size);
+    else e = launch_overlapping(merge_rows_warp_kernel<16>, grid, dim3(kMergeThreads), warp_shared, stream, with_size);
+    if (e != cudaSuccess) return e;
+    with_size.only_undecided = 1;
+    const unsigned ctas = (unsigned)(p.rows < 32 ? p.rows : 32);
+    return launch_overlapping(merge_rows_kernel, dim3(ctas), dim3(kMergeThreads), shared, stream, with_size);
 }
 
 }  // namespace psx

@@ -64,16 +64,29 @@ struct MergeParams {
     int32_t general;                 // 0: off; 1: for rows the lists declined; 2: for every row (the lists are not looked at)
     float* process_out;              // ProcessLogits: general_row rewrites the row in place instead of drawing
     int32_t dyn_bytes;               // dynamic shared memory of the launch (filled in by launch_merge_rows)
+    // Optional: one warp per row first (merge_rows_warp_impl.cuh), the block-per-row kernel afterwards only for
+    // the rows the warps left undecided.  For greedy and for a top-k of at most 64, straight after a row pass.
+    int32_t by_warp;                 // 0: off
+    int32_t warp_slot_shift;         // 2^shift slots of every list per fetch; parts << shift <= 512
+    int32_t warp_list_cap;           // entries a warp's list holds: 64 or 128
+    int32_t only_undecided;          // (set by launch_merge_rows for the second kernel)
 };
+
+constexpr int64_t kRowsByWarpFrom = 256;  // launches of fewer rows stay with one block per row
+// Plans a launch by warps for lists that usually hold about `expected` candidates; false: not for this plan.
+bool plan_merge_by_warp(MergeParams& p, int k_need, bool greedy, int expected);
 
 // Row status between the survivor stage and ProcessLogits' write-back: general_row has already
 // rewritten the row in place.  Never leaves the library.
 constexpr int kRowDoneInPlace = 64;
+// Row status between the two kernels of a launch by warps: the block-per-row kernel has yet to decide the row.
+constexpr int kRowUndecided = 65;
 
 size_t merge_rows_shared_bytes(int sort_capacity, int gather_capacity, bool overlay);
 // The slot_shift for lists that usually hold about `expected` candidates, within the fetch budget.
 int merge_slot_shift(int parts, int part_cap, int expected);
 cudaError_t configure_merge_rows();  // once per device: lifts the kernel's dynamic shared-memory limit to the device's
-cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream);
+// launched (optional): how many kernels the call launched, added to what is there.
+cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream, uint64_t* launched = nullptr);
 
 }  // namespace psx

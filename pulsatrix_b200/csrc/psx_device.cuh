@@ -111,6 +111,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// exp2(-r) for the remainder r that a float exponent dropped (|r| is half an ulp of the exponent: 1e-5
+// or less for any logit whose exponential matters); the series ends after the square term there.
+__device__ __forceinline__ double exp2_of_minus_small(float r) {
+    if (fabsf(r) > 1e-4f) return exp2(-(double)r);
+    const double x = -(double)r * 0.69314718055994530942;
+    return fma(x, fma(x, 0.5, 1.0), 1.0);
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------------
 // The row pass and the survivor stage are launched so that a kernel may start while the kernel
 // before it in the stream is still running (cudaLaunchAttributeProgrammaticStreamSerialization).

@@ -133,6 +133,13 @@ inline void fill_merge_params(MergeParams& mp, const ScanParams& sp, const Plan&
         mp.banned_ids = sp.banned_ids;
         mp.num_banned = sp.num_banned;
         mp.general = plan.lists_cannot_bound ? 2 : 1;
+        // Short lists straight from a row pass: one warp per row.  (The flagged logits of the history are
+        // handed on whatever their value only when the penalty is below one.)
+        if (!plan.nucleus) {
+            const bool greedy = !mp.do_sample;
+            const int flagged = (sp.apply_penalty && sp.penalty < 1.0f) ? 24 : 4;
+            plan_merge_by_warp(mp, plan.k_need, greedy, greedy ? 2 : plan.k_need + plan.k_need / 2 + flagged);
+        }
     }
 }
 

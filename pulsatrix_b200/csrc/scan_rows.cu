@@ -107,14 +107,6 @@ constexpr int kPool = 64 / kScanWarps;  // per-thread maxima a warp can offer to
 constexpr uint32_t kKeyMinusInf = 0x007FFFFFu;  // monotone_key(-inf): the lowest key a threshold can have
 constexpr uint32_t kKeyNone = 0xFFFFFFFFu;      // "no entry" in the pool (above every key of a number)
 
-// exp2(-r) for the remainder r that a float exponent dropped (|r| is half an ulp of the exponent: 1e-5
-// or less for any logit whose exponential matters); the series ends after the square term there.
-__device__ __forceinline__ double exp2_of_minus_small(float r) {
-    if (fabsf(r) > 1e-4f) return exp2(-(double)r);
-    const double x = -(double)r * 0.69314718055994530942;
-    return fma(x, fma(x, 0.5, 1.0), 1.0);
-}
-
 }  // namespace
 
 // Profiling build only (-DPSX_STAGE_CLOCKS): thread 0 of each CTA stamps the SM clock at the stage

@@ -127,9 +127,17 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     }
 
     // First sweep: warp w takes parts w, w + 8, ...; counts what each keeps, and moves the mass of
-    // what it drops into the tails.
+    // what it drops into the tails.  A dropped candidate belongs to the raw tail like the logits the row
+    // pass left behind, and its exponential is taken the same way: ex2 in float against the rounded
+    // exponent of the maximum, the rounding put back once for the whole sum.  The processed tail is only
+    // ever read when no top-k is set; then it keeps its double-precision exponentials.
     uint32_t* s_kept = s_keys;
     uint32_t dropped = 0;  // warp-uniform
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float c_l2 = __fmul_rn(raw_max, kLog2e);
+    const float c_res = __fmaf_rn(raw_max, kLog2e, -c_l2);
+    const bool want_processed = p.top_k <= 0;
+    float dropped_raw = 0.0f;
     for (int s = warp; s < nseg; s += kPackWarps) {
         const int cnt = min((int)seg_counts[s], kPartCap);
         uint32_t kept = 0;
@@ -142,8 +150,8 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
                 const float y = processed_before_temperature(l, c.y, p.penalty);
                 keep = y >= keep_from;
                 if (!keep) {
-                    raw_tail += exp((double)l - (double)raw_max);
-                    if (y > -INFINITY) proc_tail += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
+                    dropped_raw += ex2_approx(__fmaf_rn(l, kLog2e, -c_l2));
+                    if (want_processed && y > -INFINITY) proc_tail += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
                 }
             }
             kept += __popc(__ballot_sync(0xFFFFFFFFu, keep));
@@ -151,6 +159,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
         dropped += (uint32_t)cnt - kept;
         if (lane == 0) s_kept[s] = kept;
     }
+    raw_tail += (double)dropped_raw * exp2_of_minus_small(c_res);
     raw_tail = warp_sum(raw_tail);
     proc_tail = warp_sum(proc_tail);
     if (lane == 0) {
