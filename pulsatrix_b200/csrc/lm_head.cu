@@ -18,6 +18,7 @@
 //     reads its own entry's row from there;
 //   - feature-major (d x vocab, an untied Linear): consecutive threads read consecutive floats.
 #include "lm_head.cuh"
+#include "psx_device.cuh"
 
 #include <cuda_pipeline_primitives.h>
 
@@ -84,15 +85,21 @@ __global__ void __launch_bounds__(kHeadThreads) head_token_major_kernel(const fl
         const int kc = (int)min((int64_t)kHeadChunk, d - (int64_t)c * kHeadChunk);
         const float* wrow = &s_w[buf][tid * kHeadPitch];
         auto take = [&](int p, float w) {  // acc[m] += hidden[m][p] * w, each step rounded (src/cpu_backend.cpp:193)
-            if (MT >= 4) {
+            if (MT >= 4) {  // two rows per instruction (packed fp32: the same roundings as two scalar operations)
 #pragma unroll
                 for (int m = 0; m < MT; m += 4) {
                     const float4 h = *reinterpret_cast<const float4*>(&s_h[p * MT + m]);
-                    acc[m] = __fadd_rn(acc[m], __fmul_rn(h.x, w));
-                    acc[m + 1] = __fadd_rn(acc[m + 1], __fmul_rn(h.y, w));
-                    acc[m + 2] = __fadd_rn(acc[m + 2], __fmul_rn(h.z, w));
-                    acc[m + 3] = __fadd_rn(acc[m + 3], __fmul_rn(h.w, w));
+                    float p0, p1, p2, p3;
+                    mul_pair(p0, p1, h.x, h.y, w, w);
+                    mul_pair(p2, p3, h.z, h.w, w, w);
+                    add_pair(acc[m], acc[m + 1], acc[m], acc[m + 1], p0, p1);
+                    add_pair(acc[m + 2], acc[m + 3], acc[m + 2], acc[m + 3], p2, p3);
                 }
+            } else if (MT == 2) {
+                const float2 h = *reinterpret_cast<const float2*>(&s_h[p * MT]);
+                float p0, p1;
+                mul_pair(p0, p1, h.x, h.y, w, w);
+                add_pair(acc[0], acc[1], acc[0], acc[1], p0, p1);
             } else {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) acc[m] = __fadd_rn(acc[m], __fmul_rn(s_h[p * MT + m], w));
@@ -146,8 +153,17 @@ __global__ void __launch_bounds__(kHeadThreads) head_feature_major_kernel(const 
 #pragma unroll
         for (int p = 0; p < kHeadChunk; ++p) {
             if (p < kc) {
+                if (MT >= 2) {  // two rows per instruction (packed fp32: the same roundings as two scalar operations)
 #pragma unroll
-                for (int m = 0; m < MT; ++m) acc[m] = __fadd_rn(acc[m], __fmul_rn(s_h[p * MT + m], w[p]));
+                    for (int m = 0; m < MT; m += 2) {
+                        const float2 h = *reinterpret_cast<const float2*>(&s_h[p * MT + m]);
+                        float p0, p1;
+                        mul_pair(p0, p1, h.x, h.y, w[p], w[p]);
+                        add_pair(acc[m], acc[m + 1], acc[m], acc[m + 1], p0, p1);
+                    }
+                } else {
+                    acc[0] = __fadd_rn(acc[0], __fmul_rn(s_h[p], w[p]));
+                }
             }
         }
     }

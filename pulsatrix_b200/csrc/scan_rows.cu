@@ -79,30 +79,6 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
     }
 }
 
-// Two independent IEEE single-precision operations in one instruction (sm_100 packed fp32): the same
-// results as two scalar ones, half the issue slots.
-#ifndef PSX_NO_F32X2
-__device__ __forceinline__ void fma_pair(float& r0, float& r1, float a0, float a1, float b0, float b1, float c0, float c1) {
-    asm("{\n\t.reg .b64 a, b, c, d;\n\t"
-        "mov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\tmov.b64 c, {%6, %7};\n\t"
-        "fma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}"
-        : "=f"(r0), "=f"(r1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
-}
-__device__ __forceinline__ void add_pair(float& r0, float& r1, float a0, float a1, float b0, float b1) {
-    asm("{\n\t.reg .b64 a, b, d;\n\t"
-        "mov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\t"
-        "add.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
-        : "=f"(r0), "=f"(r1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-#else
-__device__ __forceinline__ void fma_pair(float& r0, float& r1, float a0, float a1, float b0, float b1, float c0, float c1) {
-    r0 = __fmaf_rn(a0, b0, c0); r1 = __fmaf_rn(a1, b1, c1);
-}
-__device__ __forceinline__ void add_pair(float& r0, float& r1, float a0, float a1, float b0, float b1) {
-    r0 = __fadd_rn(a0, b0); r1 = __fadd_rn(a1, b1);
-}
-#endif
-
 constexpr int kPool = 64 / kScanWarps;  // per-thread maxima a warp can offer to the pooled threshold (64 in all)
 constexpr uint32_t kKeyMinusInf = 0x007FFFFFu;  // monotone_key(-inf): the lowest key a threshold can have
 constexpr uint32_t kKeyNone = 0xFFFFFFFFu;      // "no entry" in the pool (above every key of a number)
