@@ -50,7 +50,7 @@ from pulsatrix_b200.workloads import WORKLOADS  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes (read + write) of one row-pass launch as ncu counted them, per workload that has been
 # captured; workloads without a capture report no traffic figure.
-ROW_PASS_TRAFFIC = {"c2": 39087616}
+ROW_PASS_TRAFFIC = {"c2": 39070464}
 FALLBACK_HBM_GBS = 6650.0
 MIN_TIMED_MS = 50.0   # a K-step region is repeated until this much GPU time has been timed
 MAX_REPEATS = 400

@@ -8,7 +8,8 @@
 // thread here owns one vocabulary entry and up to 64 rows of hidden states, and does exactly that:
 // __fmul_rn, then __fadd_rn, p ascending.  The logits are therefore the reference's bit for bit,
 // and so is every token drawn from them.  (Tensor cores would round differently -- TF32 products,
-// tree-shaped sums -- so they are not used here.)
+// tree-shaped sums -- so they are not used here.  Neither are the packed mul.rn.f32x2 / add.rn.f32x2: a
+// build that paired two rows per instruction gave logits two ulps away from the scalar operations'.)
 //
 // Bound: at decode sizes (a few rows) by HBM -- the weight matrix is read once, 4 * vocab * d
 // bytes; from about 16 rows up by the FP32 pipes (two instructions per multiply-add).
@@ -18,7 +19,6 @@
 //     reads its own entry's row from there;
 //   - feature-major (d x vocab, an untied Linear): consecutive threads read consecutive floats.
 #include "lm_head.cuh"
-#include "psx_device.cuh"
 
 #include <cuda_pipeline_primitives.h>
 
@@ -85,21 +85,15 @@ __global__ void __launch_bounds__(kHeadThreads) head_token_major_kernel(const fl
         const int kc = (int)min((int64_t)kHeadChunk, d - (int64_t)c * kHeadChunk);
         const float* wrow = &s_w[buf][tid * kHeadPitch];
         auto take = [&](int p, float w) {  // acc[m] += hidden[m][p] * w, each step rounded (src/cpu_backend.cpp:193)
-            if (MT >= 4) {  // two rows per instruction (packed fp32: the same roundings as two scalar operations)
+            if (MT >= 4) {
 #pragma unroll
                 for (int m = 0; m < MT; m += 4) {
                     const float4 h = *reinterpret_cast<const float4*>(&s_h[p * MT + m]);
-                    float p0, p1, p2, p3;
-                    mul_pair(p0, p1, h.x, h.y, w, w);
-                    mul_pair(p2, p3, h.z, h.w, w, w);
-                    add_pair(acc[m], acc[m + 1], acc[m], acc[m + 1], p0, p1);
-                    add_pair(acc[m + 2], acc[m + 3], acc[m + 2], acc[m + 3], p2, p3);
+                    acc[m] = __fadd_rn(acc[m], __fmul_rn(h.x, w));
+                    acc[m + 1] = __fadd_rn(acc[m + 1], __fmul_rn(h.y, w));
+                    acc[m + 2] = __fadd_rn(acc[m + 2], __fmul_rn(h.z, w));
+                    acc[m + 3] = __fadd_rn(acc[m + 3], __fmul_rn(h.w, w));
                 }
-            } else if (MT == 2) {
-                const float2 h = *reinterpret_cast<const float2*>(&s_h[p * MT]);
-                float p0, p1;
-                mul_pair(p0, p1, h.x, h.y, w, w);
-                add_pair(acc[0], acc[1], acc[0], acc[1], p0, p1);
             } else {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) acc[m] = __fadd_rn(acc[m], __fmul_rn(s_h[p * MT + m], w));
@@ -153,17 +147,8 @@ __global__ void __launch_bounds__(kHeadThreads) head_feature_major_kernel(const 
 #pragma unroll
         for (int p = 0; p < kHeadChunk; ++p) {
             if (p < kc) {
-                if (MT >= 2) {  // two rows per instruction (packed fp32: the same roundings as two scalar operations)
 #pragma unroll
-                    for (int m = 0; m < MT; m += 2) {
-                        const float2 h = *reinterpret_cast<const float2*>(&s_h[p * MT + m]);
-                        float p0, p1;
-                        mul_pair(p0, p1, h.x, h.y, w[p], w[p]);
-                        add_pair(acc[m], acc[m + 1], acc[m], acc[m + 1], p0, p1);
-                    }
-                } else {
-                    acc[0] = __fadd_rn(acc[0], __fmul_rn(s_h[p], w[p]));
-                }
+                for (int m = 0; m < MT; ++m) acc[m] = __fadd_rn(acc[m], __fmul_rn(s_h[p * MT + m], w[p]));
             }
         }
     }

@@ -127,13 +127,6 @@ __device__ __forceinline__ void add_pair(float& r0, float& r1, float a0, float a
 }
 
 
-__device__ __forceinline__ void mul_pair(float& r0, float& r1, float a0, float a1, float b0, float b1) {
-    asm("{\n\t.reg .b64 a, b, d;\n\t"
-        "mov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\t"
-        "mul.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
-        : "=f"(r0), "=f"(r1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-
 // exp2(-r) for the remainder r that a float exponent dropped (|r| is half an ulp of the exponent: 1e-5
 // or less for any logit whose exponential matters); the series ends after the square term there.
 __device__ __forceinline__ double exp2_of_minus_small(float r) {
