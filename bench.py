@@ -89,6 +89,8 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work of the cpu_baseline sample")
     ap.add_argument("--lm-head", action="store_true",
                     help="time the device head + sampling step on decode-sized batches instead (one GPU; prints its own JSON line)")
+    ap.add_argument("--attention", action="store_true",
+                    help="time the attention over the KV cache instead (one GPU; prints its own JSON line)")
     ap.add_argument("--softmax", action="store_true",
                     help="time psx_b200_softmax_rows / logsumexp_rows on a few shapes instead (one GPU; prints its own JSON line)")
     ap.add_argument("--top-k", action="store_true",
@@ -862,14 +864,55 @@ def run_lm_head(args):
           "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
 
 
+ATTENTION_SHAPES = [  # (batch, heads, kv_heads, head_dim, cached positions)
+    (64, 32, 8, 128, 4096), (8, 32, 8, 128, 16384), (1, 32, 8, 128, 32768), (256, 16, 16, 64, 1024), (64, 32, 32, 128, 2048),
+]
+
+
+def run_attention(args):
+    """One new position per sequence over the KV cache (psx_b200_decode_attention): the cache is the traffic,
+    8 * (cached + 1) * head_dim bytes per (batch, kv head).  Caches rotate so that a launch never finds its
+    cache in L2."""
+    import torch
+    import pulsatrix_b200 as psx
+
+    ctx = psx.Context(0)
+    peak, peak_kind = measured_hbm_peak()
+    results = []
+    for batch, heads, kv_heads, d, cached in ATTENTION_SHAPES:
+        max_len = cached + 1
+        cache_bytes = 2 * batch * kv_heads * max_len * d * 4
+        copies = max(2, int(np.ceil(2 * L2_BYTES / cache_bytes)) + 1)
+        caches = [(torch.randn((batch, kv_heads, max_len, d), device="cuda"), torch.randn((batch, kv_heads, max_len, d), device="cuda"))
+                  for _ in range(copies)]
+        q = torch.randn((batch, heads, 1, d), device="cuda")
+        for i in range(max(args.warmup, 3)):
+            ctx.decode_attention(q, caches[i % copies][0], caches[i % copies][1], cached)
+        torch.cuda.synchronize()
+        steps = max(3, min(args.steps, 30))
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for i in range(steps):
+            ctx.decode_attention(q, caches[i % copies][0], caches[i % copies][1], cached)
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        gbs = cache_bytes / (ms * 1e-3) / 1e9
+        results.append({"batch": batch, "heads": heads, "kv_heads": kv_heads, "head_dim": d, "cached": cached, "us": ms * 1e3,
+                        "cache_mb": cache_bytes / 1e6, "cache_gbs": gbs, "frac_of_hbm_peak": gbs / peak})
+        del caches
+    emit({"metric": "attention of one new position over the KV cache", "unit": "us per call", "n_gpus": 1, "dtype": "f32",
+          "data": "synthetic", "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
+
+
 def main():
     args = parse_args()
     keep_stdout_for_the_result()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.top_k or args.softmax or args.lm_head:
+    if args.top_k or args.softmax or args.lm_head or args.attention:
         if rank == 0:
-            (run_top_k if args.top_k else run_softmax if args.softmax else run_lm_head)(args)
+            (run_top_k if args.top_k else run_softmax if args.softmax else run_lm_head if args.lm_head else run_attention)(args)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)

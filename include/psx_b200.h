@@ -266,6 +266,24 @@ PSX_API psx_status psx_b200_lm_head_sample_rows(psx_ctx* ctx, void* stream, cons
                                                 int64_t* tokens, float* log_probs, int32_t* row_status,
                                                 psx_row_diag* diag);
 
+/* Attention of the new positions over the KV cache: the core of MultiHeadAttentionModule::forward_cached
+ * (src/multihead_attention_module.cpp:562-586) -- per (batch, head) scores = q . K^T (gemm_ex), times
+ * `scale` (axpby; the module's score_scale(), 1 / sqrt(head_dim) by default, :190-192), masked entries set
+ * to the lowest float (attention_mask_fill; src/row_math.hpp:117-127: with `causal`, key j is masked for
+ * new position i when j > i + cached, or, with window > 0, when j + window <= i + cached; a key whose
+ * key_keep entry is 0 is masked), softmax over the cached positions (softmax_rows), context = P . V (gemm)
+ * -- in one pass over the cache.  q and context: (batch, heads, q_len, head_dim); keys and values: the
+ * cache, (batch, kv_heads, max_len, head_dim), holding positions 0 .. cached + q_len - 1 (the new keys and
+ * values already appended, :554-559); query head h reads kv head h / (heads / kv_heads) in place;
+ * key_keep: (batch, cached + q_len) or null.  All device pointers, stream-asynchronous.  status (device,
+ * may be null): bit 0 is set if a bounded device-side wait for a copy ran out.  Float sums in another
+ * order than the reference's loops: within its 1e-4 CPU/GPU equivalence tolerance, not bit for bit.
+ * Limits: (heads / kv_heads) * q_len <= 8, head_dim a multiple of 4 up to 128 (else PSX_ERR_UNSUPPORTED). */
+PSX_API psx_status psx_b200_decode_attention(psx_ctx* ctx, void* stream, const float* q, const float* keys, const float* values,
+                                             const float* key_keep, float* context, int64_t batch, int64_t heads,
+                                             int64_t kv_heads, int64_t q_len, int64_t head_dim, int64_t cached, int64_t max_len,
+                                             float scale, int32_t causal, int64_t window, int32_t* status);
+
 /* Replace DeviceBackend::softmax_rows, logsumexp_rows and gather_rows
  * (include/pulsatrix/device_backend.hpp:456,465,596; CUDA implementations src/cuda_backend.cu with
  * the kernels src/gpu_kernels.cuh:315-365,665; CPU semantics src/cpu_backend.cpp:292-338,459-466)

@@ -4,6 +4,7 @@
  */
 #include "psx_oracle.h"
 
+#include <float.h>
 #include <math.h>
 #include <pthread.h>
 #include <stdlib.h>
@@ -461,4 +462,44 @@ void psxo_synth_row(uint64_t seed, int64_t vocab, double sigma, double zeta, flo
         history[j] = (int64_t)(psxo_prng_next(&g) % (uint64_t)vocab);
     }
     free(perm);
+}
+
+/* src/multihead_attention_module.cpp:562-586 over the CPU backend's loops (see psx_oracle.h). */
+void psxo_decode_attention(const float* q, const float* keys, const float* values, const float* key_keep, float* context,
+                           int64_t batch, int64_t heads, int64_t kv_heads, int64_t q_len, int64_t head_dim, int64_t cached,
+                           int64_t max_len, float scale, int causal, int64_t window) {
+    const int64_t total = cached + q_len, group = heads / kv_heads;
+    float* scores = (float*)malloc((size_t)(q_len * total) * sizeof(float));
+    for (int64_t nh = 0; nh < batch * heads; ++nh) {
+        const int64_t b = nh / heads, kv = b * kv_heads + (nh % heads) / group; /* :563 */
+        const float* a = q + nh * q_len * head_dim;
+        const float* k = keys + kv * max_len * head_dim;
+        const float* v = values + kv * max_len * head_dim;
+        for (int64_t i = 0; i < q_len; ++i) {
+            for (int64_t j = 0; j < total; ++j) { /* gemm_ex, B transposed: src/cpu_backend.cpp:188-196 */
+                float acc = 0.0f;
+                for (int64_t p = 0; p < head_dim; ++p) acc += a[i * head_dim + p] * k[j * head_dim + p];
+                scores[i * total + j] = acc;
+            }
+        }
+        for (int64_t x = 0; x < q_len * total; ++x) scores[x] = scale * scores[x]; /* axpby with beta == 0: :274-276 */
+        for (int64_t i = 0; i < q_len; ++i) { /* attention_mask_fill: :429-443, src/row_math.hpp:117-127 */
+            for (int64_t j = 0; j < total; ++j) {
+                int masked = 0;
+                if (causal && j > i + cached) masked = 1;
+                if (causal && window > 0 && j + window <= i + cached) masked = 1;
+                if (!masked && key_keep != NULL && key_keep[b * total + j] == 0.0f) masked = 1;
+                if (masked) scores[i * total + j] = -FLT_MAX; /* std::numeric_limits<float>::lowest() */
+            }
+        }
+        psxo_softmax_rows(scores, scores, q_len, total); /* :578 */
+        for (int64_t i = 0; i < q_len; ++i) { /* gemm: :110-118 (one accumulator per output, products in order) */
+            for (int64_t d = 0; d < head_dim; ++d) {
+                float acc = 0.0f;
+                for (int64_t j = 0; j < total; ++j) acc += scores[i * total + j] * v[j * head_dim + d];
+                context[(nh * q_len + i) * head_dim + d] = acc;
+            }
+        }
+    }
+    free(scores);
 }

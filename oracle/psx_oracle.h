@@ -102,6 +102,16 @@ void psxo_softmax_rows(const float* in, float* out, int64_t rows, int64_t cols);
 void psxo_logsumexp_rows(const float* in, float* out, int64_t rows, int64_t cols);
 void psxo_gather_rows(const float* table, const float* indices, float* out, int64_t count, int64_t dim);
 
+/* MultiHeadAttentionModule::forward_cached, src/multihead_attention_module.cpp:562-586, with the CPU
+ * backend's loops: scores by gemm_ex against the cached keys (src/cpu_backend.cpp:186-198), the score scale
+ * (axpby, :272-277), attention_mask_fill (:429-443 with src/row_math.hpp:117-127), softmax_rows, context by
+ * gemm against the cached values (:110-118).  q, context: (batch, heads, q_len, head_dim); keys, values:
+ * (batch, kv_heads, max_len, head_dim) with cached + q_len positions filled; key_keep: (batch, cached +
+ * q_len) or NULL. */
+void psxo_decode_attention(const float* q, const float* keys, const float* values, const float* key_keep, float* context,
+                           int64_t batch, int64_t heads, int64_t kv_heads, int64_t q_len, int64_t head_dim, int64_t cached,
+                           int64_t max_len, float scale, int causal, int64_t window);
+
 /* src/determinism.cpp:24-34: the global seed stream. */
 void psxo_set_seed(uint64_t seed);
 uint64_t psxo_next_seed(void);

@@ -159,6 +159,33 @@ void psxref_gather_rows(const float* table, const float* indices, float* out, in
     cpu.gather_rows(table, indices, out, static_cast<size_t>(count), static_cast<size_t>(dim));
 }
 
+// The core of MultiHeadAttentionModule::forward_cached (src/multihead_attention_module.cpp:562-586) through the
+// reference's CPUBackend, call for call: gemm_ex, axpby, attention_mask_fill, softmax_rows, gemm.
+void psxref_decode_attention(const float* q, const float* keys, const float* values, const float* key_keep, float* context,
+                             int64_t batch, int64_t heads, int64_t kv_heads, int64_t q_len, int64_t head_dim, int64_t cached,
+                             int64_t max_len, float scale, int causal, int64_t window) {
+    pulsatrix::CPUBackend cpu;
+    const int64_t total = cached + q_len, group = heads / kv_heads;
+    const auto n = static_cast<size_t>(batch), h = static_cast<size_t>(heads), l = static_cast<size_t>(q_len),
+               d = static_cast<size_t>(head_dim), t = static_cast<size_t>(total);
+    std::vector<float> scores(n * h * l * t);
+    for (int64_t nh = 0; nh < batch * heads; ++nh) {
+        const int64_t kv = (nh / heads) * kv_heads + (nh % heads) / group;
+        cpu.gemm_ex(q + nh * q_len * head_dim, false, keys + kv * max_len * head_dim, true, scores.data() + nh * q_len * total, l, d, t,
+                    0.0f);
+    }
+    cpu.axpby(scale, scores.data(), 0.0f, nullptr, scores.data(), scores.size());
+    if (causal || key_keep != nullptr) {
+        cpu.attention_mask_fill(scores.data(), key_keep, n, h, l, t, causal != 0, static_cast<size_t>(cached),
+                                static_cast<size_t>(window), std::numeric_limits<float>::lowest());
+    }
+    cpu.softmax_rows(scores.data(), scores.data(), n * h * l, t);
+    for (int64_t nh = 0; nh < batch * heads; ++nh) {
+        const int64_t kv = (nh / heads) * kv_heads + (nh % heads) / group;
+        cpu.gemm(scores.data() + nh * q_len * total, values + kv * max_len * head_dim, context + nh * q_len * head_dim, l, t, d);
+    }
+}
+
 // A tiny Hugging Face model of the reference's own fixtures (tests/fixtures/hf_tiny/<name>), decoded
 // greedily for `steps` tokens after `prompt`: per step the input of the language-model head (the
 // final norm's output at the last position, d floats), the logits the reference's head makes of it

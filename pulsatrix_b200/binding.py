@@ -17,7 +17,7 @@ EXPORTS = [
     "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready",
     "psx_b200_ctx_set_wait_limit", "psx_b200_test_short_copy", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_shard_merge_rows",
-    "psx_b200_top_k_rows", "psx_b200_lm_head_logits", "psx_b200_lm_head_sample_rows", "psx_b200_softmax_rows", "psx_b200_logsumexp_rows", "psx_b200_gather_rows",
+    "psx_b200_top_k_rows", "psx_b200_lm_head_logits", "psx_b200_lm_head_sample_rows", "psx_b200_softmax_rows", "psx_b200_logsumexp_rows", "psx_b200_gather_rows", "psx_b200_decode_attention",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
 
@@ -120,6 +120,8 @@ def library():
         lib.psx_b200_softmax_rows.argtypes = [ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
         lib.psx_b200_logsumexp_rows.argtypes = [ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
         lib.psx_b200_gather_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t]
+        lib.psx_b200_decode_attention.argtypes = [ptr, ptr, ptr, ptr, ptr, ptr, ptr, i64, i64, i64, i64, i64, i64, i64, C.c_float, C.c_int32,
+                                                  i64, ptr]
         lib.psx_uniforms_mt19937_64.argtypes = [ptr, i64, ptr]
         lib.psx_uniforms_portable.argtypes = [ptr, i64, ptr]
         _lib = lib
@@ -424,6 +426,26 @@ class Context:
         _check(self._lib.psx_b200_gather_rows(self._ctx, C.c_void_p(stream), _dptr(table), _dptr(indices), _dptr(out),
                                               indices.shape[0], table.shape[1]))
         return out
+
+    def decode_attention(self, q, keys, values, cached, scale=None, causal=True, window=0, key_keep=None, stream=None):
+        """Attention of the new positions over the KV cache (psx_b200_decode_attention).  q: cuda float32
+        (batch, heads, q_len, head_dim); keys / values: the cache, (batch, kv_heads, max_len, head_dim), with
+        positions 0 .. cached + q_len - 1 filled; key_keep: (batch, cached + q_len) or None.  Returns the
+        context, (batch, heads, q_len, head_dim), and a one-element int32 status tensor."""
+        import torch
+        batch, heads, q_len, head_dim = q.shape
+        kv_heads, max_len = keys.shape[1], keys.shape[2]
+        if scale is None:
+            scale = 1.0 / float(np.sqrt(np.float32(head_dim)))
+        context = torch.empty_like(q)
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        if stream is None:
+            stream = torch.cuda.current_stream(q.device).cuda_stream
+        _check(self._lib.psx_b200_decode_attention(self._ctx, C.c_void_p(stream), _dptr(q), _dptr(keys), _dptr(values),
+                                                   _dptr(key_keep) if key_keep is not None else None, _dptr(context), batch, heads,
+                                                   kv_heads, q_len, head_dim, cached, max_len, C.c_float(scale), int(bool(causal)),
+                                                   window, _dptr(status)))
+        return context, status
 
     # ---- vocabulary-sharded -----------------------------------------------------------------------------
     def shard_record_bytes(self, config) -> int:

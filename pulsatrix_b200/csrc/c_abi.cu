@@ -13,6 +13,7 @@
 
 #include "lm_head.cuh"
 #include "merge_rows.cuh"
+#include "decode_attention.cuh"
 #include "process_rows.cuh"
 #include "row_ops.cuh"
 #include "sample_plan.cuh"
@@ -63,7 +64,7 @@ struct psx_ctx {
     // (see ScanParams::wait_before_writes).
     Buffer stats[2], part_counts[2], candidates[2];
     int scratch_set = 0;
-    Buffer banned, sort_keys, head_logits;
+    Buffer banned, sort_keys, head_logits, attention_partial;
     // ProcessLogits: the surviving set between the survivor stage and the write-back, dummy draw outputs
     Buffer surv_cols, surv_vals, surv_counts, pl_tokens, pl_log_probs, pl_status;
     // staging of the host entry point
@@ -226,7 +227,7 @@ void psx_b200_ctx_destroy(psx_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    for (Buffer* b : {&ctx->stats[0], &ctx->stats[1], &ctx->part_counts[0], &ctx->part_counts[1], &ctx->candidates[0], &ctx->candidates[1], &ctx->banned, &ctx->sort_keys, &ctx->head_logits, &ctx->surv_cols, &ctx->surv_vals,
+    for (Buffer* b : {&ctx->stats[0], &ctx->stats[1], &ctx->part_counts[0], &ctx->part_counts[1], &ctx->candidates[0], &ctx->candidates[1], &ctx->banned, &ctx->sort_keys, &ctx->head_logits, &ctx->attention_partial, &ctx->surv_cols, &ctx->surv_vals,
                       &ctx->surv_counts, &ctx->pl_tokens, &ctx->pl_log_probs, &ctx->pl_status, &ctx->h_logits, &ctx->h_history,
                       &ctx->h_offsets, &ctx->h_uniforms, &ctx->h_tokens, &ctx->h_log_probs, &ctx->h_status,
                       &ctx->h_diag, &ctx->shard_uniform_scratch}) {
@@ -822,6 +823,48 @@ psx_status psx_b200_gather_rows(psx_ctx* ctx, void* stream_ptr, const float* tab
     PSX_CUDA(cudaSetDevice(ctx->device));
     PSX_CUDA(psx::launch_gather_rows(table, indices, out, count, dim, static_cast<cudaStream_t>(stream_ptr)));
     ++ctx->launches;
+    return PSX_OK;
+}
+
+psx_status psx_b200_decode_attention(psx_ctx* ctx, void* stream_ptr, const float* q, const float* keys, const float* values,
+                                     const float* key_keep, float* context, int64_t batch, int64_t heads, int64_t kv_heads,
+                                     int64_t q_len, int64_t head_dim, int64_t cached, int64_t max_len, float scale,
+                                     int32_t causal, int64_t window, int32_t* status) {
+    if (!ctx) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: context is null");
+    if (batch < 0 || heads <= 0 || kv_heads <= 0 || q_len <= 0 || head_dim <= 0 || cached < 0 || window < 0) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: attention sizes must be positive");
+    }
+    if (heads % kv_heads != 0) {  // src/multihead_attention_module.cpp: num_heads must be a multiple of num_kv_heads
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: heads must be a multiple of kv_heads");
+    }
+    const int64_t total = cached + q_len;
+    if (total > max_len) return fail(PSX_ERR_BAD_ARGUMENT, "KVCache: the cache is full");  // src/kv_cache.cpp
+    if (batch == 0) return PSX_OK;
+    if (!q || !keys || !values || !context) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(values)) % 16 != 0) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the cache must start on a 16-byte boundary");
+    }
+    const int64_t group = heads / kv_heads;
+    if (group * q_len > 8 || head_dim % 4 != 0 || head_dim > 128) {
+        return fail(PSX_ERR_UNSUPPORTED,
+                    "psx_b200: attention over the cache takes at most 8 query rows per kv head (group x new positions) "
+                    "and a head dimension that is a multiple of 4 up to 128");
+    }
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    psx::AttentionParams p{};
+    p.q = q; p.keys = keys; p.values = values; p.key_keep = key_keep; p.context = context; p.status = status;
+    p.batch = batch; p.total = total; p.max_len = max_len; p.offset = cached; p.window = window;
+    p.heads = (int32_t)heads; p.kv_heads = (int32_t)kv_heads; p.group = (int32_t)group; p.q_len = (int32_t)q_len;
+    p.head_dim = (int32_t)head_dim; p.causal = causal ? 1 : 0; p.scale = scale;
+    p.wait_limit_ns = ctx->wait_limit_ns;
+    p.splits = psx::attention_splits(batch * kv_heads, total, ctx->sm_count);
+    if (p.splits > 1) {
+        if (psx_status s = reserve(ctx->attention_partial, psx::attention_partial_bytes(p))) return s;
+        p.partial = static_cast<float*>(ctx->attention_partial.ptr);
+    }
+    PSX_CUDA(psx::launch_decode_attention(p, stream));
+    ctx->launches += p.splits > 1 ? 2 : 1;
     return PSX_OK;
 }
 

@@ -1,0 +1,336 @@
+// Attention of a few new positions over the KV cache (the per-token loop of generate()):
+// MultiHeadAttentionModule::forward_cached, src/multihead_attention_module.cpp:562-586 --
+//   scores = q . K^T per (batch, head) (gemm_ex), times the score scale (axpby), masked entries set
+//   to the lowest float (attention_mask_fill: causal with the cache offset, sliding window, key
+//   padding; src/row_math.hpp:117-127), softmax over the cached positions (softmax_rows),
+//   context = P . V (gemm); grouped-query heads read K/V head h / group in place.
+// The reference makes five passes over an (N, H, L, total) score tensor; here the cache is read once
+// and the scores never exist in memory.
+//
+// HBM bound: K and V of every (batch, kv head) are read once, 8 * total * D bytes each.
+// One CTA of four warps takes one (batch, kv head) and one slice of the cached positions; the query
+// rows of the whole group -- group heads x L new positions, at most 8 -- are answered together, so
+// grouped-query heads share one pass over their K/V head.  A warp works through its positions 32 at a
+// time:
+//   - the K rows of a tile arrive in shared memory by bulk asynchronous copies (one 4*D-byte row per
+//     lane, an mbarrier per buffer, two buffers, no multicast), padded to D + 4 floats so that lanes
+//     reading different rows at the same offset fall into different banks;
+//   - lane t forms the dot products of position t with every query row (the query rows are read as
+//     broadcasts), scales and masks them;
+//   - the running maximum and sum of every query row are brought up to date (online softmax: what has
+//     been accumulated is rescaled when the maximum moves), the tile's probabilities go to shared memory;
+//   - lane c accumulates floats 4c .. 4c+3 of the context rows from the V rows, which it reads
+//     straight from global memory, coalesced.
+// The warps' partial results (maximum, sum, unnormalised context) meet in shared memory; with several
+// slices per (batch, kv head) they go to scratch and a second kernel joins them.
+//
+// Float arithmetic in another order than the reference's loops: results agree within the reference's
+// own CPU/GPU equivalence tolerance (1e-4, tests/backend_primitive_equivalence_cases.hpp:22), not bit
+// for bit.  A fully masked row comes out as the reference's: every score equals the lowest float, so
+// the softmax is uniform over all positions.
+#include "decode_attention.cuh"
+
+#include "psx_async.cuh"
+#include "psx_device.cuh"
+
+namespace psx {
+
+namespace {
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kTile = 32;          // positions per warp and tile: one per lane
+constexpr float kMasked = -FLT_MAX;  // std::numeric_limits<float>::lowest()
+
+// src/row_math.hpp:117-127 (i: new position, j: cached position, offset: positions cached before).
+__device__ __forceinline__ bool masked(const float* keep_row, int64_t i, int64_t j, bool causal, int64_t offset, int64_t window) {
+    if (causal && j > i + offset) return true;
+    if (causal && window > 0 && j + window <= i + offset) return true;
+    return keep_row != nullptr && keep_row[j] == 0.0f;
+}
+
+// R: query rows answered together (group x L, padded to 1, 2, 4 or 8); C: float4 chunks of a
+// context row per lane (D <= 128 C; only C = 1 is instantiated).
+template <int R, int C>
+__global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const AttentionParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int D = p.head_dim, pitch = D + 4;
+    const int rows = p.group * p.q_len;  // query rows of this kv head (<= R)
+    // shared memory: the query rows, then per warp two K tiles, the tile's probabilities, and at the end
+    // the warps' partial results
+    float* s_q = reinterpret_cast<float*>(smem);                                  // R x D
+    float* s_k = s_q + R * D + (size_t)warp * 2 * kTile * pitch;                  // 2 x 32 x (D + 4), per warp
+    float* s_p = s_q + R * D + (size_t)kAttnWarps * 2 * kTile * pitch + warp * kTile * R;  // 32 x R, per warp
+    float* s_ctx = s_q + R * D + (size_t)kAttnWarps * (2 * kTile * pitch + kTile * R);     // warps x R x D
+    float* s_ml = s_ctx + kAttnWarps * R * D;                                     // warps x R x 2
+    __shared__ __align__(8) uint64_t s_bar[kAttnWarps][2];
+
+    const int64_t nkv = blockIdx.x;  // (batch, kv head)
+    const int64_t n = nkv / p.kv_heads, kvh = nkv % p.kv_heads;
+    const int split = blockIdx.y;
+    const float* keys = p.keys + nkv * p.max_len * D;
+    const float* values = p.values + nkv * p.max_len * D;
+    const float* keep_row = p.key_keep ? p.key_keep + n * p.total : nullptr;
+
+    // the query rows of the group: row r = (head within the group) * L + (new position)
+    for (int i = threadIdx.x; i < R * D; i += kAttnThreads) {
+        const int r = i / D, d = i % D;
+        float v = 0.0f;
+        if (r < rows) {
+            const int64_t head = kvh * p.group + r / p.q_len;
+            v = p.q[((n * p.heads + head) * p.q_len + r % p.q_len) * D + d];
+        }
+        s_q[i] = v;
+    }
+    if (lane == 0) {
+        barrier_init(&s_bar[warp][0], 1);
+        barrier_init(&s_bar[warp][1], 1);
+        barrier_init_fence();
+    }
+    __syncthreads();
+
+    // this warp's positions: the split's share, cut into the warps' shares, in whole tiles
+    const int64_t per_split = (p.total + p.splits - 1) / p.splits;
+    const int64_t s0 = split * per_split, s1 = min(s0 + per_split, p.total);
+    const int64_t tiles_in_split = s1 > s0 ? (s1 - s0 + kTile - 1) / kTile : 0;
+    const int64_t tiles_per_warp = (tiles_in_split + kAttnWarps - 1) / kAttnWarps;
+    const int64_t t_begin = s0 + warp * tiles_per_warp * kTile, t_end = min(t_begin + tiles_per_warp * kTile, s1);
+    const int64_t my_tiles = t_end > t_begin ? (t_end - t_begin + kTile - 1) / kTile : 0;
+
+    auto fetch_tile = [&](int64_t tile, int buffer) {  // lane t asks for the K row of position t
+        const int64_t first = t_begin + tile * kTile;
+        const int count = (int)min((int64_t)kTile, t_end - first);
+        if (lane == 0) barrier_expect_bytes(&s_bar[warp][buffer], (uint32_t)count * (uint32_t)D * 4u);
+        __syncwarp();
+        if (lane < count) {
+            bulk_copy_to_shared(s_k + ((size_t)buffer * kTile + lane) * pitch, keys + (first + lane) * D, (uint32_t)D * 4u,
+                                &s_bar[warp][buffer]);
+        }
+    };
+
+    float m_run[R], l_run[R];
+    float4 ctx[R][C];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        m_run[r] = kMasked;  // (a score is never below the lowest float, so the first tile always sets it)
+        l_run[r] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) ctx[r][c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    bool landed = true;
+    int64_t issued = -1, waited = 0;  // the last tile asked for; the tiles waited for so far
+    if (my_tiles > 0) { fetch_tile(0, 0); issued = 0; }
+    for (int64_t tile = 0; tile < my_tiles; ++tile) {
+        const int buffer = (int)(tile & 1);
+        if (tile + 1 < my_tiles) {
+            // every lane has finished with the other buffer (the warp met after the tile before); its reads
+            // through ordinary loads are ordered before the copy engine's writes
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            fetch_tile(tile + 1, buffer ^ 1);
+            issued = tile + 1;
+        }
+        landed = barrier_wait_bounded(&s_bar[warp][buffer], (uint32_t)((tile >> 1) & 1), p.wait_limit_ns) && landed;
+        if (!__all_sync(0xFFFFFFFFu, landed)) break;
+        waited = tile + 1;
+        const int64_t first = t_begin + tile * kTile;
+        const int count = (int)min((int64_t)kTile, t_end - first);
+        const int64_t pos = first + lane;
+
+        // ---- scores of position `pos` against every query row -----------------------------------------
+        float s[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[r] = 0.0f;
+        const float* krow = s_k + ((size_t)buffer * kTile + lane) * pitch;
+        for (int d = 0; d < D; d += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(krow + d);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float4 q4 = *reinterpret_cast<const float4*>(s_q + r * D + d);  // the same address in every lane
+                s[r] = __fmaf_rn(q4.x, k4.x, s[r]);
+                s[r] = __fmaf_rn(q4.y, k4.y, s[r]);
+                s[r] = __fmaf_rn(q4.z, k4.z, s[r]);
+                s[r] = __fmaf_rn(q4.w, k4.w, s[r]);
+            }
+        }
+        // ---- scale, mask, and the running softmax of every query row ------------------------------------
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float x = kMasked;
+            if (lane < count && r < rows) {
+                x = __fmul_rn(p.scale, s[r]);
+                if (masked(keep_row, r % p.q_len, pos, p.causal != 0, p.offset, p.window)) x = kMasked;
+            }
+            const bool counts = lane < count;  // (a lane beyond the tile adds nothing)
+            const float tile_max = warp_max(counts ? x : kMasked);
+            const float m_new = fmaxf(m_run[r], tile_max);
+            const float e = counts ? __expf(x - m_new) : 0.0f;
+            float e_sum = e;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) e_sum += __shfl_xor_sync(0xFFFFFFFFu, e_sum, o);
+            const float rescale = __expf(m_run[r] - m_new);  // 1 when the maximum stays; 0 from the very first tile
+            l_run[r] = __fmaf_rn(l_run[r], rescale, e_sum);
+            m_run[r] = m_new;
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                ctx[r][c].x *= rescale; ctx[r][c].y *= rescale; ctx[r][c].z *= rescale; ctx[r][c].w *= rescale;
+            }
+            s_p[lane * R + r] = e;
+        }
+        __syncwarp();
+        // ---- context: lane c owns floats 4c .. 4c + 3 (and 128 further on) of every row ----------------------
+        const float* vrow = values + first * D;
+#pragma unroll 4
+        for (int t = 0; t < count; ++t) {
+            float4 v4[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const int d = 4 * (lane + 32 * c);
+                v4[c] = d < D ? *reinterpret_cast<const float4*>(vrow + (size_t)t * D + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float pr = s_p[t * R + r];  // the same address in every lane
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    ctx[r][c].x = __fmaf_rn(pr, v4[c].x, ctx[r][c].x);
+                    ctx[r][c].y = __fmaf_rn(pr, v4[c].y, ctx[r][c].y);
+                    ctx[r][c].z = __fmaf_rn(pr, v4[c].z, ctx[r][c].z);
+                    ctx[r][c].w = __fmaf_rn(pr, v4[c].w, ctx[r][c].w);
+                }
+            }
+        }
+        __syncwarp();  // the probabilities and this K buffer are done with
+    }
+
+    // ---- the warps' partial results meet ----------------------------------------------------------------------
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const int d = 4 * (lane + 32 * c);
+            if (d < D) *reinterpret_cast<float4*>(s_ctx + ((size_t)warp * R + r) * D + d) = ctx[r][c];
+        }
+        if (lane == 0) {
+            s_ml[(warp * R + r) * 2] = m_run[r];
+            s_ml[(warp * R + r) * 2 + 1] = l_run[r];
+        }
+    }
+    const int timed_out = __syncthreads_or(landed ? 0 : 1);
+    if (timed_out) {  // a copy did not complete in time: say so, let the copies in flight drain, leave
+        if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, 1);
+        if (lane == 0) {  // the last two fetches of this warp, if they have not been waited for
+            for (int64_t t = max(issued - 1, (int64_t)0); t <= issued; ++t) {
+                if (t >= waited) barrier_wait_bounded(&s_bar[warp][t & 1], (uint32_t)((t >> 1) & 1), p.wait_limit_ns);
+            }
+        }
+        return;
+    }
+    // thread (r, d): joins the four warps' row r at column d
+    for (int i = threadIdx.x; i < rows * D; i += kAttnThreads) {
+        const int r = i / D, d = i % D;
+        float m = kMasked;
+        bool any = false;
+        for (int w = 0; w < kAttnWarps; ++w) {
+            if (s_ml[(w * R + r) * 2 + 1] > 0.0f) { m = fmaxf(m, s_ml[(w * R + r) * 2]); any = true; }
+        }
+        float l = 0.0f, acc = 0.0f;
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float lw = s_ml[(w * R + r) * 2 + 1];
+            if (lw > 0.0f) {
+                const float f = __expf(s_ml[(w * R + r) * 2] - m);
+                l = __fmaf_rn(lw, f, l);
+                acc = __fmaf_rn(s_ctx[((size_t)w * R + r) * D + d], f, acc);
+            }
+        }
+        const int64_t head = kvh * p.group + r / p.q_len;
+        const int64_t out_row = (n * p.heads + head) * p.q_len + r % p.q_len;
+        if (p.splits == 1) {
+            p.context[out_row * D + d] = any ? __fdiv_rn(acc, l) : 0.0f;
+        } else {  // unnormalised, with its maximum and sum, for the second kernel
+            float* part = p.partial + ((out_row * p.splits + split) * (D + 2));
+            part[d] = acc;
+            if (d == 0) { part[D] = any ? m : kMasked; part[D + 1] = l; }
+        }
+    }
+}
+
+// Joins the slices of every query row: thread per (row, column).
+__global__ void join_attention_splits_kernel(const AttentionParams p) {
+    const int D = p.head_dim;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t out_rows = p.batch * p.heads * p.q_len;
+    if (i >= out_rows * D) return;
+    const int64_t row = i / D;
+    const int d = (int)(i % D);
+    const float* part = p.partial + row * p.splits * (D + 2);
+    float m = kMasked;
+    for (int s = 0; s < p.splits; ++s) {
+        if (part[s * (D + 2) + D + 1] > 0.0f) m = fmaxf(m, part[s * (D + 2) + D]);
+    }
+    float l = 0.0f, acc = 0.0f;
+    for (int s = 0; s < p.splits; ++s) {
+        const float ls = part[s * (D + 2) + D + 1];
+        if (ls > 0.0f) {
+            const float f = __expf(part[s * (D + 2) + D] - m);
+            l = __fmaf_rn(ls, f, l);
+            acc = __fmaf_rn(part[s * (D + 2) + d], f, acc);
+        }
+    }
+    p.context[i] = l > 0.0f ? __fdiv_rn(acc, l) : 0.0f;
+}
+
+template <int R, int C>
+cudaError_t launch_one(const AttentionParams& p, size_t shared, cudaStream_t stream) {
+    static bool configured = false;  // (per instantiation; raising the limit twice is harmless)
+    if (!configured) {
+        const cudaError_t e = allow_all_dynamic_shared(decode_attention_kernel<R, C>);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    decode_attention_kernel<R, C><<<dim3((unsigned)(p.batch * p.kv_heads), (unsigned)p.splits), kAttnThreads, shared, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int attention_rows_padded(int rows) { return rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8; }
+
+size_t attention_shared_bytes(int rows_padded, int head_dim) {
+    const size_t floats = (size_t)rows_padded * head_dim + (size_t)kAttnWarps * (2 * kTile * (head_dim + 4) + kTile * rows_padded) +
+                          (size_t)kAttnWarps * rows_padded * head_dim + (size_t)kAttnWarps * rows_padded * 2;
+    return floats * sizeof(float);
+}
+
+int attention_splits(int64_t batch_kv, int64_t total, int sm_count) {
+    // Enough CTAs to fill the GPU (one CTA of four warps per SM and more), each with at least a few tiles per warp.
+    int splits = 1;
+    while (batch_kv * splits < 2 * (int64_t)sm_count && total / (2 * splits) >= 4 * kAttnWarps * kTile && splits < 64) splits *= 2;
+    return splits;
+}
+
+size_t attention_partial_bytes(const AttentionParams& p) {
+    return p.splits > 1 ? (size_t)p.batch * p.heads * p.q_len * p.splits * (p.head_dim + 2) * sizeof(float) : 0;
+}
+
+cudaError_t launch_decode_attention(const AttentionParams& p, cudaStream_t stream) {
+    if (p.batch <= 0 || p.total <= 0) return cudaSuccess;
+    const int rows = p.group * p.q_len;
+    // (a head dimension beyond 128 would need more shared memory for the K tiles than an SM has)
+    if (rows < 1 || rows > 8 || p.head_dim % 4 != 0 || p.head_dim > 128 || p.head_dim < 4) return cudaErrorInvalidValue;
+    const int R = attention_rows_padded(rows);
+    const size_t shared = attention_shared_bytes(R, p.head_dim);
+    cudaError_t e;
+    switch (R) {
+        case 1: e = launch_one<1, 1>(p, shared, stream); break;
+        case 2: e = launch_one<2, 1>(p, shared, stream); break;
+        case 4: e = launch_one<4, 1>(p, shared, stream); break;
+        default: e = launch_one<8, 1>(p, shared, stream); break;
+    }
+    if (e != cudaSuccess || p.splits == 1) return e;
+    const int64_t elements = p.batch * p.heads * p.q_len * p.head_dim;
+    join_attention_splits_kernel<<<(unsigned)((elements + 255) / 256), 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace psx

@@ -199,6 +199,24 @@ def row_primitive(lib_kind, name, *arrays):
     return out
 
 
+def decode_attention(lib_kind, q, keys, values, cached, scale, causal=True, window=0, key_keep=None):
+    """Attention of the new positions over the KV cache through a CPU checker.  q: (batch, heads, q_len, d);
+    keys / values: (batch, kv_heads, max_len, d)."""
+    lib = oracle() if lib_kind == "oracle" else reference()
+    fn = getattr(lib, ("psxo_" if lib_kind == "oracle" else "psxref_") + "decode_attention")
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    keys = np.ascontiguousarray(keys, dtype=np.float32)
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    keep = None if key_keep is None else np.ascontiguousarray(key_keep, dtype=np.float32)
+    batch, heads, q_len, d = q.shape
+    out = np.empty_like(q)
+    fn.restype = None
+    fn(_ptr(q, C.c_float), _ptr(keys, C.c_float), _ptr(values, C.c_float), _ptr(keep, C.c_float) if keep is not None else None,
+       _ptr(out, C.c_float), C.c_int64(batch), C.c_int64(heads), C.c_int64(keys.shape[1]), C.c_int64(q_len), C.c_int64(d),
+       C.c_int64(cached), C.c_int64(keys.shape[2]), C.c_float(scale), C.c_int(int(bool(causal))), C.c_int64(window))
+    return out
+
+
 def mt_uniforms(seeds):
     """First uniform of std::mt19937_64(seed) for each seed: (engine() >> 11) * 2^-53."""
     lib = oracle()

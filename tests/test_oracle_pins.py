@@ -328,3 +328,29 @@ def test_row_primitive_restatements_equal_the_reference_bit_for_bit():
     idx = rng.randint(0, 50, size=31).astype(np.float32)
     assert ol.row_primitive("oracle", "gather_rows", table, idx).tobytes() == \
         ol.row_primitive("reference", "gather_rows", table, idx).tobytes()
+
+
+@needs_reference
+def test_decode_attention_restatement_equals_the_reference_bit_for_bit():
+    """psxo_decode_attention against the reference's own CPUBackend calls of forward_cached's core
+    (src/multihead_attention_module.cpp:562-586): grouped-query heads, new positions, every mask."""
+    rng = np.random.RandomState(11)
+    cases = [dict(batch=2, heads=4, kv_heads=2, q_len=1, d=16, cached=37, max_len=48, causal=True, window=0, padding=False),
+             dict(batch=1, heads=6, kv_heads=3, q_len=3, d=8, cached=20, max_len=32, causal=True, window=7, padding=True),
+             dict(batch=3, heads=2, kv_heads=2, q_len=2, d=12, cached=0, max_len=4, causal=False, window=0, padding=True),
+             dict(batch=2, heads=8, kv_heads=1, q_len=1, d=64, cached=300, max_len=301, causal=True, window=0, padding=False)]
+    for c in cases:
+        q = rng.randn(c["batch"], c["heads"], c["q_len"], c["d"]).astype(np.float32)
+        keys = rng.randn(c["batch"], c["kv_heads"], c["max_len"], c["d"]).astype(np.float32)
+        values = rng.randn(c["batch"], c["kv_heads"], c["max_len"], c["d"]).astype(np.float32)
+        keep = None
+        if c["padding"]:
+            keep = (rng.rand(c["batch"], c["cached"] + c["q_len"]) > 0.4).astype(np.float32)
+            keep[0, :] = 0.0  # a fully masked entry: every score is the lowest float, the softmax uniform
+        scale = float(1.0 / np.sqrt(np.float32(c["d"])))
+        a = ol.decode_attention("oracle", q, keys, values, c["cached"], scale, c["causal"], c["window"], keep)
+        b = ol.decode_attention("reference", q, keys, values, c["cached"], scale, c["causal"], c["window"], keep)
+        assert a.tobytes() == b.tobytes()
+        if keep is not None and not c["causal"]:
+            total = c["cached"] + c["q_len"]
+            assert np.allclose(a[0, 0, 0], values[0, 0, :total].mean(axis=0), rtol=1e-5, atol=1e-6)  # uniform over all positions
