@@ -57,14 +57,16 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int D = p.head_dim, pitch = D + 4;
     const int rows = p.group * p.q_len;  // query rows of this kv head (<= R)
-    // shared memory: the query rows, then per warp two K tiles, the tile's probabilities, and at the end
-    // the warps' partial results
-    float* s_q = reinterpret_cast<float*>(smem);                                  // R x D
-    float* s_k = s_q + R * D + (size_t)warp * 2 * kTile * pitch;                  // 2 x 32 x (D + 4), per warp
-    float* s_p = s_q + R * D + (size_t)kAttnWarps * 2 * kTile * pitch + warp * kTile * R;  // 32 x R, per warp
-    float* s_ctx = s_q + R * D + (size_t)kAttnWarps * (2 * kTile * pitch + kTile * R);     // warps x R x D
-    float* s_ml = s_ctx + kAttnWarps * R * D;                                     // warps x R x 2
-    __shared__ __align__(8) uint64_t s_bar[kAttnWarps][2];
+    // shared memory: the query rows; per warp two K tiles, one V tile and the tile's probabilities; the warps'
+    // maxima and sums.  (At the end a warp's partial context rows lie over its own K tiles.)
+    const size_t per_warp = (size_t)2 * kTile * pitch + (size_t)kTile * D + (size_t)kTile * R;
+    float* s_q = reinterpret_cast<float*>(smem);                        // R x D
+    float* s_k = s_q + R * D + warp * per_warp;                         // 2 x 32 x (D + 4)
+    float* s_v = s_k + 2 * kTile * pitch;                               // 32 x D
+    float* s_p = s_v + kTile * D;                                       // 32 x R
+    float* s_ml = s_q + R * D + kAttnWarps * per_warp;                  // warps x R x 2
+    auto ctx_of_warp = [&](int w) { return s_q + R * D + w * per_warp; };  // R x D, over warp w's K tiles
+    __shared__ __align__(8) uint64_t s_bar[kAttnWarps][3];              // K buffer 0, K buffer 1, V
 
     const int64_t nkv = blockIdx.x;  // (batch, kv head)
     const int64_t n = nkv / p.kv_heads, kvh = nkv % p.kv_heads;
@@ -86,6 +88,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     if (lane == 0) {
         barrier_init(&s_bar[warp][0], 1);
         barrier_init(&s_bar[warp][1], 1);
+        barrier_init(&s_bar[warp][2], 1);
         barrier_init_fence();
     }
     __syncthreads();
@@ -98,6 +101,14 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     const int64_t t_begin = s0 + warp * tiles_per_warp * kTile, t_end = min(t_begin + tiles_per_warp * kTile, s1);
     const int64_t my_tiles = t_end > t_begin ? (t_end - t_begin + kTile - 1) / kTile : 0;
 
+    auto fetch_values = [&](int64_t tile) {  // the V rows of a tile are one contiguous run: one copy
+        const int64_t first = t_begin + tile * kTile;
+        const int count = (int)min((int64_t)kTile, t_end - first);
+        if (lane == 0) {
+            barrier_expect_bytes(&s_bar[warp][2], (uint32_t)count * (uint32_t)D * 4u);
+            bulk_copy_to_shared(s_v, values + first * D, (uint32_t)count * (uint32_t)D * 4u, &s_bar[warp][2]);
+        }
+    };
     auto fetch_tile = [&](int64_t tile, int buffer) {  // lane t asks for the K row of position t
         const int64_t first = t_begin + tile * kTile;
         const int count = (int)min((int64_t)kTile, t_end - first);
@@ -120,16 +131,19 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     }
     bool landed = true;
     int64_t issued = -1, waited = 0;  // the last tile asked for; the tiles waited for so far
+    int64_t values_issued = -1, values_waited = 0;
     if (my_tiles > 0) { fetch_tile(0, 0); issued = 0; }
     for (int64_t tile = 0; tile < my_tiles; ++tile) {
         const int buffer = (int)(tile & 1);
+        // every lane has finished with the other K buffer and with the V tile (the warp met after the tile
+        // before); its reads through ordinary loads are ordered before the copy engine's writes
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (tile + 1 < my_tiles) {
-            // every lane has finished with the other buffer (the warp met after the tile before); its reads
-            // through ordinary loads are ordered before the copy engine's writes
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             fetch_tile(tile + 1, buffer ^ 1);
             issued = tile + 1;
         }
+        fetch_values(tile);
+        values_issued = tile;  // (the warp met after the context of the tile before: the V tile is free; fenced above or below)
         landed = barrier_wait_bounded(&s_bar[warp][buffer], (uint32_t)((tile >> 1) & 1), p.wait_limit_ns) && landed;
         if (!__all_sync(0xFFFFFFFFu, landed)) break;
         waited = tile + 1;
@@ -178,38 +192,36 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             s_p[lane * R + r] = e;
         }
         __syncwarp();
-        // ---- context: lane c owns floats 4c .. 4c + 3 (and 128 further on) of every row ----------------------
-        const float* vrow = values + first * D;
+        // ---- context: lane c owns floats 4c .. 4c + 3 of every row; the V tile has had the scores' time to land ----
+        landed = barrier_wait_bounded(&s_bar[warp][2], (uint32_t)(tile & 1), p.wait_limit_ns) && landed;
+        if (!__all_sync(0xFFFFFFFFu, landed)) break;
+        values_waited = tile + 1;
+        if (4 * lane < D) {
 #pragma unroll 4
-        for (int t = 0; t < count; ++t) {
-            float4 v4[C];
+            for (int t = 0; t < count; ++t) {
+                const float4 v4 = *reinterpret_cast<const float4*>(s_v + (size_t)t * D + 4 * lane);
 #pragma unroll
-            for (int c = 0; c < C; ++c) {
-                const int d = 4 * (lane + 32 * c);
-                v4[c] = d < D ? *reinterpret_cast<const float4*>(vrow + (size_t)t * D + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const float pr = s_p[t * R + r];  // the same address in every lane
-#pragma unroll
-                for (int c = 0; c < C; ++c) {
-                    ctx[r][c].x = __fmaf_rn(pr, v4[c].x, ctx[r][c].x);
-                    ctx[r][c].y = __fmaf_rn(pr, v4[c].y, ctx[r][c].y);
-                    ctx[r][c].z = __fmaf_rn(pr, v4[c].z, ctx[r][c].z);
-                    ctx[r][c].w = __fmaf_rn(pr, v4[c].w, ctx[r][c].w);
+                for (int r = 0; r < R; ++r) {
+                    const float pr = s_p[t * R + r];  // the same address in every lane
+                    ctx[r][0].x = __fmaf_rn(pr, v4.x, ctx[r][0].x);
+                    ctx[r][0].y = __fmaf_rn(pr, v4.y, ctx[r][0].y);
+                    ctx[r][0].z = __fmaf_rn(pr, v4.z, ctx[r][0].z);
+                    ctx[r][0].w = __fmaf_rn(pr, v4.w, ctx[r][0].w);
                 }
             }
         }
         __syncwarp();  // the probabilities and this K buffer are done with
     }
 
-    // ---- the warps' partial results meet ----------------------------------------------------------------------
+    // ---- the warps' partial results meet (a warp whose wait ran out may still have copies in flight into its
+    // tiles and writes nothing there; the block then leaves below) ----------------------------------------------
+    const bool warp_landed = __all_sync(0xFFFFFFFFu, landed);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
 #pragma unroll
         for (int c = 0; c < C; ++c) {
             const int d = 4 * (lane + 32 * c);
-            if (d < D) *reinterpret_cast<float4*>(s_ctx + ((size_t)warp * R + r) * D + d) = ctx[r][c];
+            if (warp_landed && d < D) *reinterpret_cast<float4*>(ctx_of_warp(warp) + (size_t)r * D + d) = ctx[r][c];
         }
         if (lane == 0) {
             s_ml[(warp * R + r) * 2] = m_run[r];
@@ -223,6 +235,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             for (int64_t t = max(issued - 1, (int64_t)0); t <= issued; ++t) {
                 if (t >= waited) barrier_wait_bounded(&s_bar[warp][t & 1], (uint32_t)((t >> 1) & 1), p.wait_limit_ns);
             }
+            if (values_issued >= values_waited) barrier_wait_bounded(&s_bar[warp][2], (uint32_t)(values_issued & 1), p.wait_limit_ns);
         }
         return;
     }
@@ -240,7 +253,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
             if (lw > 0.0f) {
                 const float f = __expf(s_ml[(w * R + r) * 2] - m);
                 l = __fmaf_rn(lw, f, l);
-                acc = __fmaf_rn(s_ctx[((size_t)w * R + r) * D + d], f, acc);
+                acc = __fmaf_rn(ctx_of_warp(w)[(size_t)r * D + d], f, acc);
             }
         }
         const int64_t head = kvh * p.group + r / p.q_len;
@@ -297,8 +310,8 @@ cudaError_t launch_one(const AttentionParams& p, size_t shared, cudaStream_t str
 int attention_rows_padded(int rows) { return rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8; }
 
 size_t attention_shared_bytes(int rows_padded, int head_dim) {
-    const size_t floats = (size_t)rows_padded * head_dim + (size_t)kAttnWarps * (2 * kTile * (head_dim + 4) + kTile * rows_padded) +
-                          (size_t)kAttnWarps * rows_padded * head_dim + (size_t)kAttnWarps * rows_padded * 2;
+    const size_t per_warp = (size_t)2 * kTile * (head_dim + 4) + (size_t)kTile * head_dim + (size_t)kTile * rows_padded;
+    const size_t floats = (size_t)rows_padded * head_dim + (size_t)kAttnWarps * per_warp + (size_t)kAttnWarps * rows_padded * 2;
     return floats * sizeof(float);
 }
 

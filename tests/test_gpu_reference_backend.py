@@ -1,7 +1,7 @@
 """The boundary against the reference's real classes.  oracle/_ref/libpsx_refcuda.so holds the
 reference's own src/cuda_backend.cu, src/top_k.cpp and friends compiled in place, plus a harness
 that derives from the reference's CUDABackend and overrides top_k_rows with the call into
-libpsx_b200.so -- the binding INTEGRATION.md shows.  Through it run the reference's own top_k()
+libpsx_b200.so -- the binding a maintainer of the reference would add.  Through it run the reference's own top_k()
 and the inputs and checks of its TopKRowsMatchCPUBitExactly case
 (tests/backend_primitive_equivalence_cases.hpp:345-375); the reference's unmodified kernel answers
 the same questions beside it.  Skipped where the compiled reference is not present."""
