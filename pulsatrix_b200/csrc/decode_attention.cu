@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
 #pragma unroll
         for (int r = 0; r < R; ++r) s[r] = 0.0f;
         const float* krow = s_k + ((size_t)buffer * kTile + lane) * pitch;
+#pragma unroll 4
         for (int d = 0; d < D; d += 4) {
             const float4 k4 = *reinterpret_cast<const float4*>(krow + d);
 #pragma unroll
