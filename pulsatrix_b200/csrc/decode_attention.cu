@@ -8,19 +8,21 @@
 // and the scores never exist in memory.
 //
 // HBM bound: K and V of every (batch, kv head) are read once, 8 * total * D bytes each.
-// One CTA of four warps takes one (batch, kv head) and one slice of the cached positions; the query
+// One CTA of six warps takes one (batch, kv head) and one slice of the cached positions; the query
 // rows of the whole group -- group heads x L new positions, at most 8 -- are answered together, so
 // grouped-query heads share one pass over their K/V head.  A warp works through its positions 32 at a
 // time:
 //   - the K rows of a tile arrive in shared memory by bulk asynchronous copies (one 4*D-byte row per
-//     lane, an mbarrier per buffer, two buffers, no multicast), padded to D + 4 floats so that lanes
-//     reading different rows at the same offset fall into different banks;
+//     lane, completing on an mbarrier, no multicast), padded to D + 4 floats so that lanes reading
+//     different rows at the same offset fall into different banks; the next tile's rows are asked for as
+//     soon as this tile's scores are formed, and land under the softmax and the context;
 //   - lane t forms the dot products of position t with every query row (the query rows are read as
 //     broadcasts), scales and masks them;
 //   - the running maximum and sum of every query row are brought up to date (online softmax: what has
 //     been accumulated is rescaled when the maximum moves), the tile's probabilities go to shared memory;
-//   - lane c accumulates floats 4c .. 4c+3 of the context rows from the V rows, which it reads
-//     straight from global memory, coalesced.
+//   - lane c accumulates floats 4c .. 4c+3 of the context rows from the V rows (one contiguous run per
+//     tile, one bulk copy, asked for when the tile starts: it lands while the scores are formed).
+// One K tile and one V tile per warp (34 KB for a head dimension of 128) leave room for six warps per SM.
 // The warps' partial results (maximum, sum, unnormalised context) meet in shared memory; with several
 // slices per (batch, kv head) they go to scratch and a second kernel joins them.
 //
@@ -37,7 +39,7 @@ namespace psx {
 
 namespace {
 
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 6;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kTile = 32;          // positions per warp and tile: one per lane
 constexpr float kMasked = -FLT_MAX;  // std::numeric_limits<float>::lowest()
@@ -57,16 +59,16 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int D = p.head_dim, pitch = D + 4;
     const int rows = p.group * p.q_len;  // query rows of this kv head (<= R)
-    // shared memory: the query rows; per warp two K tiles, one V tile and the tile's probabilities; the warps'
-    // maxima and sums.  (At the end a warp's partial context rows lie over its own K tiles.)
-    const size_t per_warp = (size_t)2 * kTile * pitch + (size_t)kTile * D + (size_t)kTile * R;
+    // shared memory: the query rows; per warp a K tile, a V tile and the tile's probabilities; the warps'
+    // maxima and sums.  (At the end a warp's partial context rows lie over its own K tile.)
+    const size_t per_warp = (size_t)kTile * pitch + (size_t)kTile * D + (size_t)kTile * R;
     float* s_q = reinterpret_cast<float*>(smem);                        // R x D
-    float* s_k = s_q + R * D + warp * per_warp;                         // 2 x 32 x (D + 4)
-    float* s_v = s_k + 2 * kTile * pitch;                               // 32 x D
+    float* s_k = s_q + R * D + warp * per_warp;                         // 32 x (D + 4)
+    float* s_v = s_k + kTile * pitch;                                   // 32 x D
     float* s_p = s_v + kTile * D;                                       // 32 x R
     float* s_ml = s_q + R * D + kAttnWarps * per_warp;                  // warps x R x 2
-    auto ctx_of_warp = [&](int w) { return s_q + R * D + w * per_warp; };  // R x D, over warp w's K tiles
-    __shared__ __align__(8) uint64_t s_bar[kAttnWarps][3];              // K buffer 0, K buffer 1, V
+    auto ctx_of_warp = [&](int w) { return s_q + R * D + w * per_warp; };  // R x D, over warp w's K tile
+    __shared__ __align__(8) uint64_t s_bar[kAttnWarps][2];              // K, V
 
     const int64_t nkv = blockIdx.x;  // (batch, kv head)
     const int64_t n = nkv / p.kv_heads, kvh = nkv % p.kv_heads;
@@ -88,7 +90,6 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     if (lane == 0) {
         barrier_init(&s_bar[warp][0], 1);
         barrier_init(&s_bar[warp][1], 1);
-        barrier_init(&s_bar[warp][2], 1);
         barrier_init_fence();
     }
     __syncthreads();
@@ -105,18 +106,17 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         const int64_t first = t_begin + tile * kTile;
         const int count = (int)min((int64_t)kTile, t_end - first);
         if (lane == 0) {
-            barrier_expect_bytes(&s_bar[warp][2], (uint32_t)count * (uint32_t)D * 4u);
-            bulk_copy_to_shared(s_v, values + first * D, (uint32_t)count * (uint32_t)D * 4u, &s_bar[warp][2]);
+            barrier_expect_bytes(&s_bar[warp][1], (uint32_t)count * (uint32_t)D * 4u);
+            bulk_copy_to_shared(s_v, values + first * D, (uint32_t)count * (uint32_t)D * 4u, &s_bar[warp][1]);
         }
     };
-    auto fetch_tile = [&](int64_t tile, int buffer) {  // lane t asks for the K row of position t
+    auto fetch_tile = [&](int64_t tile) {  // lane t asks for the K row of position t
         const int64_t first = t_begin + tile * kTile;
         const int count = (int)min((int64_t)kTile, t_end - first);
-        if (lane == 0) barrier_expect_bytes(&s_bar[warp][buffer], (uint32_t)count * (uint32_t)D * 4u);
+        if (lane == 0) barrier_expect_bytes(&s_bar[warp][0], (uint32_t)count * (uint32_t)D * 4u);
         __syncwarp();
         if (lane < count) {
-            bulk_copy_to_shared(s_k + ((size_t)buffer * kTile + lane) * pitch, keys + (first + lane) * D, (uint32_t)D * 4u,
-                                &s_bar[warp][buffer]);
+            bulk_copy_to_shared(s_k + (size_t)lane * pitch, keys + (first + lane) * D, (uint32_t)D * 4u, &s_bar[warp][0]);
         }
     };
 
@@ -132,19 +132,14 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     bool landed = true;
     int64_t issued = -1, waited = 0;  // the last tile asked for; the tiles waited for so far
     int64_t values_issued = -1, values_waited = 0;
-    if (my_tiles > 0) { fetch_tile(0, 0); issued = 0; }
+    if (my_tiles > 0) { fetch_tile(0); issued = 0; }
     for (int64_t tile = 0; tile < my_tiles; ++tile) {
-        const int buffer = (int)(tile & 1);
-        // every lane has finished with the other K buffer and with the V tile (the warp met after the tile
-        // before); its reads through ordinary loads are ordered before the copy engine's writes
+        // every lane has finished with the V tile (the warp met after the context of the tile before); its reads
+        // through ordinary loads are ordered before the copy engine's writes
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (tile + 1 < my_tiles) {
-            fetch_tile(tile + 1, buffer ^ 1);
-            issued = tile + 1;
-        }
         fetch_values(tile);
-        values_issued = tile;  // (the warp met after the context of the tile before: the V tile is free; fenced above or below)
-        landed = barrier_wait_bounded(&s_bar[warp][buffer], (uint32_t)((tile >> 1) & 1), p.wait_limit_ns) && landed;
+        values_issued = tile;
+        landed = barrier_wait_bounded(&s_bar[warp][0], (uint32_t)(tile & 1), p.wait_limit_ns) && landed;
         if (!__all_sync(0xFFFFFFFFu, landed)) break;
         waited = tile + 1;
         const int64_t first = t_begin + tile * kTile;
@@ -155,7 +150,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         float s[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) s[r] = 0.0f;
-        const float* krow = s_k + ((size_t)buffer * kTile + lane) * pitch;
+        const float* krow = s_k + (size_t)lane * pitch;
 #pragma unroll 4
         for (int d = 0; d < D; d += 4) {
             const float4 k4 = *reinterpret_cast<const float4*>(krow + d);
@@ -167,6 +162,13 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
                 s[r] = __fmaf_rn(q4.z, k4.z, s[r]);
                 s[r] = __fmaf_rn(q4.w, k4.w, s[r]);
             }
+        }
+        // The K tile is done with: the next tile's rows can land under the rest of this tile's work.
+        __syncwarp();
+        if (tile + 1 < my_tiles) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            fetch_tile(tile + 1);
+            issued = tile + 1;
         }
         // ---- scale, mask, and the running softmax of every query row ------------------------------------
 #pragma unroll
@@ -194,7 +196,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         }
         __syncwarp();
         // ---- context: lane c owns floats 4c .. 4c + 3 of every row; the V tile has had the scores' time to land ----
-        landed = barrier_wait_bounded(&s_bar[warp][2], (uint32_t)(tile & 1), p.wait_limit_ns) && landed;
+        landed = barrier_wait_bounded(&s_bar[warp][1], (uint32_t)(tile & 1), p.wait_limit_ns) && landed;
         if (!__all_sync(0xFFFFFFFFu, landed)) break;
         values_waited = tile + 1;
         if (4 * lane < D) {
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
                 }
             }
         }
-        __syncwarp();  // the probabilities and this K buffer are done with
+        __syncwarp();  // the probabilities and the V tile are done with
     }
 
     // ---- the warps' partial results meet (a warp whose wait ran out may still have copies in flight into its
@@ -233,10 +235,8 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
     if (timed_out) {  // a copy did not complete in time: say so, let the copies in flight drain, leave
         if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, 1);
         if (lane == 0) {  // the last two fetches of this warp, if they have not been waited for
-            for (int64_t t = max(issued - 1, (int64_t)0); t <= issued; ++t) {
-                if (t >= waited) barrier_wait_bounded(&s_bar[warp][t & 1], (uint32_t)((t >> 1) & 1), p.wait_limit_ns);
-            }
-            if (values_issued >= values_waited) barrier_wait_bounded(&s_bar[warp][2], (uint32_t)(values_issued & 1), p.wait_limit_ns);
+            if (issued >= waited) barrier_wait_bounded(&s_bar[warp][0], (uint32_t)(issued & 1), p.wait_limit_ns);
+            if (values_issued >= values_waited) barrier_wait_bounded(&s_bar[warp][1], (uint32_t)(values_issued & 1), p.wait_limit_ns);
         }
         return;
     }
@@ -311,7 +311,7 @@ cudaError_t launch_one(const AttentionParams& p, size_t shared, cudaStream_t str
 int attention_rows_padded(int rows) { return rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8; }
 
 size_t attention_shared_bytes(int rows_padded, int head_dim) {
-    const size_t per_warp = (size_t)2 * kTile * (head_dim + 4) + (size_t)kTile * head_dim + (size_t)kTile * rows_padded;
+    const size_t per_warp = (size_t)kTile * (head_dim + 4) + (size_t)kTile * head_dim + (size_t)kTile * rows_padded;
     const size_t floats = (size_t)rows_padded * head_dim + (size_t)kAttnWarps * per_warp + (size_t)kAttnWarps * rows_padded * 2;
     return floats * sizeof(float);
 }

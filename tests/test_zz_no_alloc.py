@@ -136,3 +136,20 @@ def test_static_entry_point_bans_eos_ids_and_forgets_them_again():
         psx.sample_rows_static(d, None, None, gh.psx_config(many), None, *out)
     assert err.value.status == 4 and "256" in str(err.value)
     del rng
+
+
+def test_static_entry_point_with_enough_rows_for_the_survivor_stage_by_warps():
+    # 300 rows of one part each: the launch goes through the warp-per-row survivor kernel and the block
+    # kernel behind it; some rows tie 200 logits at the k-th value, more than a warp's list holds.
+    logits, hist = ol.synth_rows(np.arange(300) + 6000, 15001, 2.5, 1.0, 24)
+    offsets = np.arange(301, dtype=np.int64) * 24
+    seeds = np.arange(300, dtype=np.uint64) + 6000
+    rng = np.random.RandomState(9)
+    for r in range(0, 300, 37):
+        order = np.argsort(-logits[r])
+        logits[r, rng.choice(order[30:], 200, replace=False)] = logits[r, order[9]]
+    for settings in (dict(do_sample=True, temperature=0.9, top_k=16, top_p=0.9, repetition_penalty=1.1), dict(do_sample=False)):
+        cfg = ol.make_config(max_new_tokens=1, **settings)
+        want, got = _run_both(logits, hist, offsets, cfg, seeds)
+        assert (want[2] == 0).all() and (got[2] == 0).all()
+        assert got[0].tolist() == want[0].tolist()
