@@ -812,8 +812,17 @@ def run_softmax(args):
         results.append(entry)
         del xs, out
     peak, peak_kind = measured_hbm_peak()
+    # The reference's CPU backend beside it on a bounded sample (src/cpu_backend.cpp:292-338, single-threaded).
+    import oracle_lib as ol
+    which = "reference" if ol.reference_available() else "oracle"
+    sample = (np.random.RandomState(0).randn(64, 4096) * 3).astype(np.float32)
+    t0 = time.perf_counter()
+    ol.row_primitive(which, "softmax_rows", sample)
+    cpu_gbs = sample.size * 8 / (time.perf_counter() - t0) / 1e9
     emit({"metric": "softmax_rows / logsumexp_rows GB/s", "unit": "GB/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
-          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
+          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results,
+          "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s (softmax_rows, read + write)", "cores": 1,
+                           "kind": "reference" if which == "reference" else "port", "sample": "64 rows of 4096"}})
 
 
 LM_HEAD_SHAPES = [(1, 2048, 151936), (8, 2048, 151936), (64, 2048, 151936), (1, 576, 49152), (8, 4096, 128256)]
@@ -860,8 +869,22 @@ def run_lm_head(args):
                         "weight_gbs": 4 * vocab * d / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": 4 * vocab * d / (ms * 1e-3) / 1e9 / peak,
                         "sampling_from_host_logits_us": host_ms * 1e3})
         del weight
+    # The reference's loop beside it, on a bounded sample: one row against a 4096-entry slice of the first shape's
+    # head (src/cpu_backend.cpp:188-196: one accumulator per logit, products in order; numpy does the same
+    # arithmetic feature by feature), scaled to the whole vocabulary.
+    _, d, vocab = LM_HEAD_SHAPES[0]
+    rng = np.random.RandomState(0)
+    h = rng.randn(d).astype(np.float32)
+    wslice = (rng.randn(4096, d) * 0.05).astype(np.float32)
+    t0 = time.perf_counter()
+    acc = np.zeros(4096, dtype=np.float32)
+    for p_ in range(d):
+        acc = (acc + (h[p_] * wslice[:, p_]).astype(np.float32)).astype(np.float32)
+    cpu_us = (time.perf_counter() - t0) * 1e6 * vocab / 4096
     emit({"metric": "lm head + sampling step", "unit": "us per call", "n_gpus": 1, "dtype": "f32", "data": "synthetic",
-          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
+          "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results,
+          "cpu_baseline": {"value": cpu_us, "unit": "us per row (head alone)", "cores": 1, "kind": "port",
+                           "sample": f"one row against 4096 of {vocab} vocabulary entries, d = {d}, scaled to the vocabulary"}})
 
 
 ATTENTION_SHAPES = [  # (batch, heads, kv_heads, head_dim, cached positions)
@@ -901,8 +924,22 @@ def run_attention(args):
         results.append({"batch": batch, "heads": heads, "kv_heads": kv_heads, "head_dim": d, "cached": cached, "us": ms * 1e3,
                         "cache_mb": cache_bytes / 1e6, "cache_gbs": gbs, "frac_of_hbm_peak": gbs / peak})
         del caches
+    # The reference's CPU backend beside it, on a bounded sample: one sequence of the first shape (the loops of
+    # src/multihead_attention_module.cpp:562-586, single-threaded as there; the compiled reference when present).
+    import oracle_lib as ol
+    which = "reference" if ol.reference_available() else "oracle"
+    _, heads, kv_heads, d, cached = ATTENTION_SHAPES[0]
+    rng = np.random.RandomState(0)
+    q = rng.randn(1, heads, 1, d).astype(np.float32)
+    k = rng.randn(1, kv_heads, cached + 1, d).astype(np.float32)
+    v = rng.randn(1, kv_heads, cached + 1, d).astype(np.float32)
+    t0 = time.perf_counter()
+    ol.decode_attention(which, q, k, v, cached, float(1.0 / np.sqrt(d)))
+    cpu_us = (time.perf_counter() - t0) * 1e6
     emit({"metric": "attention of one new position over the KV cache", "unit": "us per call", "n_gpus": 1, "dtype": "f32",
-          "data": "synthetic", "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results})
+          "data": "synthetic", "hbm_peak_gbs": peak, "peak_kind": peak_kind, "results": results,
+          "cpu_baseline": {"value": cpu_us, "unit": "us per sequence", "cores": 1, "kind": "reference" if which == "reference" else "port",
+                           "sample": f"one sequence of {heads} heads over {kv_heads} kv heads, head_dim {d}, {cached} cached positions"}})
 
 
 def main():
