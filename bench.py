@@ -27,6 +27,10 @@ steps and a check of the first 48 rows against the reference fixture.
 `--impl reference` times the reference's own CPU sampler (compiled from its sources into
 oracle/_ref, or the plain-C restatement when that is absent) on a bounded sample of the same
 workload, rank 0 only.
+
+`--top-k`, `--softmax`, `--lm-head` and `--attention` time the other kernels of the library instead
+(one GPU, a JSON line of their own with the shapes, microseconds and GB/s against the measured HBM
+peak, and the reference's CPU code on a bounded sample beside them).
 """
 from __future__ import annotations
 
