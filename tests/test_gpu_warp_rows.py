@@ -9,6 +9,7 @@ import pytest
 
 import gpu_harness as gh
 import oracle_lib as ol
+import pulsatrix_b200 as psx
 
 pytestmark = pytest.mark.gpu
 
@@ -60,3 +61,31 @@ def test_eos_bans_and_unaligned_rows_by_warp():
                              eos_token_ids=eos, min_new_tokens=3)
         gh.check_rows_against_oracle(logits, hist, offsets, cfg, seeds, pad_columns=1, shift=3)
         gh.check_rows_against_oracle(logits, hist, offsets, cfg, seeds, num_new_tokens=3)
+
+
+@pytest.mark.parametrize("seed", range(5000, 5012))
+def test_randomised_settings_by_warp(seed):
+    """Random vocabularies, scales, ties on a grid, histories with ids out of range, every filter, bans: 256
+    rows or more, so the launch goes by warps (and by blocks for what the warps leave)."""
+    rng = np.random.RandomState(seed)
+    vocab = int(rng.choice([257, 1025, 4097, 16385, 20000, 33000]))
+    rows = int(rng.choice([256, 261, 300]))
+    logits = (rng.randn(rows, vocab) * float(rng.choice([0.5, 2.0, 4.0, 8.0]))).astype(np.float32)
+    zeta = float(rng.choice([0.0, 0.0, 1.0, 1.5]))
+    if zeta:
+        logits -= (zeta * np.log(rng.permutation(vocab) + 1.0)).astype(np.float32)[None, :]
+    mode = rng.rand()
+    if mode < 0.25:
+        logits = (np.round(logits * 2) / 2).astype(np.float32)   # many exact ties
+    elif mode < 0.4:
+        logits = (np.round(logits * 8) / 8).astype(np.float32)
+    hlen = int(rng.choice([1, 16, 300]))
+    hist = rng.randint(-2, vocab + 2, size=(rows, hlen)).astype(np.int64)
+    offsets = np.arange(rows + 1, dtype=np.int64) * hlen
+    seeds = rng.randint(0, 2**31, size=rows).astype(np.uint64)
+    cfg = ol.make_config(max_new_tokens=1, do_sample=bool(rng.rand() < 0.8), temperature=float(rng.choice([0.3, 0.7, 1.0, 1.5])),
+                         top_k=int(rng.choice([1, 3, 20, 33, 64])), top_p=float(rng.choice([1.0, 0.99, 0.9, 0.5])),
+                         min_p=float(rng.choice([0.0, 0.0, 0.0, 0.05])), repetition_penalty=float(rng.choice([1.0, 1.1, 1.3, 0.9])),
+                         min_new_tokens=int(rng.choice([0, 2])), eos_token_ids=rng.randint(0, vocab, size=2))
+    (_, _, status, _), _ = gh.check_rows_against_oracle(logits, hist, offsets, cfg, seeds, expect_ok=False)
+    assert set(np.unique(status)) <= {psx.ROW_OK, psx.ROW_ALL_REMOVED}  # (every token removed: as the reference says then)
