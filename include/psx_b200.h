@@ -46,7 +46,9 @@ typedef enum psx_row_status {
     PSX_ROW_NON_FINITE = 4,  /* "Generate: the model returned a non-finite logit" (src/generation.cpp:128-132) */
     PSX_ROW_ALL_REMOVED = 5, /* "Generate: every token was removed" (src/generation.cpp:136-138) */
     PSX_ROW_TOO_WIDE = 16,   /* more tokens survive the filters (or tie at a cut) than the device
-                                path holds; nothing was drawn for this row */
+                                path holds; nothing was drawn for this row.  Only where the whole row is
+                                not at hand (the vocabulary-sharded merge): with the row on the GPU such a
+                                row is decided from the row itself */
     PSX_ROW_DEVICE_TIMEOUT = 32 /* a bounded device-side wait (a bulk copy of a piece of the row into
                                 shared memory) ran out; nothing was drawn for this row */
 } psx_row_status;
@@ -164,7 +166,7 @@ PSX_API psx_status psx_b200_read_only_pass(void* stream, const void* data, size_
  * decode loop inside a serving process whose own pool already owns the GPU's memory (a cudaMalloc
  * from a plug-in would fail or stall), or a latency-critical loop that cannot afford cudaMalloc's
  * device-wide synchronisation.  It takes no context and calls no cudaMalloc / cudaFree: the
- * scratch between its two kernels is a fixed array inside the library image on every GPU (about
+ * scratch between its kernels is a fixed array inside the library image on every GPU (about
  * 8.1 MiB).  Limits: rows * ceil(vocab / 16384) <= 1024 and at most 256 banned EOS ids, else
  * PSX_ERR_UNSUPPORTED.  The
  * first call on a device looks up that array's address and sets the kernels up: make it at
