@@ -893,6 +893,7 @@ def run_lm_head(args):
 
 ATTENTION_SHAPES = [  # (batch, heads, kv_heads, head_dim, cached positions)
     (64, 32, 8, 128, 4096), (8, 32, 8, 128, 16384), (1, 32, 8, 128, 32768), (256, 16, 16, 64, 1024), (64, 32, 32, 128, 2048),
+    (64, 8, 4, 256, 4096),
 ]
 
 

@@ -280,7 +280,7 @@ PSX_API psx_status psx_b200_lm_head_sample_rows(psx_ctx* ctx, void* stream, cons
  * key_keep: (batch, cached + q_len) or null.  All device pointers, stream-asynchronous.  status (device,
  * may be null): bit 0 is set if a bounded device-side wait for a copy ran out.  Float sums in another
  * order than the reference's loops: within its 1e-4 CPU/GPU equivalence tolerance, not bit for bit.
- * Limits: (heads / kv_heads) * q_len <= 8, head_dim a multiple of 4 up to 128 (else PSX_ERR_UNSUPPORTED). */
+ * Limits: (heads / kv_heads) * q_len <= 8, head_dim a multiple of 4 up to 256 (else PSX_ERR_UNSUPPORTED). */
 PSX_API psx_status psx_b200_decode_attention(psx_ctx* ctx, void* stream, const float* q, const float* keys, const float* values,
                                              const float* key_keep, float* context, int64_t batch, int64_t heads,
                                              int64_t kv_heads, int64_t q_len, int64_t head_dim, int64_t cached, int64_t max_len,

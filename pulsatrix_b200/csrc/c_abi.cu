@@ -845,10 +845,10 @@ psx_status psx_b200_decode_attention(psx_ctx* ctx, void* stream_ptr, const float
         return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the cache must start on a 16-byte boundary");
     }
     const int64_t group = heads / kv_heads;
-    if (group * q_len > 8 || head_dim % 4 != 0 || head_dim > 128) {
+    if (group * q_len > 8 || head_dim % 4 != 0 || head_dim > 256) {
         return fail(PSX_ERR_UNSUPPORTED,
                     "psx_b200: attention over the cache takes at most 8 query rows per kv head (group x new positions) "
-                    "and a head dimension that is a multiple of 4 up to 128");
+                    "and a head dimension that is a multiple of 4 up to 256");
     }
     PSX_CUDA(cudaSetDevice(ctx->device));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -858,7 +858,7 @@ psx_status psx_b200_decode_attention(psx_ctx* ctx, void* stream_ptr, const float
     p.heads = (int32_t)heads; p.kv_heads = (int32_t)kv_heads; p.group = (int32_t)group; p.q_len = (int32_t)q_len;
     p.head_dim = (int32_t)head_dim; p.causal = causal ? 1 : 0; p.scale = scale;
     p.wait_limit_ns = ctx->wait_limit_ns;
-    p.splits = psx::attention_splits(batch * kv_heads, total, ctx->sm_count);
+    p.splits = psx::attention_splits(batch * kv_heads, total, ctx->sm_count, (int)head_dim);
     if (p.splits > 1) {
         if (psx_status s = reserve(ctx->attention_partial, psx::attention_partial_bytes(p))) return s;
         p.partial = static_cast<float*>(ctx->attention_partial.ptr);

@@ -41,8 +41,9 @@ namespace psx {
 
 namespace {
 
-constexpr int kAttnWarps = 6;
-constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kAttnWarps = 6;      // warps of a CTA up to a head dimension of 128 (34 KB of tiles each)
+constexpr int kAttnWarpsWide = 3;  // beyond it (67 KB each at 256)
+inline int attention_warps(int head_dim) { return head_dim > 128 ? kAttnWarpsWide : kAttnWarps; }
 constexpr int kTile = 32;          // positions per warp and tile: one per lane
 constexpr float kMasked = -FLT_MAX;  // std::numeric_limits<float>::lowest()
 
@@ -54,9 +55,10 @@ __device__ __forceinline__ bool masked(const float* keep_row, int64_t i, int64_t
 }
 
 // R: query rows answered together (group x L, padded to 1, 2, 4 or 8); C: float4 chunks of a
-// context row per lane (D <= 128 C; only C = 1 is instantiated).
-template <int R, int C>
-__global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const AttentionParams p) {
+// context row per lane (D <= 128 C); W: warps of a CTA.
+template <int R, int C, int W>
+__global__ void __launch_bounds__(W * 32) decode_attention_kernel(const AttentionParams p) {
+    constexpr int kAttnWarps = W, kAttnThreads = W * 32;
     extern __shared__ __align__(16) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int D = p.head_dim, pitch = D + 4;
@@ -201,17 +203,23 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const At
         landed = barrier_wait_bounded(&s_bar[warp][1], (uint32_t)(tile & 1), p.wait_limit_ns) && landed;
         if (!__all_sync(0xFFFFFFFFu, landed)) break;
         values_waited = tile + 1;
-        if (4 * lane < D) {
 #pragma unroll 4
-            for (int t = 0; t < count; ++t) {
-                const float4 v4 = *reinterpret_cast<const float4*>(s_v + (size_t)t * D + 4 * lane);
+        for (int t = 0; t < count; ++t) {
+            float4 v4[C];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const float pr = s_p[t * R + r];  // the same address in every lane
-                    ctx[r][0].x = __fmaf_rn(pr, v4.x, ctx[r][0].x);
-                    ctx[r][0].y = __fmaf_rn(pr, v4.y, ctx[r][0].y);
-                    ctx[r][0].z = __fmaf_rn(pr, v4.z, ctx[r][0].z);
-                    ctx[r][0].w = __fmaf_rn(pr, v4.w, ctx[r][0].w);
+            for (int c = 0; c < C; ++c) {
+                const int d = 4 * (lane + 32 * c);
+                v4[c] = d < D ? *reinterpret_cast<const float4*>(s_v + (size_t)t * D + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float pr = s_p[t * R + r];  // the same address in every lane
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    ctx[r][c].x = __fmaf_rn(pr, v4[c].x, ctx[r][c].x);
+                    ctx[r][c].y = __fmaf_rn(pr, v4[c].y, ctx[r][c].y);
+                    ctx[r][c].z = __fmaf_rn(pr, v4[c].z, ctx[r][c].z);
+                    ctx[r][c].w = __fmaf_rn(pr, v4[c].w, ctx[r][c].w);
                 }
             }
         }
@@ -296,15 +304,15 @@ __global__ void join_attention_splits_kernel(const AttentionParams p) {
     p.context[i] = l > 0.0f ? __fdiv_rn(acc, l) : 0.0f;
 }
 
-template <int R, int C>
+template <int R, int C, int W>
 cudaError_t launch_one(const AttentionParams& p, size_t shared, cudaStream_t stream) {
     static bool configured = false;  // (per instantiation; raising the limit twice is harmless)
     if (!configured) {
-        const cudaError_t e = allow_all_dynamic_shared(decode_attention_kernel<R, C>);
+        const cudaError_t e = allow_all_dynamic_shared(decode_attention_kernel<R, C, W>);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    decode_attention_kernel<R, C><<<dim3((unsigned)(p.batch * p.kv_heads), (unsigned)p.splits), kAttnThreads, shared, stream>>>(p);
+    decode_attention_kernel<R, C, W><<<dim3((unsigned)(p.batch * p.kv_heads), (unsigned)p.splits), W * 32, shared, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -314,16 +322,17 @@ int attention_rows_padded(int rows) { return rows <= 1 ? 1 : rows <= 2 ? 2 : row
 
 size_t attention_shared_bytes(int rows_padded, int head_dim) {
     const size_t per_warp = (size_t)kTile * (head_dim + 4) + (size_t)kTile * head_dim + (size_t)kTile * rows_padded;
-    const size_t floats = (size_t)rows_padded * head_dim + (size_t)kAttnWarps * per_warp + (size_t)kAttnWarps * rows_padded * 2;
+    const size_t warps = (size_t)attention_warps(head_dim);
+    const size_t floats = (size_t)rows_padded * head_dim + warps * per_warp + warps * rows_padded * 2;
     return floats * sizeof(float);
 }
 
-int attention_splits(int64_t batch_kv, int64_t total, int sm_count) {
+int attention_splits(int64_t batch_kv, int64_t total, int sm_count, int head_dim) {
     // One CTA fills an SM, so the CTAs run in rounds of sm_count: the slices are chosen so that the last round
     // is as full as the others (512 CTAs on 148 SMs are 3.46 rounds, i.e. four, an eighth of the time idle;
     // 1024 are 6.92), with at least two tiles per warp in a slice, and only when that wins a few per cent (the
     // slices cost a second kernel).
-    const int64_t most = std::max<int64_t>(1, std::min<int64_t>(128, total / (2 * kAttnWarps * kTile)));
+    const int64_t most = std::max<int64_t>(1, std::min<int64_t>(128, total / (2 * attention_warps(head_dim) * kTile)));
     auto filled = [&](int64_t ctas) { return (double)ctas / (double)(((ctas + sm_count - 1) / sm_count) * sm_count); };
     int best = 1;
     double best_fill = filled(batch_kv);
@@ -341,16 +350,16 @@ size_t attention_partial_bytes(const AttentionParams& p) {
 cudaError_t launch_decode_attention(const AttentionParams& p, cudaStream_t stream) {
     if (p.batch <= 0 || p.total <= 0) return cudaSuccess;
     const int rows = p.group * p.q_len;
-    // (a head dimension beyond 128 would need more shared memory for the K tiles than an SM has)
-    if (rows < 1 || rows > 8 || p.head_dim % 4 != 0 || p.head_dim > 128 || p.head_dim < 4) return cudaErrorInvalidValue;
+    if (rows < 1 || rows > 8 || p.head_dim % 4 != 0 || p.head_dim > 256 || p.head_dim < 4) return cudaErrorInvalidValue;
     const int R = attention_rows_padded(rows);
     const size_t shared = attention_shared_bytes(R, p.head_dim);
+    const bool wide = p.head_dim > 128;  // two chunks of a context row per lane, three warps per CTA
     cudaError_t e;
     switch (R) {
-        case 1: e = launch_one<1, 1>(p, shared, stream); break;
-        case 2: e = launch_one<2, 1>(p, shared, stream); break;
-        case 4: e = launch_one<4, 1>(p, shared, stream); break;
-        default: e = launch_one<8, 1>(p, shared, stream); break;
+        case 1: e = wide ? launch_one<1, 2, kAttnWarpsWide>(p, shared, stream) : launch_one<1, 1, kAttnWarps>(p, shared, stream); break;
+        case 2: e = wide ? launch_one<2, 2, kAttnWarpsWide>(p, shared, stream) : launch_one<2, 1, kAttnWarps>(p, shared, stream); break;
+        case 4: e = wide ? launch_one<4, 2, kAttnWarpsWide>(p, shared, stream) : launch_one<4, 1, kAttnWarps>(p, shared, stream); break;
+        default: e = wide ? launch_one<8, 2, kAttnWarpsWide>(p, shared, stream) : launch_one<8, 1, kAttnWarps>(p, shared, stream); break;
     }
     if (e != cudaSuccess || p.splits == 1) return e;
     const int64_t elements = p.batch * p.heads * p.q_len * p.head_dim;

@@ -26,10 +26,10 @@ struct AttentionParams {
 
 int attention_rows_padded(int rows);                              // group * q_len rounded up to 1, 2, 4 or 8
 size_t attention_shared_bytes(int rows_padded, int head_dim);     // dynamic shared memory of a CTA
-int attention_splits(int64_t batch_kv, int64_t total, int sm_count);
+int attention_splits(int64_t batch_kv, int64_t total, int sm_count, int head_dim);
 size_t attention_partial_bytes(const AttentionParams& p);
 // cudaErrorInvalidValue: more than 8 query rows per kv head, or a head dimension that is not a multiple
-// of 4 up to 128.
+// of 4 up to 256.
 cudaError_t launch_decode_attention(const AttentionParams& p, cudaStream_t stream);
 
 }  // namespace psx

@@ -47,7 +47,7 @@ def test_one_new_position_over_caches_of_every_length(cached):
 
 
 @pytest.mark.parametrize("heads,kv_heads,q_len,d", [(4, 4, 1, 128), (8, 1, 1, 64), (16, 2, 1, 128), (6, 3, 2, 32), (4, 2, 4, 96),
-                                                    (2, 2, 8, 4), (12, 12, 3, 80)])
+                                                    (2, 2, 8, 4), (12, 12, 3, 80), (4, 2, 1, 256), (8, 8, 1, 160), (2, 1, 2, 192), (8, 1, 1, 256)])
 def test_head_layouts_and_several_new_positions(heads, kv_heads, q_len, d):
     _case(batch=2, heads=heads, kv_heads=kv_heads, q_len=q_len, d=d, cached=300, max_len=512, seed=heads * 100 + d)
 
