@@ -46,7 +46,7 @@ __device__ __forceinline__ void decide_row(const MergeParams& p, const int64_t r
     }
 }
 
-__global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(kMergeThreads, kMergeThreads <= 256 ? 3 : 2) merge_rows_kernel(const MergeParams p) {
     extern __shared__ unsigned long long dyn[];
     PSX_MERGE_TIME(0);
     if (p.only_undecided) {

@@ -453,11 +453,14 @@ constexpr int kMassPasses = 8;  // histograms decide_wide needs: four passes ove
 // a piece.  What the rounding to 2^-44 loses, at most n * 2.9e-14 in all, is far inside
 // kExactMargin.
 constexpr double kMassUnit = 17592186044416.0;  // 2^44
+// `known` holds the digits above `top_shift + 8` that every key in play shares (0 when top_shift
+// is the keys' top digit): the passes over them are skipped.
 template <class KeyOf, class InPlay, class MassOf>
-__device__ inline void mass_select(KeyOf key_of, InPlay in_play, MassOf mass_of, int n, int top_shift, double start,
-                                   double target, uint32_t* hist, uint32_t& K, double& below, double& at) {
+__device__ inline void mass_select(KeyOf key_of, InPlay in_play, MassOf mass_of, int n, int top_shift, uint32_t known,
+                                   double start, double target, uint32_t* hist, uint32_t& K, double& below, double& at) {
     const int tid = threadIdx.x, lane = tid & 31;
-    uint32_t prefix = 0, mask = 0;
+    uint32_t mask = top_shift >= 24 ? 0u : ~((1u << (top_shift + 8)) - 1u);
+    uint32_t prefix = known & mask;
     // the running mass is compared as an integer: units of 2^-44 above `start`
     const double room = (target - start) * kMassUnit;
     const u64 target_units = room <= 0.0 ? 0ull : room >= 1.8e19 ? ~0ull : (u64)room;
@@ -527,10 +530,16 @@ __device__ inline void mass_select(KeyOf key_of, InPlay in_play, MassOf mass_of,
     at = (double)at_units / kMassUnit;
 }
 
+// Called by the whole block with ex[i] = exp(x_i - x_top) and alive[i] = 1 for the n entries of the list,
+// list_sum their sum in block_sum_fixed's order, top_key the largest value key and `differing` the
+// bits in which the value keys of the list are not all the same; `hist` is kWideWords words, the
+// first kMassPasses * 768 of them zero.
+constexpr int kCompactCap = 1024;                     // survivors that are drawn from a list of their own
+constexpr int kWideWords = kMassPasses * 768 + 8;
 __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const double* ex, uint8_t* alive, int n,
-                            bool rest_alive, double rest, double rest_bound, double u, double* scratch,
-                            uint32_t* hist /* kMassPasses * 768 words */, Decision& out) {
-    const int tid = threadIdx.x;
+                            bool rest_alive, double rest, double rest_bound, double u, double* scratch, uint32_t* hist,
+                            uint32_t top_key, uint32_t differing, double list_sum, Decision& out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     out.status = PSX_ROW_OK;
     out.token = -1;
     out.draw_margin = INFINITY;
@@ -543,17 +552,11 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
         }
         return block_sum_fixed(v, scratch);
     };
-    uint32_t top_key = 0;
-    for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
-    top_key = block_max_u32(top_key, scratch);
-    for (int i = tid; i < n; i += kMergeThreads) alive[i] = 1;
-    for (int i = tid; i < kMassPasses * 768; i += kMergeThreads) hist[i] = 0;
-    __syncthreads();
 
     if (p.top_p < 1.0f) {  // src/generation.cpp:89-103
         const double limit = 1.0 - (double)p.top_p;
         const double base = rest_alive ? rest : 0.0;
-        const double sum = base + masked_sum([&](int) { return true; });
+        const double sum = base + list_sum;
         double margin = INFINITY;
         if (rest_alive) {
             const double lead = base / sum;  // everything outside the list leads the ascending walk
@@ -565,8 +568,11 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
         if (limit >= 1.0 - 1e-12) return false;
         uint32_t cut;
         double mass_below, mass_at;
-        mass_select([&](int i) { return key_ord(keyA[i]); }, [&](int) { return true; }, [&](int i) { return ex[i]; }, n, 24, base,
-                    limit * sum, hist, cut, mass_below, mass_at);
+        // (neighbouring floats share their leading digits: a pass over a digit that all share would only
+        // queue every entry at one bin)
+        const int value_shift = differing >> 24 ? 24 : differing >> 16 ? 16 : differing >> 8 ? 8 : 0;
+        mass_select([&](int i) { return key_ord(keyA[i]); }, [&](int) { return true; }, [&](int i) { return ex[i]; }, n,
+                    value_shift, top_key, base, limit * sum, hist, cut, mass_below, mass_at);
         const double below = mass_below / sum;
         margin = fmin(margin, fabs(below - limit));
         // Entries equal to the cut value go in ascending column order, one probability each.
@@ -621,19 +627,66 @@ __device__ inline bool decide_wide(const MergeParams& p, const u64* keyA, const 
         }
     }
 
-    double count = 0.0;
-    for (int i = tid; i < n; i += kMergeThreads) count += alive[i] ? 1.0 : 0.0;
-    out.survivors = (int)block_sum_fixed(count, scratch);
+    // The survivors, counted warp after warp in list order; when few are left of a long list they move
+    // to a list of their own (over the histograms of the value selection, done with by now), in that
+    // same order, and the draw looks at nothing else.
+    constexpr int kWarps = kMergeThreads / 32;
+    uint32_t* warp_counts = hist + kMassPasses * 768;
+    uint32_t* small_cols = hist;
+    double* small_ex = reinterpret_cast<double*>(hist + kCompactCap);
+    const int chunk = ((n + kMergeThreads - 1) / kMergeThreads) * 32;  // entries of one warp
+    const int chunk_begin = warp * chunk, chunk_end = min(n, chunk_begin + chunk);
+    int mine = 0;
+    for (int i = chunk_begin + lane; i < chunk_begin + chunk; i += 32) {
+        mine += __popc(__ballot_sync(0xFFFFFFFFu, i < chunk_end && alive[i] != 0));
+    }
+    if (lane == 0) warp_counts[warp] = (uint32_t)mine;
+    __syncthreads();
+    int before_mine = 0, survivors = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const int c = (int)warp_counts[w];
+        before_mine += w < warp ? c : 0;
+        survivors += c;
+    }
+    out.survivors = survivors;
 
     // src/generation.cpp:140-152: the first column whose cumulative probability exceeds u.
     if (rest_alive) { out.status = PSX_ROW_TOO_WIDE; return true; }
-    const double sum = masked_sum([&](int i) { return alive[i] != 0; });
+    const bool on_their_own = survivors <= kCompactCap;
+    if (on_their_own) {
+        int at = before_mine;
+        for (int i = chunk_begin + lane; i < chunk_begin + chunk; i += 32) {
+            const bool stays = i < chunk_end && alive[i] != 0;
+            const uint32_t staying = __ballot_sync(0xFFFFFFFFu, stays);
+            if (stays) {
+                const int slot = at + __popc(staying & ((1u << lane) - 1u));
+                small_cols[slot] = key_col(keyA[i]);
+                small_ex[slot] = ex[i];
+            }
+            at += __popc(staying);
+        }
+        __syncthreads();
+    }
+    double sum;
+    if (on_their_own) {
+        double v = 0.0;
+        for (int i = tid; i < survivors; i += kMergeThreads) v += small_ex[i];
+        sum = block_sum_fixed(v, scratch);
+    } else {
+        sum = masked_sum([&](int i) { return alive[i] != 0; });
+    }
     // The first column at which the running mass rises above u * sum.
     uint32_t hi;
     double mass_before, mass_at;
     const int column_shift = p.vocab <= (1 << 16) ? 8 : p.vocab <= (1 << 24) ? 16 : 24;
-    mass_select([&](int i) { return key_col(keyA[i]); }, [&](int i) { return alive[i] != 0; }, [&](int i) { return ex[i]; }, n,
-                column_shift, 0.0, u * sum, hist + 4 * 768, hi, mass_before, mass_at);
+    if (on_their_own) {
+        mass_select([&](int i) { return small_cols[i]; }, [&](int) { return true; }, [&](int i) { return small_ex[i]; }, survivors,
+                    column_shift, 0u, 0.0, u * sum, hist + 4 * 768, hi, mass_before, mass_at);
+    } else {
+        mass_select([&](int i) { return key_col(keyA[i]); }, [&](int i) { return alive[i] != 0; }, [&](int i) { return ex[i]; }, n,
+                    column_shift, 0u, 0.0, u * sum, hist + 4 * 768, hi, mass_before, mass_at);
+    }
     const double before = mass_before / sum, upto = (mass_before + mass_at) / sum;
     out.draw_margin = before == 0.0 ? fabs(u - upto) : fmin(fabs(u - before), fabs(u - upto));
     if (out.draw_margin < kExactMargin) return false;
@@ -852,7 +905,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     PSX_MERGE_STAGE(0);
     const double u_row = (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5;
     if (tid == 0) s_count = 0;
-    reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);  // published by the barrier of step 1
+    if (tid < 256) reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);  // published by the barrier of step 1
     bool hist_clean = true;
 
     // ---- 1. join the parts; every candidate of the row into shared memory ----------------------------
@@ -963,16 +1016,29 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         }
         __syncthreads();
     } else {
-        for (int i = tid; i < total; i += kMergeThreads) {
-            const float l = __uint_as_float(cand_l[i]);
-            const uint32_t cf = cand_c[i];
-            z_raw += exp((double)l - (double)raw_max);
-            const float y = processed_before_temperature(l, cf, p.penalty);
-            if (y >= keep_from) {
+        // (a warp takes its places on the list with one addition: without a top-k thousands are listed,
+        // and one addition each would queue at the counter)
+        for (int base = 0; base < total; base += kMergeThreads) {
+            const int i = base + tid;
+            bool listed = false;
+            float y = 0.0f;
+            uint32_t cf = 0;
+            if (i < total) {
+                const float l = __uint_as_float(cand_l[i]);
+                cf = cand_c[i];
+                z_raw += exp((double)l - (double)raw_max);
+                y = processed_before_temperature(l, cf, p.penalty);
+                listed = y >= keep_from;
+            }
+            const uint32_t takers = __ballot_sync(0xFFFFFFFFu, listed);
+            int first_slot = 0;
+            if (takers != 0 && lane == 0) first_slot = atomicAdd(&s_count, __popc(takers));
+            first_slot = __shfl_sync(0xFFFFFFFFu, first_slot, 0);
+            if (listed) {
                 const float x = temper(y, apply_t, p.temperature);
-                const int slot = atomicAdd(&s_count, 1);
+                const int slot = first_slot + __popc(takers & ((1u << lane) - 1u));
                 if (slot < cap) keyA[slot] = ((u64)ordered_key(x) << 32) | (uint32_t)~(cf & kColumnMask);
-            } else if (y > -INFINITY && !top_k_on) {
+            } else if (i < total && y > -INFINITY && !top_k_on) {
                 z_rest += exp((double)temper(y, apply_t, p.temperature) - (double)x_max);
                 dropped += 1.0;
             }
@@ -1057,21 +1123,44 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     // ---- 3'. a long list without a top-k: decided by the whole block, without sorting --------------
     bool decided = false;
     if (p.do_sample && !top_k_on && n > kMergeThreads) {
-        uint32_t top_key = 0;
-        for (int i = tid; i < n; i += kMergeThreads) top_key = max(top_key, key_ord(keyA[i]));
-        top_key = block_max_u32(top_key, s_d[0]);
-        const float x_top = from_ordered_key(top_key);
+        // the largest value key, and the bits in which the value keys differ: one barrier for the three
+        uint32_t top_key = 0, in_all = ~0u, in_any = 0u;
         for (int i = tid; i < n; i += kMergeThreads) {
-            ex[i] = exp((double)from_ordered_key(key_ord(keyA[i])) - (double)x_top);  // src/generation.cpp:46
+            const uint32_t k = key_ord(keyA[i]);
+            top_key = max(top_key, k);
+            in_all &= k;
+            in_any |= k;
         }
+        top_key = __reduce_max_sync(0xFFFFFFFFu, top_key);
+        in_all = __reduce_and_sync(0xFFFFFFFFu, in_all);
+        in_any = __reduce_or_sync(0xFFFFFFFFu, in_any);
+        if (lane == 0) { s_u[0][warp] = top_key; s_u[1][warp] = in_all; s_u[2][warp] = in_any; }
         __syncthreads();
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; ++w) {
+            top_key = max(top_key, s_u[0][w]);
+            in_all &= s_u[1][w];
+            in_any |= s_u[2][w];
+        }
+        const float x_top = from_ordered_key(top_key);
+        // (the histograms lie over the second sort array, idle on this path)
+        const bool room = cap * 8 >= kWideWords * 4;
+        if (room) {
+            for (int i = tid; i < kMassPasses * 768 / 4; i += kMergeThreads) reinterpret_cast<uint4*>(keyB)[i] = make_uint4(0, 0, 0, 0);
+        }
+        double list_sum = 0.0;
+        for (int i = tid; i < n; i += kMergeThreads) {
+            const double e = exp((double)from_ordered_key(key_ord(keyA[i])) - (double)x_top);  // src/generation.cpp:46
+            ex[i] = e;
+            alive[i] = 1;
+            list_sum += e;
+        }
+        list_sum = block_sum_fixed(list_sum, s_d[0]);  // its barriers publish the arrays too
         const bool rest_in_play = (alive_tail + dropped) > 0.0;
         const double bound = exp((double)temper(keep_from, apply_t, p.temperature) - (double)x_top);
         Decision wide;
-        // (the histograms lie over the second sort array, idle on this path: kMassPasses * 3 KB of cap * 8 bytes)
-        decided = cap * 8 >= kMassPasses * 768 * 4 &&
-                  decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, u_row, s_d[0],
-                              reinterpret_cast<uint32_t*>(keyB), wide);
+        decided = room && decide_wide(p, keyA, ex, alive, n, rest_in_play, z_rest, bound, u_row, s_d[0],
+                                      reinterpret_cast<uint32_t*>(keyB), top_key, in_all ^ in_any, list_sum, wide);
         __syncthreads();
         if (decided && tid == 0) {
             s_dec = wide;
