@@ -87,6 +87,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="vocabulary-sharded steps: records and results through peer memory, or through NCCL all-gathers")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--contexts", type=int, default=4,
                     help="sampler contexts in flight per GPU (one stream and one scratch each; steps go round-robin)")
@@ -482,7 +484,7 @@ def run_ours(args, rank, world):
     emit(result)
 
 
-def sharded_setup(w, device, rank, world, n_batches_for, fixture_rows=48):
+def sharded_setup(w, device, rank, world, n_batches_for, fixture_rows=48, exchange="peer"):
     """This rank's column shards of `w` (rotating batches), the shared histories, and a ShardedSampler.
     The first `fixture_rows` rows of batch 0 are the reference fixture's rows (built by the CPU
     checker's generator), so that a step over batch 0 can be compared with tests/golden."""
@@ -515,7 +517,7 @@ def sharded_setup(w, device, rank, world, n_batches_for, fixture_rows=48):
     hist[: fixture_rows * w.history] = torch.from_numpy(f_hist.reshape(-1).astype(np.int64)).to(device)
     offsets = torch.arange(w.rows + 1, device=device, dtype=torch.int64) * w.history
     uniforms = torch.from_numpy(psx.uniforms_mt19937_64(np.arange(w.rows, dtype=np.uint64))).to(device)
-    sampler = ShardedSampler(ctx, w.rows, w.vocab, cfg, device)
+    sampler = ShardedSampler(ctx, w.rows, w.vocab, cfg, device, exchange=exchange)
     return ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, fixture_rows
 
 
@@ -539,7 +541,7 @@ def sharded_record(args, rank, world, local):
     device = torch.device("cuda", local)
     stream = torch.cuda.current_stream(device)
     ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, n_fix = sharded_setup(
-        w, device, rank, world, lambda nbytes: max(2, (2 * L2_BYTES) // nbytes + 2))
+        w, device, rank, world, lambda nbytes: max(2, (2 * L2_BYTES) // nbytes + 2), exchange=args.exchange)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -570,9 +572,10 @@ def sharded_record(args, rank, world, local):
     step_ms, scan_ms, neg_matched, failed = stats.tolist()
     peak, _ = measured_hbm_peak()
     records_bytes, results_bytes = sampler.allgather_bytes
+    sampler.close()
     return {"workload": f"c5: batch={w.rows} rows, vocab={w.vocab} in {world} column shard(s), history={w.history}, "
                         f"top_k={w.top_k}, top_p={w.top_p}",
-            "step_us": step_ms * 1e3, "rows_per_s": w.rows / (step_ms * 1e-3), "steps": steps,
+            "exchange": args.exchange, "step_us": step_ms * 1e3, "rows_per_s": w.rows / (step_ms * 1e-3), "steps": steps,
             "shard_scan_us": scan_ms * 1e3, "scan_frac": shard_bytes / (scan_ms * 1e-3) / 1e9 / peak,
             "allgather_bytes": records_bytes, "results_allgather_bytes": results_bytes,
             "fixture_rows": n_fix, "fixture_rows_matched": int(-neg_matched), "failed_rows": int(failed),
@@ -595,7 +598,7 @@ def run_sharded(args, rank, world):
         dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29591", rank=0, world_size=1,
                                 device_id=device)
     ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, n_fix = sharded_setup(
-        w, device, rank, world, lambda nbytes: max(2, (2 * L2_BYTES) // nbytes + 2))
+        w, device, rank, world, lambda nbytes: max(2, (2 * L2_BYTES) // nbytes + 2), exchange=args.exchange)
     n_batches = len(shards)
     stream = torch.cuda.current_stream(device)
 
@@ -643,6 +646,11 @@ def run_sharded(args, rank, world):
     launches = (ctx.launches - launches0) * args.steps // (warm + (len(step_ms) + 1) * args.steps)
     scan_ms = timed(scan_only, args.steps, 3)
     clocks = clock_sampler.stop() if clock_sampler else None
+    other_ms = None
+    if args.exchange == "peer":  # the same step with the two NCCL all-gathers instead, for comparison
+        from pulsatrix_b200.sharded import ShardedSampler
+        by_nccl = ShardedSampler(ctx, w.rows, w.vocab, cfg, device, exchange="nccl")
+        other_ms = timed(lambda i: by_nccl.step(shards[i % n_batches], hist, offsets, uniforms), args.steps, warm)
 
     # ---- e2e: this rank's shard comes from pinned host memory every step, the tokens go back ----
     h_shard = shards[0].cpu().pin_memory()
@@ -669,6 +677,7 @@ def run_sharded(args, rank, world):
     stats = torch.tensor([e2e_s * 1e3, -float(matched), float(failed)], dtype=torch.float64, device=device)
     dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     e2e_ms, neg_matched, failed = stats.tolist()
+    sampler.close()
     if rank != 0:
         return
     peak, peak_kind = measured_hbm_peak()
@@ -684,8 +693,13 @@ def run_sharded(args, rank, world):
         "config": {"workload": f"{w.name}: batch={w.rows} rows, vocab={w.vocab} in {world} column shard(s), "
                                f"history={w.history}, penalty={w.repetition_penalty}, T={w.temperature}, "
                                f"top_k={w.top_k}, top_p={w.top_p}",
-                   "parallelism": f"vocabulary split over {world} GPU(s); per step one NCCL all-gather of "
-                                  f"{records_bytes} bytes per rank (records) and one of {results_bytes} (results)",
+                   "parallelism": (f"vocabulary split over {world} GPU(s); per step {records_bytes} bytes of records per rank "
+                                   f"written straight into the memory of the ranks that decide the rows and {results_bytes} "
+                                   f"bytes of results into every rank's (peer stores over NVLink, counters in peer memory, "
+                                   f"no library collective)" if args.exchange == "peer" else
+                                   f"vocabulary split over {world} GPU(s); per step one NCCL all-gather of "
+                                   f"{records_bytes} bytes per rank (records) and one of {results_bytes} (results)"),
+                   "exchange": args.exchange,
                    "contexts_in_flight": 1,
                    "l2": f"shards rotate over {n_batches} batches = {n_batches * shard_bytes / 2**20:.0f} MiB > L2"},
         "e2e": {"value": w.rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": shard_bytes,
@@ -698,6 +712,8 @@ def run_sharded(args, rank, world):
                      "algorithmic_bytes": shard_bytes, "launch_ms": scan["median"]},
         "failed_rows": int(failed), "fixture_rows": n_fix, "fixture_rows_matched": int(-neg_matched),
     }
+    if other_ms is not None:
+        result["nccl_all_gather_ms_per_step"] = spread(other_ms)["median"]
     emit(result)
 
 

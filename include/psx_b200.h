@@ -235,6 +235,47 @@ PSX_API psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream, const v
                                      const psx_sampling_config* config, const double* uniforms, int64_t* tokens,
                                      float* log_probs, int32_t* row_status, psx_row_diag* diag);
 
+/* The vocabulary-sharded step without a library collective (no counterpart in the reference): the
+ * ranks (one process per GPU, up to 8 GPUs of one box) write their records straight into the memory
+ * of the rank that decides the row, over NVLink, and every rank's results straight into every
+ * rank's memory; counters in the same memory say when a row's records, and a rank's results, are
+ * complete.  Rank r decides rows r * ceil(rows / world) onwards.
+ *
+ *   psx_b200_exchange_create   allocates this rank's exchange buffer (device memory of ctx's GPU,
+ *                              zeroed) for steps of `rows` rows under settings whose record size is
+ *                              that of `config`, and writes its CUDA IPC handle
+ *                              (psx_b200_exchange_handle_bytes() bytes) to `handle`;
+ *   psx_b200_exchange_open     takes the handles of all ranks (world of them, in rank order, e.g.
+ *                              all-gathered once through the caller's process group) and maps the
+ *                              peers' buffers;
+ *   psx_b200_exchange_sample   one step: row pass over this rank's columns, records to their ranks,
+ *                              the draw for this rank's rows, results to every rank.  Asynchronous on
+ *                              `stream`; every rank must call it the same number of times.  When the
+ *                              stream has run, psx_b200_exchange_results points at `world` blocks of
+ *                              rows_per_rank rows each (rank r's rows in block r): rows_per_rank
+ *                              tokens (int64), then as many log-probs (float), then as many statuses
+ *                              (int32).  Arguments as psx_b200_shard_scan / psx_b200_shard_merge.
+ *   psx_b200_exchange_destroy  unmaps and frees; the caller makes sure (a barrier of its process
+ *                              group) that no rank is still inside a step.
+ *
+ * Every device-side wait for another rank is bounded (one second unless changed): a row whose
+ * records do not arrive, and the rows of a rank whose results do not, report
+ * PSX_ROW_DEVICE_TIMEOUT, and the context stays usable.  psx_b200_exchange_test_wait sets that
+ * bound and makes this rank's rows wait for `extra_arrivals` records more than will ever come:
+ * it exists so that the give-up path can be tested without a rank that fails. */
+typedef struct psx_exchange psx_exchange;
+PSX_API size_t psx_b200_exchange_handle_bytes(void);
+PSX_API psx_status psx_b200_exchange_create(psx_ctx* ctx, int32_t world, int32_t rank, int64_t rows,
+                                            const psx_sampling_config* config, psx_exchange** out, void* handle);
+PSX_API psx_status psx_b200_exchange_open(psx_exchange* exchange, const void* handles);
+PSX_API void psx_b200_exchange_destroy(psx_exchange* exchange);
+PSX_API psx_status psx_b200_exchange_sample(psx_exchange* exchange, void* stream, const float* shard_logits,
+                                            int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
+                                            const int64_t* history_ids, const int64_t* history_offsets,
+                                            const psx_sampling_config* config, const double* uniforms);
+PSX_API psx_status psx_b200_exchange_results(const psx_exchange* exchange, const void** results, int64_t* rows_per_rank);
+PSX_API psx_status psx_b200_exchange_test_wait(psx_exchange* exchange, uint64_t wait_limit_ns, uint32_t extra_arrivals);
+
 /* Replaces DeviceBackend::top_k_rows (include/pulsatrix/device_backend.hpp:828-837; CUDA
  * implementation src/cuda_backend.cu:851-860, kernel src/gpu_kernels.cuh:1256-1262): per row of
  * a row-major (rows, cols) device matrix, the k largest (or smallest) values in rank order and

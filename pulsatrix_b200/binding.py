@@ -17,6 +17,8 @@ EXPORTS = [
     "psx_b200_sync", "psx_b200_launch_count", "psx_b200_ctx_enable_timing", "psx_b200_ctx_read_timing", "psx_b200_ctx_inputs_are_ready",
     "psx_b200_ctx_set_wait_limit", "psx_b200_test_short_copy", "psx_b200_sample_rows", "psx_b200_sample_rows_host", "psx_b200_row_pass_only", "psx_b200_sample_rows_static", "psx_b200_read_only_pass", "psx_b200_process_logits", "psx_b200_process_logits_host",
     "psx_b200_shard_record_bytes", "psx_b200_shard_scan", "psx_b200_shard_merge", "psx_b200_shard_merge_rows",
+    "psx_b200_exchange_handle_bytes", "psx_b200_exchange_create", "psx_b200_exchange_open", "psx_b200_exchange_destroy",
+    "psx_b200_exchange_sample", "psx_b200_exchange_results", "psx_b200_exchange_test_wait",
     "psx_b200_top_k_rows", "psx_b200_lm_head_logits", "psx_b200_lm_head_sample_rows", "psx_b200_softmax_rows", "psx_b200_logsumexp_rows", "psx_b200_gather_rows", "psx_b200_decode_attention",
     "psx_uniforms_mt19937_64", "psx_uniforms_portable",
 ]
@@ -113,6 +115,15 @@ def library():
         lib.psx_b200_shard_scan.argtypes = [ptr, ptr, ptr, i64, i64, i64, i64, i64, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_merge.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
         lib.psx_b200_shard_merge_rows.argtypes = [ptr, ptr, ptr, C.c_int32, i64, i64, i64, i64, ptr, ptr, ptr, ptr, ptr, ptr]
+        lib.psx_b200_exchange_handle_bytes.restype = C.c_size_t
+        lib.psx_b200_exchange_handle_bytes.argtypes = []
+        lib.psx_b200_exchange_create.argtypes = [ptr, C.c_int32, C.c_int32, i64, ptr, ptr, ptr]
+        lib.psx_b200_exchange_open.argtypes = [ptr, ptr]
+        lib.psx_b200_exchange_destroy.argtypes = [ptr]
+        lib.psx_b200_exchange_destroy.restype = None
+        lib.psx_b200_exchange_sample.argtypes = [ptr, ptr, ptr, i64, i64, i64, i64, ptr, ptr, ptr, ptr]
+        lib.psx_b200_exchange_results.argtypes = [ptr, ptr, ptr]
+        lib.psx_b200_exchange_test_wait.argtypes = [ptr, C.c_uint64, C.c_uint32]
         lib.psx_b200_top_k_rows.argtypes = [ptr, ptr, ptr, ptr, ptr, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int]
         lib.psx_b200_lm_head_logits.argtypes = [ptr, ptr, ptr, i64, i64, ptr, i64, C.c_int32, ptr, i64]
         lib.psx_b200_lm_head_sample_rows.argtypes = [ptr, ptr, ptr, i64, i64, ptr, i64, C.c_int32, ptr, ptr, ptr, ptr, ptr, ptr,
@@ -474,3 +485,76 @@ class Context:
                                                    _dptr(out["tokens"]), _dptr(out["log_probs"]), _dptr(out["status"]),
                                                    _dptr(out.get("diag"))))
         return out
+
+    def exchange(self, world, rank, rows, config):
+        """This rank's end of a vocabulary-sharded exchange over peer memory (psx_b200_exchange_*)."""
+        return Exchange(self, world, rank, rows, config)
+
+
+class _DeviceBytes:
+    """Device memory that the library owns, as something torch.as_tensor can wrap without a copy."""
+
+    def __init__(self, address, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
+
+
+class Exchange:
+    """One rank's end of the vocabulary-sharded step over peer memory (include/psx_b200.h:
+    psx_b200_exchange_*).  `handle` (bytes) goes to every rank; open() takes all ranks' handles in
+    rank order; sample() is one step; results() are views of the library's own buffer:
+    {"tokens", "log_probs", "status"} of shape (world, rows_per_rank), rank r's rows in row r."""
+
+    def __init__(self, ctx, world, rank, rows, config):
+        self._lib, self._context = ctx._lib, ctx
+        self.world, self.rank, self.rows = world, rank, rows
+        self._ex = C.c_void_p()
+        handle = C.create_string_buffer(int(self._lib.psx_b200_exchange_handle_bytes()))
+        _check(self._lib.psx_b200_exchange_create(ctx._ctx, world, rank, rows, C.addressof(config), C.byref(self._ex), handle))
+        self.handle = handle.raw
+        self._views = None
+
+    def open(self, handles: bytes):
+        if len(handles) != self.world * len(self.handle):
+            raise ValueError("open() takes the handles of all ranks, back to back in rank order")
+        _check(self._lib.psx_b200_exchange_open(self._ex, handles))
+
+    def sample(self, shard_logits, shard_begin, vocab, history_ids, history_offsets, config, uniforms, stream=None):
+        import torch
+        rows, cols = shard_logits.shape
+        if rows != self.rows:
+            raise ValueError(f"the exchange was created for {self.rows} rows, got {rows}")
+        if stream is None:
+            stream = torch.cuda.current_stream(shard_logits.device).cuda_stream
+        _check(self._lib.psx_b200_exchange_sample(self._ex, C.c_void_p(stream), _dptr(shard_logits), cols,
+                                                  shard_logits.stride(0), shard_begin, vocab, _dptr(history_ids),
+                                                  _dptr(history_offsets), C.addressof(config), _dptr(uniforms)))
+        return self.results(shard_logits.device)
+
+    def results(self, device):
+        import torch
+        if self._views is None:
+            address, per = C.c_void_p(), C.c_int64()
+            _check(self._lib.psx_b200_exchange_results(self._ex, C.byref(address), C.byref(per)))
+            per = per.value
+            raw = torch.as_tensor(_DeviceBytes(address.value, self.world * 16 * per), device=device)
+            by_rank = raw.view(self.world, 16 * per)
+            self._views = {"tokens": by_rank[:, : 8 * per].view(torch.int64),
+                           "log_probs": by_rank[:, 8 * per: 12 * per].view(torch.float32),
+                           "status": by_rank[:, 12 * per:].view(torch.int32)}
+        return self._views
+
+    def test_wait(self, wait_limit_ns, extra_arrivals):
+        _check(self._lib.psx_b200_exchange_test_wait(self._ex, wait_limit_ns, extra_arrivals))
+
+    def close(self):
+        """Unmaps and frees.  Across ranks: only after a barrier, so that no rank is still inside a step."""
+        if self._ex:
+            self._views = None
+            self._lib.psx_b200_exchange_destroy(self._ex)
+            self._ex = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -15,7 +15,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libpsx_b200.so"
-SOURCES = ["c_abi.cu", "scan_rows.cu", "merge_rows.cu", "topk_rows.cu", "shard_records.cu", "no_alloc.cu", "read_floor.cu", "process_rows.cu", "row_ops.cu", "lm_head.cu", "decode_attention.cu"]
+SOURCES = ["c_abi.cu", "scan_rows.cu", "merge_rows.cu", "topk_rows.cu", "shard_records.cu", "peer_exchange.cu", "no_alloc.cu", "read_floor.cu", "process_rows.cu", "row_ops.cu", "lm_head.cu", "decode_attention.cu"]
 HOST_SOURCES = ["determinism.cpp", "sampler.cpp", "backend.cpp", "generation.cpp"]  # the C++ API over the C ABI
 CPP_TEST = PACKAGE.parent / "tests" / "cpp" / "host_api_test"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=true",

@@ -13,6 +13,7 @@
 
 #include "lm_head.cuh"
 #include "merge_rows.cuh"
+#include "peer_exchange.cuh"
 #include "decode_attention.cuh"
 #include "process_rows.cuh"
 #include "row_ops.cuh"
@@ -594,10 +595,13 @@ size_t psx_b200_shard_record_bytes(const psx_sampling_config* config) {
                                                               config ? config->top_k : 0));
 }
 
-psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shard_logits, int64_t rows,
-                               int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
-                               const int64_t* history_ids, const int64_t* history_offsets,
-                               const psx_sampling_config* config, void* records) {
+namespace {
+// The row pass over this GPU's columns and the packing of one record per row: into `records`, or
+// (peers != nullptr) straight into the exchange buffers of the ranks that decide the rows.
+psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_logits, int64_t rows,
+                           int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
+                           const int64_t* history_ids, const int64_t* history_offsets,
+                           const psx_sampling_config* config, void* records, const psx::PeerLayout* peers) {
     if (psx_status s = check_common(ctx, config, rows, shard_cols, row_stride, vocab, shard_logits, history_ids,
                                     history_offsets)) {
         return s;
@@ -606,7 +610,7 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
         return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the shard does not lie inside the vocabulary");
     }
     if (rows == 0) return PSX_OK;
-    if (!records) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: records is null");
+    if (!records && !peers) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: records is null");
     const bool sample = config->do_sample != 0;
     if (sample && !(config->top_k > 0 && config->top_k < vocab)) {
         return fail(PSX_ERR_UNSUPPORTED, "psx_b200: the vocabulary-sharded path samples with a top-k only");
@@ -642,9 +646,70 @@ psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shar
     pp.do_sample = sample ? 1 : 0;
     pp.top_k = sample ? (int32_t)std::min<int64_t>(config->top_k, 1 << 20) : 0;
     pp.records = records;
+    if (peers) {
+        pp.to_peers = 1;
+        pp.peers = *peers;
+    }
     PSX_CUDA(psx::launch_pack_records(pp, stream));
     ++ctx->launches;
     return PSX_OK;
+}
+
+// The survivor stage over records that lie shard-major in this GPU's memory: the record of shard s and
+// row r at base + s * shard_stride + r * record (r the absolute row).  arrivals (optional, indexed by the
+// absolute row): see MergeParams.
+psx_status shard_merge_impl(psx_ctx* ctx, cudaStream_t stream, const char* base, int64_t shard_stride, int32_t num_shards,
+                            int64_t row_begin, int64_t row_count, int64_t vocab, const psx_sampling_config* config,
+                            const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
+                            psx_row_diag* diag, const uint32_t* arrivals, uint32_t arrivals_target, uint64_t arrivals_wait_ns) {
+    const bool sample = config->do_sample != 0;
+    Plan plan;
+    plan.apply_temperature = sample && config->temperature != 1.0f;
+    plan.sort_capacity = 1024;
+    plan.gather_capacity = 4096;
+    if (psx_status s = configure_merge(ctx, plan, num_shards)) return s;
+    const int capacity = psx::shard_record_capacity(sample, config->top_k);
+    const int64_t record = (int64_t)psx::shard_record_bytes(capacity);
+    psx::MergeParams mp{};
+    mp.stats = base + psx::kRecordStatsOffset;
+    mp.part_counts = base + psx::kRecordCountOffset;
+    mp.candidates = base + psx::kRecordCandidatesOffset;
+    mp.parts = num_shards;
+    mp.part_cap = capacity;
+    mp.slot_shift = psx::merge_slot_shift(num_shards, capacity, capacity / 2);
+    mp.stats_row_stride = mp.count_row_stride = mp.cand_row_stride = record;
+    mp.stats_part_stride = mp.count_part_stride = mp.cand_part_stride = shard_stride;
+    mp.rows = row_count;
+    mp.row_begin = row_begin;
+    mp.vocab = vocab;
+    mp.do_sample = sample ? 1 : 0;
+    mp.apply_temperature = plan.apply_temperature ? 1 : 0;
+    mp.temperature = config->temperature;
+    mp.penalty = config->repetition_penalty;
+    mp.top_k = config->top_k;
+    mp.top_p = config->top_p;
+    mp.min_p = config->min_p;
+    mp.uniforms = uniforms;  // by absolute row; the outputs hold the merged rows only, the first of them at [0]
+    mp.tokens = tokens - row_begin;
+    mp.log_probs = log_probs - row_begin;
+    mp.row_status = row_status - row_begin;
+    mp.diag = diag ? diag - row_begin : nullptr;
+    mp.sort_capacity = plan.sort_capacity;
+    mp.gather_capacity = plan.gather_capacity;
+    mp.arrivals = arrivals;
+    mp.arrivals_target = arrivals_target;
+    mp.arrivals_wait_ns = arrivals_wait_ns;
+    PSX_CUDA(psx::launch_merge_rows(mp, stream, &ctx->launches));
+    return PSX_OK;
+}
+}  // namespace
+
+psx_status psx_b200_shard_scan(psx_ctx* ctx, void* stream_ptr, const float* shard_logits, int64_t rows,
+                               int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
+                               const int64_t* history_ids, const int64_t* history_offsets,
+                               const psx_sampling_config* config, void* records) {
+    return shard_scan_impl(ctx, stream_ptr, shard_logits, rows, shard_cols, row_stride, shard_begin, vocab, history_ids,
+                           history_offsets, config, records, nullptr);
 }
 
 psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream_ptr, const void* gathered, int32_t num_shards,
@@ -667,42 +732,9 @@ psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream_ptr, const void*
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     PSX_CUDA(cudaSetDevice(ctx->device));
 
-    Plan plan;
-    plan.apply_temperature = sample && config->temperature != 1.0f;
-    plan.sort_capacity = 1024;
-    plan.gather_capacity = 4096;
-    if (psx_status s = configure_merge(ctx, plan, num_shards)) return s;
-    const int capacity = psx::shard_record_capacity(sample, config->top_k);
-    const int64_t record = (int64_t)psx::shard_record_bytes(capacity);
-    const char* base = static_cast<const char*>(gathered);
-    psx::MergeParams mp{};
-    mp.stats = base + psx::kRecordStatsOffset;
-    mp.part_counts = base + psx::kRecordCountOffset;
-    mp.candidates = base + psx::kRecordCandidatesOffset;
-    mp.parts = num_shards;
-    mp.part_cap = capacity;
-    mp.slot_shift = psx::merge_slot_shift(num_shards, capacity, capacity / 2);
-    mp.stats_row_stride = mp.count_row_stride = mp.cand_row_stride = record;
-    mp.stats_part_stride = mp.count_part_stride = mp.cand_part_stride = record * rows;
-    mp.rows = row_count;
-    mp.row_begin = row_begin;
-    mp.vocab = vocab;
-    mp.do_sample = sample ? 1 : 0;
-    mp.apply_temperature = plan.apply_temperature ? 1 : 0;
-    mp.temperature = config->temperature;
-    mp.penalty = config->repetition_penalty;
-    mp.top_k = config->top_k;
-    mp.top_p = config->top_p;
-    mp.min_p = config->min_p;
-    mp.uniforms = uniforms;  // by absolute row; the outputs hold the merged rows only, the first of them at [0]
-    mp.tokens = tokens - row_begin;
-    mp.log_probs = log_probs - row_begin;
-    mp.row_status = row_status - row_begin;
-    mp.diag = diag ? diag - row_begin : nullptr;
-    mp.sort_capacity = plan.sort_capacity;
-    mp.gather_capacity = plan.gather_capacity;
-    PSX_CUDA(psx::launch_merge_rows(mp, stream, &ctx->launches));
-    return PSX_OK;
+    const int64_t record = (int64_t)psx_b200_shard_record_bytes(config);
+    return shard_merge_impl(ctx, stream, static_cast<const char*>(gathered), record * rows, num_shards, row_begin, row_count,
+                            vocab, config, uniforms, tokens, log_probs, row_status, diag, nullptr, 0, 0);
 }
 
 psx_status psx_b200_shard_merge(psx_ctx* ctx, void* stream_ptr, const void* gathered, int32_t num_shards,
@@ -883,6 +915,148 @@ void psx_uniforms_portable(const uint64_t* seeds, int64_t n, double* out) {
         z ^= z >> 31;
         out[i] = (static_cast<double>(z >> 11) + 0.5) / static_cast<double>(1ULL << 53);
     }
+}
+
+// ---- vocabulary shards exchanged over peer memory (peer_exchange.cuh) ----------------------------------
+
+struct psx_exchange {
+    psx_ctx* ctx = nullptr;
+    psx::PeerLayout layout{};
+    int64_t rows = 0;
+    size_t buffer_bytes = 0;
+    char* buffer = nullptr;  // this rank's exchange buffer (cudaMalloc: its IPC handle goes to the peers)
+    char* block = nullptr;   // this rank's results of the step, before they are published
+    bool opened[psx::kMaxPeers] = {};
+    bool ready = false;
+    uint32_t step = 0;
+    uint64_t wait_limit_ns = psx::kDefaultWaitLimitNs;
+    uint32_t test_extra_arrivals = 0;  // psx_b200_exchange_test_wait
+};
+
+size_t psx_b200_exchange_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+psx_status psx_b200_exchange_create(psx_ctx* ctx, int32_t world, int32_t rank, int64_t rows,
+                                    const psx_sampling_config* config, psx_exchange** out, void* handle) {
+    if (!ctx || !out || !handle) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    if (psx_status s = check_config(config)) return s;
+    if (world < 1 || world > psx::kMaxPeers || rank < 0 || rank >= world) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: an exchange spans 1 to 8 ranks, and the rank lies among them");
+    }
+    if (rows < 1) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: an exchange needs at least one row");
+    PSX_CUDA(cudaSetDevice(ctx->device));
+    psx_exchange* ex = new psx_exchange();
+    ex->ctx = ctx;
+    ex->rows = rows;
+    psx::PeerLayout& l = ex->layout;
+    l.world = world;
+    l.rank = rank;
+    l.rows_per_rank = (rows + world - 1) / world;
+    l.record_bytes = (int64_t)psx_b200_shard_record_bytes(config);
+    ex->buffer_bytes = (size_t)psx::peer_layout_offsets(world, l.rows_per_rank, l.record_bytes, &l.records_offset,
+                                                        &l.arrivals_offset, &l.results_offset, &l.flags_offset);
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ex->buffer), ex->buffer_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ex->block), (size_t)psx::peer_results_block_bytes(l.rows_per_rank));
+    if (e == cudaSuccess) e = cudaMemset(ex->buffer, 0, ex->buffer_bytes);
+    if (e == cudaSuccess) e = cudaMemset(ex->block, 0, (size_t)psx::peer_results_block_bytes(l.rows_per_rank));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // zero before any peer can learn the handle
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle), ex->buffer);
+    if (e != cudaSuccess) {
+        if (ex->buffer) cudaFree(ex->buffer);
+        if (ex->block) cudaFree(ex->block);
+        delete ex;
+        return fail(PSX_ERR_CUDA, std::string("psx_b200: exchange buffer: ") + cudaGetErrorString(e));
+    }
+    l.base[rank] = ex->buffer;
+    *out = ex;
+    return PSX_OK;
+}
+
+psx_status psx_b200_exchange_open(psx_exchange* ex, const void* handles) {
+    if (!ex || !handles) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    if (ex->ready) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the exchange is already open");
+    PSX_CUDA(cudaSetDevice(ex->ctx->device));
+    const cudaIpcMemHandle_t* all = static_cast<const cudaIpcMemHandle_t*>(handles);
+    for (int r = 0; r < ex->layout.world; ++r) {
+        if (r == ex->layout.rank) continue;
+        void* ptr = nullptr;
+        PSX_CUDA(cudaIpcOpenMemHandle(&ptr, all[r], cudaIpcMemLazyEnablePeerAccess));
+        ex->layout.base[r] = static_cast<char*>(ptr);
+        ex->opened[r] = true;
+    }
+    ex->ready = true;
+    return PSX_OK;
+}
+
+void psx_b200_exchange_destroy(psx_exchange* ex) {
+    if (!ex) return;
+    cudaSetDevice(ex->ctx->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < ex->layout.world; ++r) {
+        if (ex->opened[r]) cudaIpcCloseMemHandle(ex->layout.base[r]);
+    }
+    if (ex->buffer) cudaFree(ex->buffer);
+    if (ex->block) cudaFree(ex->block);
+    delete ex;
+}
+
+psx_status psx_b200_exchange_results(const psx_exchange* ex, const void** results, int64_t* rows_per_rank) {
+    if (!ex || !results || !rows_per_rank) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    *results = ex->buffer + ex->layout.results_offset;
+    *rows_per_rank = ex->layout.rows_per_rank;
+    return PSX_OK;
+}
+
+psx_status psx_b200_exchange_test_wait(psx_exchange* ex, uint64_t wait_limit_ns, uint32_t extra_arrivals) {
+    if (!ex) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    ex->wait_limit_ns = wait_limit_ns ? wait_limit_ns : psx::kDefaultWaitLimitNs;
+    ex->test_extra_arrivals = extra_arrivals;
+    return PSX_OK;
+}
+
+psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const float* shard_logits, int64_t shard_cols,
+                                    int64_t row_stride, int64_t shard_begin, int64_t vocab, const int64_t* history_ids,
+                                    const int64_t* history_offsets, const psx_sampling_config* config,
+                                    const double* uniforms) {
+    if (!ex) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
+    if (!ex->ready) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the exchange is not open yet");
+    psx_ctx* ctx = ex->ctx;
+    if (psx_status s = check_config(config)) return s;
+    const psx::PeerLayout& l = ex->layout;
+    if ((int64_t)psx_b200_shard_record_bytes(config) != l.record_bytes) {
+        return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the settings need records of another size than the exchange was created for");
+    }
+    const bool sample = config->do_sample != 0;
+    if (sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+    const uint32_t step = ex->step + 1;
+    if (psx_status s = shard_scan_impl(ctx, stream_ptr, shard_logits, ex->rows, shard_cols, row_stride, shard_begin, vocab,
+                                       history_ids, history_offsets, config, nullptr, &l)) {
+        return s;  // (the peers' waits for this rank's records of the step run out)
+    }
+    ex->step = step;
+    const int64_t row_begin = std::min<int64_t>((int64_t)l.rank * l.rows_per_rank, ex->rows);
+    const int64_t row_count = std::min<int64_t>(l.rows_per_rank, ex->rows - row_begin);
+    if (row_count > 0) {
+        // this rank's rows: their records lie here, shard after shard; absolute row r at [r - row_begin]
+        const char* base = ex->buffer + l.records_offset - row_begin * l.record_bytes;
+        const uint32_t* arrivals = reinterpret_cast<const uint32_t*>(ex->buffer + l.arrivals_offset) - row_begin;
+        int64_t* tokens = reinterpret_cast<int64_t*>(ex->block);
+        float* log_probs = reinterpret_cast<float*>(ex->block + 8 * l.rows_per_rank);
+        int32_t* status = reinterpret_cast<int32_t*>(ex->block + 12 * l.rows_per_rank);
+        if (psx_status s = shard_merge_impl(ctx, stream, base, l.rows_per_rank * l.record_bytes, l.world, row_begin, row_count,
+                                            vocab, config, uniforms, tokens, log_probs, status, nullptr, arrivals,
+                                            step * (uint32_t)l.world + ex->test_extra_arrivals, ex->wait_limit_ns)) {
+            return s;
+        }
+    }
+    psx::PublishParams pub{};
+    pub.layout = l;
+    pub.block = ex->block;
+    pub.step = step;
+    pub.wait_limit_ns = ex->wait_limit_ns;
+    PSX_CUDA(psx::launch_publish_results(pub, stream));
+    ++ctx->launches;
+    return PSX_OK;
 }
 
 }  // extern "C"

@@ -32,6 +32,7 @@ __device__ unsigned long long g_merge_times[1024 * 4];
 #include "general_row_impl.cuh"
 #include "merge_rows_impl.cuh"
 #include "merge_rows_warp_impl.cuh"
+#include "peer_exchange.cuh"
 
 namespace psx {
 
@@ -46,7 +47,7 @@ __device__ __forceinline__ void decide_row(const MergeParams& p, const int64_t r
     }
 }
 
-__global__ void __launch_bounds__(kMergeThreads, kMergeThreads <= 256 ? 3 : 2) merge_rows_kernel(const MergeParams p) {
+__global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const MergeParams p) {
     extern __shared__ unsigned long long dyn[];
     PSX_MERGE_TIME(0);
     if (p.only_undecided) {
@@ -77,6 +78,21 @@ __global__ void __launch_bounds__(kMergeThreads, kMergeThreads <= 256 ? 3 : 2) m
     grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
     grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
     PSX_MERGE_TIME(1);
+    if (p.arrivals != nullptr) {  // lists that other GPUs write: wait for this row's to be complete
+        __shared__ int s_arrived;
+        const int64_t row = p.row_begin + blockIdx.x;
+        if (threadIdx.x == 0) s_arrived = wait_until_at_least(p.arrivals + row, p.arrivals_target, p.arrivals_wait_ns) ? 1 : 0;
+        __syncthreads();
+        if (!s_arrived) {
+            if (threadIdx.x == 0) {
+                p.tokens[row] = -1;
+                p.log_probs[row] = 0.0f;
+                p.row_status[row] = PSX_ROW_DEVICE_TIMEOUT;
+                if (p.diag) p.diag[row] = psx_row_diag{0, 0, INFINITY, INFINITY};
+            }
+            return;
+        }
+    }
     decide_row(p, p.row_begin + blockIdx.x, dyn);
     PSX_MERGE_TIME(2);
 }
@@ -143,7 +159,7 @@ cudaError_t launch_merge_rows(const MergeParams& p, cudaStream_t stream, uint64_
     // By warps from 256 rows on: a warp takes longer over a row than a block does (about 13 us against 7 on
     // 64 rows of 152 K logits), so few rows are answered sooner by blocks; many rows get through faster by
     // warps (1000 x 49 K, top-k 50: 70 -> 59 us per step; 1024 greedy rows: 47 -> 37 us).
-    const bool by_warp = p.by_warp != 0 && p.general != 2 && p.survivor_cols == nullptr && p.rows >= kRowsByWarpFrom;
+    const bool by_warp = p.by_warp != 0 && p.general != 2 && p.survivor_cols == nullptr && p.arrivals == nullptr && p.rows >= kRowsByWarpFrom;
     if (launched != nullptr) *launched += by_warp ? 2 : 1;
     if (!by_warp) {
         return launch_overlapping(merge_rows_kernel, dim3((unsigned)p.rows), dim3(kMergeThreads), shared, stream, with_size);

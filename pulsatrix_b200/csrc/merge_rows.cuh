@@ -70,6 +70,12 @@ struct MergeParams {
     int32_t warp_slot_shift;         // 2^shift slots of every list per fetch; parts << shift <= 512
     int32_t warp_list_cap;           // entries a warp's list holds: 64 or 128
     int32_t only_undecided;          // (set by launch_merge_rows for the second kernel)
+    // Optional (vocabulary shards that arrive over peer memory, peer_exchange.cuh): the row's lists are
+    // complete once arrivals[row] has reached arrivals_target; the row's CTA waits for that, at most
+    // arrivals_wait_ns nanoseconds (then the row reports PSX_ROW_DEVICE_TIMEOUT).  One block per row only.
+    const uint32_t* arrivals;        // nullptr: nothing to wait for
+    uint32_t arrivals_target;
+    unsigned long long arrivals_wait_ns;
 };
 
 constexpr int64_t kRowsByWarpFrom = 256;  // launches of fewer rows stay with one block per row

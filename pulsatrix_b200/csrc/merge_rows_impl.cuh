@@ -905,7 +905,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
     PSX_MERGE_STAGE(0);
     const double u_row = (p.do_sample && p.uniforms) ? p.uniforms[row] : 0.5;
     if (tid == 0) s_count = 0;
-    if (tid < 256) reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);  // published by the barrier of step 1
+    reinterpret_cast<uint4*>(s_hist)[tid] = make_uint4(0, 0, 0, 0);  // published by the barrier of step 1
     bool hist_clean = true;
 
     // ---- 1. join the parts; every candidate of the row into shared memory ----------------------------

@@ -1,0 +1,96 @@
+// Vocabulary-sharded sampling without a library collective: the GPUs of one box write to one
+// another's memory over NVLink (plain peer stores into buffers opened through CUDA IPC) and tell one
+// another so with counters, also in peer memory.
+//
+// Every rank owns one exchange buffer of the same layout:
+//   records    world x rows_per_rank records: [shard][row of this rank's block], what the ranks' packing
+//              kernels write here, each its own shard's slice;
+//   arrivals   rows_per_rank counters: +1 by every shard whose record of that row is complete;
+//              after step e a counter stands at e * world;
+//   results    world blocks of 16 * rows_per_rank bytes (tokens | log-probs | status), block r written
+//              by rank r after it has decided its rows;
+//   flags      world words: flags[r] = e once rank r's block of step e is complete here.
+// Counters and flags only ever grow (the step number e starts at 1), so nothing is reset between
+// steps.  A step's pushes cannot overtake the step before: a rank starts step e + 1 only after its
+// last kernel of step e has seen every rank's flag of step e, and a rank raises that flag only after
+// it has finished reading its records of step e.
+//
+// Every wait is bounded: after `wait_limit_ns` a waiting kernel gives up and reports
+// PSX_ROW_DEVICE_TIMEOUT for the rows concerned.
+#pragma once
+
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+#include "psx_async.cuh"
+
+namespace psx {
+
+constexpr int kMaxPeers = 8;
+
+struct PeerLayout {
+    int32_t world;
+    int32_t rank;
+    int64_t rows_per_rank;
+    int64_t record_bytes;
+    int64_t records_offset, arrivals_offset, results_offset, flags_offset;  // the same in every rank's buffer
+    char* base[kMaxPeers];                                                  // base[r]: rank r's buffer, as this process sees it
+};
+
+__host__ __device__ inline int64_t peer_results_block_bytes(int64_t rows_per_rank) { return 16 * rows_per_rank; }
+
+// Bytes of one rank's exchange buffer and the offsets of its four sections (each 256-byte aligned).
+inline int64_t peer_layout_offsets(int world, int64_t rows_per_rank, int64_t record_bytes, int64_t* records, int64_t* arrivals,
+                                   int64_t* results, int64_t* flags) {
+    auto up = [](int64_t v) { return (v + 255) / 256 * 256; };
+    int64_t at = 0;
+    *records = at;
+    at = up(at + (int64_t)world * rows_per_rank * record_bytes);
+    *arrivals = at;
+    at = up(at + 4 * rows_per_rank);
+    *results = at;
+    at = up(at + (int64_t)world * peer_results_block_bytes(rows_per_rank));
+    *flags = at;
+    at = up(at + 4 * (int64_t)world);
+    return at;
+}
+
+__device__ __forceinline__ uint32_t load_acquire_system(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void store_release_system(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void add_release_system(uint32_t* p, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Waits until *word >= target (as a wrapping difference), for at most limit_ns nanoseconds.
+__device__ __forceinline__ bool wait_until_at_least(const uint32_t* word, uint32_t target, unsigned long long limit_ns) {
+    unsigned long long started = 0;
+    for (uint32_t tries = 1;; ++tries) {
+        if ((int32_t)(load_acquire_system(word) - target) >= 0) return true;
+        if ((tries & 15u) == 0) {
+            const unsigned long long now = global_nanoseconds();
+            if (started == 0) started = now;
+            else if (now - started > limit_ns) return false;
+        }
+    }
+}
+
+struct PublishParams {
+    PeerLayout layout;
+    const void* block;       // this rank's results of the step: 16 * rows_per_rank bytes
+    uint32_t step;
+    unsigned long long wait_limit_ns;
+};
+
+// One CTA per peer: copies this rank's block into the peer's buffer, raises this rank's flag there,
+// then waits for that peer's flag here; a peer that never answers gets PSX_ROW_DEVICE_TIMEOUT
+// written over the status words of its block here.
+cudaError_t launch_publish_results(const PublishParams& p, cudaStream_t stream);
+
+}  // namespace psx

@@ -17,10 +17,7 @@ constexpr int kScanWarps = kScanThreads / 32;
 constexpr int kVecPerThread = 16;                            // float4 a thread looks at per pass
 constexpr int kPartVecs = kScanThreads * kVecPerThread;      // 4096 vectors = 16384 logits = 64 KB per CTA, three CTAs per SM
 constexpr int kPartCap = 1024;                               // candidate slots per part
-#ifndef PSX_MERGE_THREADS
-#define PSX_MERGE_THREADS 256
-#endif
-constexpr int kMergeThreads = PSX_MERGE_THREADS;
+constexpr int kMergeThreads = 256;
 
 // A candidate is (raw logit bits, column | flags).  The flags say how the survivor stage must
 // turn the raw logit into the processed one, with the same float operations as the row pass.

@@ -170,7 +170,16 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     __syncthreads();
 
     // Second sweep: a part's kept candidates go where the parts before it end.
-    char* record = static_cast<char*>(p.records) + row * (int64_t)shard_record_bytes(p.capacity);
+    char* record;
+    uint32_t* arrival = nullptr;
+    if (p.to_peers) {
+        const PeerLayout& l = p.peers;
+        const int64_t owner = row / l.rows_per_rank, within = row - owner * l.rows_per_rank;
+        record = l.base[owner] + l.records_offset + ((int64_t)l.rank * l.rows_per_rank + within) * l.record_bytes;
+        arrival = reinterpret_cast<uint32_t*>(l.base[owner] + l.arrivals_offset) + within;
+    } else {
+        record = static_cast<char*>(p.records) + row * (int64_t)shard_record_bytes(p.capacity);
+    }
     uint2* out = reinterpret_cast<uint2*>(record + kRecordCandidatesOffset);
     for (int s = warp; s < nseg; s += kPackWarps) {
         uint32_t before = 0;
@@ -215,6 +224,13 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
         *reinterpret_cast<PartStats*>(record + kRecordStatsOffset) = s;
         *reinterpret_cast<uint32_t*>(record + kRecordCountOffset) = min(kept, (uint32_t)p.capacity);
         *reinterpret_cast<uint32_t*>(record + kRecordCountOffset + 4) = 0;
+    }
+    if (arrival != nullptr) {  // the record is complete: the whole CTA's stores before the count
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            add_release_system(arrival, 1u);
+        }
     }
 }
 

@@ -6,6 +6,7 @@
 // The survivor stage reads gathered records directly through byte strides.
 #pragma once
 
+#include "peer_exchange.cuh"
 #include "psx_device.cuh"
 
 namespace psx {
@@ -36,7 +37,12 @@ struct PackParams {
     int32_t capacity;
     int32_t do_sample;
     int32_t top_k;               // > 0: the top-k filter is on (sampling); 0: greedy
-    void* records;               // rows * shard_record_bytes(capacity)
+    void* records;               // rows * shard_record_bytes(capacity); not used when the records go to peers
+    // Optional: straight into the exchange buffers of the ranks that decide the rows (peer_exchange.cuh).
+    // Row r belongs to rank r / rows_per_rank; its record goes to that rank's records section at
+    // [this rank][r % rows_per_rank], and that rank's arrival counter of the row goes up by one.
+    int32_t to_peers;            // 0: off
+    PeerLayout peers;
 };
 
 cudaError_t launch_pack_records(const PackParams& p, cudaStream_t stream);

@@ -3,7 +3,14 @@ columns of every row, scans it locally, and one all-gather of fixed-size per-row
 every shard's candidates to every rank.  The ranks then share the rows out: a rank finishes the
 draw for its own block of rows only, and a second, tiny all-gather (16 bytes per row: token,
 log-probability, status) gives every rank every row's result.  Both collectives are plain NCCL
-all-gathers into the GPU's own memory; no kernel reads another GPU's memory."""
+all-gathers into the GPU's own memory; no kernel reads another GPU's memory.
+
+With exchange="peer" there is no library collective in a step: the packing kernel writes each
+record straight into the memory of the rank that decides the row, that rank's survivor stage waits
+(row by row, bounded) for a counter in its own memory that the writers raise, and a last kernel
+writes the rank's results into every rank's memory and waits (bounded) for everyone else's.  The
+buffers are opened once through CUDA IPC; their handles travel through one all-gather of the process
+group when the sampler is built."""
 from __future__ import annotations
 
 
@@ -43,9 +50,11 @@ class ShardedSampler:
     are views of the gathered results; row r is at [r // rows_per_rank, r % rows_per_rank] (use
     flat() for plain (rows,) copies)."""
 
-    def __init__(self, ctx, rows, vocab, config, device, group=None):
+    def __init__(self, ctx, rows, vocab, config, device, group=None, exchange="nccl"):
         import torch
         import torch.distributed as dist
+        if exchange not in ("nccl", "peer"):
+            raise ValueError('exchange is "nccl" or "peer"')
         self.ctx, self.rows, self.vocab, self.config, self.group = ctx, rows, vocab, config, group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -53,6 +62,16 @@ class ShardedSampler:
         self.row_begin, self.row_count, self.per = row_bounds(rows, self.world, self.rank)
         self.record = ctx.shard_record_bytes(config)
         self.mine = torch.empty(rows * self.record, dtype=torch.uint8, device=device)
+        self.peer = None
+        if exchange == "peer":
+            self.peer = ctx.exchange(self.world, self.rank, rows, config)
+            mine = torch.frombuffer(bytearray(self.peer.handle), dtype=torch.uint8).to(device)
+            everyone = torch.empty(self.world * mine.numel(), dtype=torch.uint8, device=device)
+            dist.all_gather_into_tensor(everyone, mine, group=group)
+            self.peer.open(everyone.cpu().numpy().tobytes())
+            dist.barrier(group=group)  # every rank has mapped every buffer before anyone writes
+            self.out = self.peer.results(device)
+            return
         self.gathered = torch.empty(self.world * rows * self.record, dtype=torch.uint8, device=device)
         per = self.per
         # a rank's block: tokens (int64 x per) | log-probs (float32 x per) | status (int32 x per)
@@ -68,13 +87,15 @@ class ShardedSampler:
 
     @property
     def allgather_bytes(self):
-        """Bytes this rank contributes to the two all-gathers of a step."""
+        """Bytes this rank contributes to the two exchanges of a step (all-gathers, or peer stores)."""
         return self.rows * self.record, 16 * self.per
 
     def step(self, shard_logits, history_ids, history_offsets, uniforms):
         import torch.distributed as dist
         if shard_logits.shape != (self.rows, self.cols):
             raise ValueError(f"rank {self.rank} should hold a {self.rows} x {self.cols} block, got {tuple(shard_logits.shape)}")
+        if self.peer is not None:
+            return self.peer.sample(shard_logits, self.begin_col, self.vocab, history_ids, history_offsets, self.config, uniforms)
         self.ctx.shard_scan(shard_logits, self.begin_col, self.vocab, history_ids, history_offsets, self.config, self.mine)
         dist.all_gather_into_tensor(self.gathered, self.mine, group=self.group)
         if self.row_count > 0:
@@ -82,6 +103,16 @@ class ShardedSampler:
                                  row_begin=self.row_begin, row_count=self.row_count)
         dist.all_gather_into_tensor(self.results, self.block, group=self.group)
         return self.out
+
+    def close(self):
+        """Frees the peer-memory exchange (after a barrier: no rank may still be inside a step)."""
+        if self.peer is not None:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            self.peer.close()
+            self.peer = None
 
     def flat(self, out=None):
         """(rows,) copies of the results, in row order."""

@@ -1,7 +1,10 @@
-"""The vocabulary-sharded path with its real collective: N ranks, one GPU each, every rank holds a
-column shard of workload C5's rows, and one NCCL all-gather of the per-row records lets every rank
-draw.  Tokens must equal the reference fixture on every rank.  Needs at least two GPUs; skipped
-otherwise (tests/test_gpu_sharded.py runs the same shards one after another on one GPU)."""
+"""The vocabulary-sharded path across real GPUs: N ranks, one GPU each, every rank holds a column
+shard of workload C5's rows.  Twice: with NCCL all-gathers of the per-row records and of the
+results, and with no library collective at all -- records and results written straight into the
+peers' memory over NVLink, counters in that memory saying when they are complete
+(ShardedSampler(exchange="peer")).  Tokens must equal the reference fixture on every rank, also
+when the rows do not divide evenly among the ranks.  Needs at least two GPUs; skipped otherwise
+(tests/test_gpu_sharded.py and tests/test_gpu_peer_exchange.py cover one GPU)."""
 import os
 import subprocess
 import sys
@@ -19,7 +22,7 @@ WORKER = textwrap.dedent("""
     root = sys.argv[1]
     sys.path[:0] = [root, os.path.join(root, "tests")]
     import gpu_harness as gh, pulsatrix_b200 as psx, workload_rows
-    from pulsatrix_b200.sharded import sample_rows_sharded, shard_bounds
+    from pulsatrix_b200.sharded import ShardedSampler, sample_rows_sharded, shard_bounds
     from pulsatrix_b200.workloads import WORKLOADS
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -43,6 +46,20 @@ WORKER = textwrap.dedent("""
         assert out["tokens"].cpu().numpy().tolist() == gold["token"][ids].tolist()
         logp = out["log_probs"].cpu().numpy()
         assert (np.abs(logp - gold["log_prob"][ids]) <= 1e-5 * np.abs(gold["log_prob"][ids]) + 1e-9).all()
+    # the same rows through peer memory; then fewer rows than divide evenly (the last ranks hold fewer, or none)
+    for count in (48, 45, 5):
+        sampler = ShardedSampler(ctx, count, w.vocab, cfg, torch.device("cuda", local), exchange="peer")
+        o = d_off[: count + 1]
+        for _ in range(4):
+            sampler.step(shard[:count], d_hist, o, d_u[:count])
+            torch.cuda.synchronize()
+            out = sampler.flat()
+            assert (out["status"].cpu().numpy() == 0).all(), (rank, count, out["status"].cpu().numpy())
+            assert out["tokens"].cpu().numpy().tolist() == gold["token"][ids[:count]].tolist(), (rank, count)
+            logp = out["log_probs"].cpu().numpy()
+            want = gold["log_prob"][ids[:count]]
+            assert (np.abs(logp - want) <= 1e-5 * np.abs(want) + 1e-9).all()
+        sampler.close()
     dist.barrier()
     dist.destroy_process_group()
     print("ok", rank)
