@@ -661,7 +661,8 @@ psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_lo
 psx_status shard_merge_impl(psx_ctx* ctx, cudaStream_t stream, const char* base, int64_t shard_stride, int32_t num_shards,
                             int64_t row_begin, int64_t row_count, int64_t vocab, const psx_sampling_config* config,
                             const double* uniforms, int64_t* tokens, float* log_probs, int32_t* row_status,
-                            psx_row_diag* diag, const uint32_t* arrivals, uint32_t arrivals_target, uint64_t arrivals_wait_ns) {
+                            psx_row_diag* diag, const uint32_t* arrivals, uint32_t arrivals_target, uint64_t arrivals_wait_ns,
+                            const psx::PeerLayout* publish_to = nullptr) {
     const bool sample = config->do_sample != 0;
     Plan plan;
     plan.apply_temperature = sample && config->temperature != 1.0f;
@@ -699,6 +700,10 @@ psx_status shard_merge_impl(psx_ctx* ctx, cudaStream_t stream, const char* base,
     mp.arrivals = arrivals;
     mp.arrivals_target = arrivals_target;
     mp.arrivals_wait_ns = arrivals_wait_ns;
+    if (publish_to) {
+        mp.publish = 1;
+        mp.peers = *publish_to;
+    }
     PSX_CUDA(psx::launch_merge_rows(mp, stream, &ctx->launches));
     return PSX_OK;
 }
@@ -1045,16 +1050,16 @@ psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const fl
         int32_t* status = reinterpret_cast<int32_t*>(ex->block + 12 * l.rows_per_rank);
         if (psx_status s = shard_merge_impl(ctx, stream, base, l.rows_per_rank * l.record_bytes, l.world, row_begin, row_count,
                                             vocab, config, uniforms, tokens, log_probs, status, nullptr, arrivals,
-                                            step * (uint32_t)l.world + ex->test_extra_arrivals, ex->wait_limit_ns)) {
+                                            step * (uint32_t)l.world + ex->test_extra_arrivals, ex->wait_limit_ns, &l)) {
             return s;
         }
     }
-    psx::PublishParams pub{};
-    pub.layout = l;
-    pub.block = ex->block;
-    pub.step = step;
-    pub.wait_limit_ns = ex->wait_limit_ns;
-    PSX_CUDA(psx::launch_publish_results(pub, stream));
+    psx::AwaitParams aw{};
+    aw.layout = l;
+    aw.rows = ex->rows;
+    aw.step = step;
+    aw.wait_limit_ns = ex->wait_limit_ns;
+    PSX_CUDA(psx::launch_await_results(aw, stream));
     ++ctx->launches;
     return PSX_OK;
 }

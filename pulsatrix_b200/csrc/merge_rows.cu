@@ -75,24 +75,40 @@ __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const Merg
         }
         return;
     }
-    grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
-    grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
-    PSX_MERGE_TIME(1);
-    if (p.arrivals != nullptr) {  // lists that other GPUs write: wait for this row's to be complete
+    if (p.arrivals != nullptr) {
+        // Lists that other GPUs write (peer_exchange.cuh): nothing here is read before the row's arrival
+        // counter says that every shard's record is complete -- this GPU's own among them, so the kernel
+        // before this one is not waited for as a whole, and the kernel after this one may start at once.
+        grid_dependents_may_launch();
         __shared__ int s_arrived;
         const int64_t row = p.row_begin + blockIdx.x;
         if (threadIdx.x == 0) s_arrived = wait_until_at_least(p.arrivals + row, p.arrivals_target, p.arrivals_wait_ns) ? 1 : 0;
         __syncthreads();
-        if (!s_arrived) {
-            if (threadIdx.x == 0) {
-                p.tokens[row] = -1;
-                p.log_probs[row] = 0.0f;
-                p.row_status[row] = PSX_ROW_DEVICE_TIMEOUT;
-                if (p.diag) p.diag[row] = psx_row_diag{0, 0, INFINITY, INFINITY};
-            }
-            return;
+        if (s_arrived) {
+            decide_row(p, row, dyn);
+        } else if (threadIdx.x == 0) {
+            p.tokens[row] = -1;
+            p.log_probs[row] = 0.0f;
+            p.row_status[row] = PSX_ROW_DEVICE_TIMEOUT;
+            if (p.diag) p.diag[row] = psx_row_diag{0, 0, INFINITY, INFINITY};
         }
+        __syncthreads();
+        if (p.publish && (int)threadIdx.x < p.peers.world) {  // one thread per rank: the row's 16 bytes, then the count
+            const PeerLayout& l = p.peers;
+            const int64_t within = row - (int64_t)l.rank * l.rows_per_rank;
+            char* block = l.base[threadIdx.x] + l.results_offset + (int64_t)l.rank * peer_results_block_bytes(l.rows_per_rank);
+            reinterpret_cast<int64_t*>(block)[within] = p.tokens[row];
+            reinterpret_cast<float*>(block + 8 * l.rows_per_rank)[within] = p.log_probs[row];
+            reinterpret_cast<int32_t*>(block + 12 * l.rows_per_rank)[within] = p.row_status[row];
+            __threadfence_system();
+            add_release_system(reinterpret_cast<uint32_t*>(l.base[threadIdx.x] + l.flags_offset) + l.rank, 1u);
+        }
+        grid_dependency_wait();  // (so that this kernel's end still implies the end of the kernel before it)
+        return;
     }
+    grid_dependency_wait();        // everything this kernel reads was written by the kernel before it
+    grid_dependents_may_launch();  // a row pass that follows reads none of this kernel's results
+    PSX_MERGE_TIME(1);
     decide_row(p, p.row_begin + blockIdx.x, dyn);
     PSX_MERGE_TIME(2);
 }

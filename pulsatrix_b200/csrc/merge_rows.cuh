@@ -1,6 +1,7 @@
 // Launch interface of the survivor stage (merge_rows.cu).
 #pragma once
 
+#include "peer_exchange.cuh"
 #include "psx_device.cuh"
 
 struct psx_row_diag;  // include/psx_b200.h
@@ -76,6 +77,11 @@ struct MergeParams {
     const uint32_t* arrivals;        // nullptr: nothing to wait for
     uint32_t arrivals_target;
     unsigned long long arrivals_wait_ns;
+    // ... and the row's result goes straight into every rank's results section, with one more on this
+    // rank's counter in each of their flags sections (the outputs above are still written: here they are
+    // this rank's own block, indexed by the absolute row).
+    int32_t publish;                 // 0: off
+    PeerLayout peers;
 };
 
 constexpr int64_t kRowsByWarpFrom = 256;  // launches of fewer rows stay with one block per row

@@ -1,51 +1,41 @@
-// The last kernel of a vocabulary-sharded step over peer memory: every rank's results to every rank.
+// The last kernel of a vocabulary-sharded step over peer memory: waits for every rank's results.
 #include "peer_exchange.cuh"
 
 #include "../../include/psx_b200.h"
+#include "psx_device.cuh"
 
 namespace psx {
 
 namespace {
 
-constexpr int kPublishThreads = 128;
-
-__global__ void __launch_bounds__(kPublishThreads) publish_results_kernel(const PublishParams p) {
+__global__ void __launch_bounds__(32) await_results_kernel(const AwaitParams p) {
+    // The kernel after this one (the next step's row pass) may start reading its logits at once; what it
+    // writes waits for this kernel's end.
+    grid_dependents_may_launch();
     const PeerLayout& l = p.layout;
-    const int peer = blockIdx.x, tid = threadIdx.x;
-    const int64_t block_bytes = peer_results_block_bytes(l.rows_per_rank);
-    // this rank's block, 16 bytes at a time (the block is a multiple of 16 bytes and 256-byte aligned on both sides)
-    const uint4* src = static_cast<const uint4*>(p.block);
-    uint4* dst = reinterpret_cast<uint4*>(l.base[peer] + l.results_offset + (int64_t)l.rank * block_bytes);
-    for (int64_t i = tid; i < block_bytes / 16; i += kPublishThreads) dst[i] = src[i];
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence_system();  // the whole CTA's stores before the flag
-        store_release_system(reinterpret_cast<uint32_t*>(l.base[peer] + l.flags_offset) + l.rank, p.step);
-    }
-    // ... and the peer's block here
-    __shared__ int s_arrived;
-    if (tid == 0) {
+    const int peer = threadIdx.x;
+    if (peer < l.world) {
+        const int64_t first = (int64_t)peer * l.rows_per_rank;
+        const int64_t count = first >= p.rows ? 0 : (p.rows - first < l.rows_per_rank ? p.rows - first : l.rows_per_rank);
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(l.base[l.rank] + l.flags_offset) + peer;
-        s_arrived = wait_until_at_least(flag, p.step, p.wait_limit_ns) ? 1 : 0;
-    }
-    __syncthreads();
-    if (!s_arrived) {
-        char* block = l.base[l.rank] + l.results_offset + (int64_t)peer * block_bytes;
-        int64_t* tokens = reinterpret_cast<int64_t*>(block);
-        int32_t* status = reinterpret_cast<int32_t*>(block + 12 * l.rows_per_rank);
-        for (int64_t i = tid; i < l.rows_per_rank; i += kPublishThreads) {
-            tokens[i] = -1;
-            status[i] = PSX_ROW_DEVICE_TIMEOUT;
+        if (count > 0 && !wait_until_at_least(flag, p.step * (uint32_t)count, p.wait_limit_ns)) {
+            char* block = l.base[l.rank] + l.results_offset + (int64_t)peer * peer_results_block_bytes(l.rows_per_rank);
+            int64_t* tokens = reinterpret_cast<int64_t*>(block);
+            int32_t* status = reinterpret_cast<int32_t*>(block + 12 * l.rows_per_rank);
+            for (int64_t i = 0; i < count; ++i) {
+                tokens[i] = -1;
+                status[i] = PSX_ROW_DEVICE_TIMEOUT;
+            }
         }
     }
+    grid_dependency_wait();  // (so that this kernel's end still implies the end of the kernels before it)
 }
 
 }  // namespace
 
-cudaError_t launch_publish_results(const PublishParams& p, cudaStream_t stream) {
+cudaError_t launch_await_results(const AwaitParams& p, cudaStream_t stream) {
     if (p.layout.world < 1 || p.layout.world > kMaxPeers) return cudaErrorInvalidValue;
-    publish_results_kernel<<<(unsigned)p.layout.world, kPublishThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_overlapping(await_results_kernel, dim3(1), dim3(32), 0, stream, p);
 }
 
 }  // namespace psx

@@ -9,11 +9,12 @@
 //              after step e a counter stands at e * world;
 //   results    world blocks of 16 * rows_per_rank bytes (tokens | log-probs | status), block r written
 //              by rank r after it has decided its rows;
-//   flags      world words: flags[r] = e once rank r's block of step e is complete here.
+//   flags      world counters: flags[r] goes up by one for every row of rank r whose result has been written
+//              here; after step e it stands at e * (rows that rank r decides).
 // Counters and flags only ever grow (the step number e starts at 1), so nothing is reset between
-// steps.  A step's pushes cannot overtake the step before: a rank starts step e + 1 only after its
-// last kernel of step e has seen every rank's flag of step e, and a rank raises that flag only after
-// it has finished reading its records of step e.
+// steps.  A step's pushes cannot overtake the step before: a rank's row pass of step e + 1 writes
+// nothing before its last kernel of step e has seen every row's result of step e arrive, and a row's
+// result is sent only after its records of step e have been read.
 //
 // Every wait is bounded: after `wait_limit_ns` a waiting kernel gives up and reports
 // PSX_ROW_DEVICE_TIMEOUT for the rows concerned.
@@ -81,16 +82,17 @@ __device__ __forceinline__ bool wait_until_at_least(const uint32_t* word, uint32
     }
 }
 
-struct PublishParams {
+struct AwaitParams {
     PeerLayout layout;
-    const void* block;       // this rank's results of the step: 16 * rows_per_rank bytes
+    int64_t rows;            // of the whole step: rank r decides rows r * rows_per_rank onwards, as many as there are
     uint32_t step;
     unsigned long long wait_limit_ns;
 };
 
-// One CTA per peer: copies this rank's block into the peer's buffer, raises this rank's flag there,
-// then waits for that peer's flag here; a peer that never answers gets PSX_ROW_DEVICE_TIMEOUT
-// written over the status words of its block here.
-cudaError_t launch_publish_results(const PublishParams& p, cudaStream_t stream);
+// The last kernel of a step: one thread per rank waits until that rank's counter in this rank's flags
+// section says that all its rows of the step have been written here; the rows of a rank that never
+// gets there report PSX_ROW_DEVICE_TIMEOUT.  (The rows themselves are written by the survivor stage of
+// the rank that decides them, one thread per destination: MergeParams::publish.)
+cudaError_t launch_await_results(const AwaitParams& p, cudaStream_t stream);
 
 }  // namespace psx

@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool apply_t = p.apply_temperature != 0;
     const PartStats* stats = p.stats + row * p.parts;
+    grid_dependents_may_launch();  // what follows either waits for this kernel's end or for its records one by one
+    grid_dependency_wait();        // everything read here was written by the row pass before this kernel
 
     // Every warp joins the parts' records for itself (a few dozen small loads out of L2).
     float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
@@ -239,8 +241,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
 cudaError_t launch_pack_records(const PackParams& p, cudaStream_t stream) {
     if (p.rows <= 0) return cudaSuccess;
     if (p.parts > kPackKeys) return cudaErrorInvalidConfiguration;
-    pack_records_kernel<<<(unsigned)p.rows, kPackThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_overlapping(pack_records_kernel, dim3((unsigned)p.rows), dim3(kPackThreads), 0, stream, p);
 }
 
 }  // namespace psx
