@@ -607,12 +607,16 @@ def run_sharded(args, rank, world):
         dist.barrier()
         torch.cuda.synchronize()
 
+    issue_s = []  # host time to enqueue the steps of a region (a step that takes the GPU less is bound by it)
+
     def region(fn, steps):
         barrier()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record(stream)
+        t0 = time.perf_counter()
         for i in range(steps):
             fn(i)
+        issue_s.append((time.perf_counter() - t0) / steps)
         end.record(stream)
         barrier()
         return begin.elapsed_time(end)
@@ -643,6 +647,7 @@ def run_sharded(args, rank, world):
         clock_sampler.start()
     launches0 = ctx.launches
     step_ms = timed(full_step, args.steps, warm)
+    host_issue_us = float(np.median(issue_s)) * 1e6
     launches = (ctx.launches - launches0) * args.steps // (warm + (len(step_ms) + 1) * args.steps)
     scan_ms = timed(scan_only, args.steps, 3)
     clocks = clock_sampler.stop() if clock_sampler else None
@@ -712,6 +717,7 @@ def run_sharded(args, rank, world):
                      "algorithmic_bytes": shard_bytes, "launch_ms": scan["median"]},
         "failed_rows": int(failed), "fixture_rows": n_fix, "fixture_rows_matched": int(-neg_matched),
     }
+    result["host_issue_us_per_step"] = host_issue_us  # rank 0's
     if other_ms is not None:
         result["nccl_all_gather_ms_per_step"] = spread(other_ms)["median"]
     emit(result)

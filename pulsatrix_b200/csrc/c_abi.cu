@@ -629,7 +629,16 @@ psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_lo
     sp.history_ids = history_ids;
     sp.history_offsets = history_offsets;
     if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
-    if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp)) return s;
+    int set = 0;
+    if (peers) {
+        // Steps through peer memory follow one another kernel under kernel: this step's row pass writes the
+        // scratch set that the step before it did not use (its packing kernel may still be reading the other),
+        // and only the row pass's last CTA waits for the step before -- which the packing kernel, waiting for
+        // the whole row pass, therefore never overtakes.
+        set = (ctx->scratch_set ^= 1);
+        sp.wait_before_writes = 0;
+    }
+    if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp, set)) return s;
     PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
     ++ctx->launches;
 

@@ -100,8 +100,7 @@ __global__ void __launch_bounds__(kMergeThreads, 3) merge_rows_kernel(const Merg
             reinterpret_cast<int64_t*>(block)[within] = p.tokens[row];
             reinterpret_cast<float*>(block + 8 * l.rows_per_rank)[within] = p.log_probs[row];
             reinterpret_cast<int32_t*>(block + 12 * l.rows_per_rank)[within] = p.row_status[row];
-            __threadfence_system();
-            add_release_system(reinterpret_cast<uint32_t*>(l.base[threadIdx.x] + l.flags_offset) + l.rank, 1u);
+            add_release_system(reinterpret_cast<uint32_t*>(l.base[threadIdx.x] + l.flags_offset) + l.rank, 1u);  // (a release)
         }
         grid_dependency_wait();  // (so that this kernel's end still implies the end of the kernel before it)
         return;

@@ -229,10 +229,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     }
     if (arrival != nullptr) {  // the record is complete: the whole CTA's stores before the count
         __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();
-            add_release_system(arrival, 1u);
-        }
+        if (tid == 0) add_release_system(arrival, 1u);  // (a release: what the CTA wrote before the barrier is visible to whoever sees the count)
     }
 }
 
