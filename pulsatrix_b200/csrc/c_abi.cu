@@ -596,12 +596,22 @@ size_t psx_b200_shard_record_bytes(const psx_sampling_config* config) {
 }
 
 namespace {
+// Where the records of a step through peer memory go, and what its packing kernel waits for.
+struct PeerTargets {
+    const psx::PeerLayout* layout;
+    uint32_t* row_ready;         // one counter per row, raised by the row pass's parts
+    uint32_t* ready_total;       // host: parts announced per row so far (all steps); this step's are added
+    const uint32_t* step_done;   // device word: the last step whose results have all arrived here
+    uint32_t step;               // this step (the first is 1)
+    uint64_t wait_limit_ns;
+};
+
 // The row pass over this GPU's columns and the packing of one record per row: into `records`, or
 // (peers != nullptr) straight into the exchange buffers of the ranks that decide the rows.
 psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_logits, int64_t rows,
                            int64_t shard_cols, int64_t row_stride, int64_t shard_begin, int64_t vocab,
                            const int64_t* history_ids, const int64_t* history_offsets,
-                           const psx_sampling_config* config, void* records, const psx::PeerLayout* peers) {
+                           const psx_sampling_config* config, void* records, const PeerTargets* peers) {
     if (psx_status s = check_common(ctx, config, rows, shard_cols, row_stride, vocab, shard_logits, history_ids,
                                     history_offsets)) {
         return s;
@@ -632,11 +642,11 @@ psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_lo
     int set = 0;
     if (peers) {
         // Steps through peer memory follow one another kernel under kernel: this step's row pass writes the
-        // scratch set that the step before it did not use (its packing kernel may still be reading the other),
-        // and only the row pass's last CTA waits for the step before -- which the packing kernel, waiting for
-        // the whole row pass, therefore never overtakes.
+        // scratch set that the step before it did not use (its packing kernel may still be reading the other)
+        // and raises a counter per row; the packing kernel takes the rows as they finish.
         set = (ctx->scratch_set ^= 1);
         sp.wait_before_writes = 0;
+        sp.row_ready = peers->row_ready;
     }
     if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp, set)) return s;
     PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
@@ -657,7 +667,13 @@ psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_lo
     pp.records = records;
     if (peers) {
         pp.to_peers = 1;
-        pp.peers = *peers;
+        pp.peers = *peers->layout;
+        *peers->ready_total += (uint32_t)plan.parts;
+        pp.row_ready = peers->row_ready;
+        pp.row_ready_target = *peers->ready_total;
+        pp.step_done = peers->step_done;
+        pp.step_done_target = peers->step - 1;
+        pp.wait_limit_ns = peers->wait_limit_ns;
     }
     PSX_CUDA(psx::launch_pack_records(pp, stream));
     ++ctx->launches;
@@ -939,7 +955,9 @@ struct psx_exchange {
     int64_t rows = 0;
     size_t buffer_bytes = 0;
     char* buffer = nullptr;  // this rank's exchange buffer (cudaMalloc: its IPC handle goes to the peers)
-    char* block = nullptr;   // this rank's results of the step, before they are published
+    char* block = nullptr;   // this rank's results of the step (the survivor stage's own outputs)
+    uint32_t* words = nullptr;   // rows + 1 device words: a counter per row for the row pass, then step_done
+    uint32_t ready_total = 0;    // parts per row announced so far, over all steps
     bool opened[psx::kMaxPeers] = {};
     bool ready = false;
     uint32_t step = 0;
@@ -972,11 +990,14 @@ psx_status psx_b200_exchange_create(psx_ctx* ctx, int32_t world, int32_t rank, i
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ex->block), (size_t)psx::peer_results_block_bytes(l.rows_per_rank));
     if (e == cudaSuccess) e = cudaMemset(ex->buffer, 0, ex->buffer_bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->block, 0, (size_t)psx::peer_results_block_bytes(l.rows_per_rank));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ex->words), sizeof(uint32_t) * (size_t)(rows + 1));
+    if (e == cudaSuccess) e = cudaMemset(ex->words, 0, sizeof(uint32_t) * (size_t)(rows + 1));
     if (e == cudaSuccess) e = cudaDeviceSynchronize();  // zero before any peer can learn the handle
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle), ex->buffer);
     if (e != cudaSuccess) {
         if (ex->buffer) cudaFree(ex->buffer);
         if (ex->block) cudaFree(ex->block);
+        if (ex->words) cudaFree(ex->words);
         delete ex;
         return fail(PSX_ERR_CUDA, std::string("psx_b200: exchange buffer: ") + cudaGetErrorString(e));
     }
@@ -1010,6 +1031,7 @@ void psx_b200_exchange_destroy(psx_exchange* ex) {
     }
     if (ex->buffer) cudaFree(ex->buffer);
     if (ex->block) cudaFree(ex->block);
+    if (ex->words) cudaFree(ex->words);
     delete ex;
 }
 
@@ -1043,8 +1065,9 @@ psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const fl
     if (sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
     const uint32_t step = ex->step + 1;
+    const PeerTargets targets{&l, ex->words, &ex->ready_total, ex->words + ex->rows, step, ex->wait_limit_ns};
     if (psx_status s = shard_scan_impl(ctx, stream_ptr, shard_logits, ex->rows, shard_cols, row_stride, shard_begin, vocab,
-                                       history_ids, history_offsets, config, nullptr, &l)) {
+                                       history_ids, history_offsets, config, nullptr, &targets)) {
         return s;  // (the peers' waits for this rank's records of the step run out)
     }
     ex->step = step;
@@ -1068,6 +1091,7 @@ psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const fl
     aw.rows = ex->rows;
     aw.step = step;
     aw.wait_limit_ns = ex->wait_limit_ns;
+    aw.step_done = ex->words + ex->rows;
     PSX_CUDA(psx::launch_await_results(aw, stream));
     ++ctx->launches;
     return PSX_OK;

@@ -28,6 +28,10 @@ __global__ void __launch_bounds__(32) await_results_kernel(const AwaitParams p) 
             }
         }
     }
+    __syncwarp();
+    // The next step's packing kernel, already waiting under its row pass, may now overwrite what this
+    // step's survivor stages have read (everywhere: every result of the step has been seen here).
+    if (threadIdx.x == 0 && p.step_done != nullptr) store_release_device(p.step_done, p.step);
     grid_dependency_wait();  // (so that this kernel's end still implies the end of the kernels before it)
 }
 

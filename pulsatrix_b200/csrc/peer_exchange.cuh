@@ -69,6 +69,27 @@ __device__ __forceinline__ void add_release_system(uint32_t* p, uint32_t v) {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ uint32_t load_acquire_device(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void store_release_device(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// The same wait as below for a word that only this GPU's kernels write.
+__device__ __forceinline__ bool wait_until_at_least_device(const uint32_t* word, uint32_t target, unsigned long long limit_ns) {
+    unsigned long long started = 0;
+    for (uint32_t tries = 1;; ++tries) {
+        if ((int32_t)(load_acquire_device(word) - target) >= 0) return true;
+        if ((tries & 15u) == 0) {
+            const unsigned long long now = global_nanoseconds();
+            if (started == 0) started = now;
+            else if (now - started > limit_ns) return false;
+        }
+    }
+}
+
 // Waits until *word >= target (as a wrapping difference), for at most limit_ns nanoseconds.
 __device__ __forceinline__ bool wait_until_at_least(const uint32_t* word, uint32_t target, unsigned long long limit_ns) {
     unsigned long long started = 0;
@@ -87,6 +108,7 @@ struct AwaitParams {
     int64_t rows;            // of the whole step: rank r decides rows r * rows_per_rank onwards, as many as there are
     uint32_t step;
     unsigned long long wait_limit_ns;
+    uint32_t* step_done;     // this GPU's own word: set to `step` once every result of the step is here
 };
 
 // The last kernel of a step: one thread per rank waits until that rank's counter in this rank's flags

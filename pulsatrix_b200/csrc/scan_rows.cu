@@ -139,6 +139,12 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t part_index = (size_t)row * p.parts + part;
+    auto announce_part = [&]() {  // (by the whole CTA, after its last write)
+        if (p.row_ready != nullptr) {
+            __syncthreads();
+            if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.row_ready + row) : "memory");
+        }
+    };
 
     // ---- geometry: the row as aligned float4 vectors ------------------------------------------
     const float* row_ptr = p.logits + row * p.row_stride;
@@ -162,6 +168,7 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
             s.nonfinite = 0; s.alive_tail = 0; s.overflow = 0;
             p.stats[part_index] = s;
         }
+        announce_part();
         return;
     }
 
@@ -402,6 +409,7 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
         if (warp == 0) {
             for (int i = 0; i < copies; ++i) barrier_wait_bounded(&s_bar[i], 0, p.wait_limit_ns);
         }
+        announce_part();
         return;
     }
     STAGE(6);
@@ -643,6 +651,7 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
             }
         }
     }
+    announce_part();
     if (ends_the_grid) grid_dependency_wait();
 #ifdef PSX_STAGE_CLOCKS
     STAGE(11);

@@ -39,6 +39,9 @@ struct ScanParams {
     PartStats* stats;                // rows * parts
     uint32_t* part_counts;           // rows * parts: candidates handed on by the part
     uint2* candidates;               // rows * parts * kPartCap: the part's candidates, back to back
+    // Optional: one counter per row, raised by one (a release at device scope) when a part of the row has
+    // written everything above -- a kernel that runs under this one can then take the rows as they finish.
+    uint32_t* row_ready;             // nullptr: off
 };
 
 constexpr uint64_t kDefaultWaitLimitNs = 1000000000ull;

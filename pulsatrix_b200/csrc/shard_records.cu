@@ -67,8 +67,22 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool apply_t = p.apply_temperature != 0;
     const PartStats* stats = p.stats + row * p.parts;
-    grid_dependents_may_launch();  // what follows either waits for this kernel's end or for its records one by one
-    grid_dependency_wait();        // everything read here was written by the row pass before this kernel
+    bool in_time = true;
+    if (p.to_peers && p.row_ready != nullptr) {
+        // Under the row pass: this row's parts, and the step before this one, are waited for by name.
+        __shared__ int s_in_time;
+        if (tid == 0) {
+            s_in_time = (wait_until_at_least_device(p.row_ready + row, p.row_ready_target, p.wait_limit_ns) &&
+                         wait_until_at_least_device(p.step_done, p.step_done_target, p.wait_limit_ns)) ? 1 : 0;
+        }
+        __syncthreads();
+        in_time = s_in_time != 0;
+    } else {
+        grid_dependency_wait();    // everything read here was written by the row pass before this kernel
+    }
+    // What follows this kernel may start now: it waits for this kernel's end, or for its records one by one.
+    // (Not earlier: whoever starts after this point may rely on what this block has just waited for.)
+    grid_dependents_may_launch();
 
     // Every warp joins the parts' records for itself (a few dozen small loads out of L2).
     float raw_max = -FLT_MAX, y_max = -INFINITY, thr = -INFINITY;
@@ -220,7 +234,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
         s.raw_max = raw_max;
         s.y_max = y_max;
         s.thr = thr;
-        s.nonfinite = nonfinite;
+        s.nonfinite = nonfinite | (in_time ? 0u : 2u);
         s.alive_tail = alive_tail + all_dropped;
         s.overflow = (overflow || kept > (uint32_t)p.capacity) ? 1u : 0u;
         *reinterpret_cast<PartStats*>(record + kRecordStatsOffset) = s;
@@ -230,6 +244,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     if (arrival != nullptr) {  // the record is complete: the whole CTA's stores before the count
         __syncthreads();
         if (tid == 0) add_release_system(arrival, 1u);  // (a release: what the CTA wrote before the barrier is visible to whoever sees the count)
+        if (p.row_ready != nullptr) grid_dependency_wait();  // (so that this kernel's end still implies the row pass's)
     }
 }
 

@@ -43,6 +43,16 @@ struct PackParams {
     // [this rank][r % rows_per_rank], and that rank's arrival counter of the row goes up by one.
     int32_t to_peers;            // 0: off
     PeerLayout peers;
+    // With to_peers the kernel runs under the row pass instead of after it: a row's block waits (bounded)
+    // until row_ready[row] has reached row_ready_target (all parts of the row written: ScanParams::row_ready)
+    // and until *step_done has reached step_done_target (the step before has been read everywhere, so its
+    // records may be overwritten: AwaitParams::step_done); a wait that runs out marks the record (bit 1 of
+    // PartStats::nonfinite, as a copy that timed out does).
+    const uint32_t* row_ready;
+    uint32_t row_ready_target;
+    const uint32_t* step_done;
+    uint32_t step_done_target;
+    unsigned long long wait_limit_ns;
 };
 
 cudaError_t launch_pack_records(const PackParams& p, cudaStream_t stream);
