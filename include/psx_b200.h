@@ -251,10 +251,13 @@ PSX_API psx_status psx_b200_shard_merge_rows(psx_ctx* ctx, void* stream, const v
  *   psx_b200_exchange_sample   one step: row pass over this rank's columns, records to their ranks,
  *                              the draw for this rank's rows, results to every rank.  Asynchronous on
  *                              `stream`; every rank must call it the same number of times.  When the
- *                              stream has run, psx_b200_exchange_results points at `world` blocks of
- *                              rows_per_rank rows each (rank r's rows in block r): rows_per_rank
- *                              tokens (int64), then as many log-probs (float), then as many statuses
- *                              (int32).  Arguments as psx_b200_shard_scan / psx_b200_shard_merge.
+ *                              stream has run, psx_b200_exchange_results (called after the step was
+ *                              enqueued) points at `world` blocks of rows_per_rank rows each (rank
+ *                              r's rows in block r): rows_per_rank tokens (int64), then as many
+ *                              log-probs (float), then as many statuses (int32).  Two steps are in
+ *                              flight at a time and the results alternate between two places: a step's
+ *                              stay where they are until the step after the next one.  Arguments as
+ *                              psx_b200_shard_scan / psx_b200_shard_merge.
  *   psx_b200_exchange_destroy  unmaps and frees; the caller makes sure (a barrier of its process
  *                              group) that no rank is still inside a step.
  *

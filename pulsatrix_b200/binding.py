@@ -531,17 +531,21 @@ class Exchange:
         return self.results(shard_logits.device)
 
     def results(self, device):
+        """Views of the last step's results (the library keeps two sets and alternates: a step's results
+        stay in place until the step after the next one)."""
         import torch
+        address, per = C.c_void_p(), C.c_int64()
+        _check(self._lib.psx_b200_exchange_results(self._ex, C.byref(address), C.byref(per)))
         if self._views is None:
-            address, per = C.c_void_p(), C.c_int64()
-            _check(self._lib.psx_b200_exchange_results(self._ex, C.byref(address), C.byref(per)))
+            self._views = {}
+        if address.value not in self._views:
             per = per.value
             raw = torch.as_tensor(_DeviceBytes(address.value, self.world * 16 * per), device=device)
             by_rank = raw.view(self.world, 16 * per)
-            self._views = {"tokens": by_rank[:, : 8 * per].view(torch.int64),
-                           "log_probs": by_rank[:, 8 * per: 12 * per].view(torch.float32),
-                           "status": by_rank[:, 12 * per:].view(torch.int32)}
-        return self._views
+            self._views[address.value] = {"tokens": by_rank[:, : 8 * per].view(torch.int64),
+                                          "log_probs": by_rank[:, 8 * per: 12 * per].view(torch.float32),
+                                          "status": by_rank[:, 12 * per:].view(torch.int32)}
+        return self._views[address.value]
 
     def test_wait(self, wait_limit_ns, extra_arrivals):
         _check(self._lib.psx_b200_exchange_test_wait(self._ex, wait_limit_ns, extra_arrivals))

@@ -604,6 +604,9 @@ struct PeerTargets {
     const uint32_t* step_done;   // device word: the last step whose results have all arrived here
     uint32_t step;               // this step (the first is 1)
     uint64_t wait_limit_ns;
+    Buffer* stats;               // this step's set of row-pass scratch (the exchange's own, one of three)
+    Buffer* part_counts;
+    Buffer* candidates;
 };
 
 // The row pass over this GPU's columns and the packing of one record per row: into `records`, or
@@ -639,16 +642,23 @@ psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_lo
     sp.history_ids = history_ids;
     sp.history_offsets = history_offsets;
     if (psx_status s = prepare_scan(ctx, stream, config, plan, sp)) return s;
-    int set = 0;
     if (peers) {
-        // Steps through peer memory follow one another kernel under kernel: this step's row pass writes the
-        // scratch set that the step before it did not use (its packing kernel may still be reading the other)
-        // and raises a counter per row; the packing kernel takes the rows as they finish.
-        set = (ctx->scratch_set ^= 1);
+        // Steps through peer memory follow one another kernel under kernel: this step's row pass writes a
+        // scratch set of the exchange's own that the two steps before it did not use (their packing kernels
+        // may still be reading theirs) and raises a counter per row; the packing kernel takes the rows as
+        // they finish.
         sp.wait_before_writes = 0;
         sp.row_ready = peers->row_ready;
+        const size_t parts = (size_t)rows * plan.parts;
+        if (psx_status s = reserve(*peers->stats, parts * sizeof(psx::PartStats))) return s;
+        if (psx_status s = reserve(*peers->part_counts, parts * sizeof(uint32_t))) return s;
+        if (psx_status s = reserve(*peers->candidates, parts * psx::kPartCap * sizeof(uint2))) return s;
+        sp.stats = static_cast<psx::PartStats*>(peers->stats->ptr);
+        sp.part_counts = static_cast<uint32_t*>(peers->part_counts->ptr);
+        sp.candidates = static_cast<uint2*>(peers->candidates->ptr);
+    } else if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp)) {
+        return s;
     }
-    if (psx_status s = reserve_scan_scratch(ctx, rows, plan, sp, set)) return s;
     PSX_CUDA(psx::launch_scan_rows(sp, plan.nucleus, stream));
     ++ctx->launches;
 
@@ -672,7 +682,7 @@ psx_status shard_scan_impl(psx_ctx* ctx, void* stream_ptr, const float* shard_lo
         pp.row_ready = peers->row_ready;
         pp.row_ready_target = *peers->ready_total;
         pp.step_done = peers->step_done;
-        pp.step_done_target = peers->step - 1;
+        pp.step_done_target = peers->step > 2 ? peers->step - 2 : 0;  // two steps are in flight: see psx_exchange
         pp.wait_limit_ns = peers->wait_limit_ns;
     }
     PSX_CUDA(psx::launch_pack_records(pp, stream));
@@ -949,13 +959,20 @@ void psx_uniforms_portable(const uint64_t* seeds, int64_t n, double* out) {
 
 // ---- vocabulary shards exchanged over peer memory (peer_exchange.cuh) ----------------------------------
 
+// Two steps are in flight at a time: everything a step exchanges exists twice, once for odd steps and once
+// for even ones (two halves of the exchange buffer, two blocks of local results), so that a step's
+// records and results never wait for the step before to have been read everywhere -- only for the step
+// before that (step_done).  The row-pass scratch exists three times: the packing kernel of step e + 2
+// only starts once step e is done everywhere, so what step e + 3 overwrites has long been read.
 struct psx_exchange {
     psx_ctx* ctx = nullptr;
-    psx::PeerLayout layout{};
+    psx::PeerLayout layout{};  // base[r]: the first half of rank r's buffer
     int64_t rows = 0;
+    size_t half_bytes = 0;
     size_t buffer_bytes = 0;
     char* buffer = nullptr;  // this rank's exchange buffer (cudaMalloc: its IPC handle goes to the peers)
-    char* block = nullptr;   // this rank's results of the step (the survivor stage's own outputs)
+    char* block = nullptr;   // this rank's results of a step (the survivor stage's own outputs), twice
+    Buffer stats[3], part_counts[3], candidates[3];
     uint32_t* words = nullptr;   // rows + 1 device words: a counter per row for the row pass, then step_done
     uint32_t ready_total = 0;    // parts per row announced so far, over all steps
     bool opened[psx::kMaxPeers] = {};
@@ -984,12 +1001,14 @@ psx_status psx_b200_exchange_create(psx_ctx* ctx, int32_t world, int32_t rank, i
     l.rank = rank;
     l.rows_per_rank = (rows + world - 1) / world;
     l.record_bytes = (int64_t)psx_b200_shard_record_bytes(config);
-    ex->buffer_bytes = (size_t)psx::peer_layout_offsets(world, l.rows_per_rank, l.record_bytes, &l.records_offset,
-                                                        &l.arrivals_offset, &l.results_offset, &l.flags_offset);
+    ex->half_bytes = (size_t)psx::peer_layout_offsets(world, l.rows_per_rank, l.record_bytes, &l.records_offset,
+                                                      &l.arrivals_offset, &l.results_offset, &l.flags_offset);
+    ex->buffer_bytes = 2 * ex->half_bytes;
+    const size_t block_bytes = (size_t)psx::peer_results_block_bytes(l.rows_per_rank);
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ex->buffer), ex->buffer_bytes);
-    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ex->block), (size_t)psx::peer_results_block_bytes(l.rows_per_rank));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ex->block), 2 * block_bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->buffer, 0, ex->buffer_bytes);
-    if (e == cudaSuccess) e = cudaMemset(ex->block, 0, (size_t)psx::peer_results_block_bytes(l.rows_per_rank));
+    if (e == cudaSuccess) e = cudaMemset(ex->block, 0, 2 * block_bytes);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&ex->words), sizeof(uint32_t) * (size_t)(rows + 1));
     if (e == cudaSuccess) e = cudaMemset(ex->words, 0, sizeof(uint32_t) * (size_t)(rows + 1));
     if (e == cudaSuccess) e = cudaDeviceSynchronize();  // zero before any peer can learn the handle
@@ -1032,12 +1051,17 @@ void psx_b200_exchange_destroy(psx_exchange* ex) {
     if (ex->buffer) cudaFree(ex->buffer);
     if (ex->block) cudaFree(ex->block);
     if (ex->words) cudaFree(ex->words);
+    for (int i = 0; i < 3; ++i) {
+        for (Buffer* b : {&ex->stats[i], &ex->part_counts[i], &ex->candidates[i]}) {
+            if (b->ptr) cudaFree(b->ptr);
+        }
+    }
     delete ex;
 }
 
 psx_status psx_b200_exchange_results(const psx_exchange* ex, const void** results, int64_t* rows_per_rank) {
     if (!ex || !results || !rows_per_rank) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: null pointer");
-    *results = ex->buffer + ex->layout.results_offset;
+    *results = ex->buffer + (ex->step & 1u) * ex->half_bytes + ex->layout.results_offset;  // the last step's half
     *rows_per_rank = ex->layout.rows_per_rank;
     return PSX_OK;
 }
@@ -1057,15 +1081,20 @@ psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const fl
     if (!ex->ready) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the exchange is not open yet");
     psx_ctx* ctx = ex->ctx;
     if (psx_status s = check_config(config)) return s;
-    const psx::PeerLayout& l = ex->layout;
+    const uint32_t step = ex->step + 1, half = step & 1u, turn = (step + 1) / 2;  // this half's turn-th step
+    psx::PeerLayout l = ex->layout;
+    for (int r = 0; r < l.world; ++r) l.base[r] += half * ex->half_bytes;
+    char* const own = ex->buffer + half * ex->half_bytes;
+    char* const block = ex->block + half * (size_t)psx::peer_results_block_bytes(l.rows_per_rank);
     if ((int64_t)psx_b200_shard_record_bytes(config) != l.record_bytes) {
         return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: the settings need records of another size than the exchange was created for");
     }
     const bool sample = config->do_sample != 0;
     if (sample && !uniforms) return fail(PSX_ERR_BAD_ARGUMENT, "psx_b200: sampling needs uniforms");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-    const uint32_t step = ex->step + 1;
-    const PeerTargets targets{&l, ex->words, &ex->ready_total, ex->words + ex->rows, step, ex->wait_limit_ns};
+    const int set = (int)(step % 3);
+    const PeerTargets targets{&l, ex->words, &ex->ready_total, ex->words + ex->rows, step, ex->wait_limit_ns,
+                              &ex->stats[set], &ex->part_counts[set], &ex->candidates[set]};
     if (psx_status s = shard_scan_impl(ctx, stream_ptr, shard_logits, ex->rows, shard_cols, row_stride, shard_begin, vocab,
                                        history_ids, history_offsets, config, nullptr, &targets)) {
         return s;  // (the peers' waits for this rank's records of the step run out)
@@ -1075,14 +1104,14 @@ psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const fl
     const int64_t row_count = std::min<int64_t>(l.rows_per_rank, ex->rows - row_begin);
     if (row_count > 0) {
         // this rank's rows: their records lie here, shard after shard; absolute row r at [r - row_begin]
-        const char* base = ex->buffer + l.records_offset - row_begin * l.record_bytes;
-        const uint32_t* arrivals = reinterpret_cast<const uint32_t*>(ex->buffer + l.arrivals_offset) - row_begin;
-        int64_t* tokens = reinterpret_cast<int64_t*>(ex->block);
-        float* log_probs = reinterpret_cast<float*>(ex->block + 8 * l.rows_per_rank);
-        int32_t* status = reinterpret_cast<int32_t*>(ex->block + 12 * l.rows_per_rank);
+        const char* base = own + l.records_offset - row_begin * l.record_bytes;
+        const uint32_t* arrivals = reinterpret_cast<const uint32_t*>(own + l.arrivals_offset) - row_begin;
+        int64_t* tokens = reinterpret_cast<int64_t*>(block);
+        float* log_probs = reinterpret_cast<float*>(block + 8 * l.rows_per_rank);
+        int32_t* status = reinterpret_cast<int32_t*>(block + 12 * l.rows_per_rank);
         if (psx_status s = shard_merge_impl(ctx, stream, base, l.rows_per_rank * l.record_bytes, l.world, row_begin, row_count,
                                             vocab, config, uniforms, tokens, log_probs, status, nullptr, arrivals,
-                                            step * (uint32_t)l.world + ex->test_extra_arrivals, ex->wait_limit_ns, &l)) {
+                                            turn * (uint32_t)l.world + ex->test_extra_arrivals, ex->wait_limit_ns, &l)) {
             return s;
         }
     }
@@ -1090,6 +1119,7 @@ psx_status psx_b200_exchange_sample(psx_exchange* ex, void* stream_ptr, const fl
     aw.layout = l;
     aw.rows = ex->rows;
     aw.step = step;
+    aw.turn = turn;
     aw.wait_limit_ns = ex->wait_limit_ns;
     aw.step_done = ex->words + ex->rows;
     PSX_CUDA(psx::launch_await_results(aw, stream));

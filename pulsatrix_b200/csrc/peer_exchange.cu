@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(32) await_results_kernel(const AwaitParams p) 
         const int64_t first = (int64_t)peer * l.rows_per_rank;
         const int64_t count = first >= p.rows ? 0 : (p.rows - first < l.rows_per_rank ? p.rows - first : l.rows_per_rank);
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(l.base[l.rank] + l.flags_offset) + peer;
-        if (count > 0 && !wait_until_at_least(flag, p.step * (uint32_t)count, p.wait_limit_ns)) {
+        if (count > 0 && !wait_until_at_least(flag, p.turn * (uint32_t)count, p.wait_limit_ns)) {
             char* block = l.base[l.rank] + l.results_offset + (int64_t)peer * peer_results_block_bytes(l.rows_per_rank);
             int64_t* tokens = reinterpret_cast<int64_t*>(block);
             int32_t* status = reinterpret_cast<int32_t*>(block + 12 * l.rows_per_rank);
@@ -31,7 +31,10 @@ __global__ void __launch_bounds__(32) await_results_kernel(const AwaitParams p) 
     __syncwarp();
     // The next step's packing kernel, already waiting under its row pass, may now overwrite what this
     // step's survivor stages have read (everywhere: every result of the step has been seen here).
-    if (threadIdx.x == 0 && p.step_done != nullptr) store_release_device(p.step_done, p.step);
+    if (threadIdx.x == 0 && p.step_done != nullptr) {
+        __threadfence();
+        atomicMax(p.step_done, p.step);  // (two steps are in flight: never back)
+    }
     grid_dependency_wait();  // (so that this kernel's end still implies the end of the kernels before it)
 }
 

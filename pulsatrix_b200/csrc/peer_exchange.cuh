@@ -106,9 +106,10 @@ __device__ __forceinline__ bool wait_until_at_least(const uint32_t* word, uint32
 struct AwaitParams {
     PeerLayout layout;
     int64_t rows;            // of the whole step: rank r decides rows r * rows_per_rank onwards, as many as there are
-    uint32_t step;
+    uint32_t step;           // counted over both halves (the first is 1)
+    uint32_t turn;           // the step's number among those of its half: the counters of layout stand at turn * rows
     unsigned long long wait_limit_ns;
-    uint32_t* step_done;     // this GPU's own word: set to `step` once every result of the step is here
+    uint32_t* step_done;     // this GPU's own word: raised to `step` once every result of the step is here
 };
 
 // The last kernel of a step: one thread per rank waits until that rank's counter in this rank's flags

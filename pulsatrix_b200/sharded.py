@@ -95,7 +95,9 @@ class ShardedSampler:
         if shard_logits.shape != (self.rows, self.cols):
             raise ValueError(f"rank {self.rank} should hold a {self.rows} x {self.cols} block, got {tuple(shard_logits.shape)}")
         if self.peer is not None:
-            return self.peer.sample(shard_logits, self.begin_col, self.vocab, history_ids, history_offsets, self.config, uniforms)
+            self.out = self.peer.sample(shard_logits, self.begin_col, self.vocab, history_ids, history_offsets, self.config,
+                                        uniforms)
+            return self.out
         self.ctx.shard_scan(shard_logits, self.begin_col, self.vocab, history_ids, history_offsets, self.config, self.mine)
         dist.all_gather_into_tensor(self.gathered, self.mine, group=self.group)
         if self.row_count > 0:
