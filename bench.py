@@ -517,7 +517,7 @@ def sharded_setup(w, device, rank, world, n_batches_for, fixture_rows=48, exchan
     hist[: fixture_rows * w.history] = torch.from_numpy(f_hist.reshape(-1).astype(np.int64)).to(device)
     offsets = torch.arange(w.rows + 1, device=device, dtype=torch.int64) * w.history
     uniforms = torch.from_numpy(psx.uniforms_mt19937_64(np.arange(w.rows, dtype=np.uint64))).to(device)
-    sampler = ShardedSampler(ctx, w.rows, w.vocab, cfg, device, exchange=exchange)
+    sampler = ShardedSampler(ctx, w.rows, w.vocab, cfg, device, exchange=exchange, fall_back=True)
     return ctx, cfg, sampler, shards, hist, offsets, uniforms, shard_bytes, begin_col, fixture_rows
 
 
@@ -575,7 +575,7 @@ def sharded_record(args, rank, world, local):
     sampler.close()
     return {"workload": f"c5: batch={w.rows} rows, vocab={w.vocab} in {world} column shard(s), history={w.history}, "
                         f"top_k={w.top_k}, top_p={w.top_p}",
-            "exchange": args.exchange, "step_us": step_ms * 1e3, "rows_per_s": w.rows / (step_ms * 1e-3), "steps": steps,
+            "exchange": sampler.exchange, "exchange_note": sampler.exchange_note, "step_us": step_ms * 1e3, "rows_per_s": w.rows / (step_ms * 1e-3), "steps": steps,
             "shard_scan_us": scan_ms * 1e3, "scan_frac": shard_bytes / (scan_ms * 1e-3) / 1e9 / peak,
             "allgather_bytes": records_bytes, "results_allgather_bytes": results_bytes,
             "fixture_rows": n_fix, "fixture_rows_matched": int(-neg_matched), "failed_rows": int(failed),
@@ -652,7 +652,7 @@ def run_sharded(args, rank, world):
     scan_ms = timed(scan_only, args.steps, 3)
     clocks = clock_sampler.stop() if clock_sampler else None
     other_ms = None
-    if args.exchange == "peer":  # the same step with the two NCCL all-gathers instead, for comparison
+    if sampler.exchange == "peer":  # the same step with the two NCCL all-gathers instead, for comparison
         from pulsatrix_b200.sharded import ShardedSampler
         by_nccl = ShardedSampler(ctx, w.rows, w.vocab, cfg, device, exchange="nccl")
         other_ms = timed(lambda i: by_nccl.step(shards[i % n_batches], hist, offsets, uniforms), args.steps, warm)
@@ -701,10 +701,10 @@ def run_sharded(args, rank, world):
                    "parallelism": (f"vocabulary split over {world} GPU(s); per step {records_bytes} bytes of records per rank "
                                    f"written straight into the memory of the ranks that decide the rows and {results_bytes} "
                                    f"bytes of results into every rank's (peer stores over NVLink, counters in peer memory, "
-                                   f"no library collective)" if args.exchange == "peer" else
+                                   f"no library collective)" if sampler.exchange == "peer" else
                                    f"vocabulary split over {world} GPU(s); per step one NCCL all-gather of "
                                    f"{records_bytes} bytes per rank (records) and one of {results_bytes} (results)"),
-                   "exchange": args.exchange,
+                   "exchange": sampler.exchange, "exchange_note": sampler.exchange_note,
                    "contexts_in_flight": 1,
                    "l2": f"shards rotate over {n_batches} batches = {n_batches * shard_bytes / 2**20:.0f} MiB > L2"},
         "e2e": {"value": w.rows * e2e_steps / (e2e_ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": shard_bytes,

@@ -2,19 +2,20 @@
 // another's memory over NVLink (plain peer stores into buffers opened through CUDA IPC) and tell one
 // another so with counters, also in peer memory.
 //
-// Every rank owns one exchange buffer of the same layout:
+// Every rank owns one exchange buffer; a half of it (one for odd steps, one for even ones: c_abi.cu's
+// psx_exchange says why) has this layout:
 //   records    world x rows_per_rank records: [shard][row of this rank's block], what the ranks' packing
 //              kernels write here, each its own shard's slice;
 //   arrivals   rows_per_rank counters: +1 by every shard whose record of that row is complete;
-//              after step e a counter stands at e * world;
+//              after the half's t-th step a counter stands at t * world;
 //   results    world blocks of 16 * rows_per_rank bytes (tokens | log-probs | status), block r written
-//              by rank r after it has decided its rows;
+//              row by row by rank r's survivor stage;
 //   flags      world counters: flags[r] goes up by one for every row of rank r whose result has been written
-//              here; after step e it stands at e * (rows that rank r decides).
-// Counters and flags only ever grow (the step number e starts at 1), so nothing is reset between
-// steps.  A step's pushes cannot overtake the step before: a rank's row pass of step e + 1 writes
-// nothing before its last kernel of step e has seen every row's result of step e arrive, and a row's
-// result is sent only after its records of step e have been read.
+//              here; after the half's t-th step it stands at t * (rows that rank r decides).
+// Counters only ever grow, so nothing is reset between steps.  A half is written again two steps later,
+// and only after the packing kernel of that step has seen, in a word of this GPU's own, that the step
+// which used the half last is done everywhere: every row's result of it has arrived here, and a row's
+// result is sent only after its records have been read.
 //
 // Every wait is bounded: after `wait_limit_ns` a waiting kernel gives up and reports
 // PSX_ROW_DEVICE_TIMEOUT for the rows concerned.

@@ -50,7 +50,7 @@ class ShardedSampler:
     are views of the gathered results; row r is at [r // rows_per_rank, r % rows_per_rank] (use
     flat() for plain (rows,) copies)."""
 
-    def __init__(self, ctx, rows, vocab, config, device, group=None, exchange="nccl"):
+    def __init__(self, ctx, rows, vocab, config, device, group=None, exchange="nccl", fall_back=False):
         import torch
         import torch.distributed as dist
         if exchange not in ("nccl", "peer"):
@@ -63,15 +63,36 @@ class ShardedSampler:
         self.record = ctx.shard_record_bytes(config)
         self.mine = torch.empty(rows * self.record, dtype=torch.uint8, device=device)
         self.peer = None
+        self.exchange, self.exchange_note = exchange, None
         if exchange == "peer":
-            self.peer = ctx.exchange(self.world, self.rank, rows, config)
-            mine = torch.frombuffer(bytearray(self.peer.handle), dtype=torch.uint8).to(device)
+            # Every rank goes through the same collectives whether or not its own buffer could be made and
+            # its peers' mapped; one rank's failure is every rank's (fall_back: all use the all-gathers instead).
+            from .binding import PsxError
+            problem = None
+            try:
+                self.peer = ctx.exchange(self.world, self.rank, rows, config)
+                handle = self.peer.handle
+            except PsxError as e:
+                problem, handle = str(e), bytes(64)
+            mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(device)
             everyone = torch.empty(self.world * mine.numel(), dtype=torch.uint8, device=device)
             dist.all_gather_into_tensor(everyone, mine, group=group)
-            self.peer.open(everyone.cpu().numpy().tobytes())
-            dist.barrier(group=group)  # every rank has mapped every buffer before anyone writes
-            self.out = self.peer.results(device)
-            return
+            if problem is None:
+                try:
+                    self.peer.open(everyone.cpu().numpy().tobytes())
+                except PsxError as e:
+                    problem = str(e)
+            failed = torch.tensor([0 if problem is None else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX, group=group)  # (also: every rank has mapped every buffer before anyone writes)
+            if int(failed.item()) == 0:
+                self.out = self.peer.results(device)
+                return
+            if self.peer is not None:
+                self.peer.close()
+                self.peer = None
+            if not fall_back:
+                raise RuntimeError("the peer-memory exchange could not be set up on every rank" + (f": {problem}" if problem else ""))
+            self.exchange, self.exchange_note = "nccl", problem or "another rank could not set up the peer-memory exchange"
         self.gathered = torch.empty(self.world * rows * self.record, dtype=torch.uint8, device=device)
         per = self.per
         # a rank's block: tokens (int64 x per) | log-probs (float32 x per) | status (int32 x per)

@@ -100,3 +100,72 @@ def test_two_gloo_ranks_gather_records_shard_major(tmp_path):
                           capture_output=True, text=True, timeout=240, env=env)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
     assert proc.stdout.count("ok") == 2
+
+
+SETUP_WORKER = textwrap.dedent("""
+    import os, sys
+    import torch, torch.distributed as dist
+    sys.path.insert(0, sys.argv[1])
+    from pulsatrix_b200.binding import PsxError
+    from pulsatrix_b200.sharded import ShardedSampler
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+
+    class FakeExchange:  # what Context.exchange() returns, without a GPU
+        def __init__(self, rank, fail_open):
+            self.handle, self.fail_open, self.opened, self.closed = bytes([rank + 1]) * 64, fail_open, None, False
+        def open(self, handles):
+            if self.fail_open:
+                raise PsxError(2, "cannot map a peer")
+            self.opened = handles
+        def results(self, device):
+            return {"tokens": torch.zeros((world, 1), dtype=torch.int64)}
+        def close(self):
+            self.closed = True
+
+    class FakeContext:
+        def __init__(self, fail_create=False, fail_open=False):
+            self.fail_create, self.fail_open, self.made = fail_create, fail_open, None
+        def shard_record_bytes(self, config):
+            return 48 + 8 * 64
+        def exchange(self, world, rank, rows, config):
+            if self.fail_create:
+                raise PsxError(2, "no memory for the exchange buffer")
+            self.made = FakeExchange(rank, self.fail_open)
+            return self.made
+
+    cpu = torch.device("cpu")
+    # every rank succeeds: each has been given all handles, in rank order
+    ctx = FakeContext()
+    s = ShardedSampler(ctx, 5, 1000, None, cpu, exchange="peer")
+    assert s.exchange == "peer" and s.peer is ctx.made
+    assert ctx.made.opened == b"".join(bytes([r + 1]) * 64 for r in range(world))
+    # one rank cannot make its buffer, another cannot map a peer's: every rank falls back, none keeps a half-open exchange
+    for kind in ("create", "open"):
+        ctx = FakeContext(fail_create=(kind == "create" and rank == 1), fail_open=(kind == "open" and rank == 0))
+        s = ShardedSampler(ctx, 5, 1000, None, cpu, exchange="peer", fall_back=True)
+        assert s.exchange == "nccl" and s.peer is None and s.exchange_note
+        assert ctx.made is None or ctx.made.closed
+        assert s.gathered.numel() == world * 5 * (48 + 8 * 64)
+        # ... or, without fall_back, every rank raises
+        ctx = FakeContext(fail_create=(kind == "create" and rank == 1), fail_open=(kind == "open" and rank == 0))
+        try:
+            ShardedSampler(ctx, 5, 1000, None, cpu, exchange="peer")
+            raise SystemExit("should have raised")
+        except RuntimeError:
+            pass
+    dist.barrier()
+    dist.destroy_process_group()
+    print("ok", rank)
+""")
+
+
+def test_two_gloo_ranks_agree_on_the_peer_exchange_or_fall_back_together(tmp_path):
+    script = tmp_path / "setup_worker.py"
+    script.write_text(SETUP_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    proc = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29673", str(script), str(ROOT)],
+                          capture_output=True, text=True, timeout=240, env=env)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert proc.stdout.count("ok") == 2
