@@ -1099,10 +1099,7 @@ __device__ __forceinline__ void merge_row(const MergeParams& p, const int64_t ro
         return;
     }
 
-#ifndef PSX_COUNT_DIRECTLY
-#define PSX_COUNT_DIRECTLY 64
-#endif
-    constexpr int kCountDirectly = PSX_COUNT_DIRECTLY;  // up to here the one-entry-per-thread path finds the k-th value by counting
+    constexpr int kCountDirectly = 64;  // up to here the one-entry-per-thread path finds the k-th value by counting
     if (top_k_on && n > kCountDirectly && n > p.top_k) {
         // A top-k over a longer list: the k-th largest value by radix selection, then only it, its
         // ties and what lies above stay (src/generation.cpp:80-87).

@@ -51,11 +51,8 @@ inline Plan make_plan(const float* logits, int64_t cols, int64_t row_stride, int
     // logit per thread: such rows skip the row pass and are decided from the row itself.
     plan.lists_cannot_bound = vectors * 4 > kPartCap &&
                               ((plan.nucleus && !(c->top_p < 1.0f) && !(c->min_p > 0.0f)) || (top_k_on && plan.k_need > kScanThreads));
-#ifndef PSX_NUCLEUS_LIST
-#define PSX_NUCLEUS_LIST 4096
-#endif
-    plan.sort_capacity = plan.nucleus ? PSX_NUCLEUS_LIST : 1024;
-    plan.gather_capacity = plan.nucleus ? 2 * PSX_NUCLEUS_LIST : 4096;
+    plan.sort_capacity = plan.nucleus ? 4096 : 1024;
+    plan.gather_capacity = plan.nucleus ? 8192 : 4096;
     if (!plan.nucleus && plan.k_need < kPartCap) {
         // A large k over many parts: a part whose threshold is a warp's 25th of 32 thread maxima hands
         // on about twice k, and the row's candidates no longer fit 4096 slots.
