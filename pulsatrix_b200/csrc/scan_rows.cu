@@ -61,8 +61,7 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
     const int64_t first_id = p.col_begin + lo;
     const uint64_t span = hi > lo ? (uint64_t)(hi - lo) : 0u;
     const uint32_t shift = (uint32_t)(lo - first_pos);
-    int64_t id = first_id_loaded;
-    for (int64_t i = begin + threadIdx.x; i < end;) {
+    auto mark = [&](int64_t id) {
         const uint64_t rel = (uint64_t)id - (uint64_t)first_id;  // wraps for ids before the interval
         if (rel < span) {
             const uint32_t e = (uint32_t)rel + shift;  // slot in this part
@@ -74,7 +73,21 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
                 if (also_count != nullptr && fresh_also) atomicAdd(also_count, 1u);
             }
         }
-        i += kScanThreads;
+    };
+    // A thread's ids four at a time: the three after the one in hand are asked for together, so a history
+    // of a thousand ids costs one trip to memory here, not three one after another.
+    int64_t id = first_id_loaded;
+    for (int64_t i = begin + threadIdx.x; i < end;) {
+        int64_t next[3];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+            const int64_t j = i + (int64_t)(q + 1) * kScanThreads;
+            next[q] = j < end ? ids[j] : (int64_t)-1;  // (-1 lies before every interval)
+        }
+        mark(id);
+#pragma unroll
+        for (int q = 0; q < 3; ++q) mark(next[q]);
+        i += 4 * kScanThreads;
         if (i < end) id = ids[i];
     }
 }
