@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     __shared__ uint32_t s_keys[kPackKeys];
     __shared__ uint32_t s_hist[256];
     __shared__ uint32_t s_pick[2];
+    __shared__ uint32_t s_begin[32];
     __shared__ double s_sum[2][kPackWarps];
     __shared__ uint32_t s_dropped[kPackWarps];
     const int64_t row = blockIdx.x;
@@ -107,20 +108,52 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     const int nseg = p.parts;  // one candidate list per part; at most kPackKeys parts (checked by the host)
     const uint32_t* seg_counts = p.part_counts + row * nseg;
     const uint2* cands = p.candidates + (size_t)row * nseg * kPartCap;
+    // The parts' counts, asked for once and all together when a lane can hold one each (every warp for
+    // itself), and their running sums: count_of(s) then costs a shuffle, not another trip to memory.
+    const bool few = nseg <= 32;
+    int my_count = 0, my_begin = 0, all_counts = 0;
+    if (few) {
+        my_count = lane < nseg ? min((int)seg_counts[lane], kPartCap) : 0;
+        int incl = my_count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        my_begin = incl - my_count;
+        all_counts = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        if (warp == 0 && lane < nseg) s_begin[lane] = (uint32_t)my_begin;
+    }
+    auto count_of = [&](int s) {  // (called by whole warps, with s the same in every lane)
+        return few ? __shfl_sync(0xFFFFFFFFu, my_count, s) : min((int)seg_counts[s], kPartCap);
+    };
 
     // The shard's own k-th largest processed value is a lower bound on the row's: nothing below
     // it (after the temperature divide's ties) can survive the merged top-k, so it need not travel.
     if (p.top_k > 0) {
         int m = 0;  // block-uniform
-        for (int s = 0; s < nseg; ++s) {
-            const int cnt = min((int)seg_counts[s], kPartCap);
-            for (int i = tid; i < cnt; i += kPackThreads) {
-                if (m + i < kPackKeys) {
-                    const uint2 c = cands[(size_t)s * kPartCap + i];
-                    s_keys[m + i] = ordered_key(processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty));
-                }
+        if (few) {
+            // all the candidates of the row as one list: a thread's loads do not wait for one another
+            __syncthreads();  // s_begin
+            m = all_counts;
+#pragma unroll 2
+            for (int f = tid; f < min(m, kPackKeys); f += kPackThreads) {
+                int s = 0;
+                while (s + 1 < nseg && (int)s_begin[s + 1] <= f) ++s;
+                const uint2 c = cands[(size_t)s * kPartCap + (f - (int)s_begin[s])];
+                s_keys[f] = ordered_key(processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty));
             }
-            m += cnt;
+        } else {
+            for (int s = 0; s < nseg; ++s) {
+                const int cnt = min((int)seg_counts[s], kPartCap);
+                for (int i = tid; i < cnt; i += kPackThreads) {
+                    if (m + i < kPackKeys) {
+                        const uint2 c = cands[(size_t)s * kPartCap + i];
+                        s_keys[m + i] = ordered_key(processed_before_temperature(__uint_as_float(c.x), c.y, p.penalty));
+                    }
+                }
+                m += cnt;
+            }
         }
         __syncthreads();
         if (m <= kPackKeys && m > p.top_k) {
@@ -155,7 +188,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
     const bool want_processed = p.top_k <= 0;
     float dropped_raw = 0.0f;
     for (int s = warp; s < nseg; s += kPackWarps) {
-        const int cnt = min((int)seg_counts[s], kPartCap);
+        const int cnt = count_of(s);
         uint32_t kept = 0;
         for (int base = 0; base < cnt; base += 32) {
             const int i = base + lane;
@@ -201,8 +234,8 @@ __global__ void __launch_bounds__(kPackThreads) pack_records_kernel(const PackPa
         uint32_t before = 0;
         for (int j = lane; j < s; j += 32) before += s_kept[j];
         before = warp_sum_u32(before);
+        const int cnt = count_of(s);
         if (s_kept[s] == 0) continue;
-        const int cnt = min((int)seg_counts[s], kPartCap);
         for (int base = 0; base < cnt; base += 32) {
             const int i = base + lane;
             bool keep = false;
