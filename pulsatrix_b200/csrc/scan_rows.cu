@@ -77,6 +77,10 @@ __device__ __forceinline__ void mark_ids(const int64_t* ids, int64_t begin, int6
     // A thread's ids four at a time: the three after the one in hand are asked for together, so a history
     // of a thousand ids costs one trip to memory here, not three one after another.
     int64_t id = first_id_loaded;
+    if (end - begin <= kScanThreads) {  // at most the one id that the caller has already fetched
+        if (begin + threadIdx.x < end) mark(id);
+        return;
+    }
     for (int64_t i = begin + threadIdx.x; i < end;) {
         int64_t next[3];
 #pragma unroll
@@ -117,7 +121,9 @@ __device__ unsigned long long g_stage_clocks[4096 * 24];
 //          when a flag can only lower a logit (penalty >= 1: l / p or l * p <= l; a ban gives -inf) and no
 //          processed tail is wanted: a flagged logit whose processed value reaches the threshold then
 //          reaches it raw as well, and the rest belong to the raw tail with their raw value.
-template <bool kNucleus, bool kRestore>
+// kAnnounce: raise ScanParams::row_ready when a part is written (a build of its own, so that the usual one
+//   carries nothing for it).
+template <bool kNucleus, bool kRestore, bool kAnnounce = false>
 __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanParams p) {
     static_assert(!(kNucleus && kRestore), "the processed tail needs the flagged logits out of the sums");
 #ifdef PSX_STAGE_CLOCKS
@@ -153,7 +159,7 @@ __global__ void __launch_bounds__(kScanThreads, 3) scan_rows_kernel(const ScanPa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t part_index = (size_t)row * p.parts + part;
     auto announce_part = [&]() {  // (by the whole CTA, after its last write)
-        if (p.row_ready != nullptr) {
+        if (kAnnounce && p.row_ready != nullptr) {
             __syncthreads();
             if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.row_ready + row) : "memory");
         }
@@ -687,6 +693,8 @@ cudaError_t configure_scan_rows() {
     cudaError_t e = allow_all_dynamic_shared(scan_rows_kernel<true, false>);
     if (e == cudaSuccess) e = allow_all_dynamic_shared(scan_rows_kernel<false, false>);
     if (e == cudaSuccess) e = allow_all_dynamic_shared(scan_rows_kernel<false, true>);
+    if (e == cudaSuccess) e = allow_all_dynamic_shared(scan_rows_kernel<false, false, true>);
+    if (e == cudaSuccess) e = allow_all_dynamic_shared(scan_rows_kernel<false, true, true>);
     return e;
 }
 
@@ -698,6 +706,10 @@ cudaError_t launch_scan_rows(const ScanParams& p, bool nucleus, cudaStream_t str
     // A flag can only lower a logit unless the penalty is below one (then l / p > l for l > 0).
     const bool flags_only_lower = !p.apply_penalty || p.penalty >= 1.0f;
     auto kernel = nucleus ? scan_rows_kernel<true, false> : flags_only_lower ? scan_rows_kernel<false, true> : scan_rows_kernel<false, false>;
+    if (p.row_ready != nullptr) {  // (asked for by the vocabulary-sharded step, which has a top-k or is greedy)
+        if (nucleus) return cudaErrorInvalidConfiguration;
+        kernel = flags_only_lower ? scan_rows_kernel<false, true, true> : scan_rows_kernel<false, false, true>;
+    }
     return launch_overlapping(kernel, grid, dim3(kScanThreads), shared, stream, p);
 }
 
