@@ -65,3 +65,17 @@ def test_shard_record_size_follows_top_k(lib):
     assert lib.psx_b200_shard_record_bytes(C.addressof(cfg)) == 48 + 8 * 128
     cfg = psx.SamplingConfig.make(do_sample=False)
     assert lib.psx_b200_shard_record_bytes(C.addressof(cfg)) == 48 + 8 * 64
+
+
+def test_exchange_entry_points_check_their_arguments_before_touching_a_gpu(lib):
+    assert lib.psx_b200_exchange_handle_bytes() == 64  # sizeof(cudaIpcMemHandle_t)
+    cfg = binding.SamplingConfig.make(do_sample=True, top_k=64)
+    out, handle = C.c_void_p(), C.create_string_buffer(64)
+    # no context: nothing is allocated, nothing is written
+    assert lib.psx_b200_exchange_create(None, 2, 0, 8, C.addressof(cfg), C.byref(out), handle) == binding.ERR_BAD_ARGUMENT
+    assert out.value is None and handle.raw == bytes(64)
+    assert lib.psx_b200_exchange_open(None, handle) == binding.ERR_BAD_ARGUMENT
+    assert lib.psx_b200_exchange_sample(None, None, None, 0, 0, 0, 0, None, None, C.addressof(cfg), None) == binding.ERR_BAD_ARGUMENT
+    assert lib.psx_b200_exchange_results(None, None, None) == binding.ERR_BAD_ARGUMENT
+    assert lib.psx_b200_exchange_test_wait(None, 0, 0) == binding.ERR_BAD_ARGUMENT
+    lib.psx_b200_exchange_destroy(None)  # a null exchange is nothing to destroy
