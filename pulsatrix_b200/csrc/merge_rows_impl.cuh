@@ -706,15 +706,11 @@ __device__ inline uint32_t block_select_kth(KeyAt key_at, int m, uint32_t k, uin
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
         uint32_t* h = hist + 256 * pass;
-        for (int base = 0; base < m; base += kMergeThreads) {
-            // Keys that share a digit (the leading digits of neighbouring floats, or plain ties) are
-            // counted by one lane for all of them.
-            const int i = base + tid;
-            const uint32_t key = i < m ? key_at(i) : 0u;
-            const bool counted = i < m && (key & mask) == prefix;
-            const uint32_t bin = counted ? (key >> shift) & 255u : 256u;
-            const uint32_t peers = __match_any_sync(0xFFFFFFFFu, bin);
-            if (counted && lane == __ffs(peers) - 1) atomicAdd(&h[bin], (uint32_t)__popc(peers));
+        for (int i = tid; i < m; i += kMergeThreads) {
+            // (Keys that share a digit -- the leading digits of neighbouring floats, or plain ties -- queue at
+            // one bin; letting one lane count for all of them with match.any cost more than the queue.)
+            const uint32_t key = key_at(i);
+            if ((key & mask) == prefix) atomicAdd(&h[(key >> shift) & 255u], 1u);
         }
         __syncthreads();
         // lane L owns digits 255-8L down to 248-8L; find where the count from the top reaches `remaining`
